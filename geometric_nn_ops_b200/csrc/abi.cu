@@ -1,0 +1,198 @@
+// extern "C" surface of libtri_b200.so: argument checks and dispatch between the
+// tensor-core (tcgen05) kernels and the exact-fp32 CUDA-core kernels.
+#include <atomic>
+#include <cstring>
+#include <mutex>
+#include <map>
+#include <string>
+#include <vector>
+
+#include "attn_simt.cuh"
+#include "common.cuh"
+#include "tc_paths.cuh"
+#include "trimul_simt.cuh"
+
+namespace tri {
+namespace {
+thread_local char g_err[512] = "";
+thread_local const char* g_path = "none";
+// Launch counter and timing records are process-wide: autograd runs the backward on its own thread.
+std::atomic<long long> g_launches{0};
+
+struct ProfRecord { const char* name; cudaEvent_t beg, end; };
+std::atomic<bool> g_prof_on{false};
+std::mutex g_prof_mu;
+std::vector<ProfRecord>* g_prof = nullptr;
+}  // namespace
+
+KernelTimer::KernelTimer(const char* name, cudaStream_t stream) : slot(-1), st(stream) {
+  if (!g_prof_on.load()) return;
+  std::lock_guard<std::mutex> lock(g_prof_mu);
+  if (g_prof == nullptr) g_prof = new std::vector<ProfRecord>();
+  ProfRecord r{name, nullptr, nullptr};
+  if (cudaEventCreate(&r.beg) != cudaSuccess || cudaEventCreate(&r.end) != cudaSuccess) return;
+  cudaEventRecord(r.beg, st);
+  g_prof->push_back(r);
+  slot = (int)g_prof->size() - 1;
+}
+KernelTimer::~KernelTimer() {
+  if (slot < 0) return;
+  std::lock_guard<std::mutex> lock(g_prof_mu);
+  if (g_prof != nullptr && slot < (int)g_prof->size()) cudaEventRecord((*g_prof)[slot].end, st);
+}
+
+char* last_error_buf() { return g_err; }
+void set_path(const char* name) { g_path = name; }
+void count_launch(int n) { g_launches += n; }
+
+static int check_attn(const TriAttnDesc* d) {
+  if (d == nullptr) return fail(TRI_ERR_ARG, "descriptor is null");
+  if (d->B <= 0 || d->n_seq <= 0 || d->n_res <= 0 || d->H <= 0 || d->D <= 0)
+    return fail(TRI_ERR_ARG, "attention sizes must be positive (B=%d n_seq=%d n_res=%d H=%d D=%d)", d->B,
+                d->n_seq, d->n_res, d->H, d->D);
+  if (d->D > 128) return fail(TRI_ERR_UNSUPPORTED, "head dim %d > 128 is not supported", d->D);
+  if (d->dtype < TRI_F32 || d->dtype > TRI_F16) return fail(TRI_ERR_ARG, "bad dtype %d", d->dtype);
+  if (d->precision != TRI_PREC_IEEE && d->precision != TRI_PREC_TF32)
+    return fail(TRI_ERR_ARG, "bad precision %d", d->precision);
+  if ((long long)d->B * d->n_seq * d->H > 2147483647LL / 4) return fail(TRI_ERR_UNSUPPORTED, "too many rows");
+  return 0;
+}
+
+static int check_mul(const TriMulDesc* d) {
+  if (d == nullptr) return fail(TRI_ERR_ARG, "descriptor is null");
+  if (d->B <= 0 || d->N <= 0 || d->C <= 0 || d->Ch <= 0)
+    return fail(TRI_ERR_ARG, "trimul sizes must be positive (B=%d N=%d C=%d Ch=%d)", d->B, d->N, d->C, d->Ch);
+  if (d->C > 1024 || d->Ch > 1024) return fail(TRI_ERR_UNSUPPORTED, "channel width above 1024 is not supported");
+  if (d->dtype < TRI_F32 || d->dtype > TRI_F16) return fail(TRI_ERR_ARG, "bad dtype %d", d->dtype);
+  if (d->precision != TRI_PREC_IEEE && d->precision != TRI_PREC_TF32)
+    return fail(TRI_ERR_ARG, "bad precision %d", d->precision);
+  if (d->direction != TRI_OUTGOING && d->direction != TRI_INCOMING)
+    return fail(TRI_ERR_ARG, "bad direction %d", d->direction);
+  if ((long long)d->B * d->N * d->N * 2 * std::max(d->C, d->Ch) > 2147483647LL * 8)
+    return fail(TRI_ERR_UNSUPPORTED, "pair tensor too large");
+  return 0;
+}
+
+}  // namespace tri
+
+using namespace tri;
+
+extern "C" {
+
+int tri_abi_version(void) { return 1; }
+const char* tri_last_error(void) { return last_error_buf(); }
+const char* tri_last_path(void) { return g_path; }
+long long tri_launch_count(void) { return g_launches.load(); }
+void tri_reset_launch_count(void) { g_launches = 0; }
+
+void tri_profile_enable(int on) {
+  std::lock_guard<std::mutex> lock(g_prof_mu);
+  if (g_prof != nullptr) {
+    for (auto& r : *g_prof) { cudaEventDestroy(r.beg); cudaEventDestroy(r.end); }
+    g_prof->clear();
+  }
+  g_prof_on = on != 0;
+}
+
+int tri_profile_summary(char* buf, size_t cap) {
+  if (buf == nullptr || cap == 0) return fail(TRI_ERR_ARG, "buffer is null");
+  buf[0] = 0;
+  std::lock_guard<std::mutex> lock(g_prof_mu);
+  if (g_prof == nullptr) return 0;
+  std::map<std::string, std::pair<int, double>> agg;
+  for (auto& r : *g_prof) {
+    TRI_CUDA_OK(cudaEventSynchronize(r.end));
+    float ms = 0.f;
+    TRI_CUDA_OK(cudaEventElapsedTime(&ms, r.beg, r.end));
+    auto& a = agg[r.name];
+    a.first += 1;
+    a.second += ms;
+  }
+  size_t off = 0;
+  for (auto& kv : agg) {
+    int n = snprintf(buf + off, cap - off, "%s %d %.6f\n", kv.first.c_str(), kv.second.first, kv.second.second);
+    if (n < 0 || (size_t)n >= cap - off) return fail(TRI_ERR_ARG, "buffer too small");
+    off += (size_t)n;
+  }
+  return 0;
+}
+
+size_t tri_attn_ws_bytes(const TriAttnDesc* d, int is_bwd) {
+  if (check_attn(d) != 0) return 0;
+  if (tc::attn_supported(d)) return tc::attn_ws_bytes(d, is_bwd);
+  return simt::attn_ws_bytes(d, is_bwd);
+}
+
+int tri_attn_fwd(const TriAttnDesc* d, const void* q, const void* k, const void* v, const void* bias,
+                 const uint8_t* mask, void* o, float* lse, void* ws, size_t ws_bytes, tri_stream_t stream) {
+  TRI_TRY(check_attn(d));
+  if (!q || !k || !v || !o || !lse) return fail(TRI_ERR_ARG, "q, k, v, o and lse must not be null");
+  if (tc::attn_supported(d)) {
+    set_path("tcgen05");
+    return tc::attn_forward(d, q, k, v, bias, mask, o, lse, ws, ws_bytes, (cudaStream_t)stream);
+  }
+  set_path("simt");
+  return simt::attn_forward(d, q, k, v, bias, mask, o, lse, (cudaStream_t)stream);
+}
+
+int tri_attn_bwd(const TriAttnDesc* d, const void* q, const void* k, const void* v, const void* bias,
+                 const uint8_t* mask, const void* o, const float* lse, const void* d_o, void* dq, void* dk,
+                 void* dv, float* dbias, void* ws, size_t ws_bytes, tri_stream_t stream) {
+  TRI_TRY(check_attn(d));
+  if (!q || !k || !v || !o || !lse || !d_o || !dq || !dk || !dv || !ws)
+    return fail(TRI_ERR_ARG, "q, k, v, o, lse, d_o, dq, dk, dv and ws must not be null");
+  if (tc::attn_supported(d)) {
+    set_path("tcgen05");
+    return tc::attn_backward(d, q, k, v, bias, mask, o, lse, d_o, dq, dk, dv, dbias, ws, ws_bytes,
+                             (cudaStream_t)stream);
+  }
+  set_path("simt");
+  return simt::attn_backward(d, q, k, v, bias, mask, o, lse, d_o, dq, dk, dv, dbias, ws, ws_bytes,
+                             (cudaStream_t)stream);
+}
+
+size_t tri_mul_saved_bytes(const TriMulDesc* d) {
+  if (check_mul(d) != 0) return 0;
+  return tc::mul_supported(d) ? tc::mul_saved_bytes(d) : simt::saved_bytes(d);
+}
+
+size_t tri_mul_ws_bytes(const TriMulDesc* d, int is_bwd) {
+  if (check_mul(d) != 0) return 0;
+  return tc::mul_supported(d) ? tc::mul_ws_bytes(d, is_bwd) : simt::ws_bytes(d, is_bwd);
+}
+
+static int check_mul_weights(const TriMulWeights* w) {
+  if (w == nullptr || !w->p_in_w || !w->g_in_w || !w->p_out_w || !w->g_out_w)
+    return fail(TRI_ERR_ARG, "p_in, g_in, p_out and g_out weights are required");
+  return 0;
+}
+
+int tri_mul_fwd(const TriMulDesc* d, const void* x, const void* mask, const TriMulWeights* w, void* out,
+                void* saved, void* ws, size_t ws_bytes, tri_stream_t stream) {
+  TRI_TRY(check_mul(d));
+  TRI_TRY(check_mul_weights(w));
+  if (!x || !out || !ws) return fail(TRI_ERR_ARG, "x, out and ws must not be null");
+  if (tc::mul_supported(d)) {
+    set_path("tcgen05");
+    return tc::mul_forward(d, x, mask, w, out, saved, ws, ws_bytes, (cudaStream_t)stream);
+  }
+  set_path("simt");
+  return simt::forward(d, x, mask, w, out, saved, ws, ws_bytes, (cudaStream_t)stream);
+}
+
+int tri_mul_bwd(const TriMulDesc* d, const void* x, const void* mask, const TriMulWeights* w, const void* saved,
+                const void* d_out, void* dx, const TriMulWeightGrads* g, void* ws, size_t ws_bytes,
+                tri_stream_t stream) {
+  TRI_TRY(check_mul(d));
+  TRI_TRY(check_mul_weights(w));
+  if (!x || !saved || !d_out || !dx || !g || !ws)
+    return fail(TRI_ERR_ARG, "x, saved, d_out, dx, grads and ws must not be null");
+  if (tc::mul_supported(d)) {
+    set_path("tcgen05");
+    return tc::mul_backward(d, x, mask, w, saved, d_out, dx, g, ws, ws_bytes, (cudaStream_t)stream);
+  }
+  set_path("simt");
+  return simt::backward(d, x, mask, w, saved, d_out, dx, g, ws, ws_bytes, (cudaStream_t)stream);
+}
+
+}  // extern "C"

@@ -1,0 +1,24 @@
+// Entry points of the tensor-core (tcgen05 / TMEM / TMA) paths.
+#pragma once
+#include "common.cuh"
+
+namespace tri {
+namespace tc {
+// True when the tensor-core kernels cover this problem (dtype, precision, shape).
+bool attn_supported(const TriAttnDesc* d);
+size_t attn_ws_bytes(const TriAttnDesc* d, int is_bwd);
+int attn_forward(const TriAttnDesc* d, const void* q, const void* k, const void* v, const void* bias,
+                 const uint8_t* mask, void* o, float* lse, void* ws, size_t ws_size, cudaStream_t st);
+int attn_backward(const TriAttnDesc* d, const void* q, const void* k, const void* v, const void* bias,
+                  const uint8_t* mask, const void* o, const float* lse, const void* d_o, void* dq, void* dk,
+                  void* dv, float* dbias, void* ws, size_t ws_size, cudaStream_t st);
+
+bool mul_supported(const TriMulDesc* d);
+size_t mul_saved_bytes(const TriMulDesc* d);
+size_t mul_ws_bytes(const TriMulDesc* d, int is_bwd);
+int mul_forward(const TriMulDesc* d, const void* x, const void* mask, const TriMulWeights* w, void* out,
+                void* saved, void* ws, size_t ws_size, cudaStream_t st);
+int mul_backward(const TriMulDesc* d, const void* x, const void* mask, const TriMulWeights* w, const void* saved,
+                 const void* d_out, void* dx, const TriMulWeightGrads* g, void* ws, size_t ws_size, cudaStream_t st);
+}  // namespace tc
+}  // namespace tri

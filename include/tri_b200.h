@@ -1,0 +1,147 @@
+/*
+ * tri_b200.h -- C ABI of libtri_b200.so: triangle attention and triangle
+ * multiplicative update for NVIDIA B200 (sm_100a).
+ *
+ * The reference project (AMDResearch/geometric-nn-ops) is pure Python and has
+ * no FFI; the seam these entry points replace is its private kernel package
+ * (geometric_nn_ops_torch/triangle/_kernels/__init__.py:4-8 declares it
+ * swappable).  Each function below names the reference kernel-layer function
+ * whose work it takes over.
+ *
+ * Conventions
+ *  - Every pointer is a DEVICE pointer unless it points to a descriptor struct.
+ *  - The caller owns all memory, including workspaces; query the size first.
+ *    No entry point here allocates, frees or synchronises; all work is queued
+ *    on the given stream.
+ *  - Return value: 0 = ok, <0 = bad argument (TRI_ERR_*), >0 = cudaError_t.
+ *    tri_last_error() returns a thread-local message for the last failure.
+ *  - Strides are in ELEMENTS.  The innermost (head-dim / channel) axis is
+ *    always contiguous.
+ */
+#ifndef TRI_B200_H_
+#define TRI_B200_H_
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+typedef struct CUstream_st* tri_stream_t; /* == cudaStream_t */
+
+enum { TRI_F32 = 0, TRI_BF16 = 1, TRI_F16 = 2 };
+/* fp32 matmul precision, as read from torch.backends.cuda.matmul.fp32_precision
+ * (geometric_nn_ops_torch/_precision.py:34-44).  Ignored for 16-bit dtypes. */
+enum { TRI_PREC_IEEE = 0, TRI_PREC_TF32 = 1 };
+enum { TRI_OUTGOING = 0, TRI_INCOMING = 1 };
+enum {
+  TRI_ERR_ARG = -1,        /* null pointer / bad enum / bad size */
+  TRI_ERR_WORKSPACE = -2,  /* workspace too small */
+  TRI_ERR_UNSUPPORTED = -3,/* shape not supported by any kernel */
+  TRI_ERR_DEVICE = -4      /* a kernel reported a failure (e.g. a bounded wait ran out) */
+};
+
+int tri_abi_version(void);
+const char* tri_last_error(void);
+/* Name of the kernel family the last forward/backward on this thread ran on:
+ * "simt" (CUDA-core fp32 path) or "tcgen05" (tensor-core path). */
+const char* tri_last_path(void);
+/* Number of kernel launches issued by this library (all threads) since the
+ * last call to tri_reset_launch_count(). */
+long long tri_launch_count(void);
+void tri_reset_launch_count(void);
+
+/* Per-kernel timing for benchmarks (no counterpart in the reference, which uses torch.profiler in
+ * benchmarks/profile_trimul.py:73-87).  While enabled, every kernel launch (any thread) is bracketed
+ * by CUDA events on its stream.  tri_profile_summary waits for them and writes one line per kernel,
+ * "name launches total_ms".  Enabling (or disabling) drops earlier records. */
+void tri_profile_enable(int on);
+int tri_profile_summary(char* buf, size_t cap);
+
+/* ------------------------------------------------------------------------ */
+/* Triangle attention                                                       */
+/* ------------------------------------------------------------------------ */
+/* q, k, v, o, dO, dq, dk, dv: logical [B, n_seq, n_res, H, D], strides for
+ * (batch, row, residue, head), D contiguous -- both the reference's native
+ * layout and the cuequivariance (B, N, H, S, D) layout are plain stride
+ * choices.  bias: [B, H, n_res, n_res] with strides (batch, head, query), key
+ * contiguous; batch stride may be 0.  mask: bytes (bool), [B, n_seq, n_res]
+ * with strides (batch, row), key contiguous; nonzero = keep.
+ * lse: fp32 [B, n_seq, H, n_res] contiguous.  dbias: fp32 [B, H, n_res, n_res]
+ * contiguous, summed over rows. */
+typedef struct TriAttnDesc {
+  int32_t B, n_seq, n_res, H, D;
+  int32_t dtype;      /* TRI_F32 / TRI_BF16 / TRI_F16 */
+  int32_t precision;  /* TRI_PREC_* */
+  float scale;
+  int64_t q_st[4], k_st[4], v_st[4], o_st[4];
+  int64_t do_st[4], dq_st[4], dk_st[4], dv_st[4];
+  int64_t bias_st[3];
+  int64_t mask_st[2];
+} TriAttnDesc;
+
+/* Replaces EvoformerAttention.forward + _attn_fwd
+ * (geometric_nn_ops_torch/triangle/_kernels/triangle_attention.py:1090-1276, 183-365). */
+int tri_attn_fwd(const TriAttnDesc* d, const void* q, const void* k, const void* v,
+                 const void* bias /*nullable*/, const uint8_t* mask /*nullable*/,
+                 void* o, float* lse, void* ws, size_t ws_bytes, tri_stream_t stream);
+
+/* Replaces EvoformerAttention.backward + _attn_bwd_preprocess / _attn_bwd_dk_dv /
+ * _attn_bwd_dbias_dq (same file :1278-1442, 548-1087). */
+int tri_attn_bwd(const TriAttnDesc* d, const void* q, const void* k, const void* v,
+                 const void* bias, const uint8_t* mask, const void* o, const float* lse,
+                 const void* d_o, void* dq, void* dk, void* dv, float* dbias /*nullable*/,
+                 void* ws, size_t ws_bytes, tri_stream_t stream);
+
+size_t tri_attn_ws_bytes(const TriAttnDesc* d, int is_bwd);
+
+/* ------------------------------------------------------------------------ */
+/* Triangle multiplicative update                                           */
+/* ------------------------------------------------------------------------ */
+/* x, out, d_out, dx: [B, N, N, C] contiguous in `dtype`.  mask: [B, N, N]
+ * contiguous in `dtype` (1 = keep), nullable.  Weights are contiguous in
+ * `dtype`; p_in / g_in are the concatenated [a; b] projections [2*Ch, C]. */
+typedef struct TriMulDesc {
+  int32_t B, N, C, Ch;
+  int32_t dtype, precision, direction;
+  float eps;
+} TriMulDesc;
+
+typedef struct TriMulWeights {
+  const void *norm_in_w, *norm_in_b;   /* [C]      nullable */
+  const void *p_in_w, *p_in_b;         /* [2Ch,C], [2Ch] (bias nullable) */
+  const void *g_in_w, *g_in_b;         /* [2Ch,C], [2Ch] */
+  const void *norm_out_w, *norm_out_b; /* [Ch]     nullable */
+  const void *p_out_w, *p_out_b;       /* [C,Ch],  [C] */
+  const void *g_out_w, *g_out_b;       /* [C,C],   [C] */
+} TriMulWeights;
+
+/* fp32 outputs, same shapes as the weights; a null member is skipped. */
+typedef struct TriMulWeightGrads {
+  float *norm_in_w, *norm_in_b, *p_in_w, *p_in_b, *g_in_w, *g_in_b;
+  float *norm_out_w, *norm_out_b, *p_out_w, *p_out_b, *g_out_w, *g_out_b;
+} TriMulWeightGrads;
+
+/* Bytes of the opaque block the forward fills for the backward. */
+size_t tri_mul_saved_bytes(const TriMulDesc* d);
+size_t tri_mul_ws_bytes(const TriMulDesc* d, int is_bwd);
+
+/* Replaces trimul_triton (geometric_nn_ops_torch/triangle/_kernels/trimul.py:404-448)
+ * and, for grad-requiring calls, the torch path trimul_torch
+ * (geometric_nn_ops_torch/triangle/_reference/trimul.py:57-97).
+ * saved == NULL means inference (nothing kept). */
+int tri_mul_fwd(const TriMulDesc* d, const void* x, const void* mask, const TriMulWeights* w,
+                void* out, void* saved /*nullable*/, void* ws, size_t ws_bytes,
+                tri_stream_t stream);
+
+/* Backward of the above.  The reference has no kernel for it: it differentiates
+ * trimul_torch with autograd (geometric_nn_ops_torch/triangle/_trimul.py:31-36). */
+int tri_mul_bwd(const TriMulDesc* d, const void* x, const void* mask, const TriMulWeights* w,
+                const void* saved, const void* d_out, void* dx, const TriMulWeightGrads* g,
+                void* ws, size_t ws_bytes, tri_stream_t stream);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* TRI_B200_H_ */

@@ -155,11 +155,24 @@ def _linear(t, w, b):
     return y if b is None else y + b
 
 
+def _cm(t):
+    """[*, r, s, c] -> channel-major [*, c, r, s] (contiguous, so matmul goes to BLAS)."""
+    return np.ascontiguousarray(np.moveaxis(t, -1, -3))
+
+
+def _pm(t):
+    """channel-major [*, c, r, s] -> [*, r, s, c]."""
+    return np.moveaxis(t, -3, -1)
+
+
+def _T(t):
+    return np.swapaxes(t, -1, -2)
+
+
 def _combine(a, b, outgoing):
-    # a, b: [*, N, N, Ch] -> t[*, i, j, c]
-    if outgoing:
-        return np.einsum("...ikc,...jkc->...ijc", a, b, optimize=True)
-    return np.einsum("...kic,...kjc->...ijc", a, b, optimize=True)
+    """t[i,j,c] = sum_k a[i,k,c] b[j,k,c] (outgoing) or sum_k a[k,i,c] b[k,j,c] (incoming)."""
+    a, b = _cm(a), _cm(b)
+    return _pm(np.matmul(a, _T(b)) if outgoing else np.matmul(_T(a), b))
 
 
 def trimul_fwd(
@@ -216,12 +229,11 @@ def trimul_bwd(x, direction, mask, d_out, *, eps=1e-5, acc=np.float64, **weights
     dt, grads["norm_out_weight"], grads["norm_out_bias"] = _layer_norm_bwd(
         du, c["that"], c["rstd_out"], w.get("norm_out_weight"))
     a, b = c["a"], c["b"]
-    if outgoing:
-        da = np.einsum("...ijc,...jkc->...ikc", dt, b, optimize=True)
-        db = np.einsum("...ijc,...ikc->...jkc", dt, a, optimize=True)
-    else:
-        da = np.einsum("...ijc,...kjc->...kic", dt, b, optimize=True)
-        db = np.einsum("...ijc,...kic->...kjc", dt, a, optimize=True)
+    a_c, b_c, dt_c = _cm(a), _cm(b), _cm(dt)
+    if outgoing:   # t = a b^T
+        da, db = _pm(np.matmul(dt_c, b_c)), _pm(np.matmul(_T(dt_c), a_c))
+    else:          # t = a^T b
+        da, db = _pm(np.matmul(b_c, _T(dt_c))), _pm(np.matmul(a_c, dt_c))
     dab = np.concatenate([da, db], axis=-1)
     if mask is not None:
         dab = dab * cv(mask)[..., None]

@@ -1,0 +1,189 @@
+"""triangle_attention on the GPU against the oracle, golden fixtures and known answers.
+
+Known-answer and structural cases mirror the reference's tests/test_triangle_attention.py
+(single unmasked key :88-104, uniform softmax :107-126, mask=None == all-keep :129-141,
+masked perturbations :144-216, no-bias == zero-bias :219-232, fully masked row :235-300,
+mask dtype :303-313, default scale :341-355, ranks :358-426, dynamic :429-443,
+precision :451-484, accuracy grid :491-509).
+"""
+
+import glob
+import os
+
+import numpy as np
+import pytest
+import torch
+
+from tests import util
+
+pytestmark = pytest.mark.gpu
+
+GOLD = sorted(glob.glob(os.path.join(os.path.dirname(__file__), "golden", "attn_*.npz")))
+
+
+@pytest.fixture(scope="module")
+def ta():
+    from geometric_nn_ops_b200.triangle import triangle_attention
+    return triangle_attention
+
+
+def _tol(dtype, precision):
+    cos_min, fro = util.ATTN_TOL[dtype, precision]
+    if dtype == torch.float32 and precision == "ieee":
+        return cos_min, util.IEEE_REL_FRO, util.MAX_ABS_REL["ieee32"]
+    if dtype == torch.float32:
+        return cos_min, fro, util.MAX_ABS_REL["tf32"]
+    return cos_min, fro, util.MAX_ABS_REL[dtype]
+
+
+@pytest.mark.parametrize("path", GOLD, ids=[os.path.basename(p) for p in GOLD])
+def test_golden_fp32_ieee(ta, path):
+    g = dict(np.load(path))
+    scale = None if g["scale"] < 0 else float(g["scale"])
+    dev = lambda n: torch.from_numpy(g[n]).cuda() if n in g else None  # noqa: E731
+    t = {"q": dev("q"), "k": dev("k"), "v": dev("v"), "bias": dev("bias")}
+    mask = dev("mask")
+    with util.matmul_precision("ieee"):
+        out, grads = util.attn_fwd_bwd(ta, t, mask, scale, dev("d_out"))
+    util.check_close("out", out, g["out"], 1 - 1e-9, util.IEEE_REL_FRO, 1e-4)
+    for name, val in grads.items():
+        util.check_close("grad_" + name, val, g["grad_" + name], 1 - 1e-9, util.IEEE_REL_FRO, 1e-4)
+
+
+SHAPES = [(1, 8, 8, 2, 8), (2, 5, 37, 3, 16), (1, 16, 100, 4, 32), (1, 3, 130, 2, 64), (1, 4, 65, 1, 48)]
+MODES = [(torch.float32, "ieee"), (torch.float32, "tf32"), (torch.bfloat16, "ieee"), (torch.float16, "ieee")]
+
+
+@pytest.mark.parametrize("shape", SHAPES, ids=str)
+@pytest.mark.parametrize("dtype,precision", MODES, ids=lambda v: str(v).replace("torch.", ""))
+def test_oracle_fwd_bwd(ta, shape, dtype, precision):
+    t, mask, d_out = util.attn_inputs(*shape, dtype, seed=sum(shape))
+    with util.matmul_precision(precision):
+        out, grads = util.attn_fwd_bwd(ta, t, mask, None, d_out)
+    o_ref, g_ref = util.attn_oracle(t, mask, None, d_out)
+    cos_min, fro, mar = _tol(dtype, precision)
+    util.check_close("out", out, o_ref, cos_min, fro, mar)
+    for name, val in grads.items():
+        util.check_close("grad_" + name, val, g_ref[name], cos_min, fro, mar)
+
+
+@pytest.mark.parametrize("n,dtype", [(256, torch.bfloat16), (128, torch.float32)])
+def test_baseline_config_forward(ta, n, dtype):
+    """BASELINE config 1 (bf16, B=1, N=256, H=4, D=32, keep 0.95) in the cuequivariance layout."""
+    t, mask, _ = util.attn_inputs(1, n, n, 4, 32, dtype, seed=1, keep=0.95)
+    cueq = {k: (v.transpose(-2, -3).contiguous().transpose(-2, -3) if k != "bias" else v) for k, v in t.items()}
+    with torch.no_grad():
+        out = ta(cueq["q"], cueq["k"], cueq["v"], cueq["bias"], mask, 32 ** -0.5)
+    assert out.stride() == cueq["q"].stride()
+    o_ref, _ = util.attn_oracle(t, mask, 32 ** -0.5, torch.zeros_like(t["q"]))
+    util.check_close("out", out, o_ref, *_tol(dtype, "ieee"))
+
+
+def test_single_unmasked_key_returns_its_value(ta):
+    t, _, _ = util.attn_inputs(1, 3, 19, 2, 16, torch.float32, seed=3)
+    mask = torch.zeros(1, 3, 1, 1, 19, dtype=torch.bool, device="cuda")
+    mask[..., 7] = True
+    out = ta(t["q"], t["k"], t["v"], t["bias"], mask)
+    want = t["v"][:, :, 7:8].expand_as(out)
+    assert torch.equal(out, want)
+
+
+def test_zero_query_gives_mean_of_values(ta):
+    B, S, N, H, D = 1, 2, 24, 2, 8
+    g = torch.Generator().manual_seed(0)
+    v = torch.randint(-4, 5, (B, S, N, H, D), generator=g).float().cuda()
+    q = torch.zeros_like(v)
+    k = torch.randn(B, S, N, H, D, generator=g).cuda()
+    out = ta(q, k, v)
+    want = v.mean(dim=2, keepdim=True).expand_as(out)
+    assert (out - want).abs().max() <= 2 * torch.finfo(torch.float32).eps * want.abs().max()
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+def test_structural_bit_exact(ta, dtype):
+    t, mask, _ = util.attn_inputs(1, 4, 70, 2, 32, dtype, seed=5)
+    base = ta(t["q"], t["k"], t["v"], t["bias"], mask)
+    # mask=None equals an all-keep mask
+    keep = torch.ones_like(mask)
+    assert torch.equal(ta(t["q"], t["k"], t["v"], t["bias"], None), ta(t["q"], t["k"], t["v"], t["bias"], keep))
+    # bias=None equals a zero bias
+    assert torch.equal(ta(t["q"], t["k"], t["v"], None, mask),
+                       ta(t["q"], t["k"], t["v"], torch.zeros_like(t["bias"]), mask))
+    # noise on masked keys / values changes nothing
+    dropped = ~mask.reshape(1, 4, 70, 1, 1).expand_as(t["v"])
+    noise = 1e3 * torch.randn_like(t["v"].float()).to(dtype)
+    v2 = torch.where(dropped, t["v"] + noise, t["v"])
+    k2 = torch.where(dropped, t["k"] + noise, t["k"])
+    assert torch.equal(ta(t["q"], t["k"], v2, t["bias"], mask), base)
+    assert torch.equal(ta(t["q"], k2, t["v"], t["bias"], mask), base)
+    # dynamic / use_exp2 flags are accepted and change nothing
+    assert torch.equal(ta(t["q"], t["k"], t["v"], t["bias"], mask, None, True, False), base)
+    # run twice: deterministic
+    assert torch.equal(ta(t["q"], t["k"], t["v"], t["bias"], mask), base)
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+def test_fully_masked_row_is_uniform(ta, dtype):
+    t, mask, d_out = util.attn_inputs(1, 3, 40, 2, 16, dtype, seed=6, bias_scale=0.1)
+    mask[0, 1] = False
+    out, grads = util.attn_fwd_bwd(ta, t, mask, None, d_out)
+    want = t["v"][0, 1].float().mean(dim=0)
+    got = out[0, 1].float()
+    assert (got - want).abs().max() <= (1e-5 if dtype == torch.float32 else 2e-2)
+    o_ref, g_ref = util.attn_oracle(t, mask, None, d_out)
+    cos_min, fro, _ = _tol(dtype, "ieee")
+    for name, val in grads.items():
+        util.check_close("grad_" + name, val, g_ref[name], cos_min, fro)
+
+
+def test_mask_must_be_bool(ta):
+    t, mask, _ = util.attn_inputs(1, 2, 8, 1, 8, torch.float32)
+    with pytest.raises(ValueError, match="mask must be bool"):
+        ta(t["q"], t["k"], t["v"], t["bias"], mask.float())
+
+
+def test_ranks_and_broadcasts(ta):
+    t, mask, _ = util.attn_inputs(2, 3, 20, 2, 8, torch.float32, seed=7)
+    full = ta(t["q"], t["k"], t["v"], t["bias"], mask, 0.5)
+    # rank 4 (no batch) with 4-D bias and lower-rank mask
+    o4 = ta(t["q"][0], t["k"][0], t["v"][0], t["bias"][0], mask[0], 0.5)
+    assert o4.shape == t["q"][0].shape and torch.equal(o4, full[0])
+    # rank 6: two leading dims fold into the batch
+    r6 = lambda x: x.reshape(2, 1, *x.shape[1:])  # noqa: E731
+    o6 = ta(r6(t["q"]), r6(t["k"]), r6(t["v"]), r6(t["bias"]), r6(mask), 0.5)
+    assert o6.shape == r6(t["q"]).shape and torch.equal(o6.reshape(full.shape), full)
+    # batch-broadcast bias: its gradient is the batch sum
+    b1 = t["bias"][:1].clone().requires_grad_()
+    out = ta(t["q"], t["k"], t["v"], b1, mask, 0.5)
+    (gb,) = torch.autograd.grad(out, [b1], grad_outputs=torch.ones_like(out))
+    tt = dict(t, bias=t["bias"][:1].expand(2, -1, -1, -1, -1).contiguous())
+    _, g_ref = util.attn_oracle(tt, mask, 0.5, torch.ones_like(out))
+    util.check_close("grad_bias", gb, g_ref["bias"].sum(axis=0, keepdims=True), 1 - 1e-9, 1e-5)
+    # fp64 inputs are computed in fp32 and cast back
+    o64 = ta(t["q"].double(), t["k"].double(), t["v"].double(), t["bias"].double(), mask, 0.5)
+    assert o64.dtype == torch.float64 and torch.equal(o64.float(), full)
+
+
+def test_tf32_differs_from_ieee(ta):
+    t, mask, d_out = util.attn_inputs(1, 4, 64, 2, 32, torch.float32, seed=8)
+    with util.matmul_precision("ieee"):
+        o1, g1 = util.attn_fwd_bwd(ta, t, mask, None, d_out)
+    with util.matmul_precision("tf32"):
+        o2, g2 = util.attn_fwd_bwd(ta, t, mask, None, d_out)
+    assert not torch.equal(o1, o2)
+    for name in g1:
+        assert not torch.equal(g1[name], g2[name]), name
+
+
+def test_rows_are_independent_at_full_size(ta):
+    """Size-independent property at the headline size: a row's result does not depend on the others."""
+    t, mask, _ = util.attn_inputs(1, 768, 768, 4, 32, torch.bfloat16, seed=9, keep=0.95)
+    with torch.no_grad():
+        full = ta(t["q"], t["k"], t["v"], t["bias"], mask)
+        part = ta(t["q"][:, 100:164], t["k"][:, 100:164], t["v"][:, 100:164], t["bias"], mask[:, 100:164])
+    assert torch.equal(full[:, 100:164], part)
+    assert torch.isfinite(full.float()).all()
+    # every output is a convex combination of that row's values
+    vmax = t["v"].float().amax(dim=2, keepdim=True)
+    vmin = t["v"].float().amin(dim=2, keepdim=True)
+    assert (full.float() <= vmax + 1e-2).all() and (full.float() >= vmin - 1e-2).all()

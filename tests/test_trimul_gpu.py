@@ -1,0 +1,153 @@
+"""triangle_multiplicative_update on the GPU against the oracle, golden fixtures and known answers.
+
+Structural cases mirror the reference's tests/test_trimul.py (zero mask :70-90, biases matter
+:93-113, directions differ :116-131, bad direction :134-148, mask=None == ones :151-164,
+broadcast mask :167-182, tf32 != ieee :185-201, accuracy :208-250, batched :253-272, widths
+:305-341, LayerNorm weights :344-382).
+"""
+
+import glob
+import os
+
+import numpy as np
+import pytest
+import torch
+
+from tests import util
+
+pytestmark = pytest.mark.gpu
+
+GOLD = sorted(glob.glob(os.path.join(os.path.dirname(__file__), "golden", "trimul_*.npz")))
+
+
+@pytest.fixture(scope="module")
+def tmu():
+    from geometric_nn_ops_b200.triangle import trimul_b200
+    return trimul_b200
+
+
+def _tol(dtype, precision):
+    cos_min, fro = util.TRIMUL_TOL[dtype, precision]
+    if dtype == torch.float32 and precision == "ieee":
+        return cos_min, util.IEEE_REL_FRO, util.MAX_ABS_REL["ieee32"]
+    if dtype == torch.float32:
+        return cos_min, fro, util.MAX_ABS_REL["tf32"]
+    return cos_min, fro, util.MAX_ABS_REL[dtype]
+
+
+@pytest.mark.parametrize("path", GOLD, ids=[os.path.basename(p) for p in GOLD])
+def test_golden_fp32_ieee(tmu, path):
+    g = dict(np.load(path))
+    dev = lambda a: torch.from_numpy(a).cuda()  # noqa: E731
+    w = {k[2:]: dev(v) for k, v in g.items() if k.startswith("w_")}
+    mask = dev(g["mask"]) if "mask" in g else None
+    with util.matmul_precision("ieee"):
+        out, grads = util.trimul_fwd_bwd(tmu, dev(g["x"]), mask, w, str(g["direction"]), dev(g["d_out"]))
+    util.check_close("out", out, g["out"], 1 - 1e-9, util.IEEE_REL_FRO, 1e-4)
+    for name, val in grads.items():
+        util.check_close("grad_" + name, val, g["grad_" + name], 1 - 1e-9, util.IEEE_REL_FRO, 1e-4)
+
+
+CASES = [  # B, N, C, Ch, biases
+    (1, 32, 128, 128, False), (2, 17, 64, 32, True), (1, 40, 96, 96, False), (1, 24, 256, 128, True),
+    (1, 128, 128, 128, False),
+]
+MODES = [(torch.float32, "ieee"), (torch.float32, "tf32"), (torch.bfloat16, "ieee"), (torch.float16, "ieee")]
+
+
+@pytest.mark.parametrize("direction", ["outgoing", "incoming"])
+@pytest.mark.parametrize("case", CASES, ids=str)
+@pytest.mark.parametrize("dtype,precision", MODES, ids=lambda v: str(v).replace("torch.", ""))
+def test_oracle_fwd_bwd(tmu, case, dtype, precision, direction):
+    B, N, C, Ch, biases = case
+    x, mask, w, d_out = util.trimul_inputs(B, N, C, Ch, dtype, seed=N + C, biases=biases)
+    with util.matmul_precision(precision):
+        out, grads = util.trimul_fwd_bwd(tmu, x, mask, w, direction, d_out)
+    o_ref, g_ref = util.trimul_oracle(x, mask, w, direction, d_out)
+    cos_min, fro, mar = _tol(dtype, precision)
+    util.check_close("out", out, o_ref, cos_min, fro, mar)
+    for name, val in grads.items():
+        util.check_close("grad_" + name, val, g_ref[name], cos_min, fro, mar)
+
+
+def test_baseline_config0_forward(tmu):
+    """BASELINE config 0: outgoing, fp32 (default precision = ieee), N=64, C=Ch=128, forward only."""
+    x, mask, w, _ = util.trimul_inputs(1, 64, 128, 128, torch.float32, seed=0)
+    with torch.no_grad():
+        out = tmu(x, "outgoing", mask, **w)
+    o_ref = util.trimul_oracle(x, mask, w, "outgoing", torch.zeros_like(x))[0]
+    util.check_close("out", out, o_ref, 1 - 1e-9, util.IEEE_REL_FRO, 1e-4)
+
+
+def test_structure(tmu):
+    x, mask, w, _ = util.trimul_inputs(2, 20, 32, 16, torch.float32, seed=1, biases=True)
+    with torch.no_grad():
+        base = tmu(x, "outgoing", mask, **w)
+        assert torch.equal(tmu(x, "outgoing", mask, **w), base)  # deterministic
+        assert not torch.equal(tmu(x, "incoming", mask, **w), base)
+        # all-zero mask: the contraction output is zero, the output depends on z only through the gate
+        zero = tmu(x, "outgoing", torch.zeros_like(mask), **w)
+        u0 = w["norm_out_bias"].float() @ w["p_out_weight"].float().T + w["p_out_bias"].float()
+        z = torch.nn.functional.layer_norm(x, (32,), w["norm_in_weight"], w["norm_in_bias"], 1e-5)
+        gate = torch.sigmoid(z @ w["g_out_weight"].T + w["g_out_bias"])
+        assert (zero - u0 * gate).abs().max() < 1e-5
+        # mask=None equals a mask of ones; a broadcast mask equals its expansion
+        assert torch.equal(tmu(x, "outgoing", None, **w), tmu(x, "outgoing", torch.ones_like(mask), **w))
+        assert torch.equal(tmu(x, "incoming", mask[0], **w), tmu(x, "incoming", mask[:1].expand(2, -1, -1), **w))
+        # every projection bias matters
+        for name in ("p_in_bias", "g_in_bias", "p_out_bias", "g_out_bias"):
+            w2 = dict(w, **{name: w[name] + 0.5})
+            assert not torch.equal(tmu(x, "outgoing", mask, **w2), base), name
+        # batch entries are independent
+        assert torch.equal(tmu(x[1:], "outgoing", mask[1:], **w), base[1:])
+    with pytest.raises(ValueError, match="direction must be one of"):
+        tmu(x, "sideways", mask, **w)
+
+
+def test_public_wrapper_and_dtypes():
+    from geometric_nn_ops_b200.triangle import triangle_multiplicative_update as op
+    x, mask, w, _ = util.trimul_inputs(1, 12, 32, 16, torch.float32, seed=2)
+    out = op(x, "incoming", mask, **w)
+    assert out.shape == x.shape and out.dtype == x.dtype
+    # 5-D input (two leading dims)
+    o5 = op(x.reshape(1, 1, 12, 12, 32), "incoming", mask.reshape(1, 1, 12, 12), **w)
+    assert torch.equal(o5.reshape(out.shape), out)
+    o64 = op(x.double(), "incoming", mask.double(), **{k: v.double() for k, v in w.items()})
+    assert o64.dtype == torch.float64 and torch.equal(o64.float(), out)
+
+
+def test_tf32_differs_from_ieee(tmu):
+    x, mask, w, d_out = util.trimul_inputs(1, 32, 64, 64, torch.float32, seed=3)
+    with util.matmul_precision("ieee"):
+        o1, g1 = util.trimul_fwd_bwd(tmu, x, mask, w, "outgoing", d_out)
+    with util.matmul_precision("tf32"):
+        o2, g2 = util.trimul_fwd_bwd(tmu, x, mask, w, "outgoing", d_out)
+    assert not torch.equal(o1, o2)
+    assert not torch.equal(g1["x"], g2["x"])
+
+
+@pytest.mark.parametrize("gamma", ["zero", "tiny"])
+def test_layernorm_weight_edge_cases(tmu, gamma):
+    x, mask, w, d_out = util.trimul_inputs(1, 16, 64, 64, torch.float32, seed=4)
+    val = 0.0 if gamma == "zero" else 1e-6
+    w = dict(w, norm_in_weight=torch.full_like(w["norm_in_weight"], val),
+             norm_out_weight=torch.full_like(w["norm_out_weight"], val))
+    out, grads = util.trimul_fwd_bwd(tmu, x, mask, w, "outgoing", d_out)
+    o_ref, g_ref = util.trimul_oracle(x, mask, w, "outgoing", d_out)
+    util.check_close("out", out, o_ref, 1 - 1e-6, 1e-4)
+    for name in ("x", "norm_in_bias", "p_out_weight"):
+        util.check_close("grad_" + name, grads[name], g_ref[name], 1 - 1e-6, 1e-3)
+
+
+@pytest.mark.parametrize("direction", ["outgoing", "incoming"])
+def test_headline_size_properties(tmu, direction):
+    """N=768, C=128 bf16: finite, deterministic, batch-independent sub-problem check via linearity in d_out."""
+    x, mask, w, d_out = util.trimul_inputs(1, 768, 128, 128, torch.bfloat16, seed=5)
+    out, g1 = util.trimul_fwd_bwd(tmu, x, mask, w, direction, d_out)
+    assert torch.isfinite(out.float()).all()
+    _, g2 = util.trimul_fwd_bwd(tmu, x, mask, w, direction, 2 * d_out)
+    for name in g1:
+        a, b = g1[name].float(), g2[name].float()
+        assert torch.isfinite(a).all(), name
+        rel = (2 * a - b).norm() / b.norm().clamp_min(1e-20)
+        assert rel < 2e-2, (name, float(rel))
