@@ -205,7 +205,11 @@ __global__ void __launch_bounds__(256) attn_fwd_kernel(TriAttnDesc d, const T* q
       int dd = tx + 16 * c;
       if (dd < D) orow[dd] = from_f32<T>(acc[r][c] * inv);
     }
-    if (tx == 0) lse[(((long long)b * d.n_seq + s) * d.H + h) * d.n_res + qi] = m[r] + logf(l[r]);
+    if (tx == 0) {
+      const long long row = (((long long)b * d.n_seq + s) * d.H + h) * d.n_res + qi;
+      lse[row] = m[r];
+      lse[(long long)d.B * d.n_seq * d.H * d.n_res + row] = logf(l[r]);
+    }
   }
 }
 
@@ -243,11 +247,13 @@ __device__ __forceinline__ void p_and_ds(const TriAttnDesc& d, const float* Qs, 
   for (int r = 0; r < 4; ++r) {
     const int ql = ty + 16 * r;
     const bool q_ok = q0 + ql < d.n_res;
-    const float ls = lse_s[ql], dl = delta_s[ql];
+    // P = exp((S - m) - log l): the two statistics stay separate because m + log l would round
+    // log l away when m is the -1e9 of a fully masked row.
+    const float ls = lse_s[ql], ll = lse_s[128 + ql], dl = delta_s[ql];
 #pragma unroll
     for (int c = 0; c < 4; ++c) {
       const bool ok = q_ok && (k0 + tx + 16 * c < d.n_res);
-      float pv = ok ? expf(sc[r][c] - ls) : 0.f;
+      float pv = ok ? expf((sc[r][c] - ls) - ll) : 0.f;
       p[r][c] = pv;
       ds[r][c] = ok ? pv * (dp[r][c] - dl) : 0.f;
     }
@@ -261,6 +267,7 @@ __device__ __forceinline__ void load_row_stats(const TriAttnDesc& d, const float
     int qi = q0 + tid;
     long long o = (((long long)b * d.n_seq + s) * d.H + h) * d.n_res + qi;
     lse_s[tid] = qi < d.n_res ? lse[o] : 0.f;
+    lse_s[128 + tid] = qi < d.n_res ? lse[(long long)d.B * d.n_seq * d.H * d.n_res + o] : 0.f;
     delta_s[tid] = qi < d.n_res ? delta[o] : 0.f;
   }
 }
@@ -458,7 +465,7 @@ int bwd_launch(const TriAttnDesc* d, const void* q, const void* k, const void* v
   TRI_LAUNCH_OK();
   const dim3 block(16, 16);
   {
-    size_t smem = (4 * 64 * DP + 2 * 64 * 65 + 128) * sizeof(float);
+    size_t smem = (4 * 64 * DP + 2 * 64 * 65 + 192) * sizeof(float);
     auto kern = attn_bwd_dkdv_kernel<T, DC, TF32>;
     TRI_TRY(set_smem(kern, smem));
     dim3 grid(cdiv(d->n_res, TK), d->B * d->n_seq * d->H);
@@ -467,7 +474,7 @@ int bwd_launch(const TriAttnDesc* d, const void* q, const void* k, const void* v
     TRI_LAUNCH_OK();
   }
   {
-    size_t smem = (4 * 64 * DP + 64 * 65 + 128) * sizeof(float);
+    size_t smem = (4 * 64 * DP + 64 * 65 + 192) * sizeof(float);
     auto kern = attn_bwd_dq_kernel<T, DC, TF32>;
     TRI_TRY(set_smem(kern, smem));
     dim3 grid(cdiv(d->n_res, TQ), d->B * d->n_seq * d->H);
@@ -476,7 +483,7 @@ int bwd_launch(const TriAttnDesc* d, const void* q, const void* k, const void* v
     TRI_LAUNCH_OK();
   }
   if (dbias != nullptr) {
-    size_t smem = (4 * 64 * DP + 128) * sizeof(float);
+    size_t smem = (4 * 64 * DP + 192) * sizeof(float);
     auto kern = attn_bwd_dbias_kernel<T, DC, TF32>;
     TRI_TRY(set_smem(kern, smem));
     dim3 grid(cdiv(d->n_res, TQ), cdiv(d->n_res, TK), d->B * d->H);

@@ -85,7 +85,7 @@ class _TriangleAttention(torch.autograd.Function):
             mask_u8 = mask.reshape(B, S, N).contiguous().view(torch.uint8)
         precision = _precision.matmul_precision(fp32_operands=q.dtype == torch.float32)
         o = _like(q)
-        lse = torch.empty(B, S, H, N, dtype=torch.float32, device=q.device)
+        lse = torch.empty(2, B, S, H, N, dtype=torch.float32, device=q.device)
         d = _desc(q, k, v, o, bias, mask_u8, scale, precision)
         ws_bytes = lib.tri_attn_ws_bytes(ctypes.byref(d), 0)
         ws = torch.empty(max(ws_bytes, 1), dtype=torch.uint8, device=q.device)

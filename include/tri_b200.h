@@ -68,7 +68,10 @@ int tri_profile_summary(char* buf, size_t cap);
  * choices.  bias: [B, H, n_res, n_res] with strides (batch, head, query), key
  * contiguous; batch stride may be 0.  mask: bytes (bool), [B, n_seq, n_res]
  * with strides (batch, row), key contiguous; nonzero = keep.
- * lse: fp32 [B, n_seq, H, n_res] contiguous.  dbias: fp32 [B, H, n_res, n_res]
+ * lse: fp32 [2, B, n_seq, H, n_res] contiguous softmax statistics: plane 0 is the row maximum m of
+ * the logits, plane 1 is log(sum_j exp(logit_j - m)); the log-sum-exp is their sum.  They are kept
+ * apart because a fully masked row has m = -1e9, where adding the second term would round it away.
+ * dbias: fp32 [B, H, n_res, n_res]
  * contiguous, summed over rows. */
 typedef struct TriAttnDesc {
   int32_t B, n_seq, n_res, H, D;
