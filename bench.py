@@ -1,0 +1,327 @@
+"""Headline benchmark: triangle attention + triangle multiplicative update, forward+backward, N=768.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl reference]
+
+One step = triangle_attention fwd+bwd (B=1, N=768, H=4, D=32, bf16, pair bias + key mask) plus
+triangle_multiplicative_update fwd+bwd in both directions (N=768, C=C_hidden=128, bf16), i.e. the
+configuration the metric in BASELINE.json is quoted on.  Inputs are seeded synthetic tensors with the
+shapes and distributions BASELINE.json lists.  Prints ONE JSON line (rank 0).
+
+value      TFLOP/s over the timed steps with inputs resident in HBM (CUDA events, max over ranks).
+e2e        the same metric through the public API with HOST (pinned) buffers: every step copies the
+           inputs host->device and the results device->host inside the timed region.
+roofline   the kernel with the largest share of the step, timed live with CUDA events on its stream
+           (the library brackets each launch when profiling is on), against MEASURED_PEAKS.json.
+cpu_baseline / --impl reference   the numpy port of the reference's pure-torch path (oracle/), timed
+           on this box's host cores on a bounded sample (smaller N, same widths).
+"""
+
+import argparse
+import json
+import os
+import statistics
+import sys
+import threading
+import time
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, ROOT)
+
+N_RES, HEADS, HEAD_DIM, C_Z, C_HID = 768, 4, 32, 128, 128
+CPU_SAMPLE_N = 192
+FALLBACK_PEAKS = {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "bf16_tflops_sustained": 1400.0}
+
+
+def attn_flops(n, h=HEADS, d=HEAD_DIM, b=1):
+    return 14.0 * b * n * h * n * n * d  # 4 fwd + 10 bwd per (row, head, query, key, d)
+
+
+def trimul_flops(n, c=C_Z, ch=C_HID, b=1):
+    m = b * n * n
+    fwd = 2.0 * m * c * 4 * ch + 2.0 * m * c * c + 2.0 * m * ch * c + 2.0 * b * n ** 3 * ch
+    return 3.0 * fwd  # backward = 2 x forward
+
+
+def step_flops(n):
+    return attn_flops(n) + 2 * trimul_flops(n)
+
+
+def peaks():
+    path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(path):
+        with open(path) as f:
+            return json.load(f), "measured"
+    return dict(FALLBACK_PEAKS), "fallback"
+
+
+class ClockSampler:
+    """Samples SM clock and throttle reasons through NVML (read-only) while the timed region runs."""
+
+    def __init__(self, index):
+        self.samples, self.reasons, self.max_mhz, self._stop = [], set(), None, threading.Event()
+        try:
+            import pynvml
+            pynvml.nvmlInit()
+            self.nv, self.h = pynvml, pynvml.nvmlDeviceGetHandleByIndex(index)
+            self.max_mhz = pynvml.nvmlDeviceGetMaxClockInfo(self.h, pynvml.NVML_CLOCK_SM)
+        except Exception:
+            self.nv = None
+        self.thread = threading.Thread(target=self._run, daemon=True)
+
+    def _run(self):
+        nv = self.nv
+        names = {
+            "hw_slowdown": getattr(nv, "nvmlClocksEventReasonHwSlowdown", 0x8),
+            "hw_thermal_slowdown": getattr(nv, "nvmlClocksEventReasonHwThermalSlowdown", 0x40),
+            "sw_thermal_slowdown": getattr(nv, "nvmlClocksEventReasonSwThermalSlowdown", 0x20),
+            "sw_power_cap": getattr(nv, "nvmlClocksEventReasonSwPowerCap", 0x4),
+        }
+        while not self._stop.is_set():
+            try:
+                self.samples.append(nv.nvmlDeviceGetClockInfo(self.h, nv.NVML_CLOCK_SM))
+                get = getattr(nv, "nvmlDeviceGetCurrentClocksEventReasons", None) or nv.nvmlDeviceGetCurrentClocksThrottleReasons
+                mask = get(self.h)
+                self.reasons |= {k for k, bit in names.items() if mask & bit}
+            except Exception:
+                pass
+            self._stop.wait(0.05)
+
+    def __enter__(self):
+        if self.nv is not None:
+            self.thread.start()
+        return self
+
+    def __exit__(self, *exc):
+        self._stop.set()
+        if self.nv is not None:
+            self.thread.join()
+
+    def summary(self):
+        return {"sm_mhz": statistics.median(self.samples) if self.samples else None,
+                "sm_max_mhz": self.max_mhz, "reasons": sorted(self.reasons)}
+
+
+# ------------------------------------------------------------------------------------------------
+# synthetic inputs (host, fp32 draw -> bf16), BASELINE.json distributions
+# ------------------------------------------------------------------------------------------------
+def host_inputs(n, seed, torch, rows=None):
+    """Inputs for one rank.  ``rows`` = (i0, i1) restricts the row axis (multi-GPU sharding)."""
+    g = torch.Generator().manual_seed(seed)
+    bf = torch.bfloat16
+    rn = lambda *s, sc=1.0: (torch.randn(*s, generator=g) * sc).to(bf)  # noqa: E731
+    i0, i1 = rows or (0, n)
+    r = i1 - i0
+    t = {
+        "q": rn(1, r, n, HEADS, HEAD_DIM), "k": rn(1, r, n, HEADS, HEAD_DIM), "v": rn(1, r, n, HEADS, HEAD_DIM),
+        "bias": rn(1, 1, HEADS, n, n), "d_o": rn(1, r, n, HEADS, HEAD_DIM),
+        "x": rn(1, n, n, C_Z), "d_out": rn(1, n, n, C_Z),
+        "pair_mask": (torch.rand(1, n, n, generator=g) < 0.9).to(bf),
+    }
+    key_mask = torch.rand(1, r, 1, 1, n, generator=g) < 0.95
+    key_mask[..., 0] = True
+    t["key_mask"] = key_mask
+    w = {
+        "norm_in_weight": 1 + rn(C_Z, sc=0.02).float(), "norm_in_bias": rn(C_Z, sc=0.02),
+        "p_in_weight": rn(2 * C_HID, C_Z, sc=C_Z ** -0.5), "g_in_weight": rn(2 * C_HID, C_Z, sc=C_Z ** -0.5),
+        "norm_out_weight": 1 + rn(C_HID, sc=0.02).float(), "norm_out_bias": rn(C_HID, sc=0.02),
+        "p_out_weight": rn(C_Z, C_HID, sc=C_HID ** -0.5), "g_out_weight": rn(C_Z, C_Z, sc=C_Z ** -0.5),
+    }
+    w = {k: v.to(bf) for k, v in w.items()}
+    return t, w
+
+
+def one_step(t, w, torch, triangle_attention, trimul):
+    """Forward+backward of the three ops through the public API; returns every result tensor."""
+    q, k, v, bias = (t[n].detach().requires_grad_() for n in ("q", "k", "v", "bias"))
+    o = triangle_attention(q, k, v, bias, t["key_mask"], HEAD_DIM ** -0.5)
+    res = [o, *torch.autograd.grad(o, [q, k, v, bias], grad_outputs=t["d_o"])]
+    for direction in ("outgoing", "incoming"):
+        x = t["x"].detach().requires_grad_()
+        wl = {n: p.detach().requires_grad_() for n, p in w.items()}
+        out = trimul(x, direction, t["pair_mask"], **wl)
+        res += [out, *torch.autograd.grad(out, [x, *wl.values()], grad_outputs=t["d_out"])]
+    return res
+
+
+# ------------------------------------------------------------------------------------------------
+# CPU baseline: numpy port of the reference's torch path, bounded sample
+# ------------------------------------------------------------------------------------------------
+def cpu_reference(steps, warmup):
+    import numpy as np
+
+    from oracle import triangle_oracle as orc
+
+    n = CPU_SAMPLE_N
+    rng = np.random.default_rng(0)
+    f = np.float32
+    rn = lambda *s, sc=1.0: (rng.standard_normal(s) * sc).astype(f)  # noqa: E731
+    q, k, v, d_o = (rn(1, n, n, HEADS, HEAD_DIM) for _ in range(4))
+    bias = rn(1, 1, HEADS, n, n)
+    mask = rng.random((1, n, 1, 1, n)) < 0.95
+    mask[..., 0] = True
+    x, d_out = rn(1, n, n, C_Z), rn(1, n, n, C_Z)
+    pm = (rng.random((1, n, n)) < 0.9).astype(f)
+    w = {"norm_in_weight": 1 + rn(C_Z, sc=0.02), "norm_in_bias": rn(C_Z, sc=0.02),
+         "p_in_weight": rn(2 * C_HID, C_Z, sc=C_Z ** -0.5), "g_in_weight": rn(2 * C_HID, C_Z, sc=C_Z ** -0.5),
+         "norm_out_weight": 1 + rn(C_HID, sc=0.02), "norm_out_bias": rn(C_HID, sc=0.02),
+         "p_out_weight": rn(C_Z, C_HID, sc=C_HID ** -0.5), "g_out_weight": rn(C_Z, C_Z, sc=C_Z ** -0.5)}
+
+    def step():
+        orc.triangle_attention_fwd(q, k, v, bias, mask, None, acc=f)
+        orc.triangle_attention_bwd(q, k, v, bias, mask, None, d_o, acc=f)
+        for direction in ("outgoing", "incoming"):
+            orc.trimul_fwd(x, direction, pm, acc=f, **w)
+            orc.trimul_bwd(x, direction, pm, d_out, acc=f, **w)  # recomputes the forward it needs
+
+    for _ in range(warmup):
+        step()
+    t0 = time.perf_counter()
+    for _ in range(steps):
+        step()
+    dt = (time.perf_counter() - t0) / steps
+    cores = os.cpu_count() or 1
+    return {
+        "value": step_flops(n) / dt / 1e12, "unit": "TFLOP/s", "cores": cores, "kind": "port",
+        "sample": f"same ops and widths at N={n} (fp32 numpy/OpenBLAS, {cores} threads), "
+                  f"{dt * 1e3:.0f} ms per step, {steps} steps",
+    }, dt
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=10)
+    ap.add_argument("--warmup", type=int, default=3)
+    ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
+    ap.add_argument("--n-res", type=int, default=N_RES, help="pair side (default: the headline 768)")
+    args = ap.parse_args()
+    rank = int(os.environ.get("RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    n = args.n_res
+    config = {"workload": f"tri-attn fwd+bwd (B=1,N={n},H={HEADS},D={HEAD_DIM}) + trimul outgoing+incoming fwd+bwd "
+                          f"(N={n},C={C_Z},Ch={C_HID}), bf16", "l2": "inputs larger than L2 (no flush)",
+              "parallelism": f"rows sharded over {world} GPU(s)" if world > 1 else "single GPU"}
+    base = {"metric": "tri-attn+trimul fwd+bwd TFLOP/s, N=768", "unit": "TFLOP/s", "n_gpus": args.gpus,
+            "steps": args.steps, "warmup": args.warmup, "higher_is_better": True, "scaling": "strong",
+            "vs_baseline": None, "dtype": "bf16", "data": "synthetic", "config": config}
+
+    if args.impl == "reference":
+        if rank != 0:
+            return
+        cpu, dt = cpu_reference(max(1, min(args.steps, 3)), min(args.warmup, 1))
+        line = dict(base, impl="reference", value=cpu["value"], ms_per_step=dt * 1e3, cpu_baseline=cpu,
+                    e2e={"value": cpu["value"], "unit": "TFLOP/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+                    gpu_launches=0)
+        line["config"] = dict(config, cpu_sample=cpu["sample"])
+        print(json.dumps(line))
+        return
+
+    import torch
+
+    from geometric_nn_ops_b200 import _lib
+    from geometric_nn_ops_b200.triangle import triangle_attention, trimul_b200
+
+    if not torch.cuda.is_available():
+        raise SystemExit("bench.py needs a GPU (there is no CPU path in the library)")
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    torch.cuda.set_device(local)
+    dist = None
+    if world > 1:
+        import torch.distributed as dist
+        dist.init_process_group("nccl", device_id=torch.device("cuda", local))
+    if world > 1:
+        from geometric_nn_ops_b200 import sharded
+        step_fn, host_t, host_w = sharded.make_bench_step(n, rank, world, host_inputs)
+    else:
+        host_t, host_w = host_inputs(n, 0, torch)
+        step_fn = lambda t, w: one_step(t, w, torch, triangle_attention, trimul_b200)  # noqa: E731
+    pin = lambda d: {k_: v_.pin_memory() for k_, v_ in d.items()}  # noqa: E731
+    host_t, host_w = pin(host_t), pin(host_w)
+    to_dev = lambda d: {k_: v_.cuda(non_blocking=True) for k_, v_ in d.items()}  # noqa: E731
+    dev_t, dev_w = to_dev(host_t), to_dev(host_w)
+    torch.cuda.synchronize()
+
+    def barrier():
+        if dist is not None:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    for _ in range(args.warmup):
+        step_fn(dev_t, dev_w)
+    barrier()
+
+    # ---- timed region: device-resident inputs -------------------------------------------------
+    _lib.reset_launch_count()
+    _lib.profile_enable(True)
+    beg, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    with ClockSampler(local) as clocks:
+        barrier()
+        beg.record()
+        for _ in range(args.steps):
+            step_fn(dev_t, dev_w)
+        end.record()
+        barrier()
+    ms = beg.elapsed_time(end) / args.steps
+    launches = _lib.launch_count()
+    prof = _lib.profile_summary()
+    _lib.profile_enable(False)
+
+    # ---- e2e: host buffers, copies inside the timed region --------------------------------------
+    h2d = sum(v.numel() * v.element_size() for v in list(host_t.values()) + list(host_w.values()))
+    out_host = None
+    e2e_steps = max(2, min(args.steps, 5))
+    barrier()
+    t_beg = torch.cuda.Event(enable_timing=True)
+    t_end = torch.cuda.Event(enable_timing=True)
+    t_beg.record()
+    for _ in range(e2e_steps):
+        res = step_fn(to_dev(host_t), to_dev(host_w))
+        if out_host is None:
+            out_host = [torch.empty(r.shape, dtype=r.dtype, pin_memory=True) for r in res]
+        for dst, src in zip(out_host, res):
+            dst.copy_(src, non_blocking=True)
+    t_end.record()
+    barrier()
+    e2e_ms = t_beg.elapsed_time(t_end) / e2e_steps
+    d2h = sum(r.numel() * r.element_size() for r in out_host)
+
+    times = torch.tensor([ms, e2e_ms], device="cuda", dtype=torch.float64)
+    if dist is not None:
+        dist.all_reduce(times, op=dist.ReduceOp.MAX)
+    ms, e2e_ms = times.tolist()
+    if rank != 0:
+        dist.destroy_process_group()
+        return
+
+    flops = step_flops(n)
+    pk, pk_kind = peaks()
+    top = max(prof.items(), key=lambda kv: kv[1][1]) if prof else None
+    roofline = None
+    if top is not None:
+        name, (cnt, tot_ms, kflops, kbytes) = top
+        sec = tot_ms / 1e3
+        tensor_bound = kflops > 0 and kflops / max(kbytes, 1.0) > pk["bf16_tflops"] * 1e12 / (pk["hbm_gbs"] * 1e9)
+        if tensor_bound:
+            ach, peak, unit = kflops / sec / 1e12, pk["bf16_tflops_sustained"], "TFLOP/s"
+        else:
+            ach, peak, unit = kbytes / sec / 1e9, pk["hbm_gbs"], "GB/s"
+        roofline = {"kernel": name, "bound": "tensor" if tensor_bound else "hbm", "achieved": ach, "peak": peak,
+                    "unit": unit, "frac": ach / peak, "traffic": None, "peak_source": f"of {pk_kind}",
+                    "launches": cnt, "avg_launch_ms": tot_ms / cnt, "share_of_step": tot_ms / args.steps / ms}
+    kernels = {k_: {"launches": v_[0], "ms_per_step": v_[1] / args.steps} for k_, v_ in
+               sorted(prof.items(), key=lambda kv: -kv[1][1])}
+    cpu, _ = cpu_reference(1, 1) if world == 1 else (None, None)
+    line = dict(base, value=flops / (ms / 1e3) / 1e12, ms_per_step=ms,
+                pct_of_bf16_peak={"measured_burst": flops / (ms / 1e3) / 1e12 / pk["bf16_tflops"] / world,
+                                  "nominal_2250": flops / (ms / 1e3) / 1e12 / 2250.0 / world},
+                e2e={"value": flops / (e2e_ms / 1e3) / 1e12, "unit": "TFLOP/s", "ms_per_step": e2e_ms,
+                     "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h},
+                gpu_launches=launches, path=_lib.last_path(), clocks=clocks.summary(), roofline=roofline,
+                kernels=kernels, cpu_baseline=cpu)
+    print(json.dumps(line))
+    if dist is not None:
+        dist.destroy_process_group()
+
+
+if __name__ == "__main__":
+    main()

@@ -33,6 +33,15 @@ class TriMulDesc(Structure):
     ]
 
 
+class TriGemmDesc(Structure):
+    _fields_ = [
+        ("M", c_int32), ("N", c_int32), ("K", c_int32), ("batch", c_int32), ("dtype", c_int32),
+        ("a_mn_major", c_int32), ("b_mn_major", c_int32), ("out_f32", c_int32),
+        ("lda", c_int64), ("ldb", c_int64), ("ldc", c_int64),
+        ("batch_a", c_int64), ("batch_b", c_int64), ("batch_c", c_int64),
+    ]
+
+
 WEIGHT_NAMES = (
     "norm_in_weight", "norm_in_bias", "p_in_weight", "p_in_bias", "g_in_weight", "g_in_bias",
     "norm_out_weight", "norm_out_bias", "p_out_weight", "p_out_bias", "g_out_weight", "g_out_bias",
@@ -65,6 +74,8 @@ EXPORTS = {
                             c_void_p, c_size_t, c_void_p]),
     "tri_mul_bwd": (c_int, [POINTER(TriMulDesc), c_void_p, c_void_p, POINTER(TriMulWeights), c_void_p, c_void_p,
                             c_void_p, POINTER(TriMulWeightGrads), c_void_p, c_size_t, c_void_p]),
+    "tri_bgemm": (c_int, [POINTER(TriGemmDesc), c_void_p, c_void_p, c_void_p, c_void_p, c_size_t, c_void_p]),
+    "tri_ws_status": (c_int, [c_void_p, c_void_p]),
 }
 
 _lib = None
@@ -111,13 +122,13 @@ def profile_enable(on: bool) -> None:
 
 
 def profile_summary() -> dict:
-    """{kernel name: (launches, total_ms)} for the launches recorded since profile_enable(True)."""
+    """{kernel name: (launches, total_ms, flops, bytes)} recorded since profile_enable(True)."""
     buf = ctypes.create_string_buffer(1 << 16)
     check(load().tri_profile_summary(buf, len(buf)), "tri_profile_summary")
     out = {}
     for line in buf.value.decode().splitlines():
-        name, n, ms = line.rsplit(" ", 2)
-        out[name] = (int(n), float(ms))
+        name, n, ms, flops, nbytes = line.rsplit(" ", 4)
+        out[name] = (int(n), float(ms), float(flops), float(nbytes))
     return out
 
 

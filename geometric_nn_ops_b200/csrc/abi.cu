@@ -9,6 +9,7 @@
 
 #include "attn_simt.cuh"
 #include "common.cuh"
+#include "tc_gemm.cuh"
 #include "tc_paths.cuh"
 #include "trimul_simt.cuh"
 
@@ -19,17 +20,17 @@ thread_local const char* g_path = "none";
 // Launch counter and timing records are process-wide: autograd runs the backward on its own thread.
 std::atomic<long long> g_launches{0};
 
-struct ProfRecord { const char* name; cudaEvent_t beg, end; };
+struct ProfRecord { const char* name; cudaEvent_t beg, end; double flops, bytes; };
 std::atomic<bool> g_prof_on{false};
 std::mutex g_prof_mu;
 std::vector<ProfRecord>* g_prof = nullptr;
 }  // namespace
 
-KernelTimer::KernelTimer(const char* name, cudaStream_t stream) : slot(-1), st(stream) {
+KernelTimer::KernelTimer(const char* name, cudaStream_t stream, double flops, double bytes) : slot(-1), st(stream) {
   if (!g_prof_on.load()) return;
   std::lock_guard<std::mutex> lock(g_prof_mu);
   if (g_prof == nullptr) g_prof = new std::vector<ProfRecord>();
-  ProfRecord r{name, nullptr, nullptr};
+  ProfRecord r{name, nullptr, nullptr, flops, bytes};
   if (cudaEventCreate(&r.beg) != cudaSuccess || cudaEventCreate(&r.end) != cudaSuccess) return;
   cudaEventRecord(r.beg, st);
   g_prof->push_back(r);
@@ -99,18 +100,22 @@ int tri_profile_summary(char* buf, size_t cap) {
   buf[0] = 0;
   std::lock_guard<std::mutex> lock(g_prof_mu);
   if (g_prof == nullptr) return 0;
-  std::map<std::string, std::pair<int, double>> agg;
+  struct Agg { int n = 0; double ms = 0, flops = 0, bytes = 0; };
+  std::map<std::string, Agg> agg;
   for (auto& r : *g_prof) {
     TRI_CUDA_OK(cudaEventSynchronize(r.end));
     float ms = 0.f;
     TRI_CUDA_OK(cudaEventElapsedTime(&ms, r.beg, r.end));
     auto& a = agg[r.name];
-    a.first += 1;
-    a.second += ms;
+    a.n += 1;
+    a.ms += ms;
+    a.flops += r.flops;
+    a.bytes += r.bytes;
   }
   size_t off = 0;
   for (auto& kv : agg) {
-    int n = snprintf(buf + off, cap - off, "%s %d %.6f\n", kv.first.c_str(), kv.second.first, kv.second.second);
+    int n = snprintf(buf + off, cap - off, "%s %d %.6f %.6e %.6e\n", kv.first.c_str(), kv.second.n, kv.second.ms,
+                     kv.second.flops, kv.second.bytes);
     if (n < 0 || (size_t)n >= cap - off) return fail(TRI_ERR_ARG, "buffer too small");
     off += (size_t)n;
   }
@@ -193,6 +198,40 @@ int tri_mul_bwd(const TriMulDesc* d, const void* x, const void* mask, const TriM
   }
   set_path("simt");
   return simt::backward(d, x, mask, w, saved, d_out, dx, g, ws, ws_bytes, (cudaStream_t)stream);
+}
+
+int tri_ws_status(const void* ws, tri_stream_t stream) {
+  if (ws == nullptr) return fail(TRI_ERR_ARG, "ws is null");
+  int code = 0;
+  TRI_CUDA_OK(cudaMemcpyAsync(&code, ws, sizeof(int), cudaMemcpyDeviceToHost, (cudaStream_t)stream));
+  TRI_CUDA_OK(cudaStreamSynchronize((cudaStream_t)stream));
+  if (code != 0) return fail(TRI_ERR_DEVICE, "a tensor-core kernel gave up waiting (code %d)", code);
+  return 0;
+}
+
+int tri_bgemm(const TriGemmDesc* d, const void* a, const void* b, void* c, void* ws, size_t ws_bytes,
+              tri_stream_t stream) {
+  if (!d || !a || !b || !c || !ws) return fail(TRI_ERR_ARG, "null argument");
+  if (ws_bytes < 256) return fail(TRI_ERR_WORKSPACE, "tri_bgemm needs a 256-byte workspace");
+  if (d->M <= 0 || d->N <= 0 || d->K <= 0 || d->batch <= 0) return fail(TRI_ERR_ARG, "sizes must be positive");
+  if (d->dtype < TRI_F32 || d->dtype > TRI_F16) return fail(TRI_ERR_ARG, "bad dtype %d", d->dtype);
+  cudaStream_t st = (cudaStream_t)stream;
+  TRI_CUDA_OK(cudaMemsetAsync(ws, 0, 256, st));
+  tc::GemmPlan p;
+  p.a[0].ptr = a; p.a[0].mn_major = d->a_mn_major != 0;
+  p.a[0].inner = d->a_mn_major ? d->M : d->K; p.a[0].outer = d->a_mn_major ? d->K : d->M;
+  p.a[0].batch = d->batch; p.a[0].st_outer = d->lda; p.a[0].st_batch = d->batch_a;
+  p.b[0].ptr = b; p.b[0].mn_major = d->b_mn_major != 0;
+  p.b[0].inner = d->b_mn_major ? d->N : d->K; p.b[0].outer = d->b_mn_major ? d->K : d->N;
+  p.b[0].batch = d->batch; p.b[0].st_outer = d->ldb; p.b[0].st_batch = d->batch_b;
+  p.M = d->M; p.N = d->N; p.K0 = d->K; p.batches = d->batch;
+  p.out0 = c; p.ld_out = d->ldc; p.batch_out = d->batch_c;
+  p.name = "tc_bgemm";
+  p.flops = 2.0 * d->batch * d->M * (double)d->N * d->K;
+  const double es = d->dtype == TRI_F32 ? 4.0 : 2.0;
+  p.bytes = d->batch * (es * ((double)d->M * d->K + (double)d->N * d->K) + (d->out_f32 ? 4.0 : es) * d->M * d->N);
+  set_path("tcgen05");
+  return tc::launch_gemm(st, d->dtype, tc::EPI_STORE, d->N > 128 ? 256 : 128, d->out_f32 != 0, p, (int*)ws);
 }
 
 }  // extern "C"

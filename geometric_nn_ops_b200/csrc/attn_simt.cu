@@ -450,6 +450,8 @@ int fwd_launch(const TriAttnDesc* d, const void* q, const void* k, const void* v
   auto kern = attn_fwd_kernel<T, DC, TF32>;
   TRI_TRY(set_smem(kern, smem));
   dim3 grid(cdiv(d->n_res, TQ), d->B * d->n_seq * d->H);
+  const double pairs = (double)d->B * d->n_seq * d->H * d->n_res * (double)d->n_res;
+  KernelTimer kt("simt_attn_fwd", st, 4.0 * pairs * d->D, 4.0 * sizeof(T) * d->B * d->n_seq * (double)d->n_res * d->H * d->D);
   kern<<<grid, dim3(16, 16), smem, st>>>(*d, (const T*)q, (const T*)k, (const T*)v, (const T*)bias, mask, (T*)o, lse);
   TRI_LAUNCH_OK();
   return 0;
@@ -461,14 +463,20 @@ int bwd_launch(const TriAttnDesc* d, const void* q, const void* k, const void* v
                float* dbias, float* delta, cudaStream_t st) {
   const int DP = 16 * DC + 1;
   const long long rows = (long long)d->B * d->n_seq * d->H * d->n_res;
-  attn_delta_kernel<T><<<cdiv(rows, 256), 256, 0, st>>>(*d, (const T*)o, (const T*)d_o, delta);
-  TRI_LAUNCH_OK();
+  const double pairs = (double)d->B * d->n_seq * d->H * d->n_res * (double)d->n_res;
+  const double tensor_bytes = sizeof(T) * (double)d->B * d->n_seq * d->n_res * d->H * d->D;
+  {
+    KernelTimer kt("simt_attn_delta", st, 0.0, 2.0 * tensor_bytes);
+    attn_delta_kernel<T><<<cdiv(rows, 256), 256, 0, st>>>(*d, (const T*)o, (const T*)d_o, delta);
+    TRI_LAUNCH_OK();
+  }
   const dim3 block(16, 16);
   {
     size_t smem = (4 * 64 * DP + 2 * 64 * 65 + 192) * sizeof(float);
     auto kern = attn_bwd_dkdv_kernel<T, DC, TF32>;
     TRI_TRY(set_smem(kern, smem));
     dim3 grid(cdiv(d->n_res, TK), d->B * d->n_seq * d->H);
+    KernelTimer kt("simt_attn_bwd_dkdv", st, 8.0 * pairs * d->D, 6.0 * tensor_bytes);
     kern<<<grid, block, smem, st>>>(*d, (const T*)q, (const T*)k, (const T*)v, (const T*)bias, mask, (const T*)d_o,
                                     lse, delta, (T*)dk, (T*)dv);
     TRI_LAUNCH_OK();
@@ -478,6 +486,7 @@ int bwd_launch(const TriAttnDesc* d, const void* q, const void* k, const void* v
     auto kern = attn_bwd_dq_kernel<T, DC, TF32>;
     TRI_TRY(set_smem(kern, smem));
     dim3 grid(cdiv(d->n_res, TQ), d->B * d->n_seq * d->H);
+    KernelTimer kt("simt_attn_bwd_dq", st, 2.0 * pairs * d->D, 5.0 * tensor_bytes);
     kern<<<grid, block, smem, st>>>(*d, (const T*)q, (const T*)k, (const T*)v, (const T*)bias, mask, (const T*)d_o,
                                     lse, delta, (T*)dq);
     TRI_LAUNCH_OK();
@@ -487,6 +496,7 @@ int bwd_launch(const TriAttnDesc* d, const void* q, const void* k, const void* v
     auto kern = attn_bwd_dbias_kernel<T, DC, TF32>;
     TRI_TRY(set_smem(kern, smem));
     dim3 grid(cdiv(d->n_res, TQ), cdiv(d->n_res, TK), d->B * d->H);
+    KernelTimer kt("simt_attn_bwd_dbias", st, 0.0, 4.0 * tensor_bytes);
     kern<<<grid, block, smem, st>>>(*d, (const T*)q, (const T*)k, (const T*)v, (const T*)bias, mask, (const T*)d_o,
                                     lse, delta, dbias);
     TRI_LAUNCH_OK();

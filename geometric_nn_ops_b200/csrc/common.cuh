@@ -20,10 +20,11 @@ void count_launch(int n = 1);
 
 // Optional per-kernel timing: when enabled (tri_profile_enable), every launch site is bracketed by a
 // pair of CUDA events on the launching stream; tri_profile_summary sums them per kernel name.
+// `flops` and `bytes` are the ALGORITHMIC work of the launch (not measured traffic).
 struct KernelTimer {
   int slot;
   cudaStream_t st;
-  KernelTimer(const char* name, cudaStream_t stream);
+  KernelTimer(const char* name, cudaStream_t stream, double flops = 0.0, double bytes = 0.0);
   ~KernelTimer();
 };
 

@@ -132,13 +132,16 @@ __host__ __device__ constexpr uint32_t make_idesc(int kind, int m, int n, bool a
 // K-major tile: rows of 128 bytes along K, 8-row groups 1024 bytes apart (SBO); LBO unused (1).
 // MN-major tile: rows of 128 bytes along MN, one row per k, 8-k groups 1024 bytes apart (SBO),
 //   successive 128-byte MN chunks `lbo_bytes` apart.
-__device__ __forceinline__ uint64_t make_smem_desc(uint32_t saddr, uint32_t lbo_bytes, uint32_t sbo_bytes) {
+// 32-bit MN-major operands (tf32) exist only in the "128-byte swizzle, 32-byte atom" form: layout = 1,
+//   4-k groups 512 bytes apart (SBO); TMA must then use CU_TENSOR_MAP_SWIZZLE_128B_ATOM_32B.
+__device__ __forceinline__ uint64_t make_smem_desc(uint32_t saddr, uint32_t lbo_bytes, uint32_t sbo_bytes,
+                                                   uint32_t layout = 2) {
   uint64_t d = 0;
   d |= (uint64_t)((saddr & 0x3FFFF) >> 4);
   d |= (uint64_t)((lbo_bytes >> 4) & 0x3FFF) << 16;
   d |= (uint64_t)((sbo_bytes >> 4) & 0x3FFF) << 32;
   d |= (uint64_t)1 << 46;
-  d |= (uint64_t)2 << 61;
+  d |= (uint64_t)layout << 61;
   return d;
 }
 
@@ -178,8 +181,8 @@ __device__ __forceinline__ bool elect_one() {
 // ---------------------------------------------------------------------------------------------
 // Rank-3 tiled map with 128-byte swizzle over a tensor whose innermost dim is contiguous.
 // dims/strides are in elements, outermost last; box_inner * elem_bytes must be 128.
-int make_tmap_3d(CUtensorMap* out, const void* base, int elem_bytes, bool is_f32, const uint64_t dims[3],
-                 const uint64_t strides_elems[2], const uint32_t box[3]);
+int make_tmap_3d(CUtensorMap* out, const void* base, int elem_bytes, bool is_f16, const uint64_t dims[3],
+                 const uint64_t strides_elems[2], const uint32_t box[3], bool atom_32b);
 
 }  // namespace tc
 }  // namespace tri

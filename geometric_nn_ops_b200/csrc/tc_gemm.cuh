@@ -1,0 +1,331 @@
+// Persistent, warp-specialised tcgen05 GEMM:  D[m, n] = sum_k A(m, k) * B(n, k), fp32 accumulation in TMEM.
+//
+//   warp 0      TMA producer: fills a ring of shared-memory stages (128-byte swizzle) with operand tiles
+//   warp 1      MMA issuer:   tcgen05.mma from the stages into one of two TMEM accumulators
+//   warps 2..5  epilogue:     tcgen05.ld the finished accumulator, apply the fused epilogue, store to HBM
+//
+// A tile is 128 (M) x BN (N); K advances 128 bytes per stage (64 bf16/fp16 or 32 fp32 elements).  Each
+// operand may be K-major (K contiguous in global memory) or MN-major (M or N contiguous); the second form
+// is what the transposed contractions and the weight-gradient GEMMs need, and costs nothing: only the TMA
+// box shape and the MMA descriptors differ.  Two K "segments" with their own tensor maps can feed the
+// same tile, either into the same accumulator columns (a sum of two products) or into the second half
+// of them (two products side by side); the fused gate epilogues use that.  With split_k the batch index
+// selects a K range instead of a batch entry (weight gradients over all pixels).
+//
+// All waits are bounded (see tc_common.cuh); a timeout lands in *args.err and the kernel drains.
+#pragma once
+
+#include "tc_common.cuh"
+
+namespace tri {
+namespace tc {
+
+enum Epilogue {
+  EPI_STORE = 0,        // out0[batch][m][n] = acc (+ bias0[n])
+  EPI_GATE_IN = 1,      // cols [P(128) | G(128)]: half-plane[c][m] = (P+b)*sigmoid(G+b)*mask[m], channel-major
+  EPI_GATE_OUT = 2,     // cols [y(128) | g(128)]: out0[m][c] = (y+b)*sigmoid(g+b)
+  EPI_GATE_OUT_BWD = 3  // same cols, aux = d_out: out0 = d_out*sig, out1 = d_out*(y+b)*sig*(1-sig)
+};
+
+constexpr int kBM = 128;
+constexpr int kStageA = kBM * 128;  // bytes
+
+struct GemmArgs {
+  int M, N;                  // output extent of one batch entry
+  int kblocks0, kblocks1;    // K blocks (of 128 bytes) in segment 0 / segment 1 (0 = no second segment)
+  int seg1_col;              // accumulator column where segment 1 lands (0 = add to segment 0's columns)
+  int seg1_n;                // N extent of segment 1's MMA (columns), segment 0 uses bn0
+  int bn0;                   // N extent of segment 0's MMA
+  int batches, tiles_m, tiles_n;
+  int split_k;               // batch index selects K range [batch*kblocks0, ...) instead of a batch entry
+  int a_mn[2], b_mn[2];      // per segment: operand is MN-major
+  uint32_t idesc[2];
+  // epilogue
+  void* out0;
+  void* out1;
+  long long ld_out, batch_out;   // elements
+  const float* bias0;            // per output column (EPI_STORE) / per accumulator column (gates)
+  const void* aux;               // mask (GATE_IN) or d_out (GATE_OUT_BWD), in the input dtype
+  long long plane;               // GATE_IN: pixels per batch entry (N*N); channel-major plane stride
+  int* err;
+};
+
+template <typename T> struct ElemTraits;
+template <> struct ElemTraits<__nv_bfloat16> { static constexpr int kind = KIND_BF16; static constexpr bool tf32 = false; };
+template <> struct ElemTraits<__half> { static constexpr int kind = KIND_F16; static constexpr bool tf32 = false; };
+template <> struct ElemTraits<float> { static constexpr int kind = KIND_TF32; static constexpr bool tf32 = true; };
+
+template <typename TOUT>
+__device__ __forceinline__ void store_row32(TOUT* dst, const float (&v)[32], int valid, bool vec_ok) {
+  if (valid >= 32 && vec_ok) {
+    if constexpr (sizeof(TOUT) == 4) {
+#pragma unroll
+      for (int i = 0; i < 8; ++i)
+        reinterpret_cast<float4*>(dst)[i] = make_float4(v[4 * i], v[4 * i + 1], v[4 * i + 2], v[4 * i + 3]);
+    } else {
+#pragma unroll
+      for (int i = 0; i < 4; ++i) {
+        union { uint4 u; TOUT h[8]; } pk;
+#pragma unroll
+        for (int j = 0; j < 8; ++j) pk.h[j] = from_f32<TOUT>(v[8 * i + j]);
+        reinterpret_cast<uint4*>(dst)[i] = pk.u;
+      }
+    }
+  } else {
+#pragma unroll
+    for (int i = 0; i < 32; ++i)
+      if (i < valid) dst[i] = from_f32<TOUT>(v[i]);
+  }
+}
+
+__device__ __forceinline__ void ld32_f(uint32_t taddr, float (&v)[32]) {
+  uint32_t r[32];
+  tmem_ld_32x32(taddr, r);
+  tmem_ld_wait();
+#pragma unroll
+  for (int i = 0; i < 32; ++i) v[i] = __uint_as_float(r[i]);
+}
+
+template <typename TIN, typename TOUT, int BN, int EPI, int STAGES>
+__global__ void __launch_bounds__(192, 1)
+tc_gemm_kernel(const __grid_constant__ CUtensorMap tmA0, const __grid_constant__ CUtensorMap tmB0,
+               const __grid_constant__ CUtensorMap tmA1, const __grid_constant__ CUtensorMap tmB1, const GemmArgs g) {
+  constexpr int ES = sizeof(TIN);
+  constexpr int BKE = 128 / ES;        // K elements per stage
+  constexpr int UK = 32 / ES;          // K elements per MMA
+  constexpr int CE = 128 / ES;         // MN elements per 128-byte chunk (MN-major operands)
+  constexpr int STAGE_B = BN * 128;
+  // MN-major tiles: 16-bit types use the plain 128-byte swizzle (8-k groups of 1024 bytes); 32-bit
+  // types only exist with the 32-byte-atom swizzle (4-k groups of 512 bytes, layout code 1).
+  constexpr uint32_t MN_SBO = ES == 4 ? 512 : 1024;
+  constexpr uint32_t MN_LAYOUT = ES == 4 ? 1 : 2;
+  constexpr int KIND = ElemTraits<TIN>::kind == KIND_TF32 ? KIND_TF32 : KIND_F16;
+
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  uint8_t* sA = smem;
+  uint8_t* sB = smem + STAGES * kStageA;
+  uint64_t* full = reinterpret_cast<uint64_t*>(sB + STAGES * STAGE_B);
+  uint64_t* empty = full + STAGES;
+  uint64_t* tfull = empty + STAGES;
+  uint64_t* tempty = tfull + 2;
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(tempty + 2);
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < STAGES; ++s) { mbar_init(&full[s], 1); mbar_init(&empty[s], 1); }
+    for (int a = 0; a < 2; ++a) { mbar_init(&tfull[a], 1); mbar_init(&tempty[a], 4); }
+    mbar_fence_init();
+    tma_prefetch_desc(&tmA0);
+    tma_prefetch_desc(&tmB0);
+  }
+  if (warp == 1) tmem_alloc(tmem_slot, 2 * BN);
+  tc_fence_before_sync();
+  __syncthreads();
+  tc_fence_after_sync();
+  const uint32_t tmem_base = *tmem_slot;
+
+  const int total = g.batches * g.tiles_m * g.tiles_n;
+  const int kb_total = g.kblocks0 + g.kblocks1;
+
+  if (warp == 0) {
+    // ------------------------------------------------------------------ producer
+    const bool leader = elect_one();
+    if (leader) {
+      int stage = 0;
+      uint32_t phase = 0;
+      bool ok = true;
+      for (int tile = blockIdx.x; tile < total && ok; tile += gridDim.x) {
+        const int tn = tile % g.tiles_n, tm = (tile / g.tiles_n) % g.tiles_m, bz = tile / (g.tiles_n * g.tiles_m);
+        const int m0 = tm * kBM, n0 = tn * BN;
+        const int zc = g.split_k ? 0 : bz;
+        const int koff = g.split_k ? bz * g.kblocks0 * BKE : 0;
+        for (int kb = 0; kb < kb_total; ++kb) {
+          if (!mbar_wait(&empty[stage], phase ^ 1, g.err, 1)) { ok = false; break; }
+          const int seg = kb >= g.kblocks0 ? 1 : 0;
+          const int kk = (seg ? kb - g.kblocks0 : kb) * BKE + koff;
+          const CUtensorMap* ma = seg ? &tmA1 : &tmA0;
+          const CUtensorMap* mb = seg ? &tmB1 : &tmB0;
+          const int bn = seg ? g.seg1_n : g.bn0;
+          mbar_expect_tx(&full[stage], kStageA + bn * 128);
+          uint8_t* a_dst = sA + stage * kStageA;
+          uint8_t* b_dst = sB + stage * STAGE_B;
+          if (!g.a_mn[seg]) {
+            tma_load_3d(a_dst, ma, &full[stage], kk, m0, zc);
+          } else {
+            for (int c = 0; c < kBM / CE; ++c) tma_load_3d(a_dst + c * (BKE * 128), ma, &full[stage], m0 + c * CE, kk, zc);
+          }
+          const int nb0 = seg && g.seg1_col ? 0 : n0;  // side-by-side segments always cover all their columns
+          if (!g.b_mn[seg]) {
+            tma_load_3d(b_dst, mb, &full[stage], kk, nb0, zc);
+          } else {
+            for (int c = 0; c < bn / CE; ++c) tma_load_3d(b_dst + c * (BKE * 128), mb, &full[stage], nb0 + c * CE, kk, zc);
+          }
+          if (++stage == STAGES) { stage = 0; phase ^= 1; }
+        }
+      }
+    }
+    __syncwarp();
+  } else if (warp == 1) {
+    // ------------------------------------------------------------------ MMA issuer
+    const bool leader = elect_one();
+    if (leader) {
+      int stage = 0, acc = 0;
+      uint32_t phase = 0, acc_phase = 0;
+      bool ok = true;
+      const uint32_t a_base = smem_u32(sA), b_base = smem_u32(sB);
+      for (int tile = blockIdx.x; tile < total && ok; tile += gridDim.x) {
+        if (!mbar_wait(&tempty[acc], acc_phase ^ 1, g.err, 2)) break;
+        tc_fence_after_sync();
+        for (int kb = 0; kb < kb_total; ++kb) {
+          if (!mbar_wait(&full[stage], phase, g.err, 3)) { ok = false; break; }
+          tc_fence_after_sync();
+          const int seg = kb >= g.kblocks0 ? 1 : 0;
+          const int kin = seg ? kb - g.kblocks0 : kb;
+          const uint32_t d_addr = tmem_base + acc * BN + (seg ? g.seg1_col : 0);
+          const bool fresh = kin == 0 && !(seg == 1 && g.seg1_col == 0);  // first product into these columns
+          const uint32_t a_stage = a_base + stage * kStageA, b_stage = b_base + stage * STAGE_B;
+#pragma unroll
+          for (int ks = 0; ks < 4; ++ks) {
+            const uint64_t ad = g.a_mn[seg] ? make_smem_desc(a_stage + ks * UK * 128, BKE * 128, MN_SBO, MN_LAYOUT)
+                                            : make_smem_desc(a_stage + ks * 32, 16, 1024);
+            const uint64_t bd = g.b_mn[seg] ? make_smem_desc(b_stage + ks * UK * 128, BKE * 128, MN_SBO, MN_LAYOUT)
+                                            : make_smem_desc(b_stage + ks * 32, 16, 1024);
+            umma<KIND>(d_addr, ad, bd, g.idesc[seg], (fresh && ks == 0) ? 0u : 1u);
+          }
+          umma_commit(&empty[stage]);
+          if (++stage == STAGES) { stage = 0; phase ^= 1; }
+        }
+        if (ok) umma_commit(&tfull[acc]);
+        acc ^= 1;
+        if (acc == 0) acc_phase ^= 1;
+      }
+    }
+    __syncwarp();
+  } else {
+    // ------------------------------------------------------------------ epilogue (4 warps = 128 TMEM lanes)
+    const int quarter = warp & 3;
+    const int row = quarter * 32 + lane;
+    int acc = 0;
+    uint32_t acc_phase = 0;
+    for (int tile = blockIdx.x; tile < total; tile += gridDim.x) {
+      const int tn = tile % g.tiles_n, tm = (tile / g.tiles_n) % g.tiles_m, bz = tile / (g.tiles_n * g.tiles_m);
+      const int m = tm * kBM + row, n0 = tn * BN;
+      if (!mbar_wait(&tfull[acc], acc_phase, g.err, 4)) break;
+      tc_fence_after_sync();
+      const uint32_t t_row = tmem_base + ((uint32_t)(quarter * 32) << 16) + acc * BN;
+      if constexpr (EPI == EPI_STORE) {
+        TOUT* out = reinterpret_cast<TOUT*>(g.out0) + bz * g.batch_out + (long long)m * g.ld_out;
+        const bool vec_ok = (g.ld_out * sizeof(TOUT)) % 16 == 0 && (g.batch_out * sizeof(TOUT)) % 16 == 0;
+#pragma unroll 1
+        for (int j = 0; j < BN / 32; ++j) {
+          float v[32];
+          ld32_f(t_row + j * 32, v);
+          const int n = n0 + j * 32;
+          if (g.bias0 != nullptr) {
+#pragma unroll
+            for (int i = 0; i < 32; ++i) if (n + i < g.N) v[i] += g.bias0[n + i];
+          }
+          if (m < g.M && n < g.N) store_row32<TOUT>(out + n, v, g.N - n, vec_ok);
+        }
+      } else if constexpr (EPI == EPI_GATE_IN) {
+        // tile column block tn selects the a (0) or b (1) half; out0 / out1 are their channel-major planes
+        TOUT* plane = reinterpret_cast<TOUT*>(tn == 0 ? g.out0 : g.out1);
+        const long long bb = m / g.plane, pix = m % g.plane;
+        const TIN* mask = reinterpret_cast<const TIN*>(g.aux);
+        const float mk = (mask != nullptr && m < g.M) ? to_f32(mask[m]) : 1.0f;
+#pragma unroll 1
+        for (int j = 0; j < 4; ++j) {
+          float p[32], gt[32];
+          ld32_f(t_row + j * 32, p);
+          ld32_f(t_row + 128 + j * 32, gt);
+          if (m < g.M) {
+#pragma unroll
+            for (int i = 0; i < 32; ++i) {
+              const int c = j * 32 + i;
+              float pv = p[i], gv = gt[i];
+              if (g.bias0 != nullptr) { pv += g.bias0[n0 + c]; gv += g.bias0[n0 + 128 + c]; }
+              plane[(bb * 128 + c) * g.plane + pix] = from_f32<TOUT>(pv * sigmoidf_acc(gv) * mk);
+            }
+          }
+        }
+      } else {
+        // EPI_GATE_OUT / EPI_GATE_OUT_BWD: cols [0,128) = y, [128,256) = gate pre-activation
+        TOUT* o0 = reinterpret_cast<TOUT*>(g.out0) + (long long)m * 128;
+        TOUT* o1 = reinterpret_cast<TOUT*>(g.out1) + (long long)m * 128;
+        const TIN* dout = reinterpret_cast<const TIN*>(g.aux) + (long long)m * 128;
+#pragma unroll 1
+        for (int j = 0; j < 4; ++j) {
+          float y[32], gt[32];
+          ld32_f(t_row + j * 32, y);
+          ld32_f(t_row + 128 + j * 32, gt);
+          if (m < g.M) {
+            float r0[32], r1[32];
+#pragma unroll
+            for (int i = 0; i < 32; ++i) {
+              const int c = j * 32 + i;
+              float yv = y[i], gv = gt[i];
+              if (g.bias0 != nullptr) { yv += g.bias0[c]; gv += g.bias0[128 + c]; }
+              const float sg = sigmoidf_acc(gv);
+              if constexpr (EPI == EPI_GATE_OUT) {
+                r0[i] = yv * sg;
+              } else {
+                const float d = to_f32(dout[c]);
+                r0[i] = d * sg;
+                r1[i] = d * yv * sg * (1.0f - sg);
+              }
+            }
+            store_row32<TOUT>(o0 + j * 32, r0, 32, true);
+            if constexpr (EPI == EPI_GATE_OUT_BWD) store_row32<TOUT>(o1 + j * 32, r1, 32, true);
+          }
+        }
+      }
+      tc_fence_before_sync();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(&tempty[acc]);
+      acc ^= 1;
+      if (acc == 0) acc_phase ^= 1;
+    }
+  }
+  tc_fence_before_sync();
+  __syncthreads();
+  if (warp == 1) {
+    tc_fence_after_sync();
+    tmem_dealloc(tmem_base, 2 * BN);
+  }
+}
+
+// ------------------------------------------------------------------------------------------------
+// host side
+// ------------------------------------------------------------------------------------------------
+// One GEMM operand: a rank-3 tensor (inner, outer, batch); inner is contiguous.  K-major: inner = K,
+// outer = rows (M or N).  MN-major: inner = rows, outer = K.
+struct Operand {
+  const void* ptr = nullptr;
+  bool mn_major = false;
+  uint64_t inner = 0, outer = 0, batch = 1;
+  uint64_t st_outer = 0, st_batch = 0;  // elements
+};
+
+struct GemmPlan {
+  Operand a[2], b[2];
+  int M = 0, N = 0;
+  int K0 = 0, K1 = 0;        // K extent per segment (per split when split_k)
+  int seg1_col = 0;
+  int batches = 1;
+  int split_k = 0;
+  void* out0 = nullptr;
+  void* out1 = nullptr;
+  long long ld_out = 0, batch_out = 0;
+  const float* bias0 = nullptr;
+  const void* aux = nullptr;
+  long long plane = 0;
+  const char* name = "tc_gemm";
+  double flops = 0, bytes = 0;
+};
+
+// dtype: TRI_F32 (tf32 MMA), TRI_BF16, TRI_F16.  out_f32: EPI_STORE writes fp32 instead of the input dtype.
+int launch_gemm(cudaStream_t st, int dtype, int epi, int bn, bool out_f32, const GemmPlan& p, int* err);
+
+}  // namespace tc
+}  // namespace tri

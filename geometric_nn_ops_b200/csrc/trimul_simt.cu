@@ -96,7 +96,7 @@ static int gemm(cudaStream_t st, bool tf32, GemmP p) {
   if (p.M <= 0 || p.N <= 0) return 0;
   dim3 grid(cdiv(p.N, 64), cdiv(p.M, 64), p.ksplit);
   dim3 block(16, 16);
-  KernelTimer kt("simt_gemm", st);
+  KernelTimer kt("simt_gemm", st, 2.0 * p.M * p.N * p.K, 4.0 * ((double)p.M * p.K + (double)p.N * p.K + (double)p.M * p.N));
   if (tf32) gemm_kernel<true><<<grid, block, 0, st>>>(p);
   else gemm_kernel<false><<<grid, block, 0, st>>>(p);
   TRI_LAUNCH_OK();
@@ -113,7 +113,7 @@ __global__ void reduce_partials_kernel(const float* partial, int nparts, long lo
 }
 
 static int reduce_partials(cudaStream_t st, const float* partial, int nparts, long long n, float* out) {
-  KernelTimer kt("simt_reduce_partials", st);
+  KernelTimer kt("simt_reduce_partials", st, 0.0, 4.0 * (nparts + 1) * n);
   reduce_partials_kernel<<<cdiv(n, 256), 256, 0, st>>>(partial, nparts, n, out);
   TRI_LAUNCH_OK();
   return 0;
@@ -191,7 +191,7 @@ static int contract(cudaStream_t st, bool tf32, int B, ContractP p) {
   p.cblocks = cdiv(p.Ch, bx);
   dim3 block(bx, by);
   dim3 grid(cdiv(p.N, 8), cdiv(p.N, 8 * by), B * p.cblocks);
-  KernelTimer kt("simt_contract", st);
+  KernelTimer kt("simt_contract", st, 2.0 * B * p.N * (double)p.N * p.N * p.Ch, 12.0 * B * (double)p.N * p.N * p.Ch);
   if (tf32) contract_kernel<true><<<grid, block, 0, st>>>(p);
   else contract_kernel<false><<<grid, block, 0, st>>>(p);
   TRI_LAUNCH_OK();
@@ -285,7 +285,7 @@ static int ln_bwd(cudaStream_t st, const float* d_out, const TI* x, const float*
   float* pg = partial;
   float* pb = partial + (size_t)blocks * C;
   {
-    KernelTimer kt("simt_ln_bwd", st);
+    KernelTimer kt("simt_ln_bwd", st, 0.0, (double)M * C * (4.0 + sizeof(TI) + sizeof(TO)));
     kern<<<blocks, 256, smem, st>>>(d_out, x, mean, rstd, gamma, M, C, d_in, pg, pb);
     TRI_LAUNCH_OK();
   }
@@ -353,7 +353,7 @@ __global__ void colsum_kernel(const float* X, long long M, int C, float* partial
 constexpr int kColsumBlocks = 256;
 static int colsum(cudaStream_t st, const float* X, long long M, int C, float* partial, float* out) {
   dim3 grid(kColsumBlocks, cdiv(C, 128));
-  KernelTimer kt("simt_colsum", st);
+  KernelTimer kt("simt_colsum", st, 0.0, 4.0 * M * C);
   colsum_kernel<<<grid, 128, 0, st>>>(X, M, C, partial);
   TRI_LAUNCH_OK();
   return reduce_partials(st, partial, kColsumBlocks, C, out);
@@ -488,12 +488,18 @@ static int forward_t(const TriMulDesc* d, const void* x, const void* mask, const
   if (!a.ok()) return fail(TRI_ERR_WORKSPACE, "trimul forward workspace too small: need %zu, got %zu", a.off, ws_size);
   TRI_TRY(convert_weights<T>(st, d, w, mask, &f));
 
-  ln_fwd_kernel<T><<<cdiv(M, 8), 256, 0, st>>>((const T*)x, f.norm_in_w, f.norm_in_b, d->eps, M, C, s.z, s.mean_in, s.rstd_in);
-  TRI_LAUNCH_OK();
+  {
+    KernelTimer kt("simt_ln_fwd", st, 0.0, (double)M * C * (sizeof(T) + 4.0));
+    ln_fwd_kernel<T><<<cdiv(M, 8), 256, 0, st>>>((const T*)x, f.norm_in_w, f.norm_in_b, d->eps, M, C, s.z, s.mean_in, s.rstd_in);
+    TRI_LAUNCH_OK();
+  }
   TRI_TRY(gemm(st, tf32, linear_p(s.z, C, f.p_in_w, f.p_in_b, s.P, 2 * Ch, M, 2 * Ch, C)));
   TRI_TRY(gemm(st, tf32, linear_p(s.z, C, f.g_in_w, f.g_in_b, s.G, 2 * Ch, M, 2 * Ch, C)));
-  gate_in_kernel<<<EW_GRID(M * 2 * Ch)>>>(s.P, s.G, f.mask, M, 2 * Ch, s.ab);
-  TRI_LAUNCH_OK();
+  {
+    KernelTimer kt("simt_gate_in", st, 0.0, 24.0 * M * Ch);
+    gate_in_kernel<<<EW_GRID(M * 2 * Ch)>>>(s.P, s.G, f.mask, M, 2 * Ch, s.ab);
+    TRI_LAUNCH_OK();
+  }
   ContractP cp{};
   cp.X = s.ab; cp.Y = s.ab; cp.O = s.t; cp.N = N; cp.Ch = Ch;
   cp.ldx = cp.ldy = 2 * Ch; cp.ldo = Ch; cp.xoff = 0; cp.yoff = Ch; cp.ooff = 0;
@@ -505,12 +511,18 @@ static int forward_t(const TriMulDesc* d, const void* x, const void* mask, const
   // with a saved block P must survive, and the workspace region that would have held it is free.
   float* u_buf = saved ? a.take<float>((size_t)M * Ch) : s.P;
   if (!a.ok()) return fail(TRI_ERR_WORKSPACE, "trimul forward workspace too small: need %zu, got %zu", a.off, ws_size);
-  ln_fwd_kernel<float><<<cdiv(M, 8), 256, 0, st>>>(s.t, f.norm_out_w, f.norm_out_b, d->eps, M, Ch, u_buf, s.mean_out, s.rstd_out);
-  TRI_LAUNCH_OK();
+  {
+    KernelTimer kt("simt_ln_fwd", st, 0.0, 8.0 * M * Ch);
+    ln_fwd_kernel<float><<<cdiv(M, 8), 256, 0, st>>>(s.t, f.norm_out_w, f.norm_out_b, d->eps, M, Ch, u_buf, s.mean_out, s.rstd_out);
+    TRI_LAUNCH_OK();
+  }
   TRI_TRY(gemm(st, tf32, linear_p(u_buf, Ch, f.p_out_w, f.p_out_b, s.y, C, M, C, Ch)));
   TRI_TRY(gemm(st, tf32, linear_p(s.z, C, f.g_out_w, f.g_out_b, s.go, C, M, C, C)));
-  gate_out_kernel<T><<<EW_GRID(M * C)>>>(s.y, s.go, M * C, (T*)out);
-  TRI_LAUNCH_OK();
+  {
+    KernelTimer kt("simt_gate_out", st, 0.0, (double)M * C * (8.0 + sizeof(T)));
+    gate_out_kernel<T><<<EW_GRID(M * C)>>>(s.y, s.go, M * C, (T*)out);
+    TRI_LAUNCH_OK();
+  }
   return 0;
 }
 
@@ -541,10 +553,16 @@ static int backward_t(const TriMulDesc* d, const void* x, const void* mask, cons
   TRI_TRY(convert_weights<T>(st, d, w, mask, &f));
 
   // output gate and projection
-  gate_out_bwd_kernel<T><<<EW_GRID(M * C)>>>((const T*)d_out, s.y, s.go, M * C, dy, dgo);
-  TRI_LAUNCH_OK();
-  ln_fwd_kernel<float><<<cdiv(M, 8), 256, 0, st>>>(s.t, f.norm_out_w, f.norm_out_b, d->eps, M, Ch, u, s.mean_out, s.rstd_out);
-  TRI_LAUNCH_OK();
+  {
+    KernelTimer kt("simt_gate_out_bwd", st, 0.0, (double)M * C * (16.0 + sizeof(T)));
+    gate_out_bwd_kernel<T><<<EW_GRID(M * C)>>>((const T*)d_out, s.y, s.go, M * C, dy, dgo);
+    TRI_LAUNCH_OK();
+  }
+  {
+    KernelTimer kt("simt_ln_fwd", st, 0.0, 8.0 * M * Ch);
+    ln_fwd_kernel<float><<<cdiv(M, 8), 256, 0, st>>>(s.t, f.norm_out_w, f.norm_out_b, d->eps, M, Ch, u, s.mean_out, s.rstd_out);
+    TRI_LAUNCH_OK();
+  }
   if (g->p_out_w) TRI_TRY(weight_grad(st, tf32, dy, C, C, u, Ch, Ch, M, partial, kWgradSplit, g->p_out_w));
   if (g->p_out_b) TRI_TRY(colsum(st, dy, M, C, partial, g->p_out_b));
   if (g->g_out_w) TRI_TRY(weight_grad(st, tf32, dgo, C, C, s.z, C, C, M, partial, kWgradSplit, g->g_out_w));
@@ -574,8 +592,11 @@ static int backward_t(const TriMulDesc* d, const void* x, const void* mask, cons
   TRI_TRY(contract(st, tf32, d->B, cb));
 
   // input gate and projections
-  gate_in_bwd_kernel<<<EW_GRID(M * 2 * Ch)>>>(dab, s.P, s.G, f.mask, M, 2 * Ch, dP, dG);
-  TRI_LAUNCH_OK();
+  {
+    KernelTimer kt("simt_gate_in_bwd", st, 0.0, 40.0 * M * Ch);
+    gate_in_bwd_kernel<<<EW_GRID(M * 2 * Ch)>>>(dab, s.P, s.G, f.mask, M, 2 * Ch, dP, dG);
+    TRI_LAUNCH_OK();
+  }
   if (g->p_in_w) TRI_TRY(weight_grad(st, tf32, dP, 2 * Ch, 2 * Ch, s.z, C, C, M, partial, kWgradSplit, g->p_in_w));
   if (g->p_in_b) TRI_TRY(colsum(st, dP, M, 2 * Ch, partial, g->p_in_b));
   if (g->g_in_w) TRI_TRY(weight_grad(st, tf32, dG, 2 * Ch, 2 * Ch, s.z, C, C, M, partial, kWgradSplit, g->g_in_w));

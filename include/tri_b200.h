@@ -55,7 +55,7 @@ void tri_reset_launch_count(void);
 /* Per-kernel timing for benchmarks (no counterpart in the reference, which uses torch.profiler in
  * benchmarks/profile_trimul.py:73-87).  While enabled, every kernel launch (any thread) is bracketed
  * by CUDA events on its stream.  tri_profile_summary waits for them and writes one line per kernel,
- * "name launches total_ms".  Enabling (or disabling) drops earlier records. */
+ * "name launches total_ms flops bytes", the last two being the ALGORITHMIC work the launches did.  Enabling (or disabling) drops earlier records. */
 void tri_profile_enable(int on);
 int tri_profile_summary(char* buf, size_t cap);
 
@@ -143,6 +143,31 @@ int tri_mul_fwd(const TriMulDesc* d, const void* x, const void* mask, const TriM
 int tri_mul_bwd(const TriMulDesc* d, const void* x, const void* mask, const TriMulWeights* w,
                 const void* saved, const void* d_out, void* dx, const TriMulWeightGrads* g,
                 void* ws, size_t ws_bytes, tri_stream_t stream);
+
+/* ------------------------------------------------------------------------ */
+/* Batched tensor-core GEMM (building block of the trimul contraction)      */
+/* ------------------------------------------------------------------------ */
+/* C[b][m][n] = sum_k A[b](m,k) * B[b](n,k), fp32 accumulation on tcgen05.  This is the per-channel
+ * N x N x N "combine" step, which the reference runs as a torch.einsum over permuted views
+ * (geometric_nn_ops_torch/triangle/_reference/trimul.py:44-54); exported for tests and benchmarks.
+ * An operand is K-major ([rows][K], ld = row stride) or MN-major ([K][rows], ld = stride between k).
+ * dtype TRI_F32 computes in tf32.  All strides in elements and multiples of 16 bytes. */
+typedef struct TriGemmDesc {
+  int32_t M, N, K, batch;
+  int32_t dtype;
+  int32_t a_mn_major, b_mn_major;
+  int32_t out_f32;           /* store fp32 instead of `dtype` */
+  int64_t lda, ldb, ldc;
+  int64_t batch_a, batch_b, batch_c;
+} TriGemmDesc;
+
+int tri_bgemm(const TriGemmDesc* d, const void* a, const void* b, void* c, void* ws, size_t ws_bytes,
+              tri_stream_t stream);
+
+/* The tensor-core kernels bound every wait; if one runs out, the kernel records a code in the first
+ * word of the workspace it was given and drains instead of hanging.  This call copies that word back
+ * (it synchronises the stream) and returns it: 0 = no failure. */
+int tri_ws_status(const void* ws, tri_stream_t stream);
 
 #ifdef __cplusplus
 }
