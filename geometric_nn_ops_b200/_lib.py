@@ -105,6 +105,12 @@ def check(code: int, what: str) -> None:
         raise RuntimeError(f"{what} failed with code {code}: {msg}")
 
 
+def check_device_status(ws, stream) -> None:
+    """With TRI_B200_CHECK=1, read back the tensor-core kernels' status word (synchronises the stream)."""
+    if os.environ.get("TRI_B200_CHECK") == "1" and last_path() == "tcgen05":
+        check(load().tri_ws_status(ctypes.c_void_p(ws.data_ptr()), stream), "device status")
+
+
 def last_path() -> str:
     return load().tri_last_path().decode()
 

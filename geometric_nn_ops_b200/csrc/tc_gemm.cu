@@ -106,6 +106,7 @@ static int launch_in(cudaStream_t st, int epi, int bn, bool out_f32, const CUten
   if (epi == EPI_GATE_IN) return launch_t<TIN, TIN, 256, EPI_GATE_IN>(st, maps, g, p);
   if (epi == EPI_GATE_OUT) return launch_t<TIN, TIN, 256, EPI_GATE_OUT>(st, maps, g, p);
   if (epi == EPI_GATE_OUT_BWD) return launch_t<TIN, TIN, 256, EPI_GATE_OUT_BWD>(st, maps, g, p);
+  if (epi == EPI_GATE_IN_BWD) return launch_t<TIN, TIN, 256, EPI_GATE_IN_BWD>(st, maps, g, p);
   return fail(TRI_ERR_ARG, "unknown epilogue %d", epi);
 }
 
@@ -134,7 +135,7 @@ int launch_gemm(cudaStream_t st, int dtype, int epi, int bn, bool out_f32, const
     g.idesc[s] = make_idesc(kind, kBM, s == 0 ? g.bn0 : (two ? g.seg1_n : g.bn0), p.a[src].mn_major, p.b[src].mn_major);
   }
   g.out0 = p.out0; g.out1 = p.out1; g.ld_out = p.ld_out; g.batch_out = p.batch_out;
-  g.bias0 = p.bias0; g.aux = p.aux; g.plane = p.plane; g.err = err;
+  g.bias0 = p.bias0; g.aux = p.aux; g.aux2 = p.aux2; g.aux3 = p.aux3; g.plane = p.plane; g.err = err;
 
   CUtensorMap maps[4];
   TRI_TRY(operand_map(&maps[0], p.a[0], dtype, kBM));

@@ -24,7 +24,9 @@ enum Epilogue {
   EPI_STORE = 0,        // out0[batch][m][n] = acc (+ bias0[n])
   EPI_GATE_IN = 1,      // cols [P(128) | G(128)]: half-plane[c][m] = (P+b)*sigmoid(G+b)*mask[m], channel-major
   EPI_GATE_OUT = 2,     // cols [y(128) | g(128)]: out0[m][c] = (y+b)*sigmoid(g+b)
-  EPI_GATE_OUT_BWD = 3  // same cols, aux = d_out: out0 = d_out*sig, out1 = d_out*(y+b)*sig*(1-sig)
+  EPI_GATE_OUT_BWD = 3, // same cols, aux = d_out: out0 = d_out*sig, out1 = d_out*(y+b)*sig*(1-sig)
+  EPI_GATE_IN_BWD = 4   // cols [P | G] recomputed; aux2/aux3 = channel-major d(a), d(b); aux = mask:
+                        //   out0[m][n0 + c] = d*sig(G),  out0[m][n0 + 128 + c] = d*P*sig*(1-sig),  d = d(half)[c][m]*mask
 };
 
 constexpr int kBM = 128;
@@ -46,7 +48,9 @@ struct GemmArgs {
   long long ld_out, batch_out;   // elements
   const float* bias0;            // per output column (EPI_STORE) / per accumulator column (gates)
   const void* aux;               // mask (GATE_IN) or d_out (GATE_OUT_BWD), in the input dtype
-  long long plane;               // GATE_IN: pixels per batch entry (N*N); channel-major plane stride
+  const void* aux2;              // GATE_IN_BWD: channel-major gradient of the a half
+  const void* aux3;              //              ... of the b half
+  long long plane;               // GATE_IN(_BWD): pixels per batch entry (N*N); channel-major plane stride
   int* err;
 };
 
@@ -249,6 +253,33 @@ tc_gemm_kernel(const __grid_constant__ CUtensorMap tmA0, const __grid_constant__
             }
           }
         }
+      } else if constexpr (EPI == EPI_GATE_IN_BWD) {
+        const TIN* dplane = reinterpret_cast<const TIN*>(tn == 0 ? g.aux2 : g.aux3);
+        const long long bb = m / g.plane, pix = m % g.plane;
+        const TIN* mask = reinterpret_cast<const TIN*>(g.aux);
+        const float mk = (mask != nullptr && m < g.M) ? to_f32(mask[m]) : 1.0f;
+        TOUT* orow = reinterpret_cast<TOUT*>(g.out0) + (long long)m * g.ld_out + n0;
+#pragma unroll 1
+        for (int j = 0; j < 4; ++j) {
+          float p[32], gt[32];
+          ld32_f(t_row + j * 32, p);
+          ld32_f(t_row + 128 + j * 32, gt);
+          if (m < g.M) {
+            float dp[32], dg[32];
+#pragma unroll
+            for (int i = 0; i < 32; ++i) {
+              const int c = j * 32 + i;
+              float pv = p[i], gv = gt[i];
+              if (g.bias0 != nullptr) { pv += g.bias0[n0 + c]; gv += g.bias0[n0 + 128 + c]; }
+              const float d = to_f32(dplane[(bb * 128 + c) * g.plane + pix]) * mk;
+              const float sg = sigmoidf_acc(gv);
+              dp[i] = d * sg;
+              dg[i] = d * pv * sg * (1.0f - sg);
+            }
+            store_row32<TOUT>(orow + j * 32, dp, 32, true);
+            store_row32<TOUT>(orow + 128 + j * 32, dg, 32, true);
+          }
+        }
       } else {
         // EPI_GATE_OUT / EPI_GATE_OUT_BWD: cols [0,128) = y, [128,256) = gate pre-activation
         TOUT* o0 = reinterpret_cast<TOUT*>(g.out0) + (long long)m * 128;
@@ -319,6 +350,8 @@ struct GemmPlan {
   long long ld_out = 0, batch_out = 0;
   const float* bias0 = nullptr;
   const void* aux = nullptr;
+  const void* aux2 = nullptr;
+  const void* aux3 = nullptr;
   long long plane = 0;
   const char* name = "tc_gemm";
   double flops = 0, bytes = 0;

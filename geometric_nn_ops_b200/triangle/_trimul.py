@@ -29,6 +29,12 @@ def _ptr(t):
     return None if t is None else ctypes.c_void_p(t.data_ptr())
 
 
+def _aligned(t):
+    """Contiguous and 16-byte aligned (TMA and the vector loads need it); copies only if it must."""
+    t = t.contiguous()
+    return t if t.data_ptr() % 16 == 0 else t.clone()
+
+
 class _TriMul(torch.autograd.Function):
     @staticmethod
     def forward(ctx, x, mask, outgoing, eps, *weights):
@@ -42,12 +48,12 @@ class _TriMul(torch.autograd.Function):
         N, C = x.shape[-2], x.shape[-1]
         if x.shape[-3] != N:
             raise ValueError(f"x must be [*, N, N, C], got {tuple(x.shape)}")
-        xc = x.reshape(-1, N, N, C).contiguous()
+        xc = _aligned(x.reshape(-1, N, N, C))
         B = xc.shape[0]
         mc = None
         if mask is not None:
-            mc = mask.to(x.dtype).broadcast_to(x.shape[:-1]).reshape(B, N, N).contiguous()
-        wc = {n: (None if t is None else t.detach().to(x.dtype).contiguous()) for n, t in named.items()}
+            mc = _aligned(mask.to(x.dtype).broadcast_to(x.shape[:-1]).reshape(B, N, N))
+        wc = {n: (None if t is None else _aligned(t.detach().to(x.dtype))) for n, t in named.items()}
         Ch = wc["p_in_weight"].shape[0] // 2
         expect = {"p_in_weight": (2 * Ch, C), "g_in_weight": (2 * Ch, C), "p_out_weight": (C, Ch),
                   "g_out_weight": (C, C), "norm_in_weight": (C,), "norm_in_bias": (C,), "norm_out_weight": (Ch,),
@@ -79,6 +85,7 @@ class _TriMul(torch.autograd.Function):
         with torch.cuda.device(x.device):
             _lib.check(lib.tri_mul_fwd(ctypes.byref(d), _ptr(xc), _ptr(mc), ctypes.byref(w), _ptr(out), _ptr(saved),
                                        _ptr(ws), ws_bytes, stream), "tri_mul_fwd")
+            _lib.check_device_status(ws, stream)
         if need_grad:
             ctx.save_for_backward(xc, mc, saved, *[t for t in wc.values() if t is not None])
             ctx.present = [t is not None for t in wc.values()]
@@ -102,7 +109,7 @@ class _TriMul(torch.autograd.Function):
             if t is not None and ctx.needs_input_grad[4 + i]:
                 grads[n] = torch.empty(t.shape, dtype=torch.float32, device=xc.device)
                 setattr(g, _lib.abi_field(n), grads[n].data_ptr())
-        dc = d_out.reshape(xc.shape).to(xc.dtype).contiguous()
+        dc = _aligned(d_out.reshape(xc.shape).to(xc.dtype))
         dx = torch.empty_like(xc)
         ws_bytes = lib.tri_mul_ws_bytes(ctypes.byref(d), 1)
         ws = torch.empty(max(ws_bytes, 1), dtype=torch.uint8, device=xc.device)
@@ -110,6 +117,7 @@ class _TriMul(torch.autograd.Function):
         with torch.cuda.device(xc.device):
             _lib.check(lib.tri_mul_bwd(ctypes.byref(d), _ptr(xc), _ptr(mc), ctypes.byref(w), _ptr(saved), _ptr(dc),
                                        _ptr(dx), ctypes.byref(g), _ptr(ws), ws_bytes, stream), "tri_mul_bwd")
+            _lib.check_device_status(ws, stream)
         out = [dx.reshape(ctx.x_shape) if ctx.needs_input_grad[0] else None, None, None, None]
         for n, dt in zip(_lib.WEIGHT_NAMES, ctx.weight_dtypes):
             out.append(grads[n].to(dt) if n in grads else None)

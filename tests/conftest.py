@@ -3,6 +3,8 @@
 import os
 import sys
 
+os.environ.setdefault("TRI_B200_CHECK", "1")  # make a timed-out tensor-core wait fail the test loudly
+
 ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
 if ROOT not in sys.path:
     sys.path.insert(0, ROOT)

@@ -63,6 +63,9 @@ def test_oracle_fwd_bwd(tmu, case, dtype, precision, direction):
     x, mask, w, d_out = util.trimul_inputs(B, N, C, Ch, dtype, seed=N + C, biases=biases)
     with util.matmul_precision(precision):
         out, grads = util.trimul_fwd_bwd(tmu, x, mask, w, direction, d_out)
+    from geometric_nn_ops_b200 import _lib
+    tensor_core = C == 128 and Ch == 128 and N % 8 == 0 and not (dtype == torch.float32 and precision == "ieee")
+    assert _lib.last_path() == ("tcgen05" if tensor_core else "simt")
     o_ref, g_ref = util.trimul_oracle(x, mask, w, direction, d_out)
     cos_min, fro, mar = _tol(dtype, precision)
     util.check_close("out", out, o_ref, cos_min, fro, mar)
@@ -144,6 +147,8 @@ def test_headline_size_properties(tmu, direction):
     """N=768, C=128 bf16: finite, deterministic, batch-independent sub-problem check via linearity in d_out."""
     x, mask, w, d_out = util.trimul_inputs(1, 768, 128, 128, torch.bfloat16, seed=5)
     out, g1 = util.trimul_fwd_bwd(tmu, x, mask, w, direction, d_out)
+    from geometric_nn_ops_b200 import _lib
+    assert _lib.last_path() == "tcgen05"
     assert torch.isfinite(out.float()).all()
     _, g2 = util.trimul_fwd_bwd(tmu, x, mask, w, direction, 2 * d_out)
     for name in g1:
