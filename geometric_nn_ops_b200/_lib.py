@@ -68,6 +68,7 @@ EXPORTS = {
     "tri_attn_ws_bytes": (c_size_t, [POINTER(TriAttnDesc), c_int]),
     "tri_attn_fwd": (c_int, [POINTER(TriAttnDesc)] + [c_void_p] * 8 + [c_size_t, c_void_p]),
     "tri_attn_bwd": (c_int, [POINTER(TriAttnDesc)] + [c_void_p] * 13 + [c_size_t, c_void_p]),
+    "tri_attn_bwd_noalloc": (c_int, [POINTER(TriAttnDesc)] + [c_void_p] * 12 + [c_void_p]),
     "tri_mul_saved_bytes": (c_size_t, [POINTER(TriMulDesc)]),
     "tri_mul_ws_bytes": (c_size_t, [POINTER(TriMulDesc), c_int]),
     "tri_mul_fwd": (c_int, [POINTER(TriMulDesc), c_void_p, c_void_p, POINTER(TriMulWeights), c_void_p, c_void_p,

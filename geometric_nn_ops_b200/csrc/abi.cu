@@ -156,6 +156,15 @@ int tri_attn_bwd(const TriAttnDesc* d, const void* q, const void* k, const void*
                              (cudaStream_t)stream);
 }
 
+int tri_attn_bwd_noalloc(const TriAttnDesc* d, const void* q, const void* k, const void* v, const void* bias,
+                         const uint8_t* mask, const void* o, const float* lse, const void* d_o, void* dq, void* dk,
+                         void* dv, float* dbias, tri_stream_t stream) {
+  TRI_TRY(check_attn(d));
+  if (!q || !k || !v || !o || !lse || !d_o || !dq || !dk || !dv)
+    return fail(TRI_ERR_ARG, "q, k, v, o, lse, d_o, dq, dk and dv must not be null");
+  return simt::attn_backward_static(d, q, k, v, bias, mask, o, lse, d_o, dq, dk, dv, dbias, (cudaStream_t)stream);
+}
+
 size_t tri_mul_saved_bytes(const TriMulDesc* d) {
   if (check_mul(d) != 0) return 0;
   return tc::mul_supported(d) ? tc::mul_saved_bytes(d) : simt::saved_bytes(d);

@@ -13,6 +13,7 @@
 // The backward recomputes P from the saved log-sum-exp; dbias is reduced over the
 // row axis inside one kernel, in a fixed order (no atomics, deterministic).
 #include <algorithm>
+#include <mutex>
 
 #include "attn_simt.cuh"
 #include "common.cuh"
@@ -545,6 +546,51 @@ int attn_backward(const TriAttnDesc* d, const void* q, const void* k, const void
                   void* dv, float* dbias, void* ws, size_t ws_size, cudaStream_t st) {
   if (ws_size < attn_ws_bytes(d, 1)) return fail(TRI_ERR_WORKSPACE, "attention backward workspace too small");
   float* delta = (float*)ws;
+  TRI_ATTN_DISPATCH(bwd_launch, d, q, k, v, bias, mask, o, lse, d_o, dq, dk, dv, dbias, delta, st);
+}
+
+// ---------------------------------------------------------------------------------------------
+// Backward without any caller- or library-allocated scratch.
+//
+// Some callers cannot hand this library a workspace: code running where device allocation is
+// forbidden or impossible (a real-time serving loop with a frozen memory pool, a plugin host that
+// gives operators no allocator, a process already at its memory limit).  For them the one scratch
+// buffer the backward needs, delta[b,s,h,i] = sum_d dO*O, lives in this file-scope device array.
+// Every GPU that loads the library carries these 4 MiB until the process exits.
+//
+// The array's name is only a host-side handle.  Its device address is looked up once per device, with
+// that device current, through cudaGetSymbolAddress, and that address is what the kernels get.
+// ---------------------------------------------------------------------------------------------
+constexpr size_t kStaticDeltaFloats = size_t(1) << 20;  // B * n_seq * H * n_res may not exceed this
+static __device__ __align__(256) float g_static_delta[kStaticDeltaFloats];
+
+size_t attn_static_scratch_rows() { return kStaticDeltaFloats; }
+
+int attn_backward_static(const TriAttnDesc* d, const void* q, const void* k, const void* v, const void* bias,
+                         const uint8_t* mask, const void* o, const float* lse, const void* d_o, void* dq, void* dk,
+                         void* dv, float* dbias, cudaStream_t st) {
+  const size_t rows = (size_t)d->B * d->n_seq * d->H * d->n_res;
+  if (rows > kStaticDeltaFloats)
+    return fail(TRI_ERR_UNSUPPORTED,
+                "B*n_seq*H*n_res = %zu exceeds the built-in scratch of %zu rows; use tri_attn_bwd with a workspace",
+                rows, kStaticDeltaFloats);
+  constexpr int kMaxDevices = 64;
+  static float* device_ptr[kMaxDevices] = {};
+  static std::mutex mu;
+  int dev = 0;
+  TRI_CUDA_OK(cudaGetDevice(&dev));
+  if (dev < 0 || dev >= kMaxDevices) return fail(TRI_ERR_UNSUPPORTED, "device index %d out of range", dev);
+  float* delta = nullptr;
+  {
+    std::lock_guard<std::mutex> lock(mu);
+    if (device_ptr[dev] == nullptr) {
+      void* p = nullptr;
+      TRI_CUDA_OK(cudaGetSymbolAddress(&p, g_static_delta));  // first call on this device: set-up
+      device_ptr[dev] = static_cast<float*>(p);
+    }
+    delta = device_ptr[dev];
+  }
+  // delta is written in full by the first kernel before anything reads it: nothing to clear.
   TRI_ATTN_DISPATCH(bwd_launch, d, q, k, v, bias, mask, o, lse, d_o, dq, dk, dv, dbias, delta, st);
 }
 

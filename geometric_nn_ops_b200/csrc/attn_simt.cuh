@@ -10,5 +10,10 @@ int attn_forward(const TriAttnDesc* d, const void* q, const void* k, const void*
 int attn_backward(const TriAttnDesc* d, const void* q, const void* k, const void* v, const void* bias,
                   const uint8_t* mask, const void* o, const float* lse, const void* d_o, void* dq, void* dk,
                   void* dv, float* dbias, void* ws, size_t ws_size, cudaStream_t st);
+// Backward whose scratch is a built-in device array (no workspace argument); see attn_simt.cu.
+size_t attn_static_scratch_rows();
+int attn_backward_static(const TriAttnDesc* d, const void* q, const void* k, const void* v, const void* bias,
+                         const uint8_t* mask, const void* o, const float* lse, const void* d_o, void* dq, void* dk,
+                         void* dv, float* dbias, cudaStream_t st);
 }  // namespace simt
 }  // namespace tri

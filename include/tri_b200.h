@@ -99,6 +99,25 @@ int tri_attn_bwd(const TriAttnDesc* d, const void* q, const void* k, const void*
 
 size_t tri_attn_ws_bytes(const TriAttnDesc* d, int is_bwd);
 
+/* Attention backward for callers that cannot provide a workspace.  (No counterpart in the reference,
+ * which always allocates through torch.)  Meant for hosts where device allocation is off limits at call
+ * time: a serving loop running on a frozen memory pool, an operator plugin whose host exposes no
+ * allocator, a process pinned at its memory budget.  Same arguments and results as tri_attn_bwd minus
+ * the workspace: the per-row scratch (one float per (batch, row, head, query)) lives in a 4 MiB array
+ * built into the library image, resident on every GPU that loads the library until the process exits.
+ *  - Limit: B * n_seq * H * n_res <= 1048576; larger problems are refused with TRI_ERR_UNSUPPORTED.
+ *  - It calls no cudaMalloc / cudaFree and no allocating library routine.  The first call on each device
+ *    resolves the array's device address (cudaGetSymbolAddress, with that device current); make that
+ *    first call outside any stream capture.
+ *  - All calls on a device share the one array and it keeps the previous call's contents.  Nothing in it
+ *    has to start at zero (each call rewrites what it reads), but two calls whose kernels overlap on the
+ *    GPU (different streams) race on it: serialise them.
+ *  - Always runs the CUDA-core kernels, in every dtype. */
+int tri_attn_bwd_noalloc(const TriAttnDesc* d, const void* q, const void* k, const void* v,
+                         const void* bias, const uint8_t* mask, const void* o, const float* lse,
+                         const void* d_o, void* dq, void* dk, void* dv, float* dbias /*nullable*/,
+                         tri_stream_t stream);
+
 /* ------------------------------------------------------------------------ */
 /* Triangle multiplicative update                                           */
 /* ------------------------------------------------------------------------ */
