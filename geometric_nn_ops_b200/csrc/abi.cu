@@ -1,5 +1,6 @@
 // extern "C" surface of libtri_b200.so: argument checks and dispatch between the
 // tensor-core (tcgen05) kernels and the exact-fp32 CUDA-core kernels.
+#include <algorithm>
 #include <atomic>
 #include <cstring>
 #include <mutex>
@@ -124,15 +125,14 @@ int tri_profile_summary(char* buf, size_t cap) {
 
 size_t tri_attn_ws_bytes(const TriAttnDesc* d, int is_bwd) {
   if (check_attn(d) != 0) return 0;
-  if (tc::attn_supported(d)) return tc::attn_ws_bytes(d, is_bwd);
-  return simt::attn_ws_bytes(d, is_bwd);
+  return std::max(tc::attn_ws_bytes(d, is_bwd), simt::attn_ws_bytes(d, is_bwd));
 }
 
 int tri_attn_fwd(const TriAttnDesc* d, const void* q, const void* k, const void* v, const void* bias,
                  const uint8_t* mask, void* o, float* lse, void* ws, size_t ws_bytes, tri_stream_t stream) {
   TRI_TRY(check_attn(d));
   if (!q || !k || !v || !o || !lse) return fail(TRI_ERR_ARG, "q, k, v, o and lse must not be null");
-  if (tc::attn_supported(d)) {
+  if (tc::attn_fwd_supported(d)) {
     set_path("tcgen05");
     return tc::attn_forward(d, q, k, v, bias, mask, o, lse, ws, ws_bytes, (cudaStream_t)stream);
   }
@@ -146,7 +146,7 @@ int tri_attn_bwd(const TriAttnDesc* d, const void* q, const void* k, const void*
   TRI_TRY(check_attn(d));
   if (!q || !k || !v || !o || !lse || !d_o || !dq || !dk || !dv || !ws)
     return fail(TRI_ERR_ARG, "q, k, v, o, lse, d_o, dq, dk, dv and ws must not be null");
-  if (tc::attn_supported(d)) {
+  if (tc::attn_bwd_supported(d)) {
     set_path("tcgen05");
     return tc::attn_backward(d, q, k, v, bias, mask, o, lse, d_o, dq, dk, dv, dbias, ws, ws_bytes,
                              (cudaStream_t)stream);

@@ -83,6 +83,23 @@ __device__ __forceinline__ void tma_load_3d(void* dst, const CUtensorMap* m, uin
       : "memory");
 }
 
+__device__ __forceinline__ void tma_load_4d(void* dst, const CUtensorMap* m, uint64_t* bar, int c0, int c1, int c2,
+                                            int c3) {
+  asm volatile(
+      "cp.async.bulk.tensor.4d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4, %5, %6}], [%2];" ::"r"(
+          smem_u32(dst)),
+      "l"((uint64_t)m), "r"(smem_u32(bar)), "r"(c0), "r"(c1), "r"(c2), "r"(c3)
+      : "memory");
+}
+__device__ __forceinline__ void tma_load_5d(void* dst, const CUtensorMap* m, uint64_t* bar, int c0, int c1, int c2,
+                                            int c3, int c4) {
+  asm volatile(
+      "cp.async.bulk.tensor.5d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4, %5, %6, %7}], "
+      "[%2];" ::"r"(smem_u32(dst)),
+      "l"((uint64_t)m), "r"(smem_u32(bar)), "r"(c0), "r"(c1), "r"(c2), "r"(c3), "r"(c4)
+      : "memory");
+}
+
 // ---------------------------------------------------------------------------------------------
 // TMEM
 // ---------------------------------------------------------------------------------------------
@@ -111,6 +128,12 @@ __device__ __forceinline__ void tmem_ld_32x32(uint32_t taddr, uint32_t (&v)[32])
       : "r"(taddr)
       : "memory");
 }
+__device__ __forceinline__ float ex2_approx(float x) {
+  float y;
+  asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+  return y;
+}
+
 __device__ __forceinline__ void tmem_ld_wait() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
 
 // ---------------------------------------------------------------------------------------------
@@ -181,6 +204,11 @@ __device__ __forceinline__ bool elect_one() {
 // ---------------------------------------------------------------------------------------------
 // Rank-3 tiled map with 128-byte swizzle over a tensor whose innermost dim is contiguous.
 // dims/strides are in elements, outermost last; box_inner * elem_bytes must be 128.
+// General form: rank 2..5, swizzle_bytes in {64, 128} (or 32 for the 32-byte-atom 128-byte swizzle).
+// dtype: TRI_F32 / TRI_BF16 / TRI_F16.  strides_elems[i] is the stride of dim i+1.
+int make_tmap(CUtensorMap* out, const void* base, int dtype, int rank, const uint64_t* dims,
+              const uint64_t* strides_elems, const uint32_t* box, int swizzle_bytes);
+
 int make_tmap_3d(CUtensorMap* out, const void* base, int elem_bytes, bool is_f16, const uint64_t dims[3],
                  const uint64_t strides_elems[2], const uint32_t box[3], bool atom_32b);
 

@@ -62,6 +62,35 @@ int make_tmap_3d(CUtensorMap* out, const void* base, int elem_bytes, bool is_f16
   return 0;
 }
 
+int make_tmap(CUtensorMap* out, const void* base, int dtype, int rank, const uint64_t* dims,
+              const uint64_t* strides_elems, const uint32_t* box, int swizzle_bytes) {
+  EncodeFn fn = encode_fn();
+  if (fn == nullptr) return fail(TRI_ERR_DEVICE, "cuTensorMapEncodeTiled is not available from the driver");
+  if (rank < 2 || rank > 5) return fail(TRI_ERR_ARG, "tensor map rank %d out of range", rank);
+  if ((reinterpret_cast<uintptr_t>(base) & 15) != 0) return fail(TRI_ERR_ARG, "TMA base address must be 16-byte aligned");
+  const int es = dtype == TRI_F32 ? 4 : 2;
+  cuuint64_t gdim[5], gstr[4];
+  cuuint32_t bdim[5], estr[5];
+  for (int i = 0; i < rank; ++i) { gdim[i] = dims[i]; bdim[i] = box[i]; estr[i] = 1; }
+  for (int i = 0; i + 1 < rank; ++i) {
+    gstr[i] = strides_elems[i] * es;
+    // a dimension of extent one may carry any stride (even zero): give it a legal one
+    if (dims[i + 1] == 1 && (gstr[i] == 0 || gstr[i] % 16 != 0)) gstr[i] = (i == 0 ? dims[0] * es : gstr[i - 1] * dims[i]);
+    if (gstr[i] % 16 != 0 || gstr[i] == 0)
+      return fail(TRI_ERR_ARG, "TMA stride %d is %llu bytes: must be a non-zero multiple of 16", i, (unsigned long long)gstr[i]);
+  }
+  CUtensorMapDataType dt = dtype == TRI_F32 ? CU_TENSOR_MAP_DATA_TYPE_FLOAT32
+                                            : (dtype == TRI_F16 ? CU_TENSOR_MAP_DATA_TYPE_FLOAT16 : CU_TENSOR_MAP_DATA_TYPE_BFLOAT16);
+  CUtensorMapSwizzle sw = swizzle_bytes == 128 ? CU_TENSOR_MAP_SWIZZLE_128B
+                          : swizzle_bytes == 64 ? CU_TENSOR_MAP_SWIZZLE_64B
+                          : swizzle_bytes == 32 ? CU_TENSOR_MAP_SWIZZLE_128B_ATOM_32B : CU_TENSOR_MAP_SWIZZLE_NONE;
+  CUresult r = fn(out, dt, (cuuint32_t)rank, const_cast<void*>(base), gdim, gstr, bdim, estr,
+                  CU_TENSOR_MAP_INTERLEAVE_NONE, sw, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                  CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  if (r != CUDA_SUCCESS) return fail(TRI_ERR_ARG, "cuTensorMapEncodeTiled failed (%d) for a rank-%d map", (int)r, rank);
+  return 0;
+}
+
 static int operand_map(CUtensorMap* out, const Operand& o, int dtype, int rows_box) {
   const int es = dtype == TRI_F32 ? 4 : 2;
   const uint32_t span = 128 / es;  // elements in 128 bytes

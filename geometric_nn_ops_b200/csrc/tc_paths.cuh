@@ -4,8 +4,9 @@
 
 namespace tri {
 namespace tc {
-// True when the tensor-core kernels cover this problem (dtype, precision, shape).
-bool attn_supported(const TriAttnDesc* d);
+// True when the tensor-core kernels cover this problem (dtype, precision, shape, strides).
+bool attn_fwd_supported(const TriAttnDesc* d);
+bool attn_bwd_supported(const TriAttnDesc* d);
 size_t attn_ws_bytes(const TriAttnDesc* d, int is_bwd);
 int attn_forward(const TriAttnDesc* d, const void* q, const void* k, const void* v, const void* bias,
                  const uint8_t* mask, void* o, float* lse, void* ws, size_t ws_size, cudaStream_t st);

@@ -93,6 +93,7 @@ class _TriangleAttention(torch.autograd.Function):
         with torch.cuda.device(q.device):
             _lib.check(lib.tri_attn_fwd(ctypes.byref(d), _ptr(q), _ptr(k), _ptr(v), _ptr(bias), _ptr(mask_u8),
                                         _ptr(o), _ptr(lse), _ptr(ws), ws_bytes, stream), "tri_attn_fwd")
+            _lib.check_device_status(ws, stream)
         ctx.save_for_backward(q, k, v, bias, mask_u8, o, lse)
         ctx.scale, ctx.precision = scale, precision
         return o
@@ -115,6 +116,7 @@ class _TriangleAttention(torch.autograd.Function):
             _lib.check(lib.tri_attn_bwd(ctypes.byref(d), _ptr(q), _ptr(k), _ptr(v), _ptr(bias), _ptr(mask_u8),
                                         _ptr(o), _ptr(lse), _ptr(d_o), _ptr(dq), _ptr(dk), _ptr(dv), _ptr(dbias),
                                         _ptr(ws), ws_bytes, stream), "tri_attn_bwd")
+            _lib.check_device_status(ws, stream)
         grad_bias = None
         if want_dbias:
             grad_bias = dbias.to(bias.dtype).reshape(B, 1, H, N, N)

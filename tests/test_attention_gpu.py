@@ -50,7 +50,8 @@ def test_golden_fp32_ieee(ta, path):
         util.check_close("grad_" + name, val, g["grad_" + name], 1 - 1e-9, util.IEEE_REL_FRO, 1e-4)
 
 
-SHAPES = [(1, 8, 8, 2, 8), (2, 5, 37, 3, 16), (1, 16, 100, 4, 32), (1, 3, 130, 2, 64), (1, 4, 65, 1, 48)]
+SHAPES = [(1, 8, 8, 2, 8), (2, 5, 37, 3, 16), (1, 16, 100, 4, 32), (1, 3, 130, 2, 64), (1, 4, 65, 1, 48),
+          (1, 4, 64, 4, 32), (1, 6, 136, 4, 32), (2, 3, 256, 2, 64), (1, 2, 384, 4, 32)]
 MODES = [(torch.float32, "ieee"), (torch.float32, "tf32"), (torch.bfloat16, "ieee"), (torch.float16, "ieee")]
 
 
@@ -58,7 +59,12 @@ MODES = [(torch.float32, "ieee"), (torch.float32, "tf32"), (torch.bfloat16, "iee
 @pytest.mark.parametrize("dtype,precision", MODES, ids=lambda v: str(v).replace("torch.", ""))
 def test_oracle_fwd_bwd(ta, shape, dtype, precision):
     t, mask, d_out = util.attn_inputs(*shape, dtype, seed=sum(shape))
+    from geometric_nn_ops_b200 import _lib
     with util.matmul_precision(precision):
+        with torch.no_grad():
+            ta(t["q"], t["k"], t["v"], t["bias"], mask)
+        tensor_core = dtype != torch.float32 and shape[4] in (32, 64) and shape[2] % 8 == 0
+        assert _lib.last_path() == ("tcgen05" if tensor_core else "simt")
         out, grads = util.attn_fwd_bwd(ta, t, mask, None, d_out)
     o_ref, g_ref = util.attn_oracle(t, mask, None, d_out)
     cos_min, fro, mar = _tol(dtype, precision)
@@ -99,9 +105,10 @@ def test_zero_query_gives_mean_of_values(ta):
     assert (out - want).abs().max() <= 2 * torch.finfo(torch.float32).eps * want.abs().max()
 
 
+@pytest.mark.parametrize("n", [70, 136])
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
-def test_structural_bit_exact(ta, dtype):
-    t, mask, _ = util.attn_inputs(1, 4, 70, 2, 32, dtype, seed=5)
+def test_structural_bit_exact(ta, dtype, n):
+    t, mask, _ = util.attn_inputs(1, 4, n, 2, 32, dtype, seed=5)
     base = ta(t["q"], t["k"], t["v"], t["bias"], mask)
     # mask=None equals an all-keep mask
     keep = torch.ones_like(mask)
@@ -110,7 +117,7 @@ def test_structural_bit_exact(ta, dtype):
     assert torch.equal(ta(t["q"], t["k"], t["v"], None, mask),
                        ta(t["q"], t["k"], t["v"], torch.zeros_like(t["bias"]), mask))
     # noise on masked keys / values changes nothing
-    dropped = ~mask.reshape(1, 4, 70, 1, 1).expand_as(t["v"])
+    dropped = ~mask.reshape(1, 4, n, 1, 1).expand_as(t["v"])
     noise = 1e3 * torch.randn_like(t["v"].float()).to(dtype)
     v2 = torch.where(dropped, t["v"] + noise, t["v"])
     k2 = torch.where(dropped, t["k"] + noise, t["k"])
@@ -122,9 +129,10 @@ def test_structural_bit_exact(ta, dtype):
     assert torch.equal(ta(t["q"], t["k"], t["v"], t["bias"], mask), base)
 
 
+@pytest.mark.parametrize("n,d", [(40, 16), (136, 32)])
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
-def test_fully_masked_row_is_uniform(ta, dtype):
-    t, mask, d_out = util.attn_inputs(1, 3, 40, 2, 16, dtype, seed=6, bias_scale=0.1)
+def test_fully_masked_row_is_uniform(ta, dtype, n, d):
+    t, mask, d_out = util.attn_inputs(1, 3, n, 2, d, dtype, seed=6, bias_scale=0.1)
     mask[0, 1] = False
     out, grads = util.attn_fwd_bwd(ta, t, mask, None, d_out)
     want = t["v"][0, 1].float().mean(dim=0)
