@@ -17,7 +17,7 @@
 namespace tri {
 namespace {
 thread_local char g_err[512] = "";
-thread_local const char* g_path = "none";
+std::atomic<const char*> g_path{"none"};  // process-wide: the backward runs on autograd's thread
 // Launch counter and timing records are process-wide: autograd runs the backward on its own thread.
 std::atomic<long long> g_launches{0};
 
@@ -44,7 +44,7 @@ KernelTimer::~KernelTimer() {
 }
 
 char* last_error_buf() { return g_err; }
-void set_path(const char* name) { g_path = name; }
+void set_path(const char* name) { g_path.store(name); }
 void count_launch(int n) { g_launches += n; }
 
 static int check_attn(const TriAttnDesc* d) {
@@ -83,7 +83,7 @@ extern "C" {
 
 int tri_abi_version(void) { return 1; }
 const char* tri_last_error(void) { return last_error_buf(); }
-const char* tri_last_path(void) { return g_path; }
+const char* tri_last_path(void) { return g_path.load(); }
 long long tri_launch_count(void) { return g_launches.load(); }
 void tri_reset_launch_count(void) { g_launches = 0; }
 

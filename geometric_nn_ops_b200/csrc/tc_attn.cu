@@ -269,6 +269,631 @@ attn_fwd_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
   }
 }
 
+
+// =================================================================================================
+// Backward.  Three deterministic passes, each recomputing P from the saved statistics:
+//   dK/dV : one CTA per (b, row, head, 128-key block), thread = key.  Per 64-query tile:
+//           S^T = K Q^T and dP^T = V dO^T (TMEM), P^T and dS^T to smem, dV += P^T dO, dK += dS^T Q (TMEM).
+//   dQ    : one CTA per (b, row, head, 128-query block), thread = query.  Per 64-key tile:
+//           S = Q K^T, dP = dO V^T, dS to smem, dQ += dS K (TMEM).
+//   dbias : one CTA per (b, head, 128-query block, 128-key block) looping over all rows in order and
+//           summing dS in registers (no atomics: the row reduction has a fixed order).
+// P = exp((x - m) - log l), dS = P * (dP - delta), delta = sum_d dO*O (computed by a small kernel first).
+// =================================================================================================
+struct AttnBwdArgs {
+  int B, S, N, H;
+  float scale;
+  const float* stats;    // [2][B][S][H][N]
+  const float* delta;    // [B][S][H][N]
+  const uint8_t* mask;
+  int64_t mask_st[2];
+  int has_bias, bias_b_mul;
+  void* out0;            // dq (MODE_DQ), dk (dK/dV kernel), dbias fp32 (MODE_DBIAS)
+  void* out1;            // dv
+  int64_t out0_st[4], out1_st[4];
+  uint32_t idesc_a, idesc_b;   // the two MMA shapes of the kernel
+  int* err;
+};
+
+// byte offset of 16-byte chunk g (0..7) of row r inside a one-block SW128 tile (rows of 64 16-bit elements)
+__device__ __forceinline__ int sw128_chunk1(int r, int g) { return r * 128 + ((g ^ (r & 7)) << 4); }
+
+enum { MODE_DQ = 0, MODE_DBIAS = 1 };
+
+template <int HD, int TKV, int MODE> struct GeoR {
+  static constexpr int RB = HD * 2;
+  static constexpr int TA = 128 * RB;                    // Q / dO tile
+  static constexpr int TB = TKV * RB;                    // K / V tile
+  static constexpr int NA = MODE == MODE_DQ ? 1 : 2;     // buffers of the 128-row tiles
+  static constexpr uint32_t LAYOUT = RB == 128 ? 2 : 4;
+  static constexpr uint32_t SBO = 8 * RB;
+  static constexpr int OFF_Q = 0;
+  static constexpr int OFF_DO = OFF_Q + NA * TA;
+  static constexpr int OFF_K = OFF_DO + NA * TA;
+  static constexpr int OFF_V = OFF_K + 2 * TB;
+  static constexpr int OFF_DS = OFF_V + 2 * TB;                              // [128 x 64] SW128 (MODE_DQ)
+  static constexpr int OFF_BIAS = OFF_DS + (MODE == MODE_DQ ? 16384 : 0);    // [128 x TKV], 64-column blocks
+  static constexpr int OFF_MB = OFF_BIAS + 128 * TKV * 2;
+  static constexpr int OFF_BAR = OFF_MB + 512;
+  static constexpr int SMEM = OFF_BAR + 128 + 1024;
+};
+
+template <typename T, int HD, int TKV, int MODE>
+__global__ void __launch_bounds__(128, 2)
+attn_bwd_rows_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmDO,
+                     const __grid_constant__ CUtensorMap tmK, const __grid_constant__ CUtensorMap tmV,
+                     const __grid_constant__ CUtensorMap tmBias, const AttnBwdArgs a) {
+  using G = GeoR<HD, TKV, MODE>;
+  static_assert(MODE == MODE_DBIAS || TKV == 64, "dQ pass uses 64-key tiles");
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  uint8_t* sQ = smem + G::OFF_Q;
+  uint8_t* sDO = smem + G::OFF_DO;
+  uint8_t* sK = smem + G::OFF_K;
+  uint8_t* sV = smem + G::OFF_V;
+  uint8_t* sDS = smem + G::OFF_DS;
+  uint8_t* sBias = smem + G::OFF_BIAS;
+  float* sMb = reinterpret_cast<float*>(smem + G::OFF_MB);
+  uint64_t* bar_once = reinterpret_cast<uint64_t*>(smem + G::OFF_BAR);  // Q+dO (DQ) or bias (DBIAS)
+  uint64_t* bar_in = bar_once + 1;   // [2] per-step operand stages
+  uint64_t* bar_bias = bar_once + 3; // per-step bias (DQ)
+  uint64_t* bar_s = bar_once + 4;
+  uint64_t* bar_dq = bar_once + 5;
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bar_once + 6);
+
+  const int tid = threadIdx.x, warp = tid >> 5;
+  const int qblocks = (a.N + 127) / 128;
+  int z = blockIdx.x, b, h, s = 0, qb, kvb = 0, nsteps;
+  if constexpr (MODE == MODE_DQ) {
+    qb = z % qblocks; z /= qblocks;
+    h = z % a.H; z /= a.H;
+    s = z % a.S; b = z / a.S;
+    nsteps = (a.N + TKV - 1) / TKV;
+  } else {
+    const int kblocks = (a.N + TKV - 1) / TKV;
+    kvb = z % kblocks; z /= kblocks;
+    qb = z % qblocks; z /= qblocks;
+    h = z % a.H; b = z / a.H;
+    nsteps = a.S;
+  }
+  const int q0 = qb * 128;
+  const int bias_b = b * a.bias_b_mul;
+
+  if (tid == 0) {
+    mbar_init(bar_once, 1); mbar_init(&bar_in[0], 1); mbar_init(&bar_in[1], 1);
+    mbar_init(bar_bias, 1); mbar_init(bar_s, 1); mbar_init(bar_dq, 1);
+    mbar_fence_init();
+  }
+  if (warp == 0) tmem_alloc(tmem_slot, 256);
+  tc_fence_before_sync();
+  __syncthreads();
+  tc_fence_after_sync();
+  const uint32_t tmem_base = *tmem_slot;
+  const uint32_t t_row = tmem_base + ((uint32_t)(warp * 32) << 16);
+  constexpr uint32_t COL_DP = TKV, COL_DQ = 2 * TKV;
+
+  auto load_bias = [&](int k0) {
+#pragma unroll
+    for (int blk = 0; blk < TKV / 64; ++blk)
+      tma_load_4d(sBias + blk * 16384, &tmBias, MODE == MODE_DQ ? bar_bias : bar_once, k0 + blk * 64, q0, h, bias_b);
+  };
+  auto load_step = [&](int step, int stg) {
+    if constexpr (MODE == MODE_DQ) {
+      mbar_expect_tx(&bar_in[stg], 2 * G::TB);
+      tma_load_5d(sK + stg * G::TB, &tmK, &bar_in[stg], 0, h, step * TKV, s, b);
+      tma_load_5d(sV + stg * G::TB, &tmV, &bar_in[stg], 0, h, step * TKV, s, b);
+    } else {
+      mbar_expect_tx(&bar_in[stg], 2 * G::TB + 2 * G::TA);
+      tma_load_5d(sQ + stg * G::TA, &tmQ, &bar_in[stg], 0, h, q0, step, b);
+      tma_load_5d(sDO + stg * G::TA, &tmDO, &bar_in[stg], 0, h, q0, step, b);
+      tma_load_5d(sK + stg * G::TB, &tmK, &bar_in[stg], 0, h, kvb * TKV, step, b);
+      tma_load_5d(sV + stg * G::TB, &tmV, &bar_in[stg], 0, h, kvb * TKV, step, b);
+    }
+  };
+
+  if (tid == 0) {
+    if constexpr (MODE == MODE_DQ) {
+      mbar_expect_tx(bar_once, 2 * G::TA);
+      tma_load_5d(sQ, &tmQ, bar_once, 0, h, q0, s, b);
+      tma_load_5d(sDO, &tmDO, bar_once, 0, h, q0, s, b);
+      if (a.has_bias) { mbar_expect_tx(bar_bias, 128 * TKV * 2); load_bias(0); }
+    } else if (a.has_bias) {
+      mbar_expect_tx(bar_once, 128 * TKV * 2);
+      load_bias(kvb * TKV);
+    }
+    for (int st = 0; st < 2 && st < nsteps; ++st) load_step(st, st);
+  }
+
+  const int qi = q0 + tid;
+  const bool q_ok = qi < a.N;
+  const long long plane = (long long)a.B * a.S * a.H * a.N;
+  float m_row = 0.f, l_row = 0.f, d_row = 0.f;
+  auto load_stats = [&](int ss) {
+    if (q_ok) {
+      const long long row = (((long long)b * a.S + ss) * a.H + h) * a.N + qi;
+      m_row = a.stats[row]; l_row = a.stats[plane + row]; d_row = a.delta[row];
+    }
+  };
+  if constexpr (MODE == MODE_DQ) load_stats(s);
+  float acc[MODE == MODE_DBIAS ? TKV : 1];
+  if constexpr (MODE == MODE_DBIAS) {
+#pragma unroll
+    for (int i = 0; i < TKV; ++i) acc[i] = 0.f;
+  }
+  bool ok = true;
+  if (MODE == MODE_DBIAS && a.has_bias) ok = mbar_wait(bar_once, 0, a.err, 21);
+
+  for (int j = 0; j < nsteps; ++j) {
+    const int stg = j & 1;
+    const uint32_t par = j & 1, in_par = (j >> 1) & 1;
+    const int row_s = MODE == MODE_DQ ? s : j;
+    const int k0 = MODE == MODE_DQ ? j * TKV : kvb * TKV;
+    if constexpr (MODE == MODE_DBIAS) load_stats(j);
+    if (tid == 0) {
+      if (MODE == MODE_DQ && j == 0) ok = mbar_wait(bar_once, 0, a.err, 22);
+      ok = mbar_wait(&bar_in[stg], in_par, a.err, 23) && ok;
+      tc_fence_after_sync();
+      const int sa = MODE == MODE_DQ ? 0 : stg;
+      const uint32_t qa = smem_u32(sQ + sa * G::TA), da = smem_u32(sDO + sa * G::TA);
+      const uint32_t ka = smem_u32(sK + stg * G::TB), va = smem_u32(sV + stg * G::TB);
+#pragma unroll
+      for (int ks = 0; ks < HD / 16; ++ks)
+        umma<KIND_F16>(tmem_base, make_smem_desc(qa + ks * 32, 16, G::SBO, G::LAYOUT),
+                       make_smem_desc(ka + ks * 32, 16, G::SBO, G::LAYOUT), a.idesc_a, ks > 0);
+#pragma unroll
+      for (int ks = 0; ks < HD / 16; ++ks)
+        umma<KIND_F16>(tmem_base + COL_DP, make_smem_desc(da + ks * 32, 16, G::SBO, G::LAYOUT),
+                       make_smem_desc(va + ks * 32, 16, G::SBO, G::LAYOUT), a.idesc_a, ks > 0);
+      umma_commit(bar_s);
+    }
+    if (tid < TKV) {
+      const int kj = k0 + tid;
+      float mb = 0.f;
+      if (kj >= a.N) mb = -INFINITY;
+      else if (a.mask != nullptr) mb = kMaskSentinel * ((a.mask[b * a.mask_st[0] + row_s * a.mask_st[1] + kj] ? 1.0f : 0.0f) - 1.0f);
+      sMb[tid] = mb;
+    }
+    __syncthreads();
+    ok = mbar_wait(bar_s, par, a.err, 24) && ok;
+    tc_fence_after_sync();
+    if (MODE == MODE_DQ && a.has_bias) ok = mbar_wait(bar_bias, par, a.err, 25) && ok;
+    if (MODE == MODE_DQ && j > 0) ok = mbar_wait(bar_dq, (j - 1) & 1, a.err, 26) && ok;  // dS buffer and K/V stage free
+    if (MODE == MODE_DQ && tid == 0 && j > 0 && j + 1 < nsteps) load_step(j + 1, (j + 1) & 1);
+
+#pragma unroll
+    for (int c = 0; c < TKV / 32; ++c) {
+      uint32_t rs[32], rp[32];
+      tmem_ld_32x32(t_row + c * 32, rs);
+      tmem_ld_32x32(t_row + COL_DP + c * 32, rp);
+      tmem_ld_wait();
+#pragma unroll
+      for (int u = 0; u < 4; ++u) {
+        float bv[8], ds[8];
+        if (a.has_bias) {
+          const int g = c * 4 + u;
+          const uint4 raw = *reinterpret_cast<const uint4*>(sBias + (g >> 3) * 16384 + sw128_chunk1(tid, g & 7));
+          unpack8<T>(raw, bv);
+        }
+#pragma unroll
+        for (int i = 0; i < 8; ++i) {
+          const int col = c * 32 + u * 8 + i;
+          float x = __uint_as_float(rs[u * 8 + i]) * a.scale;
+          if (a.has_bias) x += bv[i];
+          x += sMb[col];
+          const float p = ex2_approx(((x - m_row) - l_row) * kLog2e);
+          ds[i] = p * (__uint_as_float(rp[u * 8 + i]) - d_row);
+          if constexpr (MODE == MODE_DBIAS) acc[col] += ds[i];
+        }
+        if constexpr (MODE == MODE_DQ) {
+          uint4 pk;
+          pk.x = pack2<T>(ds[0], ds[1]); pk.y = pack2<T>(ds[2], ds[3]);
+          pk.z = pack2<T>(ds[4], ds[5]); pk.w = pack2<T>(ds[6], ds[7]);
+          *reinterpret_cast<uint4*>(sDS + sw128_chunk1(tid, c * 4 + u)) = pk;
+        }
+      }
+    }
+    if constexpr (MODE == MODE_DQ) fence_proxy_async_smem();
+    tc_fence_before_sync();
+    __syncthreads();
+    if (tid == 0) {
+      tc_fence_after_sync();
+      if constexpr (MODE == MODE_DQ) {
+        const uint32_t dsa = smem_u32(sDS), ka = smem_u32(sK + stg * G::TB);
+#pragma unroll
+        for (int kk = 0; kk < TKV / 16; ++kk)
+          umma<KIND_F16>(tmem_base + COL_DQ, make_smem_desc(dsa + kk * 32, 16, 1024, 2),
+                         make_smem_desc(ka + kk * 16 * G::RB, TKV * G::RB, G::SBO, G::LAYOUT), a.idesc_b,
+                         (j > 0 || kk > 0) ? 1u : 0u);
+        umma_commit(bar_dq);
+        if (a.has_bias && j + 1 < nsteps) { mbar_expect_tx(bar_bias, 128 * TKV * 2); load_bias((j + 1) * TKV); }
+      } else {
+        if (j + 2 < nsteps) load_step(j + 2, stg);  // this step's MMAs have completed (bar_s), all reads are done
+      }
+    }
+    if (!ok) break;
+  }
+
+  if constexpr (MODE == MODE_DQ) {
+    ok = mbar_wait(bar_dq, (nsteps - 1) & 1, a.err, 27) && ok;
+    tc_fence_after_sync();
+    {
+      // tcgen05.ld is warp-collective: every thread loads, only valid rows store
+      const bool st_ok = q_ok && ok;
+      T* row = reinterpret_cast<T*>(a.out0) + b * a.out0_st[0] + s * a.out0_st[1] + qi * a.out0_st[2] + h * a.out0_st[3];
+#pragma unroll
+      for (int c = 0; c < HD / 32; ++c) {
+        uint32_t r[32];
+        tmem_ld_32x32(t_row + COL_DQ + c * 32, r);
+        tmem_ld_wait();
+        if (st_ok) {
+#pragma unroll
+          for (int g = 0; g < 4; ++g) {
+            uint4 pk;
+            pk.x = pack2<T>(__uint_as_float(r[g * 8 + 0]) * a.scale, __uint_as_float(r[g * 8 + 1]) * a.scale);
+            pk.y = pack2<T>(__uint_as_float(r[g * 8 + 2]) * a.scale, __uint_as_float(r[g * 8 + 3]) * a.scale);
+            pk.z = pack2<T>(__uint_as_float(r[g * 8 + 4]) * a.scale, __uint_as_float(r[g * 8 + 5]) * a.scale);
+            pk.w = pack2<T>(__uint_as_float(r[g * 8 + 6]) * a.scale, __uint_as_float(r[g * 8 + 7]) * a.scale);
+            reinterpret_cast<uint4*>(row)[c * 4 + g] = pk;
+          }
+        }
+      }
+    }
+  } else {
+    if (q_ok && ok) {
+      float* row = reinterpret_cast<float*>(a.out0) + (((long long)b * a.H + h) * a.N + qi) * a.N + kvb * TKV;
+      const int valid = a.N - kvb * TKV;
+      if (valid >= TKV && (a.N % 4) == 0) {
+#pragma unroll
+        for (int i = 0; i < TKV / 4; ++i)
+          reinterpret_cast<float4*>(row)[i] = make_float4(acc[4 * i], acc[4 * i + 1], acc[4 * i + 2], acc[4 * i + 3]);
+      } else {
+#pragma unroll
+        for (int i = 0; i < TKV; ++i)
+          if (i < valid) row[i] = acc[i];
+      }
+    }
+  }
+  tc_fence_before_sync();
+  __syncthreads();
+  if (warp == 0) {
+    tc_fence_after_sync();
+    tmem_dealloc(tmem_base, 256);
+  }
+}
+
+// ------------------------------------------------------------------------------------------------
+// dK / dV pass (thread = key, 64-query tiles)
+// ------------------------------------------------------------------------------------------------
+template <int HD> struct GeoC {
+  static constexpr int RB = HD * 2;
+  static constexpr int TK = 128 * RB;   // K / V tile
+  static constexpr int TQ = 64 * RB;    // Q / dO tile
+  static constexpr uint32_t LAYOUT = RB == 128 ? 2 : 4;
+  static constexpr uint32_t SBO = 8 * RB;
+  static constexpr int OFF_K = 0;
+  static constexpr int OFF_V = OFF_K + TK;
+  static constexpr int OFF_Q = OFF_V + TK;          // [2]
+  static constexpr int OFF_DO = OFF_Q + 2 * TQ;     // [2]
+  static constexpr int OFF_PT = OFF_DO + 2 * TQ;    // [128 keys x 64 queries] SW128
+  static constexpr int OFF_DST = OFF_PT + 16384;
+  static constexpr int OFF_BIAS = OFF_DST + 16384;  // [64 queries x 128 keys] as two [64 x 64] SW128 blocks
+  static constexpr int OFF_ST = OFF_BIAS + 16384;   // m[64], log l[64], delta[64]
+  static constexpr int OFF_BAR = OFF_ST + 1024;
+  static constexpr int SMEM = OFF_BAR + 128 + 1024;
+};
+
+template <typename T, int HD>
+__global__ void __launch_bounds__(128, 2)
+attn_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmDO,
+                     const __grid_constant__ CUtensorMap tmK, const __grid_constant__ CUtensorMap tmV,
+                     const __grid_constant__ CUtensorMap tmBias, const AttnBwdArgs a) {
+  using G = GeoC<HD>;
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  uint8_t* sK = smem + G::OFF_K;
+  uint8_t* sV = smem + G::OFF_V;
+  uint8_t* sQ = smem + G::OFF_Q;
+  uint8_t* sDO = smem + G::OFF_DO;
+  uint8_t* sPT = smem + G::OFF_PT;
+  uint8_t* sDST = smem + G::OFF_DST;
+  uint8_t* sBias = smem + G::OFF_BIAS;
+  float* sM = reinterpret_cast<float*>(smem + G::OFF_ST);
+  float* sL = sM + 64;
+  float* sD = sM + 128;
+  uint64_t* bar_kv = reinterpret_cast<uint64_t*>(smem + G::OFF_BAR);
+  uint64_t* bar_in = bar_kv + 1;  // [2]
+  uint64_t* bar_bias = bar_kv + 3;
+  uint64_t* bar_s = bar_kv + 4;
+  uint64_t* bar_acc = bar_kv + 5;
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bar_kv + 6);
+
+  const int tid = threadIdx.x, warp = tid >> 5;
+  const int kblocks = (a.N + 127) / 128;
+  int z = blockIdx.x;
+  const int kvb = z % kblocks; z /= kblocks;
+  const int h = z % a.H; z /= a.H;
+  const int s = z % a.S;
+  const int b = z / a.S;
+  const int k0 = kvb * 128;
+  const int nsteps = (a.N + 63) / 64;
+  const int bias_b = b * a.bias_b_mul;
+
+  if (tid == 0) {
+    mbar_init(bar_kv, 1); mbar_init(&bar_in[0], 1); mbar_init(&bar_in[1], 1);
+    mbar_init(bar_bias, 1); mbar_init(bar_s, 1); mbar_init(bar_acc, 1);
+    mbar_fence_init();
+  }
+  if (warp == 0) tmem_alloc(tmem_slot, 256);
+  tc_fence_before_sync();
+  __syncthreads();
+  tc_fence_after_sync();
+  const uint32_t tmem_base = *tmem_slot;
+  const uint32_t t_row = tmem_base + ((uint32_t)(warp * 32) << 16);
+  constexpr uint32_t COL_DP = 64, COL_DV = 128, COL_DK = 128 + HD;
+
+  auto load_step = [&](int step, int stg) {
+    mbar_expect_tx(&bar_in[stg], 2 * G::TQ);
+    tma_load_5d(sQ + stg * G::TQ, &tmQ, &bar_in[stg], 0, h, step * 64, s, b);
+    tma_load_5d(sDO + stg * G::TQ, &tmDO, &bar_in[stg], 0, h, step * 64, s, b);
+  };
+  auto load_bias = [&](int step) {
+    mbar_expect_tx(bar_bias, 16384);
+    tma_load_4d(sBias, &tmBias, bar_bias, k0, step * 64, h, bias_b);
+    tma_load_4d(sBias + 8192, &tmBias, bar_bias, k0 + 64, step * 64, h, bias_b);
+  };
+  if (tid == 0) {
+    mbar_expect_tx(bar_kv, 2 * G::TK);
+    tma_load_5d(sK, &tmK, bar_kv, 0, h, k0, s, b);
+    tma_load_5d(sV, &tmV, bar_kv, 0, h, k0, s, b);
+    for (int st = 0; st < 2 && st < nsteps; ++st) load_step(st, st);
+    if (a.has_bias) load_bias(0);
+  }
+  const int kj = k0 + tid;
+  float mb = 0.f;
+  if (kj >= a.N) mb = -INFINITY;
+  else if (a.mask != nullptr) mb = kMaskSentinel * ((a.mask[b * a.mask_st[0] + s * a.mask_st[1] + kj] ? 1.0f : 0.0f) - 1.0f);
+  const long long plane = (long long)a.B * a.S * a.H * a.N;
+  const long long row_base = (((long long)b * a.S + s) * a.H + h) * a.N;
+  bool ok = true;
+
+  for (int j = 0; j < nsteps; ++j) {
+    const int stg = j & 1, q0 = j * 64;
+    const uint32_t par = j & 1, in_par = (j >> 1) & 1;
+    if (tid == 0) {
+      if (j == 0) ok = mbar_wait(bar_kv, 0, a.err, 31);
+      ok = mbar_wait(&bar_in[stg], in_par, a.err, 32) && ok;
+      tc_fence_after_sync();
+      const uint32_t ka = smem_u32(sK), va = smem_u32(sV);
+      const uint32_t qa = smem_u32(sQ + stg * G::TQ), da = smem_u32(sDO + stg * G::TQ);
+#pragma unroll
+      for (int ks = 0; ks < HD / 16; ++ks)   // S^T = K Q^T
+        umma<KIND_F16>(tmem_base, make_smem_desc(ka + ks * 32, 16, G::SBO, G::LAYOUT),
+                       make_smem_desc(qa + ks * 32, 16, G::SBO, G::LAYOUT), a.idesc_a, ks > 0);
+#pragma unroll
+      for (int ks = 0; ks < HD / 16; ++ks)   // dP^T = V dO^T
+        umma<KIND_F16>(tmem_base + COL_DP, make_smem_desc(va + ks * 32, 16, G::SBO, G::LAYOUT),
+                       make_smem_desc(da + ks * 32, 16, G::SBO, G::LAYOUT), a.idesc_a, ks > 0);
+      umma_commit(bar_s);
+    }
+    if (tid < 64) {
+      const int qi = q0 + tid;
+      const bool v = qi < a.N;
+      sM[tid] = v ? a.stats[row_base + qi] : 0.f;
+      sL[tid] = v ? a.stats[plane + row_base + qi] : 0.f;
+      sD[tid] = v ? a.delta[row_base + qi] : 0.f;
+    }
+    __syncthreads();
+    ok = mbar_wait(bar_s, par, a.err, 33) && ok;
+    tc_fence_after_sync();
+    if (a.has_bias) ok = mbar_wait(bar_bias, par, a.err, 34) && ok;
+    if (j > 0) ok = mbar_wait(bar_acc, (j - 1) & 1, a.err, 35) && ok;   // P^T / dS^T buffers and the other stage are free
+    if (tid == 0 && j > 0 && j + 1 < nsteps) load_step(j + 1, (j + 1) & 1);
+
+    const uint8_t* bias_col = sBias + (tid >> 6) * 8192 + (tid & 7) * 2;  // element (q, key tid): + q*128 + swizzled chunk
+    const int key_chunk = (tid & 63) >> 3;
+#pragma unroll
+    for (int c = 0; c < 2; ++c) {
+      uint32_t rs[32], rp[32];
+      tmem_ld_32x32(t_row + c * 32, rs);
+      tmem_ld_32x32(t_row + COL_DP + c * 32, rp);
+      tmem_ld_wait();
+#pragma unroll
+      for (int u = 0; u < 4; ++u) {
+        float pv[8], ds[8];
+#pragma unroll
+        for (int i = 0; i < 8; ++i) {
+          const int q = c * 32 + u * 8 + i;
+          float x = __uint_as_float(rs[u * 8 + i]) * a.scale;
+          if (a.has_bias) x += to_f32(*reinterpret_cast<const T*>(bias_col + q * 128 + ((key_chunk ^ (q & 7)) << 4)));
+          x += mb;
+          pv[i] = ex2_approx(((x - sM[q]) - sL[q]) * kLog2e);
+          ds[i] = pv[i] * (__uint_as_float(rp[u * 8 + i]) - sD[q]);
+        }
+        uint4 pk;
+        pk.x = pack2<T>(pv[0], pv[1]); pk.y = pack2<T>(pv[2], pv[3]);
+        pk.z = pack2<T>(pv[4], pv[5]); pk.w = pack2<T>(pv[6], pv[7]);
+        *reinterpret_cast<uint4*>(sPT + sw128_chunk1(tid, c * 4 + u)) = pk;
+        pk.x = pack2<T>(ds[0], ds[1]); pk.y = pack2<T>(ds[2], ds[3]);
+        pk.z = pack2<T>(ds[4], ds[5]); pk.w = pack2<T>(ds[6], ds[7]);
+        *reinterpret_cast<uint4*>(sDST + sw128_chunk1(tid, c * 4 + u)) = pk;
+      }
+    }
+    fence_proxy_async_smem();
+    tc_fence_before_sync();
+    __syncthreads();
+    if (tid == 0) {
+      tc_fence_after_sync();
+      const uint32_t pa = smem_u32(sPT), dsa = smem_u32(sDST);
+      const uint32_t qa = smem_u32(sQ + stg * G::TQ), da = smem_u32(sDO + stg * G::TQ);
+#pragma unroll
+      for (int kk = 0; kk < 4; ++kk)   // dV += P^T dO   (B = dO as [n = d, k = query]: MN-major)
+        umma<KIND_F16>(tmem_base + COL_DV, make_smem_desc(pa + kk * 32, 16, 1024, 2),
+                       make_smem_desc(da + kk * 16 * G::RB, 64 * G::RB, G::SBO, G::LAYOUT), a.idesc_b,
+                       (j > 0 || kk > 0) ? 1u : 0u);
+#pragma unroll
+      for (int kk = 0; kk < 4; ++kk)   // dK += dS^T Q
+        umma<KIND_F16>(tmem_base + COL_DK, make_smem_desc(dsa + kk * 32, 16, 1024, 2),
+                       make_smem_desc(qa + kk * 16 * G::RB, 64 * G::RB, G::SBO, G::LAYOUT), a.idesc_b,
+                       (j > 0 || kk > 0) ? 1u : 0u);
+      umma_commit(bar_acc);
+      if (a.has_bias && j + 1 < nsteps) load_bias(j + 1);
+    }
+    if (!ok) break;
+  }
+  ok = mbar_wait(bar_acc, (nsteps - 1) & 1, a.err, 36) && ok;
+  tc_fence_after_sync();
+  {
+    const bool st_ok = kj < a.N && ok;
+    T* krow = reinterpret_cast<T*>(a.out0) + b * a.out0_st[0] + s * a.out0_st[1] + kj * a.out0_st[2] + h * a.out0_st[3];
+    T* vrow = reinterpret_cast<T*>(a.out1) + b * a.out1_st[0] + s * a.out1_st[1] + kj * a.out1_st[2] + h * a.out1_st[3];
+#pragma unroll
+    for (int c = 0; c < HD / 32; ++c) {
+      uint32_t rk[32], rv[32];
+      tmem_ld_32x32(t_row + COL_DK + c * 32, rk);
+      tmem_ld_32x32(t_row + COL_DV + c * 32, rv);
+      tmem_ld_wait();
+      if (st_ok) {
+#pragma unroll
+        for (int g = 0; g < 4; ++g) {
+          uint4 pk;
+          pk.x = pack2<T>(__uint_as_float(rk[g * 8 + 0]) * a.scale, __uint_as_float(rk[g * 8 + 1]) * a.scale);
+          pk.y = pack2<T>(__uint_as_float(rk[g * 8 + 2]) * a.scale, __uint_as_float(rk[g * 8 + 3]) * a.scale);
+          pk.z = pack2<T>(__uint_as_float(rk[g * 8 + 4]) * a.scale, __uint_as_float(rk[g * 8 + 5]) * a.scale);
+          pk.w = pack2<T>(__uint_as_float(rk[g * 8 + 6]) * a.scale, __uint_as_float(rk[g * 8 + 7]) * a.scale);
+          reinterpret_cast<uint4*>(krow)[c * 4 + g] = pk;
+          pk.x = pack2<T>(__uint_as_float(rv[g * 8 + 0]), __uint_as_float(rv[g * 8 + 1]));
+          pk.y = pack2<T>(__uint_as_float(rv[g * 8 + 2]), __uint_as_float(rv[g * 8 + 3]));
+          pk.z = pack2<T>(__uint_as_float(rv[g * 8 + 4]), __uint_as_float(rv[g * 8 + 5]));
+          pk.w = pack2<T>(__uint_as_float(rv[g * 8 + 6]), __uint_as_float(rv[g * 8 + 7]));
+          reinterpret_cast<uint4*>(vrow)[c * 4 + g] = pk;
+        }
+      }
+    }
+  }
+  tc_fence_before_sync();
+  __syncthreads();
+  if (warp == 0) {
+    tc_fence_after_sync();
+    tmem_dealloc(tmem_base, 256);
+  }
+}
+
+// delta[b,s,h,i] = sum_d dO * O
+template <typename T>
+__global__ void attn_delta_tc_kernel(TriAttnDesc d, const T* o, const T* d_o, float* delta) {
+  const long long idx = blockIdx.x * (long long)blockDim.x + threadIdx.x;
+  const long long total = (long long)d.B * d.n_seq * d.H * d.n_res;
+  if (idx >= total) return;
+  const int i = idx % d.n_res; long long z = idx / d.n_res;
+  const int h = z % d.H; z /= d.H;
+  const int s = z % d.n_seq; const int b = z / d.n_seq;
+  const T* orow = o + b * d.o_st[0] + s * d.o_st[1] + i * d.o_st[2] + h * d.o_st[3];
+  const T* grow = d_o + b * d.do_st[0] + s * d.do_st[1] + i * d.do_st[2] + h * d.do_st[3];
+  float acc = 0.f;
+  for (int g = 0; g < d.D / 8; ++g) {
+    float x[8], y[8];
+    unpack8<T>(reinterpret_cast<const uint4*>(orow)[g], x);
+    unpack8<T>(reinterpret_cast<const uint4*>(grow)[g], y);
+#pragma unroll
+    for (int e = 0; e < 8; ++e) acc = fmaf(x[e], y[e], acc);
+  }
+  delta[idx] = acc;
+}
+
+// rank-5 map with a caller-chosen number of residues per box
+int qkv_map_rows(CUtensorMap* out, const void* p, const TriAttnDesc* d, const int64_t* st, int rows) {
+  const uint64_t dims[5] = {(uint64_t)d->D, (uint64_t)d->H, (uint64_t)d->n_res, (uint64_t)d->n_seq, (uint64_t)d->B};
+  const uint64_t str[4] = {(uint64_t)st[3], (uint64_t)st[2], (uint64_t)st[1], (uint64_t)st[0]};
+  const uint32_t box[5] = {(uint32_t)d->D, 1, (uint32_t)rows, 1, 1};
+  return make_tmap(out, p, d->dtype, 5, dims, str, box, d->D * 2);
+}
+
+int bias_map(CUtensorMap* out, const void* bias, const TriAttnDesc* d, int rows) {
+  const uint64_t nb = d->bias_st[0] != 0 ? (uint64_t)d->B : 1;
+  const uint64_t dims[4] = {(uint64_t)d->n_res, (uint64_t)d->n_res, (uint64_t)d->H, nb};
+  const uint64_t str[3] = {(uint64_t)d->bias_st[2], (uint64_t)d->bias_st[1], (uint64_t)d->bias_st[0]};
+  const uint32_t box[4] = {64, (uint32_t)rows, 1, 1};
+  return make_tmap(out, bias, d->dtype, 4, dims, str, box, 128);
+}
+
+template <typename KernelT>
+int set_dyn_smem(KernelT kern, int bytes) {
+  TRI_CUDA_OK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, bytes));
+  return 0;
+}
+
+template <typename T, int HD>
+int bwd_launch(const TriAttnDesc* d, const void* q, const void* k, const void* v, const void* bias,
+               const uint8_t* mask, const void* o, const float* stats, const void* d_o, void* dq, void* dk, void* dv,
+               float* dbias, int* err, float* delta, cudaStream_t st) {
+  const long long rows = (long long)d->B * d->n_seq * d->H * d->n_res;
+  const double pairs = (double)rows * d->n_res;
+  const double tensor_bytes = 2.0 * d->B * d->n_seq * (double)d->n_res * d->H * d->D;
+  {
+    KernelTimer kt("tc_attn_delta", st, 0.0, 2.0 * tensor_bytes);
+    attn_delta_tc_kernel<T><<<cdiv(rows, 256), 256, 0, st>>>(*d, (const T*)o, (const T*)d_o, delta);
+    TRI_LAUNCH_OK();
+  }
+  const int kind = d->dtype == TRI_BF16 ? KIND_BF16 : KIND_F16;
+  AttnBwdArgs a;
+  a.B = d->B; a.S = d->n_seq; a.N = d->n_res; a.H = d->H; a.scale = d->scale;
+  a.stats = stats; a.delta = delta; a.mask = mask; a.mask_st[0] = d->mask_st[0]; a.mask_st[1] = d->mask_st[1];
+  a.has_bias = bias != nullptr; a.bias_b_mul = d->bias_st[0] != 0 ? 1 : 0; a.err = err;
+  const int qblocks = (d->n_res + 127) / 128;
+  CUtensorMap tq, tdo, tk, tv, tb;
+
+  // ---- dK / dV -------------------------------------------------------------------------------
+  TRI_TRY(qkv_map_rows(&tq, q, d, d->q_st, 64));
+  TRI_TRY(qkv_map_rows(&tdo, d_o, d, d->do_st, 64));
+  TRI_TRY(qkv_map_rows(&tk, k, d, d->k_st, 128));
+  TRI_TRY(qkv_map_rows(&tv, v, d, d->v_st, 128));
+  if (bias) TRI_TRY(bias_map(&tb, bias, d, 64)); else tb = tq;
+  a.out0 = dk; a.out1 = dv;
+  for (int i = 0; i < 4; ++i) { a.out0_st[i] = d->dk_st[i]; a.out1_st[i] = d->dv_st[i]; }
+  a.idesc_a = make_idesc(kind, 128, 64, false, false);
+  a.idesc_b = make_idesc(kind, 128, HD, false, true);
+  {
+    auto kern = attn_bwd_dkdv_kernel<T, HD>;
+    static bool configured = false;
+    if (!configured) { TRI_TRY(set_dyn_smem(kern, GeoC<HD>::SMEM)); configured = true; }
+    KernelTimer kt("tc_attn_bwd_dkdv", st, 8.0 * pairs * d->D, 6.0 * tensor_bytes);
+    kern<<<(unsigned)((long long)qblocks * d->B * d->n_seq * d->H), 128, GeoC<HD>::SMEM, st>>>(tq, tdo, tk, tv, tb, a);
+    TRI_LAUNCH_OK();
+  }
+  // ---- dQ ------------------------------------------------------------------------------------
+  TRI_TRY(qkv_map_rows(&tq, q, d, d->q_st, 128));
+  TRI_TRY(qkv_map_rows(&tdo, d_o, d, d->do_st, 128));
+  TRI_TRY(qkv_map_rows(&tk, k, d, d->k_st, 64));
+  TRI_TRY(qkv_map_rows(&tv, v, d, d->v_st, 64));
+  if (bias) TRI_TRY(bias_map(&tb, bias, d, 128));
+  a.out0 = dq; a.out1 = nullptr;
+  for (int i = 0; i < 4; ++i) a.out0_st[i] = d->dq_st[i];
+  a.idesc_a = make_idesc(kind, 128, 64, false, false);
+  a.idesc_b = make_idesc(kind, 128, HD, false, true);
+  {
+    auto kern = attn_bwd_rows_kernel<T, HD, 64, MODE_DQ>;
+    static bool configured = false;
+    if (!configured) { TRI_TRY(set_dyn_smem(kern, GeoR<HD, 64, MODE_DQ>::SMEM)); configured = true; }
+    KernelTimer kt("tc_attn_bwd_dq", st, 2.0 * pairs * d->D, 5.0 * tensor_bytes);
+    kern<<<(unsigned)((long long)qblocks * d->B * d->n_seq * d->H), 128, GeoR<HD, 64, MODE_DQ>::SMEM, st>>>(tq, tdo, tk, tv, tb, a);
+    TRI_LAUNCH_OK();
+  }
+  // ---- dbias ---------------------------------------------------------------------------------
+  if (dbias != nullptr) {
+    TRI_TRY(qkv_map_rows(&tk, k, d, d->k_st, 128));
+    TRI_TRY(qkv_map_rows(&tv, v, d, d->v_st, 128));
+    a.out0 = dbias;
+    a.idesc_a = make_idesc(kind, 128, 128, false, false);
+    auto kern = attn_bwd_rows_kernel<T, HD, 128, MODE_DBIAS>;
+    static bool configured = false;
+    if (!configured) { TRI_TRY(set_dyn_smem(kern, GeoR<HD, 128, MODE_DBIAS>::SMEM)); configured = true; }
+    KernelTimer kt("tc_attn_bwd_dbias", st, 0.0, 4.0 * tensor_bytes);
+    kern<<<(unsigned)((long long)qblocks * qblocks * d->B * d->H), 128, GeoR<HD, 128, MODE_DBIAS>::SMEM, st>>>(tq, tdo, tk, tv, tb, a);
+    TRI_LAUNCH_OK();
+  }
+  return 0;
+}
+
 bool forced_simt() {
   const char* e = getenv("TRI_B200_FORCE_SIMT");
   return e != nullptr && e[0] == '1';
@@ -340,9 +965,15 @@ bool attn_fwd_supported(const TriAttnDesc* d) {
   return true;
 }
 
-bool attn_bwd_supported(const TriAttnDesc* d) { (void)d; return false; }
+bool attn_bwd_supported(const TriAttnDesc* d) {
+  return attn_fwd_supported(d) && strides_ok(d->do_st) && strides_ok(d->dq_st) && strides_ok(d->dk_st) &&
+         strides_ok(d->dv_st) && d->n_seq <= 65535;
+}
 
-size_t attn_ws_bytes(const TriAttnDesc* d, int is_bwd) { (void)d; (void)is_bwd; return 512; }
+size_t attn_ws_bytes(const TriAttnDesc* d, int is_bwd) {
+  if (!is_bwd) return 512;
+  return 512 + align_up((size_t)d->B * d->n_seq * d->H * d->n_res * sizeof(float));
+}
 
 int attn_forward(const TriAttnDesc* d, const void* q, const void* k, const void* v, const void* bias,
                  const uint8_t* mask, void* o, float* lse, void* ws, size_t ws_size, cudaStream_t st) {
@@ -357,9 +988,19 @@ int attn_forward(const TriAttnDesc* d, const void* q, const void* k, const void*
   return fwd_launch<__half, 64>(d, q, k, v, bias, mask, o, lse, err, st);
 }
 
-int attn_backward(const TriAttnDesc*, const void*, const void*, const void*, const void*, const uint8_t*,
-                  const void*, const float*, const void*, void*, void*, void*, float*, void*, size_t, cudaStream_t) {
-  return fail(TRI_ERR_UNSUPPORTED, "no tensor-core attention backward for this problem");
+int attn_backward(const TriAttnDesc* d, const void* q, const void* k, const void* v, const void* bias,
+                  const uint8_t* mask, const void* o, const float* lse, const void* d_o, void* dq, void* dk,
+                  void* dv, float* dbias, void* ws, size_t ws_size, cudaStream_t st) {
+  if (ws == nullptr || ws_size < attn_ws_bytes(d, 1)) return fail(TRI_ERR_WORKSPACE, "attention backward workspace too small");
+  TRI_CUDA_OK(cudaMemsetAsync(ws, 0, 256, st));
+  int* err = static_cast<int*>(ws);
+  float* delta = reinterpret_cast<float*>(static_cast<char*>(ws) + 512);
+  if (d->dtype == TRI_BF16) {
+    if (d->D == 32) return bwd_launch<__nv_bfloat16, 32>(d, q, k, v, bias, mask, o, lse, d_o, dq, dk, dv, dbias, err, delta, st);
+    return bwd_launch<__nv_bfloat16, 64>(d, q, k, v, bias, mask, o, lse, d_o, dq, dk, dv, dbias, err, delta, st);
+  }
+  if (d->D == 32) return bwd_launch<__half, 32>(d, q, k, v, bias, mask, o, lse, d_o, dq, dk, dv, dbias, err, delta, st);
+  return bwd_launch<__half, 64>(d, q, k, v, bias, mask, o, lse, d_o, dq, dk, dv, dbias, err, delta, st);
 }
 
 }  // namespace tc

@@ -44,7 +44,7 @@ enum {
 
 int tri_abi_version(void);
 const char* tri_last_error(void);
-/* Name of the kernel family the last forward/backward on this thread ran on:
+/* Name of the kernel family the most recent forward/backward (on any thread) ran on:
  * "simt" (CUDA-core fp32 path) or "tcgen05" (tensor-core path). */
 const char* tri_last_path(void);
 /* Number of kernel launches issued by this library (all threads) since the

@@ -66,6 +66,8 @@ def test_oracle_fwd_bwd(ta, shape, dtype, precision):
         tensor_core = dtype != torch.float32 and shape[4] in (32, 64) and shape[2] % 8 == 0
         assert _lib.last_path() == ("tcgen05" if tensor_core else "simt")
         out, grads = util.attn_fwd_bwd(ta, t, mask, None, d_out)
+        torch.cuda.synchronize()
+        assert _lib.last_path() == ("tcgen05" if tensor_core else "simt")  # the backward ran last
     o_ref, g_ref = util.attn_oracle(t, mask, None, d_out)
     cos_min, fro, mar = _tol(dtype, precision)
     util.check_close("out", out, o_ref, cos_min, fro, mar)
