@@ -194,6 +194,8 @@ def main():
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
     ap.add_argument("--n-res", type=int, default=N_RES, help="pair side (default: the headline 768)")
+    ap.add_argument("--quick", action="store_true",
+                    help="timed region only: no end-to-end leg and no CPU baseline (for profiler captures)")
     args = ap.parse_args()
     rank = int(os.environ.get("RANK", "0"))
     world = int(os.environ.get("WORLD_SIZE", "1"))
@@ -269,7 +271,7 @@ def main():
     # ---- e2e: host buffers, copies inside the timed region --------------------------------------
     h2d = sum(v.numel() * v.element_size() for v in list(host_t.values()) + list(host_w.values()))
     out_host = None
-    e2e_steps = max(2, min(args.steps, 5))
+    e2e_steps = 1 if args.quick else max(2, min(args.steps, 5))
     barrier()
     t_beg = torch.cuda.Event(enable_timing=True)
     t_end = torch.cuda.Event(enable_timing=True)
@@ -310,7 +312,7 @@ def main():
                     "launches": cnt, "avg_launch_ms": tot_ms / cnt, "share_of_step": tot_ms / args.steps / ms}
     kernels = {k_: {"launches": v_[0], "ms_per_step": v_[1] / args.steps} for k_, v_ in
                sorted(prof.items(), key=lambda kv: -kv[1][1])}
-    cpu, _ = cpu_reference(1, 1) if world == 1 else (None, None)
+    cpu, _ = cpu_reference(1, 1) if world == 1 and not args.quick else (None, None)
     line = dict(base, value=flops / (ms / 1e3) / 1e12, ms_per_step=ms,
                 pct_of_bf16_peak={"measured_burst": flops / (ms / 1e3) / 1e12 / pk["bf16_tflops"] / world,
                                   "nominal_2250": flops / (ms / 1e3) / 1e12 / 2250.0 / world},
