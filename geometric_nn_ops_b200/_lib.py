@@ -57,6 +57,23 @@ class TriMulWeightGrads(Structure):
     _fields_ = [(_ABI_FIELD[n], c_void_p) for n in WEIGHT_NAMES]
 
 
+class TriMulShardDesc(Structure):
+    _fields_ = [
+        ("B", c_int32), ("rows", c_int32), ("N", c_int32), ("C", c_int32), ("Ch", c_int32),
+        ("dtype", c_int32), ("precision", c_int32), ("eps", c_float),
+    ]
+
+
+class TriMulShardBufs(Structure):
+    _fields_ = [
+        ("x", c_void_p), ("mask", c_void_p), ("w", POINTER(TriMulWeights)), ("saved", c_void_p),
+        ("a_cm", c_void_p), ("b_cm", c_void_p), ("t_cm", c_void_p), ("out", c_void_p),
+        ("d_out", c_void_p), ("dt_cm", c_void_p), ("dx", c_void_p), ("g", POINTER(TriMulWeightGrads)),
+    ]
+
+
+PHASE_PROJECT, PHASE_OUTPUT, PHASE_OUTPUT_BWD, PHASE_PROJECT_BWD = 0, 1, 2, 3
+
 EXPORTS = {
     "tri_abi_version": (c_int, []),
     "tri_last_error": (c_char_p, []),
@@ -75,6 +92,10 @@ EXPORTS = {
                             c_void_p, c_size_t, c_void_p]),
     "tri_mul_bwd": (c_int, [POINTER(TriMulDesc), c_void_p, c_void_p, POINTER(TriMulWeights), c_void_p, c_void_p,
                             c_void_p, POINTER(TriMulWeightGrads), c_void_p, c_size_t, c_void_p]),
+    "tri_mul_shard_saved_bytes": (c_size_t, [POINTER(TriMulShardDesc)]),
+    "tri_mul_shard_ws_bytes": (c_size_t, [POINTER(TriMulShardDesc), c_int]),
+    "tri_mul_shard_phase": (c_int, [POINTER(TriMulShardDesc), c_int, POINTER(TriMulShardBufs), c_void_p, c_size_t,
+                                    c_void_p]),
     "tri_bgemm": (c_int, [POINTER(TriGemmDesc), c_void_p, c_void_p, c_void_p, c_void_p, c_size_t, c_void_p]),
     "tri_ws_status": (c_int, [c_void_p, c_void_p]),
 }

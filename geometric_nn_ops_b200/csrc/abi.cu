@@ -209,6 +209,32 @@ int tri_mul_bwd(const TriMulDesc* d, const void* x, const void* mask, const TriM
   return simt::backward(d, x, mask, w, saved, d_out, dx, g, ws, ws_bytes, (cudaStream_t)stream);
 }
 
+static int check_shard(const TriMulShardDesc* d) {
+  if (d == nullptr) return fail(TRI_ERR_ARG, "descriptor is null");
+  if (d->B <= 0 || d->rows <= 0 || d->N <= 0) return fail(TRI_ERR_ARG, "shard sizes must be positive");
+  if (d->dtype < TRI_F32 || d->dtype > TRI_F16) return fail(TRI_ERR_ARG, "bad dtype %d", d->dtype);
+  if (!tc::mul_shard_supported(d))
+    return fail(TRI_ERR_UNSUPPORTED, "sharded trimul needs C = Ch = 128, N %% 8 == 0 and bf16/fp16 or fp32-tf32");
+  return 0;
+}
+
+size_t tri_mul_shard_saved_bytes(const TriMulShardDesc* d) {
+  return check_shard(d) != 0 ? 0 : tc::mul_shard_saved_bytes(d);
+}
+
+size_t tri_mul_shard_ws_bytes(const TriMulShardDesc* d, int phase) {
+  return check_shard(d) != 0 ? 0 : tc::mul_shard_ws_bytes(d, phase);
+}
+
+int tri_mul_shard_phase(const TriMulShardDesc* d, int phase, const TriMulShardBufs* bufs, void* ws, size_t ws_bytes,
+                        tri_stream_t stream) {
+  TRI_TRY(check_shard(d));
+  if (!bufs || !bufs->w || !bufs->saved || !ws) return fail(TRI_ERR_ARG, "bufs, weights, saved and ws must not be null");
+  TRI_TRY(check_mul_weights(bufs->w));
+  set_path("tcgen05");
+  return tc::mul_shard_phase(d, phase, bufs, ws, ws_bytes, (cudaStream_t)stream);
+}
+
 int tri_ws_status(const void* ws, tri_stream_t stream) {
   if (ws == nullptr) return fail(TRI_ERR_ARG, "ws is null");
   int code = 0;

@@ -21,5 +21,11 @@ int mul_forward(const TriMulDesc* d, const void* x, const void* mask, const TriM
                 void* saved, void* ws, size_t ws_size, cudaStream_t st);
 int mul_backward(const TriMulDesc* d, const void* x, const void* mask, const TriMulWeights* w, const void* saved,
                  const void* d_out, void* dx, const TriMulWeightGrads* g, void* ws, size_t ws_size, cudaStream_t st);
+// Row-sharded trimul: the pixel-wise phases on their own (see tri_mul_shard_phase in the C header).
+bool mul_shard_supported(const TriMulShardDesc* d);
+size_t mul_shard_saved_bytes(const TriMulShardDesc* d);
+size_t mul_shard_ws_bytes(const TriMulShardDesc* d, int phase);
+int mul_shard_phase(const TriMulShardDesc* d, int phase, const TriMulShardBufs* bufs, void* ws, size_t ws_size,
+                    cudaStream_t st);
 }  // namespace tc
 }  // namespace tri

@@ -296,36 +296,28 @@ __global__ void reduce_wcat_kernel(const float* partial, int nparts, int rowlen,
 // ---------------------------------------------------------------------------------------------
 // memory plan
 // ---------------------------------------------------------------------------------------------
+// Geometry of the pixel-wise phases: M pixels in all, `plane` pixels per batch entry (the stride between
+// channel planes of a channel-major buffer).  For the single-GPU op plane = N*N; for a row shard
+// plane = rows*N.  Nothing in these phases knows about the pair structure beyond that.
+struct Geom {
+  int dtype;
+  float eps;
+  long long M, plane;
+  size_t es() const { return dtype == TRI_F32 ? 4 : 2; }
+  double unit() const { return (double)M * CW * es(); }
+};
+
 struct Prep { int* err; void* wcat; float* bias_cat; float* bias_out; };
-struct SavedT { void *z, *a, *b, *t, *u; float *mean_in, *rstd_in, *mean_out, *rstd_out; };
 
-size_t es_of(const TriMulDesc* d) { return d->dtype == TRI_F32 ? 4 : 2; }
-
-void carve_prep(Arena& a, const TriMulDesc* d, Prep* p) {
+void carve_prep(Arena& a, size_t es, Prep* p) {
   p->err = a.take<int>(64);
-  p->wcat = a.take<char>(4 * CW * CW * es_of(d));
+  p->wcat = a.take<char>(4 * CW * CW * es);
   p->bias_cat = a.take<float>(4 * CW);
   p->bias_out = a.take<float>(2 * CW);
 }
 
-void carve_saved(Arena& a, const TriMulDesc* d, SavedT* s) {
-  const size_t M = (size_t)d->B * d->N * d->N, unit = M * CW * es_of(d);
-  s->z = a.take<char>(unit); s->a = a.take<char>(unit); s->b = a.take<char>(unit);
-  s->t = a.take<char>(unit); s->u = a.take<char>(unit);
-  s->mean_in = a.take<float>(M); s->rstd_in = a.take<float>(M);
-  s->mean_out = a.take<float>(M); s->rstd_out = a.take<float>(M);
-}
-
 constexpr int kSplitK = 148;
-
-struct BwdBufs { void *dy, *dgo, *du, *dt, *da, *db, *dpg, *dz; float* partial; };
-void carve_bwd(Arena& a, const TriMulDesc* d, BwdBufs* w) {
-  const size_t M = (size_t)d->B * d->N * d->N, unit = M * CW * es_of(d);
-  w->dy = a.take<char>(unit); w->dgo = a.take<char>(unit); w->du = a.take<char>(unit);
-  w->dt = a.take<char>(unit); w->da = a.take<char>(unit); w->db = a.take<char>(unit);
-  w->dpg = a.take<char>(4 * unit); w->dz = a.take<char>(unit);
-  w->partial = a.take<float>(std::max((size_t)kSplitK * 4 * CW * CW, (size_t)2 * kPersist * 4 * CW));
-}
+size_t partial_floats() { return std::max((size_t)kSplitK * 4 * CW * CW, (size_t)2 * kPersist * 4 * CW); }
 
 Operand rows_operand(const void* p, int width, long long rows, bool as_mn) {
   // pixel-major [rows, width]: K-major with K = width, or MN-major with MN = width and K = rows
@@ -340,18 +332,18 @@ Operand plane_operand(const void* p, int n, int planes, bool mn) {
   return o;
 }
 
-int contraction(cudaStream_t st, const TriMulDesc* d, const void* a, bool a_mn, const void* b, bool b_mn, void* out,
-                int* err, const char* name) {
+// One N x N x N product per channel plane: out[p] = A[p] B[p]^T with the given operand majors.
+int contraction(cudaStream_t st, int dtype, int planes, int n, const void* a, bool a_mn, const void* b, bool b_mn,
+                void* out, int* err, const char* name) {
   GemmPlan p;
-  const int planes = d->B * CW, n = d->N;
   p.a[0] = plane_operand(a, n, planes, a_mn);
   p.b[0] = plane_operand(b, n, planes, b_mn);
   p.M = n; p.N = n; p.K0 = n; p.batches = planes;
   p.out0 = out; p.ld_out = n; p.batch_out = (long long)n * n;
   p.name = name;
   p.flops = 2.0 * planes * n * (double)n * n;
-  p.bytes = 3.0 * planes * (double)n * n * es_of(d);
-  return launch_gemm(st, d->dtype, EPI_STORE, n > 128 ? 256 : 128, false, p, err);
+  p.bytes = 3.0 * planes * (double)n * n * (dtype == TRI_F32 ? 4 : 2);
+  return launch_gemm(st, dtype, EPI_STORE, n > 128 ? 256 : 128, false, p, err);
 }
 
 template <typename T>
@@ -365,61 +357,54 @@ int run_prep(cudaStream_t st, const TriMulWeights* w, const Prep& pr) {
   return 0;
 }
 
+// ---- phase 1: x -> z (LayerNorm), a / b (gated, masked projections, channel-major) ---------------------
 template <typename T>
-int forward_t(const TriMulDesc* d, const void* x, const void* mask, const TriMulWeights* w, void* out, void* saved,
-              void* ws, size_t ws_size, cudaStream_t st) {
-  const long long M = (long long)d->B * d->N * d->N, NN = (long long)d->N * d->N;
-  const double unit = (double)M * CW * sizeof(T);
-  Arena a(ws, ws_size);
-  Prep pr;
-  carve_prep(a, d, &pr);
-  SavedT s;
-  if (saved) { Arena sa(saved, mul_saved_bytes(d)); carve_saved(sa, d, &s); }
-  else carve_saved(a, d, &s);
-  if (!a.ok()) return fail(TRI_ERR_WORKSPACE, "trimul forward workspace too small: need %zu, got %zu", a.off, ws_size);
-  TRI_TRY(run_prep<T>(st, w, pr));
-  const bool in_bias = w->p_in_b || w->g_in_b, out_bias = w->p_out_b || w->g_out_b;
+int phase_project(cudaStream_t st, const Geom& gm, const void* x, const void* mask, const TriMulWeights* w,
+                  const Prep& pr, void* z, float* mean_in, float* rstd_in, void* a_cm, void* b_cm) {
+  const long long M = gm.M;
   {
-    KernelTimer kt("tc_ln_rows", st, 0.0, 2.0 * unit);
-    ln_rows_kernel<T><<<cdiv(M, 8), 256, 0, st>>>((const T*)x, (const T*)w->norm_in_w, (const T*)w->norm_in_b, d->eps,
-                                                  M, (T*)s.z, s.mean_in, s.rstd_in);
+    KernelTimer kt("tc_ln_rows", st, 0.0, 2.0 * gm.unit());
+    ln_rows_kernel<T><<<cdiv(M, 8), 256, 0, st>>>((const T*)x, (const T*)w->norm_in_w, (const T*)w->norm_in_b, gm.eps,
+                                                  M, (T*)z, mean_in, rstd_in);
     TRI_LAUNCH_OK();
   }
-  {
-    GemmPlan p;
-    p.a[0] = rows_operand(s.z, CW, M, false);
-    p.b[0] = rows_operand(pr.wcat, CW, 4 * CW, false);
-    p.M = (int)M; p.N = 4 * CW; p.K0 = CW;
-    p.out0 = s.a; p.out1 = s.b; p.bias0 = in_bias ? pr.bias_cat : nullptr; p.aux = mask; p.plane = NN;
-    p.name = "tc_gemm_gate_in"; p.flops = 2.0 * M * CW * 4 * CW; p.bytes = 3.0 * unit;
-    TRI_TRY(launch_gemm(st, d->dtype, EPI_GATE_IN, 256, false, p, pr.err));
-  }
-  const bool incoming = d->direction == TRI_INCOMING;
-  TRI_TRY(contraction(st, d, s.a, incoming, s.b, incoming, s.t, pr.err, "tc_gemm_contract"));
-  {
-    KernelTimer kt("tc_ln_cm", st, 0.0, 2.0 * unit);
-    ln_cm_kernel<T><<<kPersist, 256, 0, st>>>((const T*)s.t, (const T*)w->norm_out_w, (const T*)w->norm_out_b, d->eps,
-                                              M, NN, (T*)s.u, s.mean_out, s.rstd_out);
-    TRI_LAUNCH_OK();
-  }
-  {
-    GemmPlan p;
-    p.a[0] = rows_operand(s.u, CW, M, false);
-    p.b[0] = rows_operand(w->p_out_w, CW, CW, false);
-    p.a[1] = rows_operand(s.z, CW, M, false);
-    p.b[1] = rows_operand(w->g_out_w, CW, CW, false);
-    p.M = (int)M; p.N = 2 * CW; p.K0 = CW; p.K1 = CW; p.seg1_col = CW;
-    p.out0 = out; p.bias0 = out_bias ? pr.bias_out : nullptr;
-    p.name = "tc_gemm_gate_out"; p.flops = 2.0 * M * CW * 2 * CW; p.bytes = 3.0 * unit;
-    TRI_TRY(launch_gemm(st, d->dtype, EPI_GATE_OUT, 256, false, p, pr.err));
-  }
-  return 0;
+  GemmPlan p;
+  p.a[0] = rows_operand(z, CW, M, false);
+  p.b[0] = rows_operand(pr.wcat, CW, 4 * CW, false);
+  p.M = (int)M; p.N = 4 * CW; p.K0 = CW;
+  p.out0 = a_cm; p.out1 = b_cm; p.bias0 = (w->p_in_b || w->g_in_b) ? pr.bias_cat : nullptr; p.aux = mask;
+  p.plane = gm.plane;
+  p.name = "tc_gemm_gate_in"; p.flops = 2.0 * M * CW * 4 * CW; p.bytes = 3.0 * gm.unit();
+  return launch_gemm(st, gm.dtype, EPI_GATE_IN, 256, false, p, pr.err);
 }
 
-int split_k_grad(cudaStream_t st, const TriMulDesc* d, const void* lhs, int lhs_w, const void* rhs, long long M,
-                 float* partial, int* err, const char* name, int* nparts) {
+// ---- phase 3: t -> u (LayerNorm over channels), out = (u Wo^T + bo) * sigmoid(z Wgo^T + bgo) --------------
+template <typename T>
+int phase_output(cudaStream_t st, const Geom& gm, const void* t_cm, const void* z, const TriMulWeights* w,
+                 const Prep& pr, void* u, float* mean_out, float* rstd_out, void* out) {
+  const long long M = gm.M;
+  {
+    KernelTimer kt("tc_ln_cm", st, 0.0, 2.0 * gm.unit());
+    ln_cm_kernel<T><<<kPersist, 256, 0, st>>>((const T*)t_cm, (const T*)w->norm_out_w, (const T*)w->norm_out_b, gm.eps,
+                                              M, gm.plane, (T*)u, mean_out, rstd_out);
+    TRI_LAUNCH_OK();
+  }
+  GemmPlan p;
+  p.a[0] = rows_operand(u, CW, M, false);
+  p.b[0] = rows_operand(w->p_out_w, CW, CW, false);
+  p.a[1] = rows_operand(z, CW, M, false);
+  p.b[1] = rows_operand(w->g_out_w, CW, CW, false);
+  p.M = (int)M; p.N = 2 * CW; p.K0 = CW; p.K1 = CW; p.seg1_col = CW;
+  p.out0 = out; p.bias0 = (w->p_out_b || w->g_out_b) ? pr.bias_out : nullptr;
+  p.name = "tc_gemm_gate_out"; p.flops = 2.0 * M * CW * 2 * CW; p.bytes = 3.0 * gm.unit();
+  return launch_gemm(st, gm.dtype, EPI_GATE_OUT, 256, false, p, pr.err);
+}
+
+int split_k_grad(cudaStream_t st, const Geom& gm, const void* lhs, int lhs_w, const void* rhs, float* partial,
+                 int* err, const char* name, int* nparts) {
   // partial[s][lhs_w][128] = sum over the rows of split s of lhs[row][:]^T rhs[row][:]
-  const int bke = d->dtype == TRI_F32 ? 32 : 64;
+  const long long M = gm.M;
+  const int bke = gm.dtype == TRI_F32 ? 32 : 64;
   int splits = (int)std::min<long long>(kSplitK, (M + bke - 1) / bke);
   long long kper = ((M + splits - 1) / splits + bke - 1) / bke * bke;
   splits = (int)((M + kper - 1) / kper);
@@ -428,9 +413,9 @@ int split_k_grad(cudaStream_t st, const TriMulDesc* d, const void* lhs, int lhs_
   p.b[0] = rows_operand(rhs, CW, M, true);
   p.M = lhs_w; p.N = CW; p.K0 = (int)kper; p.batches = splits; p.split_k = 1;
   p.out0 = partial; p.ld_out = CW; p.batch_out = (long long)lhs_w * CW;
-  p.name = name; p.flops = 2.0 * M * lhs_w * CW; p.bytes = (double)M * (lhs_w + CW) * es_of(d);
+  p.name = name; p.flops = 2.0 * M * lhs_w * CW; p.bytes = (double)M * (lhs_w + CW) * gm.es();
   *nparts = splits;
-  return launch_gemm(st, d->dtype, EPI_STORE, 128, true, p, err);
+  return launch_gemm(st, gm.dtype, EPI_STORE, 128, true, p, err);
 }
 
 int reduce_to(cudaStream_t st, const float* partial, int nparts, int n, float* out) {
@@ -450,129 +435,250 @@ int colsum_to(cudaStream_t st, const void* X, long long M, int W, float* partial
   return 0;
 }
 
+// ---- backward of phase 3: d_out -> dy, dgo, gradients of the output weights, dt (channel-major) ------------
 template <typename T>
-int backward_t(const TriMulDesc* d, const void* x, const void* mask, const TriMulWeights* w, const void* saved,
-               const void* d_out, void* dx, const TriMulWeightGrads* g, void* ws, size_t ws_size, cudaStream_t st) {
-  const long long M = (long long)d->B * d->N * d->N, NN = (long long)d->N * d->N;
-  const double unit = (double)M * CW * sizeof(T);
-  Arena a(ws, ws_size);
-  Prep pr;
-  carve_prep(a, d, &pr);
-  BwdBufs b;
-  carve_bwd(a, d, &b);
-  if (!a.ok()) return fail(TRI_ERR_WORKSPACE, "trimul backward workspace too small: need %zu, got %zu", a.off, ws_size);
-  SavedT s;
-  { Arena sa(const_cast<void*>(saved), mul_saved_bytes(d)); carve_saved(sa, d, &s); }
-  TRI_TRY(run_prep<T>(st, w, pr));
-  const bool in_bias = w->p_in_b || w->g_in_b, out_bias = w->p_out_b || w->g_out_b;
+int phase_output_bwd(cudaStream_t st, const Geom& gm, const void* d_out, const void* u, const void* z,
+                     const void* t_cm, const float* mean_out, const float* rstd_out, const TriMulWeights* w,
+                     const Prep& pr, const TriMulWeightGrads* g, void* dy, void* dgo, void* du, void* dt_cm,
+                     float* partial) {
+  const long long M = gm.M;
   int nparts = 0;
-
-  // output gate: dy = d_out * sig(go), dgo = d_out * y * sig * (1 - sig), with y and go recomputed
   {
-    GemmPlan p;
-    p.a[0] = rows_operand(s.u, CW, M, false);
+    GemmPlan p;   // dy = d_out * sig(go), dgo = d_out * y * sig * (1 - sig), with y and go recomputed
+    p.a[0] = rows_operand(u, CW, M, false);
     p.b[0] = rows_operand(w->p_out_w, CW, CW, false);
-    p.a[1] = rows_operand(s.z, CW, M, false);
+    p.a[1] = rows_operand(z, CW, M, false);
     p.b[1] = rows_operand(w->g_out_w, CW, CW, false);
     p.M = (int)M; p.N = 2 * CW; p.K0 = CW; p.K1 = CW; p.seg1_col = CW;
-    p.out0 = b.dy; p.out1 = b.dgo; p.aux = d_out; p.bias0 = out_bias ? pr.bias_out : nullptr;
-    p.name = "tc_gemm_gate_out_bwd"; p.flops = 0.0; p.bytes = 5.0 * unit;  // recompute: no algorithmic flops
-    TRI_TRY(launch_gemm(st, d->dtype, EPI_GATE_OUT_BWD, 256, false, p, pr.err));
+    p.out0 = dy; p.out1 = dgo; p.aux = d_out; p.bias0 = (w->p_out_b || w->g_out_b) ? pr.bias_out : nullptr;
+    p.name = "tc_gemm_gate_out_bwd"; p.flops = 0.0; p.bytes = 5.0 * gm.unit();  // recompute: no algorithmic flops
+    TRI_TRY(launch_gemm(st, gm.dtype, EPI_GATE_OUT_BWD, 256, false, p, pr.err));
   }
   if (g->p_out_w) {
-    TRI_TRY(split_k_grad(st, d, b.dy, CW, s.u, M, b.partial, pr.err, "tc_gemm_wgrad", &nparts));
-    TRI_TRY(reduce_to(st, b.partial, nparts, CW * CW, g->p_out_w));
+    TRI_TRY(split_k_grad(st, gm, dy, CW, u, partial, pr.err, "tc_gemm_wgrad", &nparts));
+    TRI_TRY(reduce_to(st, partial, nparts, CW * CW, g->p_out_w));
   }
   if (g->g_out_w) {
-    TRI_TRY(split_k_grad(st, d, b.dgo, CW, s.z, M, b.partial, pr.err, "tc_gemm_wgrad", &nparts));
-    TRI_TRY(reduce_to(st, b.partial, nparts, CW * CW, g->g_out_w));
+    TRI_TRY(split_k_grad(st, gm, dgo, CW, z, partial, pr.err, "tc_gemm_wgrad", &nparts));
+    TRI_TRY(reduce_to(st, partial, nparts, CW * CW, g->g_out_w));
   }
   if (g->p_out_b) {
-    TRI_TRY(colsum_to<T>(st, b.dy, M, CW, b.partial, &nparts));
-    TRI_TRY(reduce_to(st, b.partial, nparts, CW, g->p_out_b));
+    TRI_TRY(colsum_to<T>(st, dy, M, CW, partial, &nparts));
+    TRI_TRY(reduce_to(st, partial, nparts, CW, g->p_out_b));
   }
   if (g->g_out_b) {
-    TRI_TRY(colsum_to<T>(st, b.dgo, M, CW, b.partial, &nparts));
-    TRI_TRY(reduce_to(st, b.partial, nparts, CW, g->g_out_b));
+    TRI_TRY(colsum_to<T>(st, dgo, M, CW, partial, &nparts));
+    TRI_TRY(reduce_to(st, partial, nparts, CW, g->g_out_b));
   }
-  // du = dy Wo
   {
-    GemmPlan p;
-    p.a[0] = rows_operand(b.dy, CW, M, false);
+    GemmPlan p;   // du = dy Wo
+    p.a[0] = rows_operand(dy, CW, M, false);
     p.b[0] = rows_operand(w->p_out_w, CW, CW, true);  // B(n = ch, k = c) = Wo[c][ch]: n contiguous
-    p.M = (int)M; p.N = CW; p.K0 = CW; p.out0 = b.du; p.ld_out = CW;
-    p.name = "tc_gemm_du"; p.flops = 2.0 * M * CW * CW; p.bytes = 2.0 * unit;
-    TRI_TRY(launch_gemm(st, d->dtype, EPI_STORE, 128, false, p, pr.err));
+    p.M = (int)M; p.N = CW; p.K0 = CW; p.out0 = du; p.ld_out = CW;
+    p.name = "tc_gemm_du"; p.flops = 2.0 * M * CW * CW; p.bytes = 2.0 * gm.unit();
+    TRI_TRY(launch_gemm(st, gm.dtype, EPI_STORE, 128, false, p, pr.err));
   }
+  float* pg = partial;
+  float* pb = partial + (size_t)kPersist * CW;
   {
-    float* pg = b.partial;
-    float* pb = b.partial + (size_t)kPersist * CW;
-    {
-      KernelTimer kt("tc_ln_cm_bwd", st, 0.0, 3.0 * unit);
-      ln_cm_bwd_kernel<T><<<kPersist, 256, 0, st>>>((const T*)b.du, (const T*)s.t, s.mean_out, s.rstd_out,
-                                                    (const T*)w->norm_out_w, M, NN, (T*)b.dt, pg, pb);
-      TRI_LAUNCH_OK();
-    }
-    if (g->norm_out_w) TRI_TRY(reduce_to(st, pg, kPersist, CW, g->norm_out_w));
-    if (g->norm_out_b) TRI_TRY(reduce_to(st, pb, kPersist, CW, g->norm_out_b));
+    KernelTimer kt("tc_ln_cm_bwd", st, 0.0, 3.0 * gm.unit());
+    ln_cm_bwd_kernel<T><<<kPersist, 256, 0, st>>>((const T*)du, (const T*)t_cm, mean_out, rstd_out,
+                                                  (const T*)w->norm_out_w, M, gm.plane, (T*)dt_cm, pg, pb);
+    TRI_LAUNCH_OK();
   }
-  // contraction backward (operand majors per direction; see the header comment)
-  if (d->direction == TRI_OUTGOING) {
-    TRI_TRY(contraction(st, d, b.dt, false, s.b, true, b.da, pr.err, "tc_gemm_contract_bwd"));  // da[i,k] = sum_j dt[i,j] b[j,k]
-    TRI_TRY(contraction(st, d, b.dt, true, s.a, true, b.db, pr.err, "tc_gemm_contract_bwd"));   // db[j,k] = sum_i dt[i,j] a[i,k]
-  } else {
-    TRI_TRY(contraction(st, d, s.b, false, b.dt, false, b.da, pr.err, "tc_gemm_contract_bwd")); // da[k,i] = sum_j b[k,j] dt[i,j]
-    TRI_TRY(contraction(st, d, s.a, false, b.dt, true, b.db, pr.err, "tc_gemm_contract_bwd"));  // db[k,j] = sum_i a[k,i] dt[i,j]
-  }
-  // input gate backward fused into the recomputed projection GEMM
+  if (g->norm_out_w) TRI_TRY(reduce_to(st, pg, kPersist, CW, g->norm_out_w));
+  if (g->norm_out_b) TRI_TRY(reduce_to(st, pb, kPersist, CW, g->norm_out_b));
+  return 0;
+}
+
+// ---- backward of phase 1: da, db (channel-major), dgo -> gradients of the input weights, dx ---------------
+template <typename T>
+int phase_project_bwd(cudaStream_t st, const Geom& gm, const void* x, const void* mask, const void* z,
+                      const void* da_cm, const void* db_cm, const void* dgo, const float* mean_in,
+                      const float* rstd_in, const TriMulWeights* w, const Prep& pr, const TriMulWeightGrads* g,
+                      void* dpg, void* dz, void* dx, float* partial) {
+  const long long M = gm.M;
+  int nparts = 0;
   {
-    GemmPlan p;
-    p.a[0] = rows_operand(s.z, CW, M, false);
+    GemmPlan p;   // input gate backward fused into the recomputed projection GEMM
+    p.a[0] = rows_operand(z, CW, M, false);
     p.b[0] = rows_operand(pr.wcat, CW, 4 * CW, false);
     p.M = (int)M; p.N = 4 * CW; p.K0 = CW;
-    p.out0 = b.dpg; p.ld_out = 4 * CW; p.bias0 = in_bias ? pr.bias_cat : nullptr;
-    p.aux = mask; p.aux2 = b.da; p.aux3 = b.db; p.plane = NN;
-    p.name = "tc_gemm_gate_in_bwd"; p.flops = 0.0; p.bytes = 7.0 * unit;
-    TRI_TRY(launch_gemm(st, d->dtype, EPI_GATE_IN_BWD, 256, false, p, pr.err));
+    p.out0 = dpg; p.ld_out = 4 * CW; p.bias0 = (w->p_in_b || w->g_in_b) ? pr.bias_cat : nullptr;
+    p.aux = mask; p.aux2 = da_cm; p.aux3 = db_cm; p.plane = gm.plane;
+    p.name = "tc_gemm_gate_in_bwd"; p.flops = 0.0; p.bytes = 7.0 * gm.unit();
+    TRI_TRY(launch_gemm(st, gm.dtype, EPI_GATE_IN_BWD, 256, false, p, pr.err));
   }
   if (g->p_in_w || g->g_in_w) {
-    TRI_TRY(split_k_grad(st, d, b.dpg, 4 * CW, s.z, M, b.partial, pr.err, "tc_gemm_wgrad", &nparts));
+    TRI_TRY(split_k_grad(st, gm, dpg, 4 * CW, z, partial, pr.err, "tc_gemm_wgrad", &nparts));
     KernelTimer kt("tc_reduce", st, 0.0, 4.0 * (nparts + 1) * 4 * CW * CW);
-    reduce_wcat_kernel<<<cdiv(4 * CW * CW, 256), 256, 0, st>>>(b.partial, nparts, CW, g->p_in_w, g->g_in_w);
+    reduce_wcat_kernel<<<cdiv(4 * CW * CW, 256), 256, 0, st>>>(partial, nparts, CW, g->p_in_w, g->g_in_w);
     TRI_LAUNCH_OK();
   }
   if (g->p_in_b || g->g_in_b) {
-    TRI_TRY(colsum_to<T>(st, b.dpg, M, 4 * CW, b.partial, &nparts));
+    TRI_TRY(colsum_to<T>(st, dpg, M, 4 * CW, partial, &nparts));
     KernelTimer kt("tc_reduce", st, 0.0, 4.0 * (nparts + 1) * 4 * CW);
-    reduce_wcat_kernel<<<cdiv(4 * CW, 256), 256, 0, st>>>(b.partial, nparts, 1, g->p_in_b, g->g_in_b);
+    reduce_wcat_kernel<<<cdiv(4 * CW, 256), 256, 0, st>>>(partial, nparts, 1, g->p_in_b, g->g_in_b);
     TRI_LAUNCH_OK();
   }
-  // dz = dPG Wcat + dgo Wgo
   {
-    GemmPlan p;
-    p.a[0] = rows_operand(b.dpg, 4 * CW, M, false);
+    GemmPlan p;   // dz = dPG Wcat + dgo Wgo
+    p.a[0] = rows_operand(dpg, 4 * CW, M, false);
     p.b[0] = rows_operand(pr.wcat, CW, 4 * CW, true);   // B(n = c, k = row of Wcat): n contiguous
-    p.a[1] = rows_operand(b.dgo, CW, M, false);
+    p.a[1] = rows_operand(dgo, CW, M, false);
     p.b[1] = rows_operand(w->g_out_w, CW, CW, true);
     p.M = (int)M; p.N = CW; p.K0 = 4 * CW; p.K1 = CW; p.seg1_col = 0;
-    p.out0 = b.dz; p.ld_out = CW;
-    p.name = "tc_gemm_dz"; p.flops = 2.0 * M * CW * 5 * CW; p.bytes = 6.0 * unit;
-    TRI_TRY(launch_gemm(st, d->dtype, EPI_STORE, 128, false, p, pr.err));
+    p.out0 = dz; p.ld_out = CW;
+    p.name = "tc_gemm_dz"; p.flops = 2.0 * M * CW * 5 * CW; p.bytes = 6.0 * gm.unit();
+    TRI_TRY(launch_gemm(st, gm.dtype, EPI_STORE, 128, false, p, pr.err));
   }
+  const int blocks = (int)std::min<long long>(kPersist, (M + 7) / 8);
+  float* pg = partial;
+  float* pb = partial + (size_t)kPersist * CW;
   {
-    const int blocks = (int)std::min<long long>(kPersist, (M + 7) / 8);
-    float* pg = b.partial;
-    float* pb = b.partial + (size_t)kPersist * CW;
-    {
-      KernelTimer kt("tc_ln_rows_bwd", st, 0.0, 3.0 * unit);
-      ln_rows_bwd_kernel<T><<<blocks, 256, 0, st>>>((const T*)b.dz, (const T*)x, s.mean_in, s.rstd_in,
-                                                    (const T*)w->norm_in_w, M, (T*)dx, pg, pb);
-      TRI_LAUNCH_OK();
-    }
-    if (g->norm_in_w) TRI_TRY(reduce_to(st, pg, blocks, CW, g->norm_in_w));
-    if (g->norm_in_b) TRI_TRY(reduce_to(st, pb, blocks, CW, g->norm_in_b));
+    KernelTimer kt("tc_ln_rows_bwd", st, 0.0, 3.0 * gm.unit());
+    ln_rows_bwd_kernel<T><<<blocks, 256, 0, st>>>((const T*)dz, (const T*)x, mean_in, rstd_in, (const T*)w->norm_in_w,
+                                                  M, (T*)dx, pg, pb);
+    TRI_LAUNCH_OK();
   }
+  if (g->norm_in_w) TRI_TRY(reduce_to(st, pg, blocks, CW, g->norm_in_w));
+  if (g->norm_in_b) TRI_TRY(reduce_to(st, pb, blocks, CW, g->norm_in_b));
   return 0;
+}
+
+// ---------------------------------------------------------------------------------------------
+// single-GPU op: memory plan and drivers
+// ---------------------------------------------------------------------------------------------
+struct SavedT { void *z, *a, *b, *t, *u; float *mean_in, *rstd_in, *mean_out, *rstd_out; };
+
+Geom geom_of(const TriMulDesc* d) {
+  Geom g;
+  g.dtype = d->dtype; g.eps = d->eps;
+  g.plane = (long long)d->N * d->N; g.M = g.plane * d->B;
+  return g;
+}
+
+void carve_saved(Arena& a, const Geom& gm, SavedT* s) {
+  const size_t M = (size_t)gm.M, unit = M * CW * gm.es();
+  s->z = a.take<char>(unit); s->a = a.take<char>(unit); s->b = a.take<char>(unit);
+  s->t = a.take<char>(unit); s->u = a.take<char>(unit);
+  s->mean_in = a.take<float>(M); s->rstd_in = a.take<float>(M);
+  s->mean_out = a.take<float>(M); s->rstd_out = a.take<float>(M);
+}
+
+struct BwdBufs { void *dy, *dgo, *du, *dt, *da, *db, *dpg, *dz; float* partial; };
+void carve_bwd(Arena& a, const Geom& gm, BwdBufs* w) {
+  const size_t unit = (size_t)gm.M * CW * gm.es();
+  w->dy = a.take<char>(unit); w->dgo = a.take<char>(unit); w->du = a.take<char>(unit);
+  w->dt = a.take<char>(unit); w->da = a.take<char>(unit); w->db = a.take<char>(unit);
+  w->dpg = a.take<char>(4 * unit); w->dz = a.take<char>(unit);
+  w->partial = a.take<float>(partial_floats());
+}
+
+template <typename T>
+int forward_t(const TriMulDesc* d, const void* x, const void* mask, const TriMulWeights* w, void* out, void* saved,
+              void* ws, size_t ws_size, cudaStream_t st) {
+  const Geom gm = geom_of(d);
+  Arena a(ws, ws_size);
+  Prep pr;
+  carve_prep(a, gm.es(), &pr);
+  SavedT s;
+  if (saved) { Arena sa(saved, mul_saved_bytes(d)); carve_saved(sa, gm, &s); }
+  else carve_saved(a, gm, &s);
+  if (!a.ok()) return fail(TRI_ERR_WORKSPACE, "trimul forward workspace too small: need %zu, got %zu", a.off, ws_size);
+  TRI_TRY(run_prep<T>(st, w, pr));
+  TRI_TRY(phase_project<T>(st, gm, x, mask, w, pr, s.z, s.mean_in, s.rstd_in, s.a, s.b));
+  const bool incoming = d->direction == TRI_INCOMING;
+  TRI_TRY(contraction(st, d->dtype, d->B * CW, d->N, s.a, incoming, s.b, incoming, s.t, pr.err, "tc_gemm_contract"));
+  return phase_output<T>(st, gm, s.t, s.z, w, pr, s.u, s.mean_out, s.rstd_out, out);
+}
+
+template <typename T>
+int backward_t(const TriMulDesc* d, const void* x, const void* mask, const TriMulWeights* w, const void* saved,
+               const void* d_out, void* dx, const TriMulWeightGrads* g, void* ws, size_t ws_size, cudaStream_t st) {
+  const Geom gm = geom_of(d);
+  Arena a(ws, ws_size);
+  Prep pr;
+  carve_prep(a, gm.es(), &pr);
+  BwdBufs b;
+  carve_bwd(a, gm, &b);
+  if (!a.ok()) return fail(TRI_ERR_WORKSPACE, "trimul backward workspace too small: need %zu, got %zu", a.off, ws_size);
+  SavedT s;
+  { Arena sa(const_cast<void*>(saved), mul_saved_bytes(d)); carve_saved(sa, gm, &s); }
+  TRI_TRY(run_prep<T>(st, w, pr));
+  TRI_TRY(phase_output_bwd<T>(st, gm, d_out, s.u, s.z, s.t, s.mean_out, s.rstd_out, w, pr, g, b.dy, b.dgo, b.du, b.dt,
+                              b.partial));
+  // contraction backward: the same batched GEMM, only the operand majors change
+  const int planes = d->B * CW, n = d->N, dt = d->dtype;
+  if (d->direction == TRI_OUTGOING) {
+    TRI_TRY(contraction(st, dt, planes, n, b.dt, false, s.b, true, b.da, pr.err, "tc_gemm_contract_bwd"));  // da[i,k] = sum_j dt[i,j] b[j,k]
+    TRI_TRY(contraction(st, dt, planes, n, b.dt, true, s.a, true, b.db, pr.err, "tc_gemm_contract_bwd"));   // db[j,k] = sum_i dt[i,j] a[i,k]
+  } else {
+    TRI_TRY(contraction(st, dt, planes, n, s.b, false, b.dt, false, b.da, pr.err, "tc_gemm_contract_bwd")); // da[k,i] = sum_j b[k,j] dt[i,j]
+    TRI_TRY(contraction(st, dt, planes, n, s.a, false, b.dt, true, b.db, pr.err, "tc_gemm_contract_bwd"));  // db[k,j] = sum_i a[k,i] dt[i,j]
+  }
+  return phase_project_bwd<T>(st, gm, x, mask, s.z, b.da, b.db, b.dgo, s.mean_in, s.rstd_in, w, pr, g, b.dpg, b.dz, dx,
+                              b.partial);
+}
+
+// ---------------------------------------------------------------------------------------------
+// row-sharded op: the four pixel-wise phases on their own (the contraction runs through tri_bgemm)
+// ---------------------------------------------------------------------------------------------
+struct ShardSaved { void *z, *u, *dgo; float *mean_in, *rstd_in, *mean_out, *rstd_out; };
+
+Geom geom_of(const TriMulShardDesc* d) {
+  Geom g;
+  g.dtype = d->dtype; g.eps = d->eps;
+  g.plane = (long long)d->rows * d->N; g.M = g.plane * d->B;
+  return g;
+}
+
+void carve_shard_saved(Arena& a, const Geom& gm, ShardSaved* s) {
+  const size_t M = (size_t)gm.M, unit = M * CW * gm.es();
+  s->z = a.take<char>(unit); s->u = a.take<char>(unit); s->dgo = a.take<char>(unit);
+  s->mean_in = a.take<float>(M); s->rstd_in = a.take<float>(M);
+  s->mean_out = a.take<float>(M); s->rstd_out = a.take<float>(M);
+}
+
+struct ShardWs { void *dy, *du, *dpg, *dz; float* partial; };
+void carve_shard_ws(Arena& a, const Geom& gm, int phase, ShardWs* w) {
+  const size_t unit = (size_t)gm.M * CW * gm.es();
+  *w = ShardWs{};
+  if (phase == TRI_PHASE_OUTPUT_BWD) { w->dy = a.take<char>(unit); w->du = a.take<char>(unit); }
+  if (phase == TRI_PHASE_PROJECT_BWD) { w->dpg = a.take<char>(4 * unit); w->dz = a.take<char>(unit); }
+  if (phase >= TRI_PHASE_OUTPUT_BWD) w->partial = a.take<float>(partial_floats());
+}
+
+template <typename T>
+int shard_phase_t(const TriMulShardDesc* d, int phase, const TriMulShardBufs* bf, void* ws, size_t ws_size,
+                  cudaStream_t st) {
+  const Geom gm = geom_of(d);
+  Arena a(ws, ws_size);
+  Prep pr;
+  carve_prep(a, gm.es(), &pr);
+  ShardWs sw;
+  carve_shard_ws(a, gm, phase, &sw);
+  if (!a.ok()) return fail(TRI_ERR_WORKSPACE, "trimul shard workspace too small: need %zu, got %zu", a.off, ws_size);
+  ShardSaved s;
+  { Arena sa(bf->saved, mul_shard_saved_bytes(d)); carve_shard_saved(sa, gm, &s); }
+  TRI_TRY(run_prep<T>(st, bf->w, pr));
+  switch (phase) {
+    case TRI_PHASE_PROJECT:
+      if (!bf->x || !bf->a_cm || !bf->b_cm) return fail(TRI_ERR_ARG, "project phase needs x, a_cm, b_cm");
+      return phase_project<T>(st, gm, bf->x, bf->mask, bf->w, pr, s.z, s.mean_in, s.rstd_in, bf->a_cm, bf->b_cm);
+    case TRI_PHASE_OUTPUT:
+      if (!bf->t_cm || !bf->out) return fail(TRI_ERR_ARG, "output phase needs t_cm, out");
+      return phase_output<T>(st, gm, bf->t_cm, s.z, bf->w, pr, s.u, s.mean_out, s.rstd_out, bf->out);
+    case TRI_PHASE_OUTPUT_BWD:
+      if (!bf->d_out || !bf->t_cm || !bf->dt_cm || !bf->g) return fail(TRI_ERR_ARG, "output backward needs d_out, t_cm, dt_cm, g");
+      return phase_output_bwd<T>(st, gm, bf->d_out, s.u, s.z, bf->t_cm, s.mean_out, s.rstd_out, bf->w, pr, bf->g, sw.dy,
+                                 s.dgo, sw.du, bf->dt_cm, sw.partial);
+    case TRI_PHASE_PROJECT_BWD:
+      if (!bf->x || !bf->a_cm || !bf->b_cm || !bf->dx || !bf->g) return fail(TRI_ERR_ARG, "project backward needs x, a_cm, b_cm (gradients), dx, g");
+      return phase_project_bwd<T>(st, gm, bf->x, bf->mask, s.z, bf->a_cm, bf->b_cm, s.dgo, s.mean_in, s.rstd_in, bf->w,
+                                  pr, bf->g, sw.dpg, sw.dz, bf->dx, sw.partial);
+  }
+  return fail(TRI_ERR_ARG, "bad phase %d", phase);
 }
 
 bool forced_simt() {
@@ -593,17 +699,51 @@ bool mul_supported(const TriMulDesc* d) {
 size_t mul_saved_bytes(const TriMulDesc* d) {
   Arena a(nullptr, 0);
   SavedT s;
-  carve_saved(a, d, &s);
+  carve_saved(a, geom_of(d), &s);
   return a.off;
 }
 
 size_t mul_ws_bytes(const TriMulDesc* d, int is_bwd) {
   Arena a(nullptr, 0);
   Prep p;
-  carve_prep(a, d, &p);
-  if (is_bwd) { BwdBufs b; carve_bwd(a, d, &b); }
-  else { SavedT s; carve_saved(a, d, &s); }
+  const Geom gm = geom_of(d);
+  carve_prep(a, gm.es(), &p);
+  if (is_bwd) { BwdBufs b; carve_bwd(a, gm, &b); }
+  else { SavedT s; carve_saved(a, gm, &s); }
   return a.off + 256;
+}
+
+bool mul_shard_supported(const TriMulShardDesc* d) {
+  if (d->C != CW || d->Ch != CW) return false;
+  if (d->dtype == TRI_F32 && d->precision != TRI_PREC_TF32) return false;
+  return d->N % 8 == 0 && d->rows > 0 && d->rows <= d->N;
+}
+
+size_t mul_shard_saved_bytes(const TriMulShardDesc* d) {
+  Arena a(nullptr, 0);
+  ShardSaved s;
+  carve_shard_saved(a, geom_of(d), &s);
+  return a.off;
+}
+
+size_t mul_shard_ws_bytes(const TriMulShardDesc* d, int phase) {
+  Arena a(nullptr, 0);
+  Prep p;
+  const Geom gm = geom_of(d);
+  carve_prep(a, gm.es(), &p);
+  ShardWs w;
+  carve_shard_ws(a, gm, phase, &w);
+  return a.off + 256;
+}
+
+int mul_shard_phase(const TriMulShardDesc* d, int phase, const TriMulShardBufs* bf, void* ws, size_t ws_size,
+                    cudaStream_t st) {
+  switch (d->dtype) {
+    case TRI_F32: return shard_phase_t<float>(d, phase, bf, ws, ws_size, st);
+    case TRI_BF16: return shard_phase_t<__nv_bfloat16>(d, phase, bf, ws, ws_size, st);
+    case TRI_F16: return shard_phase_t<__half>(d, phase, bf, ws, ws_size, st);
+  }
+  return fail(TRI_ERR_ARG, "bad dtype %d", d->dtype);
 }
 
 int mul_forward(const TriMulDesc* d, const void* x, const void* mask, const TriMulWeights* w, void* out, void* saved,

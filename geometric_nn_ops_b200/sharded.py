@@ -1,0 +1,279 @@
+"""Row-sharded (multi-GPU) forms of the two triangle ops: one process per GPU, NCCL for the exchanges.
+
+The pair representation ``[B, N, N, C]`` is sharded over its first pair axis: rank ``r`` of ``P`` holds rows
+``[r*N/P, (r+1)*N/P)``.  The reference is single-device; these wrappers are new.
+
+* Triangle attention around the starting node attends along the second axis for a fixed row, so it is
+  local; only the pair bias has to be whole on every rank and its gradient (a sum over rows) is
+  all-reduced.  The ending-node variant is the same op on the transposed pair tensor:
+  :func:`all_to_all_transpose` does that transpose with one all-to-all.
+* The triangle multiplicative update is pixel-wise except for the contraction, and the contraction is
+  independent per channel.  So the projected operands go from row shards to channel shards with one
+  all-to-all, each rank contracts its ``C/P`` channels over the full ``N x N`` planes (either direction, it
+  is only an operand-major flag), and the result returns to row shards with a second all-to-all.  Per
+  rank that moves ``3/P`` of a pair-sized tensor per forward, against ``(P-1)/P`` for all-gathering ``b``.
+  Weight gradients are partial sums per rank and are all-reduced.
+
+Every tensor handed to a collective lives in this GPU's memory; the kernels never read a peer's memory.
+"""
+
+import ctypes
+
+import torch
+import torch.distributed as dist
+
+from . import _lib, _precision
+from .gemm import bgemm
+from .triangle._triattn import triangle_attention
+from .triangle._trimul import _DTYPES, _aligned, is_outgoing
+
+
+def _world(group):
+    return dist.get_world_size(group), dist.get_rank(group)
+
+
+def shard_rows(n, rank, world):
+    """Row range ``[i0, i1)`` of rank ``rank`` when ``n`` rows are split evenly over ``world`` ranks."""
+    if n % world != 0:
+        raise ValueError(f"N={n} is not divisible by the number of ranks {world}")
+    r = n // world
+    return rank * r, (rank + 1) * r
+
+
+# ---------------------------------------------------------------------------------------------------
+# exchanges (plain torch + one collective each; differentiable where a caller needs it)
+# ---------------------------------------------------------------------------------------------------
+def rows_to_channels(t, group=None):
+    """``[L, Ch, R, N]`` (all channels, this rank's R rows) -> ``[L, Ch/P, P*R, N]`` (this rank's channels, all rows)."""
+    world, _ = _world(group)
+    L, Ch, R, N = t.shape
+    if Ch % world != 0:
+        raise ValueError(f"{Ch} channels are not divisible by {world} ranks")
+    cs = Ch // world
+    send = t.reshape(L, world, cs, R * N).permute(1, 0, 2, 3).contiguous()
+    recv = torch.empty_like(send)
+    dist.all_to_all_single(recv, send, group=group)
+    return recv.reshape(world, L, cs, R, N).permute(1, 2, 0, 3, 4).reshape(L, cs, world * R, N)
+
+
+def channels_to_rows(t, group=None):
+    """Inverse of :func:`rows_to_channels`: ``[L, Ch/P, N_rows, N]`` -> ``[L, Ch, N_rows/P, N]``."""
+    world, _ = _world(group)
+    L, cs, rows, N = t.shape
+    if rows % world != 0:
+        raise ValueError(f"{rows} rows are not divisible by {world} ranks")
+    R = rows // world
+    send = t.reshape(L, cs, world, R * N).permute(2, 0, 1, 3).contiguous()
+    recv = torch.empty_like(send)
+    dist.all_to_all_single(recv, send, group=group)
+    return recv.permute(1, 0, 2, 3).reshape(L, world * cs, R, N)
+
+
+class _Transpose(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, x, group):
+        ctx.group = group
+        return _transpose_impl(x, group)
+
+    @staticmethod
+    def backward(ctx, g):
+        return _transpose_impl(g.contiguous(), ctx.group), None
+
+
+def _transpose_impl(x, group):
+    world, _ = _world(group)
+    B, R, N = x.shape[0], x.shape[1], x.shape[2]
+    tail = x.shape[3:]
+    if N != R * world:
+        raise ValueError(f"expected [B, N/P, N, ...] with N = {R * world}, got {tuple(x.shape)}")
+    # chunk s of the column axis goes to rank s
+    send = x.reshape(B, R, world, R, *tail).movedim(2, 0).contiguous()    # [P, B, R(i), R(j), ...]
+    recv = torch.empty_like(send)
+    dist.all_to_all_single(recv, send, group=group)
+    # recv[s] = x[i in shard s, j in my shard]  ->  out[j, i]
+    return recv.movedim(0, 1).reshape(B, world * R, R, *tail).transpose(1, 2).contiguous()
+
+
+def all_to_all_transpose(x, group=None):
+    """Transpose the two pair axes of a row-sharded tensor ``[B, N/P, N, ...]``: the result is the shard
+    ``[B, N/P, N, ...]`` of ``x^T``.  One all-to-all; differentiable (it is its own inverse)."""
+    return _Transpose.apply(x, group)
+
+
+class _SumGradOverRanks(torch.autograd.Function):
+    """Identity whose gradient is all-reduced: for tensors replicated on every rank (the pair bias)."""
+
+    @staticmethod
+    def forward(ctx, t, group):
+        ctx.group = group
+        return t.view_as(t)
+
+    @staticmethod
+    def backward(ctx, g):
+        g = g.contiguous()
+        dist.all_reduce(g, op=dist.ReduceOp.SUM, group=ctx.group)
+        return g, None
+
+
+def sharded_triangle_attention(q, k, v, bias=None, mask=None, scale=None, group=None):
+    """Triangle attention on this rank's rows.  ``q, k, v``: ``[B, N/P, N, H, D]``; ``bias``: the whole
+    ``[B, 1, H, N, N]`` on every rank (its gradient is summed over ranks); ``mask``: this rank's rows."""
+    if bias is not None and bias.requires_grad:
+        bias = _SumGradOverRanks.apply(bias, group)
+    return triangle_attention(q, k, v, bias, mask, scale)
+
+
+# ---------------------------------------------------------------------------------------------------
+# triangle multiplicative update
+# ---------------------------------------------------------------------------------------------------
+def _ptr(t):
+    return None if t is None else ctypes.c_void_p(t.data_ptr())
+
+
+def _phase(lib, desc, phase, bufs, device):
+    ws_bytes = lib.tri_mul_shard_ws_bytes(ctypes.byref(desc), phase)
+    ws = torch.empty(max(ws_bytes, 1), dtype=torch.uint8, device=device)
+    stream = ctypes.c_void_p(torch.cuda.current_stream(device).cuda_stream)
+    with torch.cuda.device(device):
+        _lib.check(lib.tri_mul_shard_phase(ctypes.byref(desc), phase, ctypes.byref(bufs), _ptr(ws), ws_bytes, stream),
+                   "tri_mul_shard_phase")
+        _lib.check_device_status(ws, stream)
+
+
+class _ShardedTriMul(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, x, mask, outgoing, eps, group, *weights):
+        lib = _lib.load()
+        if not x.is_cuda:
+            raise RuntimeError("sharded trimul needs CUDA tensors: there is no CPU implementation")
+        named = dict(zip(_lib.WEIGHT_NAMES, weights))
+        B, R, N, C = x.shape
+        xc = _aligned(x)
+        mc = None if mask is None else _aligned(mask.to(x.dtype).broadcast_to(x.shape[:-1]))
+        wc = {n: (None if t is None else _aligned(t.detach().to(x.dtype))) for n, t in named.items()}
+        Ch = wc["p_in_weight"].shape[0] // 2
+        d = _lib.TriMulShardDesc()
+        d.B, d.rows, d.N, d.C, d.Ch = B, R, N, C, Ch
+        d.dtype = _DTYPES[x.dtype]
+        precision = _precision.matmul_precision(fp32_operands=x.dtype == torch.float32)
+        d.precision = _lib.PREC_TF32 if precision == _precision.TF32 else _lib.PREC_IEEE
+        d.eps = eps
+        nbytes = lib.tri_mul_shard_saved_bytes(ctypes.byref(d))
+        if nbytes == 0:
+            raise RuntimeError("sharded trimul: " + lib.tri_last_error().decode())
+        saved = torch.empty(nbytes, dtype=torch.uint8, device=x.device)
+        w = _lib.TriMulWeights()
+        for n, t in wc.items():
+            setattr(w, _lib.abi_field(n), None if t is None else t.data_ptr())
+
+        ab = torch.empty(2, B, Ch, R, N, dtype=x.dtype, device=x.device)
+        bufs = _lib.TriMulShardBufs()
+        bufs.x, bufs.mask, bufs.w, bufs.saved = xc.data_ptr(), None if mc is None else mc.data_ptr(), ctypes.pointer(w), saved.data_ptr()
+        bufs.a_cm, bufs.b_cm = ab[0].data_ptr(), ab[1].data_ptr()
+        _phase(lib, d, _lib.PHASE_PROJECT, bufs, x.device)
+        ab_ch = rows_to_channels(ab.reshape(2 * B, Ch, R, N), group)          # [2B, Cs, N, N]
+        cs = ab_ch.shape[1]
+        a_ch = ab_ch[:B].reshape(B * cs, N, N)
+        b_ch = ab_ch[B:].reshape(B * cs, N, N)
+        inc = not outgoing
+        t_ch = bgemm(a_ch, b_ch, a_mn_major=inc, b_mn_major=inc)              # [B*Cs, N, N]
+        t_loc = channels_to_rows(t_ch.reshape(B, cs, N, N), group)            # [B, Ch, R, N]
+        out = torch.empty_like(xc)
+        bufs.t_cm, bufs.out = t_loc.data_ptr(), out.data_ptr()
+        _phase(lib, d, _lib.PHASE_OUTPUT, bufs, x.device)
+
+        ctx.save_for_backward(xc, mc, saved, a_ch, b_ch, t_loc, *[t for t in wc.values() if t is not None])
+        ctx.present = [t is not None for t in wc.values()]
+        ctx.desc, ctx.group, ctx.outgoing = d, group, outgoing
+        ctx.weight_dtypes = [None if t is None else t.dtype for t in weights]
+        return out
+
+    @staticmethod
+    def backward(ctx, d_out):
+        lib = _lib.load()
+        xc, mc, saved, a_ch, b_ch, t_loc, *present_w = ctx.saved_tensors
+        it = iter(present_w)
+        wc = {n: (next(it) if has else None) for n, has in zip(_lib.WEIGHT_NAMES, ctx.present)}
+        d, group = ctx.desc, ctx.group
+        B, R, N, Ch = d.B, d.rows, d.N, d.Ch
+        dev = xc.device
+        w = _lib.TriMulWeights()
+        g = _lib.TriMulWeightGrads()
+        names = [n for n, t in wc.items() if t is not None]
+        sizes = [wc[n].numel() for n in names]
+        flat = torch.zeros(sum(sizes), dtype=torch.float32, device=dev)        # one buffer -> one all-reduce
+        grads, off = {}, 0
+        for n, sz in zip(names, sizes):
+            grads[n] = flat[off:off + sz].view(wc[n].shape)
+            off += sz
+        for n, t in wc.items():
+            setattr(w, _lib.abi_field(n), None if t is None else t.data_ptr())
+            if t is not None:
+                setattr(g, _lib.abi_field(n), grads[n].data_ptr())
+        dc = _aligned(d_out.to(xc.dtype))
+        dt_loc = torch.empty_like(t_loc)
+        bufs = _lib.TriMulShardBufs()
+        bufs.x, bufs.mask, bufs.w, bufs.saved = xc.data_ptr(), None if mc is None else mc.data_ptr(), ctypes.pointer(w), saved.data_ptr()
+        bufs.g = ctypes.pointer(g)
+        bufs.d_out, bufs.t_cm, bufs.dt_cm = dc.data_ptr(), t_loc.data_ptr(), dt_loc.data_ptr()
+        _phase(lib, d, _lib.PHASE_OUTPUT_BWD, bufs, dev)
+        dt_ch = rows_to_channels(dt_loc, group)
+        cs = dt_ch.shape[1]
+        dt_ch = dt_ch.reshape(B * cs, N, N)
+        if ctx.outgoing:   # da[i,k] = sum_j dt[i,j] b[j,k];  db[j,k] = sum_i dt[i,j] a[i,k]
+            da = bgemm(dt_ch, b_ch, a_mn_major=False, b_mn_major=True)
+            db = bgemm(dt_ch, a_ch, a_mn_major=True, b_mn_major=True)
+        else:              # da[k,i] = sum_j b[k,j] dt[i,j];  db[k,j] = sum_i a[k,i] dt[i,j]
+            da = bgemm(b_ch, dt_ch, a_mn_major=False, b_mn_major=False)
+            db = bgemm(a_ch, dt_ch, a_mn_major=False, b_mn_major=True)
+        dab = channels_to_rows(torch.stack([da.reshape(B, cs, N, N), db.reshape(B, cs, N, N)]).reshape(2 * B, cs, N, N),
+                               group).reshape(2, B, Ch, R, N)
+        dx = torch.empty_like(xc)
+        bufs.a_cm, bufs.b_cm, bufs.dx = dab[0].data_ptr(), dab[1].data_ptr(), dx.data_ptr()
+        _phase(lib, d, _lib.PHASE_PROJECT_BWD, bufs, dev)
+        dist.all_reduce(flat, op=dist.ReduceOp.SUM, group=group)
+        out = [dx if ctx.needs_input_grad[0] else None, None, None, None, None]
+        for i, (n, dt) in enumerate(zip(_lib.WEIGHT_NAMES, ctx.weight_dtypes)):
+            out.append(grads[n].to(dt) if n in grads and ctx.needs_input_grad[5 + i] else None)
+        return tuple(out)
+
+
+def sharded_triangle_multiplicative_update(x, direction="outgoing", mask=None, *, eps=1e-5, group=None,
+                                           norm_in_weight=None, norm_in_bias=None, p_in_weight=None, p_in_bias=None,
+                                           g_in_weight=None, g_in_bias=None, norm_out_weight=None,
+                                           norm_out_bias=None, p_out_weight=None, p_out_bias=None,
+                                           g_out_weight=None, g_out_bias=None):
+    """Triangle multiplicative update on a row shard.  ``x``: ``[B, N/P, N, C]`` (this rank's rows of the pair
+    tensor), ``mask``: ``[B, N/P, N]``; weights replicated.  Returns this rank's rows of the result; weight
+    gradients come back already summed over ranks.  Needs C = C_hidden = 128 (the tensor-core kernels)."""
+    outgoing = is_outgoing(direction)
+    world, _ = _world(group)
+    if x.dim() != 4 or x.shape[2] != x.shape[1] * world:
+        raise ValueError(f"x must be [B, N/P, N, C] with P = {world}, got {tuple(x.shape)}")
+    return _ShardedTriMul.apply(x, mask, outgoing, float(eps), group, norm_in_weight, norm_in_bias, p_in_weight,
+                                p_in_bias, g_in_weight, g_in_bias, norm_out_weight, norm_out_bias, p_out_weight,
+                                p_out_bias, g_out_weight, g_out_bias)
+
+
+# ---------------------------------------------------------------------------------------------------
+# benchmark step (used by bench.py --gpus N)
+# ---------------------------------------------------------------------------------------------------
+def make_bench_step(n, rank, world, host_inputs):
+    """One forward+backward of the three ops on this rank's row shard of the N-sized problem."""
+    i0, i1 = shard_rows(n, rank, world)
+    t, w = host_inputs(n, 0, torch)                  # same seed everywhere: weights and bias are replicated
+    for name in ("q", "k", "v", "d_o", "key_mask", "x", "d_out", "pair_mask"):
+        t[name] = t[name][:, i0:i1].contiguous()
+
+    def step(td, wd):
+        q, k, v, bias = (td[m].detach().requires_grad_() for m in ("q", "k", "v", "bias"))
+        o = sharded_triangle_attention(q, k, v, bias, td["key_mask"], q.shape[-1] ** -0.5)
+        res = [o, *torch.autograd.grad(o, [q, k, v, bias], grad_outputs=td["d_o"])]
+        for direction in ("outgoing", "incoming"):
+            x = td["x"].detach().requires_grad_()
+            wl = {m: p.detach().requires_grad_() for m, p in wd.items()}
+            out = sharded_triangle_multiplicative_update(x, direction, td["pair_mask"], **wl)
+            res += [out, *torch.autograd.grad(out, [x, *wl.values()], grad_outputs=td["d_out"])]
+        return res
+
+    return step, t, w

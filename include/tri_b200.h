@@ -164,6 +164,49 @@ int tri_mul_bwd(const TriMulDesc* d, const void* x, const void* mask, const TriM
                 void* ws, size_t ws_bytes, tri_stream_t stream);
 
 /* ------------------------------------------------------------------------ */
+/* Row-sharded triangle multiplicative update (one GPU per shard of rows)   */
+/* ------------------------------------------------------------------------ */
+/* No counterpart in the reference, which is single-device.  The pair tensor is sharded over its first
+ * pair axis: this rank holds x[:, i0:i0+rows, :, :].  Everything except the contraction is pixel-wise, so
+ * the op splits into phases around two exchanges that the caller performs (NCCL all-to-all):
+ *   PROJECT      x -> a_cm, b_cm  [B, Ch, rows, N]   (channel-major gated projections of the local rows)
+ *   ... exchange rows -> channels; contraction per channel with tri_bgemm; exchange channels -> rows ...
+ *   OUTPUT       t_cm [B, Ch, rows, N] -> out [B, rows, N, C]
+ *   OUTPUT_BWD   d_out, t_cm -> dt_cm, gradients of norm_out / p_out / g_out (this rank's partial sums)
+ *   ... the two backward contractions between the same exchanges ...
+ *   PROJECT_BWD  gradients da, db passed in a_cm, b_cm -> dx, gradients of norm_in / p_in / g_in (partial)
+ * `saved` (tri_mul_shard_saved_bytes) carries z, u, dgo and the LayerNorm statistics between phases.
+ * Weight gradients are per-rank partial sums: all-reduce them.  Tensor-core path only
+ * (C = Ch = 128, N % 8 == 0, bf16 / fp16, or fp32 with precision tf32). */
+typedef struct TriMulShardDesc {
+  int32_t B, rows, N, C, Ch;
+  int32_t dtype, precision;
+  float eps;
+} TriMulShardDesc;
+
+typedef struct TriMulShardBufs {
+  const void* x;            /* [B, rows, N, C] */
+  const void* mask;         /* [B, rows, N], nullable */
+  const TriMulWeights* w;
+  void* saved;
+  void* a_cm;               /* PROJECT: out a;  PROJECT_BWD: in da */
+  void* b_cm;               /* PROJECT: out b;  PROJECT_BWD: in db */
+  const void* t_cm;         /* OUTPUT, OUTPUT_BWD: in */
+  void* out;                /* OUTPUT: out */
+  const void* d_out;        /* OUTPUT_BWD: in */
+  void* dt_cm;              /* OUTPUT_BWD: out */
+  void* dx;                 /* PROJECT_BWD: out */
+  const TriMulWeightGrads* g;
+} TriMulShardBufs;
+
+enum { TRI_PHASE_PROJECT = 0, TRI_PHASE_OUTPUT = 1, TRI_PHASE_OUTPUT_BWD = 2, TRI_PHASE_PROJECT_BWD = 3 };
+
+size_t tri_mul_shard_saved_bytes(const TriMulShardDesc* d);
+size_t tri_mul_shard_ws_bytes(const TriMulShardDesc* d, int phase);
+int tri_mul_shard_phase(const TriMulShardDesc* d, int phase, const TriMulShardBufs* bufs, void* ws,
+                        size_t ws_bytes, tri_stream_t stream);
+
+/* ------------------------------------------------------------------------ */
 /* Batched tensor-core GEMM (building block of the trimul contraction)      */
 /* ------------------------------------------------------------------------ */
 /* C[b][m][n] = sum_k A[b](m,k) * B[b](n,k), fp32 accumulation on tcgen05.  This is the per-channel

@@ -1,0 +1,92 @@
+"""Host logic of the row-sharded wrappers on two gloo ranks (CPU): the exchanges and the row partition."""
+
+import os
+import socket
+
+import pytest
+import torch
+import torch.distributed as dist
+import torch.multiprocessing as mp
+
+
+def _free_port():
+    with socket.socket() as s:
+        s.bind(("127.0.0.1", 0))
+        return s.getsockname()[1]
+
+
+def _worker(rank, world, port, fn_name, ret):
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port))
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    try:
+        globals()[fn_name](rank, world)
+        ret[rank] = "ok"
+    except Exception as exc:  # report instead of hanging the other rank
+        ret[rank] = repr(exc)
+    finally:
+        dist.destroy_process_group()
+
+
+def _run(fn_name, world=2):
+    ctx = mp.get_context("spawn")
+    ret = ctx.Manager().dict()
+    port = _free_port()
+    procs = [ctx.Process(target=_worker, args=(r, world, port, fn_name, ret)) for r in range(world)]
+    for p in procs:
+        p.start()
+    for p in procs:
+        p.join(120)
+        assert not p.is_alive(), "rank did not finish"
+    assert dict(ret) == {r: "ok" for r in range(world)}, dict(ret)
+
+
+def _full(shape, seed=0):
+    return torch.randn(*shape, generator=torch.Generator().manual_seed(seed))
+
+
+def check_channel_exchange(rank, world):
+    from geometric_nn_ops_b200 import sharded
+    L, Ch, N = 3, 8, 6
+    R, cs = N // world, Ch // world
+    full = _full((L, Ch, N, N))                       # the same on every rank
+    i0, i1 = sharded.shard_rows(N, rank, world)
+    mine = full[:, :, i0:i1].contiguous()             # all channels, my rows
+    got = sharded.rows_to_channels(mine)
+    assert torch.equal(got, full[:, rank * cs:(rank + 1) * cs])   # my channels, all rows
+    back = sharded.channels_to_rows(got)
+    assert torch.equal(back, mine)
+
+
+def check_transpose(rank, world):
+    from geometric_nn_ops_b200 import sharded
+    B, N, C = 2, 8, 5
+    full = _full((B, N, N, C), seed=1)
+    i0, i1 = sharded.shard_rows(N, rank, world)
+    x = full[:, i0:i1].clone().requires_grad_()
+    y = sharded.all_to_all_transpose(x)
+    assert torch.equal(y, full.transpose(1, 2)[:, i0:i1])
+    # gradient: the transpose of the upstream gradient's shard
+    gfull = _full((B, N, N, C), seed=2)
+    y.backward(gfull[:, i0:i1])
+    assert torch.equal(x.grad, gfull.transpose(1, 2)[:, i0:i1])
+    assert torch.equal(sharded.all_to_all_transpose(sharded.all_to_all_transpose(x.detach())), x.detach())
+
+
+def check_replicated_grad(rank, world):
+    from geometric_nn_ops_b200 import sharded
+    bias = torch.ones(4, requires_grad=True)
+    out = sharded._SumGradOverRanks.apply(bias, None) * float(rank + 1)
+    out.sum().backward()
+    assert torch.equal(bias.grad, torch.full((4,), float(sum(range(1, world + 1)))))
+
+
+@pytest.mark.parametrize("fn", ["check_channel_exchange", "check_transpose", "check_replicated_grad"])
+def test_two_ranks(fn):
+    _run(fn)
+
+
+def test_shard_rows_rejects_uneven_split():
+    from geometric_nn_ops_b200 import sharded
+    assert sharded.shard_rows(768, 3, 8) == (288, 384)
+    with pytest.raises(ValueError, match="not divisible"):
+        sharded.shard_rows(10, 0, 4)
