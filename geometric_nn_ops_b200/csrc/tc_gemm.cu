@@ -115,7 +115,7 @@ static int launch_t(cudaStream_t st, const CUtensorMap* maps, const GemmArgs& g,
   const int total = g.batches * g.tiles_m * g.tiles_n;
   const int grid = std::min(total, sm_count());
   KernelTimer kt(p.name, st, p.flops, p.bytes);
-  kern<<<grid, 192, smem, st>>>(maps[0], maps[1], maps[2], maps[3], g);
+  kern<<<grid, kGemmThreads, smem, st>>>(maps[0], maps[1], maps[2], maps[3], g);
   TRI_LAUNCH_OK();
   return 0;
 }
@@ -153,8 +153,9 @@ int launch_gemm(cudaStream_t st, int dtype, int epi, int bn, bool out_f32, const
   g.bn0 = side_by_side ? 128 : bn;
   g.seg1_n = two ? (side_by_side ? 128 : bn) : 0;
   g.batches = p.batches;
-  g.tiles_m = (p.M + kBM - 1) / kBM;
-  g.tiles_n = side_by_side ? 1 : (p.N + bn - 1) / bn;
+  g.a_tile_batch = p.a_tiles > 0;
+  g.tiles_m = p.a_tiles > 0 ? p.a_tiles : (p.M + kBM - 1) / kBM;
+  g.tiles_n = side_by_side ? (p.N + 127) / 128 : (p.N + bn - 1) / bn;
   g.split_k = p.split_k;
   const int kind = dtype == TRI_F32 ? KIND_TF32 : (dtype == TRI_BF16 ? KIND_BF16 : KIND_F16);
   for (int s = 0; s < 2; ++s) {

@@ -2,7 +2,8 @@
 //
 //   warp 0      TMA producer: fills a ring of shared-memory stages (128-byte swizzle) with operand tiles
 //   warp 1      MMA issuer:   tcgen05.mma from the stages into one of two TMEM accumulators
-//   warps 2..5  epilogue:     tcgen05.ld the finished accumulator, apply the fused epilogue, store to HBM
+//   warps 2..9  epilogue:     two groups of four warps (each group covers the 128 TMEM lanes and takes half
+//                             of the accumulator columns): tcgen05.ld, fused epilogue, 16/32-byte stores
 //
 // A tile is 128 (M) x BN (N); K advances 128 bytes per stage (64 bf16/fp16 or 32 fp32 elements).  Each
 // operand may be K-major (K contiguous in global memory) or MN-major (M or N contiguous); the second form
@@ -11,6 +12,10 @@
 // same tile, either into the same accumulator columns (a sum of two products) or into the second half
 // of them (two products side by side); the fused gate epilogues use that.  With split_k the batch index
 // selects a K range instead of a batch entry (weight gradients over all pixels).
+//
+// The input-gate GEMMs run TRANSPOSED (weights are the M operand, pixels the N operand), so that a thread
+// owns one channel and its registers hold consecutive pixels: the channel-major a / b / dPG tensors are
+// then written and read with plain contiguous vector accesses instead of 2-byte scatters.
 //
 // All waits are bounded (see tc_common.cuh); a timeout lands in *args.err and the kernel drains.
 #pragma once
@@ -21,16 +26,19 @@ namespace tri {
 namespace tc {
 
 enum Epilogue {
-  EPI_STORE = 0,        // out0[batch][m][n] = acc (+ bias0[n])
-  EPI_GATE_IN = 1,      // cols [P(128) | G(128)]: half-plane[c][m] = (P+b)*sigmoid(G+b)*mask[m], channel-major
-  EPI_GATE_OUT = 2,     // cols [y(128) | g(128)]: out0[m][c] = (y+b)*sigmoid(g+b)
-  EPI_GATE_OUT_BWD = 3, // same cols, aux = d_out: out0 = d_out*sig, out1 = d_out*(y+b)*sig*(1-sig)
-  EPI_GATE_IN_BWD = 4   // cols [P | G] recomputed; aux2/aux3 = channel-major d(a), d(b); aux = mask:
-                        //   out0[m][n0 + c] = d*sig(G),  out0[m][n0 + 128 + c] = d*P*sig*(1-sig),  d = d(half)[c][m]*mask
+  EPI_STORE = 0,         // out0[batch][m][n] = acc (+ bias0[n])
+  EPI_GATE_IN = 1,       // transposed: rows = channels of one half (tile_m = a or b), cols [P(128 px) | G(128 px)]:
+                         //   half-plane[c][px] = (P+bp)*sigmoid(G+bg)*mask[px]
+  EPI_GATE_OUT = 2,      // rows = pixels, cols [y(128) | g(128)]: out0[m][c] = (y+b)*sigmoid(g+b)
+  EPI_GATE_OUT_BWD = 3,  // same cols, aux = d_out: out0 = d_out*sig, out1 = d_out*(y+b)*sig*(1-sig)
+  EPI_GATE_IN_BWD = 4    // transposed like GATE_IN; aux2/aux3 = channel-major d(a), d(b); aux = mask;
+                         //   d = d(half)[c][px]*mask;  out0 is channel-major [512][M]:
+                         //   row half*256+c = d*sig(G),  row half*256+128+c = d*P*sig*(1-sig)
 };
 
 constexpr int kBM = 128;
 constexpr int kStageA = kBM * 128;  // bytes
+constexpr int kGemmThreads = 320;
 
 struct GemmArgs {
   int M, N;                  // output extent of one batch entry
@@ -40,41 +48,59 @@ struct GemmArgs {
   int bn0;                   // N extent of segment 0's MMA
   int batches, tiles_m, tiles_n;
   int split_k;               // batch index selects K range [batch*kblocks0, ...) instead of a batch entry
+  int a_tile_batch;          // the M-tile index is A's batch coordinate (rows 0..127 of plane tile_m)
   int a_mn[2], b_mn[2];      // per segment: operand is MN-major
   uint32_t idesc[2];
   // epilogue
   void* out0;
   void* out1;
   long long ld_out, batch_out;   // elements
-  const float* bias0;            // per output column (EPI_STORE) / per accumulator column (gates)
-  const void* aux;               // mask (GATE_IN) or d_out (GATE_OUT_BWD), in the input dtype
+  const float* bias0;            // per output column (EPI_STORE) / per accumulator column or row (gates)
+  const void* aux;               // mask (GATE_IN*) or d_out (GATE_OUT_BWD), in the input dtype
   const void* aux2;              // GATE_IN_BWD: channel-major gradient of the a half
   const void* aux3;              //              ... of the b half
-  long long plane;               // GATE_IN(_BWD): pixels per batch entry (N*N); channel-major plane stride
+  long long plane;               // GATE_IN(_BWD): pixels per batch entry; channel-major plane stride
   int* err;
 };
 
 template <typename T> struct ElemTraits;
-template <> struct ElemTraits<__nv_bfloat16> { static constexpr int kind = KIND_BF16; static constexpr bool tf32 = false; };
-template <> struct ElemTraits<__half> { static constexpr int kind = KIND_F16; static constexpr bool tf32 = false; };
-template <> struct ElemTraits<float> { static constexpr int kind = KIND_TF32; static constexpr bool tf32 = true; };
+template <> struct ElemTraits<__nv_bfloat16> { static constexpr int kind = KIND_BF16; };
+template <> struct ElemTraits<__half> { static constexpr int kind = KIND_F16; };
+template <> struct ElemTraits<float> { static constexpr int kind = KIND_TF32; };
+
+__device__ __forceinline__ float fast_sigmoid(float x) {
+  return __fdividef(1.0f, 1.0f + ex2_approx(-1.4426950408889634f * x));
+}
+
+// 8 consecutive elements <-> registers, with 16-byte (16-bit types) or 2 x 16-byte (fp32) accesses
+template <typename T> __device__ __forceinline__ void load8(const T* p, float (&v)[8]) {
+  if constexpr (sizeof(T) == 4) {
+    const float4 a = reinterpret_cast<const float4*>(p)[0], b = reinterpret_cast<const float4*>(p)[1];
+    v[0] = a.x; v[1] = a.y; v[2] = a.z; v[3] = a.w; v[4] = b.x; v[5] = b.y; v[6] = b.z; v[7] = b.w;
+  } else {
+    union { uint4 u; T h[8]; } pk;
+    pk.u = *reinterpret_cast<const uint4*>(p);
+#pragma unroll
+    for (int i = 0; i < 8; ++i) v[i] = to_f32(pk.h[i]);
+  }
+}
+template <typename T> __device__ __forceinline__ void store8(T* p, const float* v) {
+  if constexpr (sizeof(T) == 4) {
+    reinterpret_cast<float4*>(p)[0] = make_float4(v[0], v[1], v[2], v[3]);
+    reinterpret_cast<float4*>(p)[1] = make_float4(v[4], v[5], v[6], v[7]);
+  } else {
+    union { uint4 u; T h[8]; } pk;
+#pragma unroll
+    for (int i = 0; i < 8; ++i) pk.h[i] = from_f32<T>(v[i]);
+    *reinterpret_cast<uint4*>(p) = pk.u;
+  }
+}
 
 template <typename TOUT>
 __device__ __forceinline__ void store_row32(TOUT* dst, const float (&v)[32], int valid, bool vec_ok) {
   if (valid >= 32 && vec_ok) {
-    if constexpr (sizeof(TOUT) == 4) {
 #pragma unroll
-      for (int i = 0; i < 8; ++i)
-        reinterpret_cast<float4*>(dst)[i] = make_float4(v[4 * i], v[4 * i + 1], v[4 * i + 2], v[4 * i + 3]);
-    } else {
-#pragma unroll
-      for (int i = 0; i < 4; ++i) {
-        union { uint4 u; TOUT h[8]; } pk;
-#pragma unroll
-        for (int j = 0; j < 8; ++j) pk.h[j] = from_f32<TOUT>(v[8 * i + j]);
-        reinterpret_cast<uint4*>(dst)[i] = pk.u;
-      }
-    }
+    for (int i = 0; i < 4; ++i) store8<TOUT>(dst + 8 * i, &v[8 * i]);
   } else {
 #pragma unroll
     for (int i = 0; i < 32; ++i)
@@ -82,6 +108,15 @@ __device__ __forceinline__ void store_row32(TOUT* dst, const float (&v)[32], int
   }
 }
 
+// two 32-column loads (columns c0.. and c1..) with one wait
+__device__ __forceinline__ void ld32x2_f(uint32_t t0, uint32_t t1, float (&a)[32], float (&b)[32]) {
+  uint32_t ra[32], rb[32];
+  tmem_ld_32x32(t0, ra);
+  tmem_ld_32x32(t1, rb);
+  tmem_ld_wait();
+#pragma unroll
+  for (int i = 0; i < 32; ++i) { a[i] = __uint_as_float(ra[i]); b[i] = __uint_as_float(rb[i]); }
+}
 __device__ __forceinline__ void ld32_f(uint32_t taddr, float (&v)[32]) {
   uint32_t r[32];
   tmem_ld_32x32(taddr, r);
@@ -91,7 +126,7 @@ __device__ __forceinline__ void ld32_f(uint32_t taddr, float (&v)[32]) {
 }
 
 template <typename TIN, typename TOUT, int BN, int EPI, int STAGES>
-__global__ void __launch_bounds__(192, 1)
+__global__ void __launch_bounds__(kGemmThreads, 1)
 tc_gemm_kernel(const __grid_constant__ CUtensorMap tmA0, const __grid_constant__ CUtensorMap tmB0,
                const __grid_constant__ CUtensorMap tmA1, const __grid_constant__ CUtensorMap tmB1, const GemmArgs g) {
   constexpr int ES = sizeof(TIN);
@@ -118,7 +153,7 @@ tc_gemm_kernel(const __grid_constant__ CUtensorMap tmA0, const __grid_constant__
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   if (threadIdx.x == 0) {
     for (int s = 0; s < STAGES; ++s) { mbar_init(&full[s], 1); mbar_init(&empty[s], 1); }
-    for (int a = 0; a < 2; ++a) { mbar_init(&tfull[a], 1); mbar_init(&tempty[a], 4); }
+    for (int a = 0; a < 2; ++a) { mbar_init(&tfull[a], 1); mbar_init(&tempty[a], 8); }
     mbar_fence_init();
     tma_prefetch_desc(&tmA0);
     tma_prefetch_desc(&tmB0);
@@ -131,6 +166,13 @@ tc_gemm_kernel(const __grid_constant__ CUtensorMap tmA0, const __grid_constant__
 
   const int total = g.batches * g.tiles_m * g.tiles_n;
   const int kb_total = g.kblocks0 + g.kblocks1;
+  // tile -> (batch, tile_m, tile_n); with a_tile_batch the M tiles (weight blocks) of one pixel tile are
+  // adjacent in the schedule so the shared activation tile is still in L2 for the second one
+  auto decode = [&](int tile, int& tm, int& tn, int& bz) {
+    if (g.a_tile_batch) { tm = tile % g.tiles_m; tn = (tile / g.tiles_m) % g.tiles_n; }
+    else { tn = tile % g.tiles_n; tm = (tile / g.tiles_n) % g.tiles_m; }
+    bz = tile / (g.tiles_n * g.tiles_m);
+  };
 
   if (warp == 0) {
     // ------------------------------------------------------------------ producer
@@ -140,10 +182,12 @@ tc_gemm_kernel(const __grid_constant__ CUtensorMap tmA0, const __grid_constant__
       uint32_t phase = 0;
       bool ok = true;
       for (int tile = blockIdx.x; tile < total && ok; tile += gridDim.x) {
-        const int tn = tile % g.tiles_n, tm = (tile / g.tiles_n) % g.tiles_m, bz = tile / (g.tiles_n * g.tiles_m);
-        const int m0 = tm * kBM, n0 = tn * BN;
+        int tm, tn, bz;
+        decode(tile, tm, tn, bz);
+        const int n0 = tn * (g.seg1_col ? g.bn0 : BN);
         const int zc = g.split_k ? 0 : bz;
         const int koff = g.split_k ? bz * g.kblocks0 * BKE : 0;
+        const int am = g.a_tile_batch ? 0 : tm * kBM, az = g.a_tile_batch ? tm : zc;
         for (int kb = 0; kb < kb_total; ++kb) {
           if (!mbar_wait(&empty[stage], phase ^ 1, g.err, 1)) { ok = false; break; }
           const int seg = kb >= g.kblocks0 ? 1 : 0;
@@ -155,15 +199,14 @@ tc_gemm_kernel(const __grid_constant__ CUtensorMap tmA0, const __grid_constant__
           uint8_t* a_dst = sA + stage * kStageA;
           uint8_t* b_dst = sB + stage * STAGE_B;
           if (!g.a_mn[seg]) {
-            tma_load_3d(a_dst, ma, &full[stage], kk, m0, zc);
+            tma_load_3d(a_dst, ma, &full[stage], kk, am, az);
           } else {
-            for (int c = 0; c < kBM / CE; ++c) tma_load_3d(a_dst + c * (BKE * 128), ma, &full[stage], m0 + c * CE, kk, zc);
+            for (int c = 0; c < kBM / CE; ++c) tma_load_3d(a_dst + c * (BKE * 128), ma, &full[stage], am + c * CE, kk, az);
           }
-          const int nb0 = seg && g.seg1_col ? 0 : n0;  // side-by-side segments always cover all their columns
           if (!g.b_mn[seg]) {
-            tma_load_3d(b_dst, mb, &full[stage], kk, nb0, zc);
+            tma_load_3d(b_dst, mb, &full[stage], kk, n0, zc);
           } else {
-            for (int c = 0; c < bn / CE; ++c) tma_load_3d(b_dst + c * (BKE * 128), mb, &full[stage], nb0 + c * CE, kk, zc);
+            for (int c = 0; c < bn / CE; ++c) tma_load_3d(b_dst + c * (BKE * 128), mb, &full[stage], n0 + c * CE, kk, zc);
           }
           if (++stage == STAGES) { stage = 0; phase ^= 1; }
         }
@@ -207,22 +250,26 @@ tc_gemm_kernel(const __grid_constant__ CUtensorMap tmA0, const __grid_constant__
     }
     __syncwarp();
   } else {
-    // ------------------------------------------------------------------ epilogue (4 warps = 128 TMEM lanes)
-    const int quarter = warp & 3;
+    // ------------------------------------------------------------------ epilogue: 2 groups x 4 warps
+    const int quarter = warp & 3;            // the TMEM lane quarter this warp may read
+    const int grp = (warp - 2) >> 2;         // column half this warp's group takes
     const int row = quarter * 32 + lane;
     int acc = 0;
     uint32_t acc_phase = 0;
     for (int tile = blockIdx.x; tile < total; tile += gridDim.x) {
-      const int tn = tile % g.tiles_n, tm = (tile / g.tiles_n) % g.tiles_m, bz = tile / (g.tiles_n * g.tiles_m);
-      const int m = tm * kBM + row, n0 = tn * BN;
+      int tm, tn, bz;
+      decode(tile, tm, tn, bz);
       if (!mbar_wait(&tfull[acc], acc_phase, g.err, 4)) break;
       tc_fence_after_sync();
       const uint32_t t_row = tmem_base + ((uint32_t)(quarter * 32) << 16) + acc * BN;
       if constexpr (EPI == EPI_STORE) {
+        const int m = tm * kBM + row, n0 = tn * BN;
         TOUT* out = reinterpret_cast<TOUT*>(g.out0) + bz * g.batch_out + (long long)m * g.ld_out;
         const bool vec_ok = (g.ld_out * sizeof(TOUT)) % 16 == 0 && (g.batch_out * sizeof(TOUT)) % 16 == 0;
+        constexpr int CH = BN / 64;  // 32-column chunks per group
 #pragma unroll 1
-        for (int j = 0; j < BN / 32; ++j) {
+        for (int jj = 0; jj < CH; ++jj) {
+          const int j = grp * CH + jj;
           float v[32];
           ld32_f(t_row + j * 32, v);
           const int n = n0 + j * 32;
@@ -232,82 +279,82 @@ tc_gemm_kernel(const __grid_constant__ CUtensorMap tmA0, const __grid_constant__
           }
           if (m < g.M && n < g.N) store_row32<TOUT>(out + n, v, g.N - n, vec_ok);
         }
-      } else if constexpr (EPI == EPI_GATE_IN) {
-        // tile column block tn selects the a (0) or b (1) half; out0 / out1 are their channel-major planes
-        TOUT* plane = reinterpret_cast<TOUT*>(tn == 0 ? g.out0 : g.out1);
-        const long long bb = m / g.plane, pix = m % g.plane;
+      } else if constexpr (EPI == EPI_GATE_IN || EPI == EPI_GATE_IN_BWD) {
+        // row = channel of half tm; columns: P for pixels n0..n0+127, then G for the same pixels
+        const long long n0 = (long long)tn * 128;
         const TIN* mask = reinterpret_cast<const TIN*>(g.aux);
-        const float mk = (mask != nullptr && m < g.M) ? to_f32(mask[m]) : 1.0f;
+        float bp = 0.f, bg = 0.f;
+        if (g.bias0 != nullptr) { bp = g.bias0[tm * 256 + row]; bg = g.bias0[tm * 256 + 128 + row]; }
 #pragma unroll 1
-        for (int j = 0; j < 4; ++j) {
+        for (int jj = 0; jj < 2; ++jj) {
+          const int j = grp * 2 + jj;
           float p[32], gt[32];
-          ld32_f(t_row + j * 32, p);
-          ld32_f(t_row + 128 + j * 32, gt);
-          if (m < g.M) {
+          ld32x2_f(t_row + j * 32, t_row + 128 + j * 32, p, gt);
 #pragma unroll
-            for (int i = 0; i < 32; ++i) {
-              const int c = j * 32 + i;
-              float pv = p[i], gv = gt[i];
-              if (g.bias0 != nullptr) { pv += g.bias0[n0 + c]; gv += g.bias0[n0 + 128 + c]; }
-              plane[(bb * 128 + c) * g.plane + pix] = from_f32<TOUT>(pv * sigmoidf_acc(gv) * mk);
-            }
-          }
-        }
-      } else if constexpr (EPI == EPI_GATE_IN_BWD) {
-        const TIN* dplane = reinterpret_cast<const TIN*>(tn == 0 ? g.aux2 : g.aux3);
-        const long long bb = m / g.plane, pix = m % g.plane;
-        const TIN* mask = reinterpret_cast<const TIN*>(g.aux);
-        const float mk = (mask != nullptr && m < g.M) ? to_f32(mask[m]) : 1.0f;
-        TOUT* orow = reinterpret_cast<TOUT*>(g.out0) + (long long)m * g.ld_out + n0;
-#pragma unroll 1
-        for (int j = 0; j < 4; ++j) {
-          float p[32], gt[32];
-          ld32_f(t_row + j * 32, p);
-          ld32_f(t_row + 128 + j * 32, gt);
-          if (m < g.M) {
-            float dp[32], dg[32];
+          for (int u = 0; u < 4; ++u) {
+            const long long m8 = n0 + j * 32 + u * 8;   // 8 pixels: same batch entry, all valid or none
+            if (m8 >= g.N) continue;
+            const long long bb = m8 / g.plane, pix = m8 % g.plane;
+            float mk[8];
+            if (mask != nullptr) load8<TIN>(mask + m8, mk);
+            if constexpr (EPI == EPI_GATE_IN) {
+              float r[8];
 #pragma unroll
-            for (int i = 0; i < 32; ++i) {
-              const int c = j * 32 + i;
-              float pv = p[i], gv = gt[i];
-              if (g.bias0 != nullptr) { pv += g.bias0[n0 + c]; gv += g.bias0[n0 + 128 + c]; }
-              const float d = to_f32(dplane[(bb * 128 + c) * g.plane + pix]) * mk;
-              const float sg = sigmoidf_acc(gv);
-              dp[i] = d * sg;
-              dg[i] = d * pv * sg * (1.0f - sg);
+              for (int i = 0; i < 8; ++i) {
+                r[i] = (p[u * 8 + i] + bp) * fast_sigmoid(gt[u * 8 + i] + bg);
+                if (mask != nullptr) r[i] *= mk[i];
+              }
+              TOUT* plane = reinterpret_cast<TOUT*>(tm == 0 ? g.out0 : g.out1);
+              store8<TOUT>(plane + (bb * 128 + row) * g.plane + pix, r);
+            } else {
+              const TIN* dplane = reinterpret_cast<const TIN*>(tm == 0 ? g.aux2 : g.aux3);
+              float d[8], dp[8], dg[8];
+              load8<TIN>(dplane + (bb * 128 + row) * g.plane + pix, d);
+#pragma unroll
+              for (int i = 0; i < 8; ++i) {
+                const float dd = mask != nullptr ? d[i] * mk[i] : d[i];
+                const float sg = fast_sigmoid(gt[u * 8 + i] + bg);
+                dp[i] = dd * sg;
+                dg[i] = dd * (p[u * 8 + i] + bp) * sg * (1.0f - sg);
+              }
+              TOUT* o = reinterpret_cast<TOUT*>(g.out0);
+              store8<TOUT>(o + (long long)(tm * 256 + row) * g.ld_out + m8, dp);
+              store8<TOUT>(o + (long long)(tm * 256 + 128 + row) * g.ld_out + m8, dg);
             }
-            store_row32<TOUT>(orow + j * 32, dp, 32, true);
-            store_row32<TOUT>(orow + 128 + j * 32, dg, 32, true);
           }
         }
       } else {
-        // EPI_GATE_OUT / EPI_GATE_OUT_BWD: cols [0,128) = y, [128,256) = gate pre-activation
+        // EPI_GATE_OUT / EPI_GATE_OUT_BWD: row = pixel; cols [0,128) = y, [128,256) = gate pre-activation
+        const int m = tm * kBM + row;
         TOUT* o0 = reinterpret_cast<TOUT*>(g.out0) + (long long)m * 128;
         TOUT* o1 = reinterpret_cast<TOUT*>(g.out1) + (long long)m * 128;
         const TIN* dout = reinterpret_cast<const TIN*>(g.aux) + (long long)m * 128;
 #pragma unroll 1
-        for (int j = 0; j < 4; ++j) {
+        for (int jj = 0; jj < 2; ++jj) {
+          const int j = grp * 2 + jj;
           float y[32], gt[32];
-          ld32_f(t_row + j * 32, y);
-          ld32_f(t_row + 128 + j * 32, gt);
+          ld32x2_f(t_row + j * 32, t_row + 128 + j * 32, y, gt);
           if (m < g.M) {
-            float r0[32], r1[32];
 #pragma unroll
-            for (int i = 0; i < 32; ++i) {
-              const int c = j * 32 + i;
-              float yv = y[i], gv = gt[i];
-              if (g.bias0 != nullptr) { yv += g.bias0[c]; gv += g.bias0[128 + c]; }
-              const float sg = sigmoidf_acc(gv);
-              if constexpr (EPI == EPI_GATE_OUT) {
-                r0[i] = yv * sg;
-              } else {
-                const float d = to_f32(dout[c]);
-                r0[i] = d * sg;
-                r1[i] = d * yv * sg * (1.0f - sg);
+            for (int u = 0; u < 4; ++u) {
+              float r0[8], r1[8], d[8];
+              if constexpr (EPI == EPI_GATE_OUT_BWD) load8<TIN>(dout + j * 32 + u * 8, d);
+#pragma unroll
+              for (int i = 0; i < 8; ++i) {
+                const int c = j * 32 + u * 8 + i;
+                float yv = y[u * 8 + i], gv = gt[u * 8 + i];
+                if (g.bias0 != nullptr) { yv += g.bias0[c]; gv += g.bias0[128 + c]; }
+                const float sg = fast_sigmoid(gv);
+                if constexpr (EPI == EPI_GATE_OUT) {
+                  r0[i] = yv * sg;
+                } else {
+                  r0[i] = d[i] * sg;
+                  r1[i] = d[i] * yv * sg * (1.0f - sg);
+                }
               }
+              store8<TOUT>(o0 + j * 32 + u * 8, r0);
+              if constexpr (EPI == EPI_GATE_OUT_BWD) store8<TOUT>(o1 + j * 32 + u * 8, r1);
             }
-            store_row32<TOUT>(o0 + j * 32, r0, 32, true);
-            if constexpr (EPI == EPI_GATE_OUT_BWD) store_row32<TOUT>(o1 + j * 32, r1, 32, true);
           }
         }
       }
@@ -345,6 +392,7 @@ struct GemmPlan {
   int seg1_col = 0;
   int batches = 1;
   int split_k = 0;
+  int a_tiles = 0;           // > 0: A's batch dimension enumerates this many 128-row M tiles (gate-in GEMMs)
   void* out0 = nullptr;
   void* out1 = nullptr;
   long long ld_out = 0, batch_out = 0;

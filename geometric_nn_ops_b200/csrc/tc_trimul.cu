@@ -6,7 +6,7 @@
 //
 // Data layout in HBM (M = B*N*N pixels, NN = N*N):
 //   z, u, dy, dgo, du, dz   pixel-major   [M, 128]
-//   dPG                     pixel-major   [M, 512], columns [dP_a | dG_a | dP_b | dG_b]
+//   dPG                     channel-major [512, M], rows [dP_a | dG_a | dP_b | dG_b]
 //   a, b, t, dt, da, db     channel-major [B, 128, N, N]: one N x N plane per channel, so the per-channel
 //                           contraction is a plain batched GEMM and both directions (and all four
 //                           backward products) differ only in which operand is read K-major / MN-major.
@@ -280,6 +280,24 @@ __global__ void reduce_kernel(const float* partial, int nparts, int n, float* ou
   out[j] = s;
 }
 
+// Row sums of the channel-major dPG [512, M] scattered to the p_in / g_in bias gradients (one block per row,
+// fixed summation order).
+template <typename T>
+__global__ void __launch_bounds__(256) rowsum_wcat_kernel(const T* dpg, long long M, float* d_p, float* d_g) {
+  __shared__ float red[256];
+  const int r = blockIdx.x, blk = r / CW, c = r % CW;
+  float* dst = (blk & 1) ? d_g : d_p;
+  float s = 0.f;
+  for (long long i = threadIdx.x; i < M; i += 256) s += to_f32(dpg[(long long)r * M + i]);
+  red[threadIdx.x] = s;
+  __syncthreads();
+  for (int o = 128; o > 0; o >>= 1) {
+    if (threadIdx.x < o) red[threadIdx.x] += red[threadIdx.x + o];
+    __syncthreads();
+  }
+  if (threadIdx.x == 0 && dst != nullptr) dst[(blk >> 1) * CW + c] = red[0];
+}
+
 // Sum partials of a [512, rowlen] tensor in Wcat row order and scatter the rows to the p_in / g_in gradients.
 __global__ void reduce_wcat_kernel(const float* partial, int nparts, int rowlen, float* d_p, float* d_g) {
   const int j = blockIdx.x * blockDim.x + threadIdx.x;
@@ -357,6 +375,19 @@ int run_prep(cudaStream_t st, const TriMulWeights* w, const Prep& pr) {
   return 0;
 }
 
+// The input-gate GEMM runs transposed: M = the 128 channels of one half (tile_m = a or b; P and G blocks of
+// Wcat side by side as the two segments), N = pixels.  A thread then owns a channel and holds consecutive
+// pixels, which is the order of the channel-major tensors it writes (a, b, dPG) or reads (da, db).
+void gate_in_operands(GemmPlan* p, const Geom& gm, const Prep& pr, const void* z) {
+  for (int seg = 0; seg < 2; ++seg) {
+    Operand& a = p->a[seg];
+    a.ptr = static_cast<const char*>(pr.wcat) + (size_t)seg * CW * CW * gm.es();   // P block / G block of each half
+    a.mn_major = false; a.inner = CW; a.outer = CW; a.batch = 2; a.st_outer = CW; a.st_batch = 2 * CW * CW;
+    p->b[seg] = rows_operand(z, CW, gm.M, false);
+  }
+  p->M = CW; p->N = (int)gm.M; p->K0 = CW; p->K1 = CW; p->seg1_col = CW; p->a_tiles = 2;
+}
+
 // ---- phase 1: x -> z (LayerNorm), a / b (gated, masked projections, channel-major) ---------------------
 template <typename T>
 int phase_project(cudaStream_t st, const Geom& gm, const void* x, const void* mask, const TriMulWeights* w,
@@ -369,9 +400,7 @@ int phase_project(cudaStream_t st, const Geom& gm, const void* x, const void* ma
     TRI_LAUNCH_OK();
   }
   GemmPlan p;
-  p.a[0] = rows_operand(z, CW, M, false);
-  p.b[0] = rows_operand(pr.wcat, CW, 4 * CW, false);
-  p.M = (int)M; p.N = 4 * CW; p.K0 = CW;
+  gate_in_operands(&p, gm, pr, z);
   p.out0 = a_cm; p.out1 = b_cm; p.bias0 = (w->p_in_b || w->g_in_b) ? pr.bias_cat : nullptr; p.aux = mask;
   p.plane = gm.plane;
   p.name = "tc_gemm_gate_in"; p.flops = 2.0 * M * CW * 4 * CW; p.bytes = 3.0 * gm.unit();
@@ -394,15 +423,16 @@ int phase_output(cudaStream_t st, const Geom& gm, const void* t_cm, const void* 
   p.b[0] = rows_operand(w->p_out_w, CW, CW, false);
   p.a[1] = rows_operand(z, CW, M, false);
   p.b[1] = rows_operand(w->g_out_w, CW, CW, false);
-  p.M = (int)M; p.N = 2 * CW; p.K0 = CW; p.K1 = CW; p.seg1_col = CW;
+  p.M = (int)M; p.N = CW; p.K0 = CW; p.K1 = CW; p.seg1_col = CW;
   p.out0 = out; p.bias0 = (w->p_out_b || w->g_out_b) ? pr.bias_out : nullptr;
   p.name = "tc_gemm_gate_out"; p.flops = 2.0 * M * CW * 2 * CW; p.bytes = 3.0 * gm.unit();
   return launch_gemm(st, gm.dtype, EPI_GATE_OUT, 256, false, p, pr.err);
 }
 
 int split_k_grad(cudaStream_t st, const Geom& gm, const void* lhs, int lhs_w, const void* rhs, float* partial,
-                 int* err, const char* name, int* nparts) {
-  // partial[s][lhs_w][128] = sum over the rows of split s of lhs[row][:]^T rhs[row][:]
+                 int* err, const char* name, int* nparts, bool lhs_channel_major = false) {
+  // partial[s][lhs_w][128] = sum over the pixels of split s of lhs[pixel][:]^T rhs[pixel][:]
+  // (lhs pixel-major [M, lhs_w], or channel-major [lhs_w, M])
   const long long M = gm.M;
   const int bke = gm.dtype == TRI_F32 ? 32 : 64;
   int splits = (int)std::min<long long>(kSplitK, (M + bke - 1) / bke);
@@ -410,6 +440,9 @@ int split_k_grad(cudaStream_t st, const Geom& gm, const void* lhs, int lhs_w, co
   splits = (int)((M + kper - 1) / kper);
   GemmPlan p;
   p.a[0] = rows_operand(lhs, lhs_w, M, true);
+  if (lhs_channel_major) {  // K (pixels) contiguous: a K-major operand with lhs_w rows
+    p.a[0].mn_major = false; p.a[0].inner = M; p.a[0].outer = lhs_w; p.a[0].st_outer = M;
+  }
   p.b[0] = rows_operand(rhs, CW, M, true);
   p.M = lhs_w; p.N = CW; p.K0 = (int)kper; p.batches = splits; p.split_k = 1;
   p.out0 = partial; p.ld_out = CW; p.batch_out = (long long)lhs_w * CW;
@@ -449,7 +482,7 @@ int phase_output_bwd(cudaStream_t st, const Geom& gm, const void* d_out, const v
     p.b[0] = rows_operand(w->p_out_w, CW, CW, false);
     p.a[1] = rows_operand(z, CW, M, false);
     p.b[1] = rows_operand(w->g_out_w, CW, CW, false);
-    p.M = (int)M; p.N = 2 * CW; p.K0 = CW; p.K1 = CW; p.seg1_col = CW;
+    p.M = (int)M; p.N = CW; p.K0 = CW; p.K1 = CW; p.seg1_col = CW;
     p.out0 = dy; p.out1 = dgo; p.aux = d_out; p.bias0 = (w->p_out_b || w->g_out_b) ? pr.bias_out : nullptr;
     p.name = "tc_gemm_gate_out_bwd"; p.flops = 0.0; p.bytes = 5.0 * gm.unit();  // recompute: no algorithmic flops
     TRI_TRY(launch_gemm(st, gm.dtype, EPI_GATE_OUT_BWD, 256, false, p, pr.err));
@@ -501,29 +534,27 @@ int phase_project_bwd(cudaStream_t st, const Geom& gm, const void* x, const void
   int nparts = 0;
   {
     GemmPlan p;   // input gate backward fused into the recomputed projection GEMM
-    p.a[0] = rows_operand(z, CW, M, false);
-    p.b[0] = rows_operand(pr.wcat, CW, 4 * CW, false);
-    p.M = (int)M; p.N = 4 * CW; p.K0 = CW;
-    p.out0 = dpg; p.ld_out = 4 * CW; p.bias0 = (w->p_in_b || w->g_in_b) ? pr.bias_cat : nullptr;
+    gate_in_operands(&p, gm, pr, z);
+    p.out0 = dpg; p.ld_out = M; p.bias0 = (w->p_in_b || w->g_in_b) ? pr.bias_cat : nullptr;
     p.aux = mask; p.aux2 = da_cm; p.aux3 = db_cm; p.plane = gm.plane;
     p.name = "tc_gemm_gate_in_bwd"; p.flops = 0.0; p.bytes = 7.0 * gm.unit();
     TRI_TRY(launch_gemm(st, gm.dtype, EPI_GATE_IN_BWD, 256, false, p, pr.err));
   }
   if (g->p_in_w || g->g_in_w) {
-    TRI_TRY(split_k_grad(st, gm, dpg, 4 * CW, z, partial, pr.err, "tc_gemm_wgrad", &nparts));
+    TRI_TRY(split_k_grad(st, gm, dpg, 4 * CW, z, partial, pr.err, "tc_gemm_wgrad", &nparts, /*lhs_channel_major=*/true));
     KernelTimer kt("tc_reduce", st, 0.0, 4.0 * (nparts + 1) * 4 * CW * CW);
     reduce_wcat_kernel<<<cdiv(4 * CW * CW, 256), 256, 0, st>>>(partial, nparts, CW, g->p_in_w, g->g_in_w);
     TRI_LAUNCH_OK();
   }
   if (g->p_in_b || g->g_in_b) {
-    TRI_TRY(colsum_to<T>(st, dpg, M, 4 * CW, partial, &nparts));
-    KernelTimer kt("tc_reduce", st, 0.0, 4.0 * (nparts + 1) * 4 * CW);
-    reduce_wcat_kernel<<<cdiv(4 * CW, 256), 256, 0, st>>>(partial, nparts, 1, g->p_in_b, g->g_in_b);
+    KernelTimer kt("tc_rowsum", st, 0.0, 4.0 * gm.unit());
+    rowsum_wcat_kernel<T><<<4 * CW, 256, 0, st>>>((const T*)dpg, M, g->p_in_b, g->g_in_b);
     TRI_LAUNCH_OK();
   }
   {
     GemmPlan p;   // dz = dPG Wcat + dgo Wgo
     p.a[0] = rows_operand(dpg, 4 * CW, M, false);
+    p.a[0].mn_major = true; p.a[0].inner = M; p.a[0].outer = 4 * CW; p.a[0].st_outer = M;   // A(m = pixel, k = row of dPG): m contiguous
     p.b[0] = rows_operand(pr.wcat, CW, 4 * CW, true);   // B(n = c, k = row of Wcat): n contiguous
     p.a[1] = rows_operand(dgo, CW, M, false);
     p.b[1] = rows_operand(w->g_out_w, CW, CW, true);
