@@ -292,6 +292,7 @@ struct AttnBwdArgs {
   void* out1;            // dv
   int64_t out0_st[4], out1_st[4];
   uint32_t idesc_a, idesc_b;   // the two MMA shapes of the kernel
+  int row_chunks;              // MODE_DBIAS: the row loop is split into this many CTAs, each writing its own partial
   int* err;
 };
 
@@ -343,7 +344,7 @@ attn_bwd_rows_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_const
 
   const int tid = threadIdx.x, warp = tid >> 5;
   const int qblocks = (a.N + 127) / 128;
-  int z = blockIdx.x, b, h, s = 0, qb, kvb = 0, nsteps;
+  int z = blockIdx.x, b, h, s = 0, qb, kvb = 0, nsteps, s_lo = 0, rc = 0;
   if constexpr (MODE == MODE_DQ) {
     qb = z % qblocks; z /= qblocks;
     h = z % a.H; z /= a.H;
@@ -353,8 +354,11 @@ attn_bwd_rows_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_const
     const int kblocks = (a.N + TKV - 1) / TKV;
     kvb = z % kblocks; z /= kblocks;
     qb = z % qblocks; z /= qblocks;
-    h = z % a.H; b = z / a.H;
-    nsteps = a.S;
+    h = z % a.H; z /= a.H;
+    b = z % a.B; rc = z / a.B;
+    const int per = (a.S + a.row_chunks - 1) / a.row_chunks;
+    s_lo = rc * per;
+    nsteps = max(0, min(a.S, s_lo + per) - s_lo);
   }
   const int q0 = qb * 128;
   const int bias_b = b * a.bias_b_mul;
@@ -384,10 +388,10 @@ attn_bwd_rows_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_const
       tma_load_5d(sV + stg * G::TB, &tmV, &bar_in[stg], 0, h, step * TKV, s, b);
     } else {
       mbar_expect_tx(&bar_in[stg], 2 * G::TB + 2 * G::TA);
-      tma_load_5d(sQ + stg * G::TA, &tmQ, &bar_in[stg], 0, h, q0, step, b);
-      tma_load_5d(sDO + stg * G::TA, &tmDO, &bar_in[stg], 0, h, q0, step, b);
-      tma_load_5d(sK + stg * G::TB, &tmK, &bar_in[stg], 0, h, kvb * TKV, step, b);
-      tma_load_5d(sV + stg * G::TB, &tmV, &bar_in[stg], 0, h, kvb * TKV, step, b);
+      tma_load_5d(sQ + stg * G::TA, &tmQ, &bar_in[stg], 0, h, q0, s_lo + step, b);
+      tma_load_5d(sDO + stg * G::TA, &tmDO, &bar_in[stg], 0, h, q0, s_lo + step, b);
+      tma_load_5d(sK + stg * G::TB, &tmK, &bar_in[stg], 0, h, kvb * TKV, s_lo + step, b);
+      tma_load_5d(sV + stg * G::TB, &tmV, &bar_in[stg], 0, h, kvb * TKV, s_lo + step, b);
     }
   };
 
@@ -426,9 +430,9 @@ attn_bwd_rows_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_const
   for (int j = 0; j < nsteps; ++j) {
     const int stg = j & 1;
     const uint32_t par = j & 1, in_par = (j >> 1) & 1;
-    const int row_s = MODE == MODE_DQ ? s : j;
+    const int row_s = MODE == MODE_DQ ? s : s_lo + j;
     const int k0 = MODE == MODE_DQ ? j * TKV : kvb * TKV;
-    if constexpr (MODE == MODE_DBIAS) load_stats(j);
+    if constexpr (MODE == MODE_DBIAS) load_stats(s_lo + j);
     if (tid == 0) {
       if (MODE == MODE_DQ && j == 0) ok = mbar_wait(bar_once, 0, a.err, 22);
       ok = mbar_wait(&bar_in[stg], in_par, a.err, 23) && ok;
@@ -540,7 +544,8 @@ attn_bwd_rows_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_const
     }
   } else {
     if (q_ok && ok) {
-      float* row = reinterpret_cast<float*>(a.out0) + (((long long)b * a.H + h) * a.N + qi) * a.N + kvb * TKV;
+      float* row = reinterpret_cast<float*>(a.out0) + (long long)rc * a.B * a.H * a.N * a.N +
+                   (((long long)b * a.H + h) * a.N + qi) * a.N + kvb * TKV;
       const int valid = a.N - kvb * TKV;
       if (valid >= TKV && (a.N % 4) == 0) {
 #pragma unroll
@@ -800,6 +805,16 @@ __global__ void attn_delta_tc_kernel(TriAttnDesc d, const T* o, const T* d_o, fl
   delta[idx] = acc;
 }
 
+__global__ void sum_partials_kernel(const float* partial, int nparts, long long n, float* out) {
+  const long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x;
+  if (i >= n) return;
+  float s = 0.f;
+  for (int p = 0; p < nparts; ++p) s += partial[p * n + i];
+  out[i] = s;
+}
+
+constexpr int kDbiasRowChunks = 4;
+
 // rank-5 map with a caller-chosen number of residues per box
 int qkv_map_rows(CUtensorMap* out, const void* p, const TriAttnDesc* d, const int64_t* st, int rows) {
   const uint64_t dims[5] = {(uint64_t)d->D, (uint64_t)d->H, (uint64_t)d->n_res, (uint64_t)d->n_seq, (uint64_t)d->B};
@@ -825,7 +840,7 @@ int set_dyn_smem(KernelT kern, int bytes) {
 template <typename T, int HD>
 int bwd_launch(const TriAttnDesc* d, const void* q, const void* k, const void* v, const void* bias,
                const uint8_t* mask, const void* o, const float* stats, const void* d_o, void* dq, void* dk, void* dv,
-               float* dbias, int* err, float* delta, cudaStream_t st) {
+               float* dbias, int* err, float* delta, float* dbias_partial, cudaStream_t st) {
   const long long rows = (long long)d->B * d->n_seq * d->H * d->n_res;
   const double pairs = (double)rows * d->n_res;
   const double tensor_bytes = 2.0 * d->B * d->n_seq * (double)d->n_res * d->H * d->D;
@@ -839,6 +854,7 @@ int bwd_launch(const TriAttnDesc* d, const void* q, const void* k, const void* v
   a.B = d->B; a.S = d->n_seq; a.N = d->n_res; a.H = d->H; a.scale = d->scale;
   a.stats = stats; a.delta = delta; a.mask = mask; a.mask_st[0] = d->mask_st[0]; a.mask_st[1] = d->mask_st[1];
   a.has_bias = bias != nullptr; a.bias_b_mul = d->bias_st[0] != 0 ? 1 : 0; a.err = err;
+  a.row_chunks = 1;
   const int qblocks = (d->n_res + 127) / 128;
   CUtensorMap tq, tdo, tk, tv, tb;
 
@@ -882,14 +898,21 @@ int bwd_launch(const TriAttnDesc* d, const void* q, const void* k, const void* v
   if (dbias != nullptr) {
     TRI_TRY(qkv_map_rows(&tk, k, d, d->k_st, 128));
     TRI_TRY(qkv_map_rows(&tv, v, d, d->v_st, 128));
-    a.out0 = dbias;
+    const int chunks = d->n_seq >= 2 * kDbiasRowChunks ? kDbiasRowChunks : 1;
+    const long long nb = (long long)d->B * d->H * d->n_res * d->n_res;
+    a.row_chunks = chunks;
+    a.out0 = chunks > 1 ? dbias_partial : dbias;
     a.idesc_a = make_idesc(kind, 128, 128, false, false);
     auto kern = attn_bwd_rows_kernel<T, HD, 128, MODE_DBIAS>;
     static bool configured = false;
     if (!configured) { TRI_TRY(set_dyn_smem(kern, GeoR<HD, 128, MODE_DBIAS>::SMEM)); configured = true; }
     KernelTimer kt("tc_attn_bwd_dbias", st, 0.0, 4.0 * tensor_bytes);
-    kern<<<(unsigned)((long long)qblocks * qblocks * d->B * d->H), 128, GeoR<HD, 128, MODE_DBIAS>::SMEM, st>>>(tq, tdo, tk, tv, tb, a);
+    kern<<<(unsigned)((long long)qblocks * qblocks * d->B * d->H * chunks), 128, GeoR<HD, 128, MODE_DBIAS>::SMEM, st>>>(tq, tdo, tk, tv, tb, a);
     TRI_LAUNCH_OK();
+    if (chunks > 1) {   // fixed-order sum of the row-chunk partials
+      sum_partials_kernel<<<cdiv(nb, 256), 256, 0, st>>>(dbias_partial, chunks, nb, dbias);
+      TRI_LAUNCH_OK();
+    }
   }
   return 0;
 }
@@ -972,7 +995,8 @@ bool attn_bwd_supported(const TriAttnDesc* d) {
 
 size_t attn_ws_bytes(const TriAttnDesc* d, int is_bwd) {
   if (!is_bwd) return 512;
-  return 512 + align_up((size_t)d->B * d->n_seq * d->H * d->n_res * sizeof(float));
+  return 512 + align_up((size_t)d->B * d->n_seq * d->H * d->n_res * sizeof(float)) +
+         align_up((size_t)kDbiasRowChunks * d->B * d->H * d->n_res * d->n_res * sizeof(float));
 }
 
 int attn_forward(const TriAttnDesc* d, const void* q, const void* k, const void* v, const void* bias,
@@ -995,12 +1019,14 @@ int attn_backward(const TriAttnDesc* d, const void* q, const void* k, const void
   TRI_CUDA_OK(cudaMemsetAsync(ws, 0, 256, st));
   int* err = static_cast<int*>(ws);
   float* delta = reinterpret_cast<float*>(static_cast<char*>(ws) + 512);
+  float* part = reinterpret_cast<float*>(static_cast<char*>(ws) + 512 +
+                                         align_up((size_t)d->B * d->n_seq * d->H * d->n_res * sizeof(float)));
   if (d->dtype == TRI_BF16) {
-    if (d->D == 32) return bwd_launch<__nv_bfloat16, 32>(d, q, k, v, bias, mask, o, lse, d_o, dq, dk, dv, dbias, err, delta, st);
-    return bwd_launch<__nv_bfloat16, 64>(d, q, k, v, bias, mask, o, lse, d_o, dq, dk, dv, dbias, err, delta, st);
+    if (d->D == 32) return bwd_launch<__nv_bfloat16, 32>(d, q, k, v, bias, mask, o, lse, d_o, dq, dk, dv, dbias, err, delta, part, st);
+    return bwd_launch<__nv_bfloat16, 64>(d, q, k, v, bias, mask, o, lse, d_o, dq, dk, dv, dbias, err, delta, part, st);
   }
-  if (d->D == 32) return bwd_launch<__half, 32>(d, q, k, v, bias, mask, o, lse, d_o, dq, dk, dv, dbias, err, delta, st);
-  return bwd_launch<__half, 64>(d, q, k, v, bias, mask, o, lse, d_o, dq, dk, dv, dbias, err, delta, st);
+  if (d->D == 32) return bwd_launch<__half, 32>(d, q, k, v, bias, mask, o, lse, d_o, dq, dk, dv, dbias, err, delta, part, st);
+  return bwd_launch<__half, 64>(d, q, k, v, bias, mask, o, lse, d_o, dq, dk, dv, dbias, err, delta, part, st);
 }
 
 }  // namespace tc
