@@ -165,7 +165,7 @@ attn_fwd_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
 
     // ---- logits into registers, running max --------------------------------------------------
     float x[128];
-    float mx = -INFINITY;
+    float mx4[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};   // independent chains: no 128-long dependency
 #pragma unroll
     for (int c = 0; c < 4; ++c) {
       uint32_t r[32];
@@ -185,27 +185,28 @@ attn_fwd_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
           if (a.has_bias) v += bv[i];
           v += sMb[col];
           x[col] = v;
-          mx = fmaxf(mx, v);
+          mx4[i & 3] = fmaxf(mx4[i & 3], v);
         }
       }
     }
+    const float mx = fmaxf(fmaxf(mx4[0], mx4[1]), fmaxf(mx4[2], mx4[3]));
     const float m_new = fmaxf(m_run, mx);
     const float alpha = ex2_approx((m_run - m_new) * kLog2e);
-    float psum = 0.f;
+    float ps4[4] = {0.f, 0.f, 0.f, 0.f};
 #pragma unroll
     for (int g = 0; g < 16; ++g) {
       float p[8];
 #pragma unroll
       for (int i = 0; i < 8; ++i) {
         p[i] = ex2_approx((x[g * 8 + i] - m_new) * kLog2e);
-        psum += p[i];
+        ps4[i & 3] += p[i];
       }
       uint4 pk;
       pk.x = pack2<T>(p[0], p[1]); pk.y = pack2<T>(p[2], p[3]);
       pk.z = pack2<T>(p[4], p[5]); pk.w = pack2<T>(p[6], p[7]);
       *reinterpret_cast<uint4*>(sP + sw128_chunk(tid, g)) = pk;
     }
-    l_run = l_run * alpha + psum;
+    l_run = l_run * alpha + ((ps4[0] + ps4[1]) + (ps4[2] + ps4[3]));
     m_run = m_new;
     fence_proxy_async_smem();
     tc_fence_before_sync();
