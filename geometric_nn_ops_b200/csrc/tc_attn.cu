@@ -58,12 +58,15 @@ __device__ __forceinline__ int sw128_chunk(int r, int g) {
   return (g >> 3) * 16384 + r * 128 + (((g & 7) ^ (r & 7)) << 4);
 }
 
-template <typename T>
-__device__ __forceinline__ uint32_t pack2(float a, float b) {
-  union { uint32_t u; T h[2]; } pk;
-  pk.h[0] = from_f32<T>(a);
-  pk.h[1] = from_f32<T>(b);
-  return pk.u;
+// two fp32 -> one packed pair of 16-bit values with a single conversion instruction
+template <typename T> __device__ __forceinline__ uint32_t pack2(float a, float b);
+template <> __device__ __forceinline__ uint32_t pack2<__nv_bfloat16>(float a, float b) {
+  __nv_bfloat162 v = __floats2bfloat162_rn(a, b);
+  return *reinterpret_cast<uint32_t*>(&v);
+}
+template <> __device__ __forceinline__ uint32_t pack2<__half>(float a, float b) {
+  __half2 v = __floats2half2_rn(a, b);
+  return *reinterpret_cast<uint32_t*>(&v);
 }
 template <typename T>
 __device__ __forceinline__ void unpack8(const uint4& v, float (&f)[8]) {
@@ -320,8 +323,8 @@ template <int HD, int TKV, int MODE> struct GeoR {
   static constexpr int SMEM = OFF_BAR + 128 + 1024;
 };
 
-template <typename T, int HD, int TKV, int MODE>
-__global__ void __launch_bounds__(128, 2)
+template <typename T, int HD, int TKV, int MODE, int HALVES>
+__global__ void __launch_bounds__(128 * HALVES, 2)
 attn_bwd_rows_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmDO,
                      const __grid_constant__ CUtensorMap tmK, const __grid_constant__ CUtensorMap tmV,
                      const __grid_constant__ CUtensorMap tmBias, const AttnBwdArgs a) {
@@ -343,7 +346,10 @@ attn_bwd_rows_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_const
   uint64_t* bar_dq = bar_once + 5;
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bar_once + 6);
 
-  const int tid = threadIdx.x, warp = tid >> 5;
+  // 128 * HALVES threads: thread (r, hh) owns row r of the tile and, with HALVES == 2, the column half hh,
+  // so an SM holds twice the warps for the same shared memory and TMEM.  That pays for the dQ pass
+  // (2.03 -> 1.81 ms at N=768); the dbias pass, with its register accumulators, is faster with one thread per row.
+  const int tid = threadIdx.x, warp = tid >> 5, r = tid & 127, hh = tid >> 7;
   const int qblocks = (a.N + 127) / 128;
   int z = blockIdx.x, b, h, s = 0, qb, kvb = 0, nsteps, s_lo = 0, rc = 0;
   if constexpr (MODE == MODE_DQ) {
@@ -374,8 +380,10 @@ attn_bwd_rows_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_const
   __syncthreads();
   tc_fence_after_sync();
   const uint32_t tmem_base = *tmem_slot;
-  const uint32_t t_row = tmem_base + ((uint32_t)(warp * 32) << 16);
+  const uint32_t t_row = tmem_base + ((uint32_t)((warp & 3) * 32) << 16);
   constexpr uint32_t COL_DP = TKV, COL_DQ = 2 * TKV;
+  constexpr int CPT = TKV / 32 / HALVES;   // 32-column chunks per thread
+  constexpr int COLS = TKV / HALVES;       // columns per thread
 
   auto load_bias = [&](int k0) {
 #pragma unroll
@@ -409,7 +417,7 @@ attn_bwd_rows_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_const
     for (int st = 0; st < 2 && st < nsteps; ++st) load_step(st, st);
   }
 
-  const int qi = q0 + tid;
+  const int qi = q0 + r;
   const bool q_ok = qi < a.N;
   const long long plane = (long long)a.B * a.S * a.H * a.N;
   float m_row = 0.f, l_row = 0.f, d_row = 0.f;
@@ -420,10 +428,10 @@ attn_bwd_rows_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_const
     }
   };
   if constexpr (MODE == MODE_DQ) load_stats(s);
-  float acc[MODE == MODE_DBIAS ? TKV : 1];
+  float acc[MODE == MODE_DBIAS ? TKV / HALVES : 1];
   if constexpr (MODE == MODE_DBIAS) {
 #pragma unroll
-    for (int i = 0; i < TKV; ++i) acc[i] = 0.f;
+    for (int i = 0; i < TKV / HALVES; ++i) acc[i] = 0.f;
   }
   bool ok = true;
   if (MODE == MODE_DBIAS && a.has_bias) ok = mbar_wait(bar_once, 0, a.err, 21);
@@ -466,7 +474,8 @@ attn_bwd_rows_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_const
     if (MODE == MODE_DQ && tid == 0 && j > 0 && j + 1 < nsteps) load_step(j + 1, (j + 1) & 1);
 
 #pragma unroll
-    for (int c = 0; c < TKV / 32; ++c) {
+    for (int cc = 0; cc < CPT; ++cc) {
+      const int c = hh * CPT + cc;
       uint32_t rs[32], rp[32];
       tmem_ld_32x32(t_row + c * 32, rs);
       tmem_ld_32x32(t_row + COL_DP + c * 32, rp);
@@ -476,7 +485,7 @@ attn_bwd_rows_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_const
         float bv[8], ds[8];
         if (a.has_bias) {
           const int g = c * 4 + u;
-          const uint4 raw = *reinterpret_cast<const uint4*>(sBias + (g >> 3) * 16384 + sw128_chunk1(tid, g & 7));
+          const uint4 raw = *reinterpret_cast<const uint4*>(sBias + (g >> 3) * 16384 + sw128_chunk1(r, g & 7));
           unpack8<T>(raw, bv);
         }
 #pragma unroll
@@ -487,13 +496,13 @@ attn_bwd_rows_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_const
           x += sMb[col];
           const float p = ex2_approx(((x - m_row) - l_row) * kLog2e);
           ds[i] = p * (__uint_as_float(rp[u * 8 + i]) - d_row);
-          if constexpr (MODE == MODE_DBIAS) acc[col] += ds[i];
+          if constexpr (MODE == MODE_DBIAS) acc[cc * 32 + u * 8 + i] += ds[i];
         }
         if constexpr (MODE == MODE_DQ) {
           uint4 pk;
           pk.x = pack2<T>(ds[0], ds[1]); pk.y = pack2<T>(ds[2], ds[3]);
           pk.z = pack2<T>(ds[4], ds[5]); pk.w = pack2<T>(ds[6], ds[7]);
-          *reinterpret_cast<uint4*>(sDS + sw128_chunk1(tid, c * 4 + u)) = pk;
+          *reinterpret_cast<uint4*>(sDS + sw128_chunk1(r, c * 4 + u)) = pk;
         }
       }
     }
@@ -523,7 +532,7 @@ attn_bwd_rows_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_const
     tc_fence_after_sync();
     {
       // tcgen05.ld is warp-collective: every thread loads, only valid rows store
-      const bool st_ok = q_ok && ok;
+      const bool st_ok = q_ok && ok && hh == 0;
       T* row = reinterpret_cast<T*>(a.out0) + b * a.out0_st[0] + s * a.out0_st[1] + qi * a.out0_st[2] + h * a.out0_st[3];
 #pragma unroll
       for (int c = 0; c < HD / 32; ++c) {
@@ -546,15 +555,15 @@ attn_bwd_rows_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_const
   } else {
     if (q_ok && ok) {
       float* row = reinterpret_cast<float*>(a.out0) + (long long)rc * a.B * a.H * a.N * a.N +
-                   (((long long)b * a.H + h) * a.N + qi) * a.N + kvb * TKV;
-      const int valid = a.N - kvb * TKV;
-      if (valid >= TKV && (a.N % 4) == 0) {
+                   (((long long)b * a.H + h) * a.N + qi) * a.N + kvb * TKV + hh * COLS;
+      const int valid = a.N - kvb * TKV - hh * COLS;
+      if (valid >= COLS && (a.N % 4) == 0) {
 #pragma unroll
-        for (int i = 0; i < TKV / 4; ++i)
+        for (int i = 0; i < COLS / 4; ++i)
           reinterpret_cast<float4*>(row)[i] = make_float4(acc[4 * i], acc[4 * i + 1], acc[4 * i + 2], acc[4 * i + 3]);
       } else {
 #pragma unroll
-        for (int i = 0; i < TKV; ++i)
+        for (int i = 0; i < COLS; ++i)
           if (i < valid) row[i] = acc[i];
       }
     }
@@ -589,7 +598,7 @@ template <int HD> struct GeoC {
 };
 
 template <typename T, int HD>
-__global__ void __launch_bounds__(128, 2)
+__global__ void __launch_bounds__(256, 2)
 attn_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmDO,
                      const __grid_constant__ CUtensorMap tmK, const __grid_constant__ CUtensorMap tmV,
                      const __grid_constant__ CUtensorMap tmBias, const AttnBwdArgs a) {
@@ -613,7 +622,8 @@ attn_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_const
   uint64_t* bar_acc = bar_kv + 5;
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bar_kv + 6);
 
-  const int tid = threadIdx.x, warp = tid >> 5;
+  // 256 threads: thread (r, hh) owns key r of the block and query half hh of each 64-query tile
+  const int tid = threadIdx.x, warp = tid >> 5, r = tid & 127, hh = tid >> 7;
   const int kblocks = (a.N + 127) / 128;
   int z = blockIdx.x;
   const int kvb = z % kblocks; z /= kblocks;
@@ -634,7 +644,7 @@ attn_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_const
   __syncthreads();
   tc_fence_after_sync();
   const uint32_t tmem_base = *tmem_slot;
-  const uint32_t t_row = tmem_base + ((uint32_t)(warp * 32) << 16);
+  const uint32_t t_row = tmem_base + ((uint32_t)((warp & 3) * 32) << 16);
   constexpr uint32_t COL_DP = 64, COL_DV = 128, COL_DK = 128 + HD;
 
   auto load_step = [&](int step, int stg) {
@@ -654,7 +664,7 @@ attn_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_const
     for (int st = 0; st < 2 && st < nsteps; ++st) load_step(st, st);
     if (a.has_bias) load_bias(0);
   }
-  const int kj = k0 + tid;
+  const int kj = k0 + r;
   float mb = 0.f;
   if (kj >= a.N) mb = -INFINITY;
   else if (a.mask != nullptr) mb = kMaskSentinel * ((a.mask[b * a.mask_st[0] + s * a.mask_st[1] + kj] ? 1.0f : 0.0f) - 1.0f);
@@ -695,10 +705,10 @@ attn_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_const
     if (j > 0) ok = mbar_wait(bar_acc, (j - 1) & 1, a.err, 35) && ok;   // P^T / dS^T buffers and the other stage are free
     if (tid == 0 && j > 0 && j + 1 < nsteps) load_step(j + 1, (j + 1) & 1);
 
-    const uint8_t* bias_col = sBias + (tid >> 6) * 8192 + (tid & 7) * 2;  // element (q, key tid): + q*128 + swizzled chunk
-    const int key_chunk = (tid & 63) >> 3;
-#pragma unroll
-    for (int c = 0; c < 2; ++c) {
+    const uint8_t* bias_col = sBias + (r >> 6) * 8192 + (r & 7) * 2;  // element (q, key r): + q*128 + swizzled chunk
+    const int key_chunk = (r & 63) >> 3;
+    {
+      const int c = hh;
       uint32_t rs[32], rp[32];
       tmem_ld_32x32(t_row + c * 32, rs);
       tmem_ld_32x32(t_row + COL_DP + c * 32, rp);
@@ -718,10 +728,10 @@ attn_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_const
         uint4 pk;
         pk.x = pack2<T>(pv[0], pv[1]); pk.y = pack2<T>(pv[2], pv[3]);
         pk.z = pack2<T>(pv[4], pv[5]); pk.w = pack2<T>(pv[6], pv[7]);
-        *reinterpret_cast<uint4*>(sPT + sw128_chunk1(tid, c * 4 + u)) = pk;
+        *reinterpret_cast<uint4*>(sPT + sw128_chunk1(r, c * 4 + u)) = pk;
         pk.x = pack2<T>(ds[0], ds[1]); pk.y = pack2<T>(ds[2], ds[3]);
         pk.z = pack2<T>(ds[4], ds[5]); pk.w = pack2<T>(ds[6], ds[7]);
-        *reinterpret_cast<uint4*>(sDST + sw128_chunk1(tid, c * 4 + u)) = pk;
+        *reinterpret_cast<uint4*>(sDST + sw128_chunk1(r, c * 4 + u)) = pk;
       }
     }
     fence_proxy_async_smem();
@@ -749,7 +759,7 @@ attn_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_const
   ok = mbar_wait(bar_acc, (nsteps - 1) & 1, a.err, 36) && ok;
   tc_fence_after_sync();
   {
-    const bool st_ok = kj < a.N && ok;
+    const bool st_ok = kj < a.N && ok && hh == 0;
     T* krow = reinterpret_cast<T*>(a.out0) + b * a.out0_st[0] + s * a.out0_st[1] + kj * a.out0_st[2] + h * a.out0_st[3];
     T* vrow = reinterpret_cast<T*>(a.out1) + b * a.out1_st[0] + s * a.out1_st[1] + kj * a.out1_st[2] + h * a.out1_st[3];
 #pragma unroll
@@ -874,7 +884,7 @@ int bwd_launch(const TriAttnDesc* d, const void* q, const void* k, const void* v
     static bool configured = false;
     if (!configured) { TRI_TRY(set_dyn_smem(kern, GeoC<HD>::SMEM)); configured = true; }
     KernelTimer kt("tc_attn_bwd_dkdv", st, 8.0 * pairs * d->D, 6.0 * tensor_bytes);
-    kern<<<(unsigned)((long long)qblocks * d->B * d->n_seq * d->H), 128, GeoC<HD>::SMEM, st>>>(tq, tdo, tk, tv, tb, a);
+    kern<<<(unsigned)((long long)qblocks * d->B * d->n_seq * d->H), 256, GeoC<HD>::SMEM, st>>>(tq, tdo, tk, tv, tb, a);
     TRI_LAUNCH_OK();
   }
   // ---- dQ ------------------------------------------------------------------------------------
@@ -888,11 +898,11 @@ int bwd_launch(const TriAttnDesc* d, const void* q, const void* k, const void* v
   a.idesc_a = make_idesc(kind, 128, 64, false, false);
   a.idesc_b = make_idesc(kind, 128, HD, false, true);
   {
-    auto kern = attn_bwd_rows_kernel<T, HD, 64, MODE_DQ>;
+    auto kern = attn_bwd_rows_kernel<T, HD, 64, MODE_DQ, 2>;
     static bool configured = false;
     if (!configured) { TRI_TRY(set_dyn_smem(kern, GeoR<HD, 64, MODE_DQ>::SMEM)); configured = true; }
     KernelTimer kt("tc_attn_bwd_dq", st, 2.0 * pairs * d->D, 5.0 * tensor_bytes);
-    kern<<<(unsigned)((long long)qblocks * d->B * d->n_seq * d->H), 128, GeoR<HD, 64, MODE_DQ>::SMEM, st>>>(tq, tdo, tk, tv, tb, a);
+    kern<<<(unsigned)((long long)qblocks * d->B * d->n_seq * d->H), 256, GeoR<HD, 64, MODE_DQ>::SMEM, st>>>(tq, tdo, tk, tv, tb, a);
     TRI_LAUNCH_OK();
   }
   // ---- dbias ---------------------------------------------------------------------------------
@@ -904,7 +914,7 @@ int bwd_launch(const TriAttnDesc* d, const void* q, const void* k, const void* v
     a.row_chunks = chunks;
     a.out0 = chunks > 1 ? dbias_partial : dbias;
     a.idesc_a = make_idesc(kind, 128, 128, false, false);
-    auto kern = attn_bwd_rows_kernel<T, HD, 128, MODE_DBIAS>;
+    auto kern = attn_bwd_rows_kernel<T, HD, 128, MODE_DBIAS, 1>;
     static bool configured = false;
     if (!configured) { TRI_TRY(set_dyn_smem(kern, GeoR<HD, 128, MODE_DBIAS>::SMEM)); configured = true; }
     KernelTimer kt("tc_attn_bwd_dbias", st, 0.0, 4.0 * tensor_bytes);
@@ -917,6 +927,234 @@ int bwd_launch(const TriAttnDesc* d, const void* q, const void* k, const void* v
   }
   return 0;
 }
+
+// ------------------------------------------------------------------------------------------------
+// Forward, pipelined form: 64-key tiles, the logit accumulator S double buffered in TMEM so that
+// S(j+1) and S(j+2) are computed while the threads exponentiate tile j, P V(j) applied one step late,
+// bias tiles double buffered, K/V in a 4-stage ring.  One __syncthreads per tile.
+// ------------------------------------------------------------------------------------------------
+template <int HD> struct GeoP {
+  static constexpr int RB = HD * 2;
+  static constexpr int TQ = 128 * RB;                    // Q tile
+  static constexpr int TK = 64 * RB;                     // K or V tile (64 keys)
+  static constexpr uint32_t LAYOUT = RB == 128 ? 2 : 4;
+  static constexpr uint32_t SBO = 8 * RB;
+  static constexpr int NST = 4;                          // K/V stages
+  static constexpr int OFF_Q = 0;
+  static constexpr int OFF_K = OFF_Q + TQ;
+  static constexpr int OFF_V = OFF_K + NST * TK;
+  static constexpr int OFF_P = OFF_V + NST * TK;         // [128 x 64] SW128
+  static constexpr int OFF_BIAS = OFF_P + 16384;         // 2 x [128 x 64] SW128
+  static constexpr int OFF_BAR = OFF_BIAS + 2 * 16384;
+  static constexpr int OFF_MB = OFF_BAR + 128;           // additive mask term of the whole key row
+  static constexpr int SMEM_BASE = OFF_MB + 1024;        // + alignment slack; the mask row is added at launch
+};
+
+template <typename T, int HD>
+__global__ void __launch_bounds__(128, 2)
+attn_fwd_pipe_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmK,
+                     const __grid_constant__ CUtensorMap tmV, const __grid_constant__ CUtensorMap tmBias,
+                     const AttnArgs a) {
+  using G = GeoP<HD>;
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  uint8_t* sQ = smem + G::OFF_Q;
+  uint8_t* sK = smem + G::OFF_K;
+  uint8_t* sV = smem + G::OFF_V;
+  uint8_t* sP = smem + G::OFF_P;
+  uint8_t* sBias = smem + G::OFF_BIAS;
+  uint64_t* bar_q = reinterpret_cast<uint64_t*>(smem + G::OFF_BAR);
+  uint64_t* bar_kv = bar_q + 1;    // [4]
+  uint64_t* bar_bias = bar_q + 5;  // [2]
+  uint64_t* bar_s = bar_q + 7;     // [2]
+  uint64_t* bar_pv = bar_q + 9;
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bar_q + 10);
+  float* sMb = reinterpret_cast<float*>(smem + G::OFF_MB);
+
+  const int tid = threadIdx.x, warp = tid >> 5;
+  const int qblocks = (a.N + 127) / 128;
+  int z = blockIdx.x;
+  const int qb = z % qblocks; z /= qblocks;
+  const int h = z % a.H; z /= a.H;
+  const int s = z % a.S;
+  const int b = z / a.S;
+  const int q0 = qb * 128;
+  const int nt = (a.N + 63) / 64;
+  const int bias_b = b * a.bias_b_mul;
+
+  if (tid == 0) {
+    mbar_init(bar_q, 1);
+    for (int i = 0; i < 4; ++i) mbar_init(&bar_kv[i], 1);
+    for (int i = 0; i < 2; ++i) { mbar_init(&bar_bias[i], 1); mbar_init(&bar_s[i], 1); }
+    mbar_init(bar_pv, 1);
+    mbar_fence_init();
+  }
+  if (warp == 0) tmem_alloc(tmem_slot, 256);
+  for (int kj = tid; kj < nt * 64; kj += 128) {
+    float mb = 0.f;
+    if (kj >= a.N) mb = -INFINITY;
+    else if (a.mask != nullptr) mb = kMaskSentinel * ((a.mask[b * a.mask_st[0] + s * a.mask_st[1] + kj] ? 1.0f : 0.0f) - 1.0f);
+    sMb[kj] = mb;
+  }
+  tc_fence_before_sync();
+  __syncthreads();
+  tc_fence_after_sync();
+  const uint32_t tmem_base = *tmem_slot;
+  const uint32_t t_row = tmem_base + ((uint32_t)(warp * 32) << 16);
+  constexpr uint32_t COL_PV = 128;
+  bool ok = true;
+
+  auto load_kv = [&](int j) {
+    const int st = j & 3;
+    mbar_expect_tx(&bar_kv[st], 2 * G::TK);
+    tma_load_5d(sK + st * G::TK, &tmK, &bar_kv[st], 0, h, j * 64, s, b);
+    tma_load_5d(sV + st * G::TK, &tmV, &bar_kv[st], 0, h, j * 64, s, b);
+  };
+  auto load_bias = [&](int j) {
+    mbar_expect_tx(&bar_bias[j & 1], 16384);
+    tma_load_4d(sBias + (j & 1) * 16384, &tmBias, &bar_bias[j & 1], j * 64, q0, h, bias_b);
+  };
+  auto issue_s = [&](int j) {   // S(j) = Q K_j^T into TMEM buffer j & 1
+    ok = mbar_wait(&bar_kv[j & 3], (j >> 2) & 1, a.err, 12) && ok;
+    tc_fence_after_sync();
+    const uint32_t qa = smem_u32(sQ), ka = smem_u32(sK + (j & 3) * G::TK);
+#pragma unroll
+    for (int ks = 0; ks < HD / 16; ++ks)
+      umma<KIND_F16>(tmem_base + (j & 1) * 64, make_smem_desc(qa + ks * 32, 16, G::SBO, G::LAYOUT),
+                     make_smem_desc(ka + ks * 32, 16, G::SBO, G::LAYOUT), a.idesc_s, ks > 0);
+    umma_commit(&bar_s[j & 1]);
+  };
+
+  if (tid == 0) {
+    mbar_expect_tx(bar_q, G::TQ);
+    tma_load_5d(sQ, &tmQ, bar_q, 0, h, q0, s, b);
+    for (int j = 0; j < 3 && j < nt; ++j) load_kv(j);
+    if (a.has_bias) for (int j = 0; j < 2 && j < nt; ++j) load_bias(j);
+    ok = mbar_wait(bar_q, 0, a.err, 11);
+    issue_s(0);
+    if (nt > 1) issue_s(1);
+  }
+
+  float m_run = -INFINITY, l_run = 0.f, alpha_prev = 0.f;
+  float o_acc[HD];
+#pragma unroll
+  for (int i = 0; i < HD; ++i) o_acc[i] = 0.f;
+  auto add_pv = [&](float alpha) {
+#pragma unroll
+    for (int c = 0; c < HD / 32; ++c) {
+      uint32_t r[32];
+      tmem_ld_32x32(t_row + COL_PV + c * 32, r);
+      tmem_ld_wait();
+#pragma unroll
+      for (int i = 0; i < 32; ++i) o_acc[c * 32 + i] = o_acc[c * 32 + i] * alpha + __uint_as_float(r[i]);
+    }
+  };
+
+  for (int j = 0; j < nt; ++j) {
+    const int buf = j & 1;
+    const uint32_t par2 = (j >> 1) & 1;
+    ok = mbar_wait(&bar_s[buf], par2, a.err, 13) && ok;
+    if (a.has_bias) ok = mbar_wait(&bar_bias[buf], par2, a.err, 14) && ok;
+    tc_fence_after_sync();
+    float x[64];
+    float mx4[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
+    const float4* mb4 = reinterpret_cast<const float4*>(sMb + j * 64);
+    const uint8_t* bias_t = sBias + buf * 16384;
+#pragma unroll
+    for (int c = 0; c < 2; ++c) {
+      uint32_t r[32];
+      tmem_ld_32x32(t_row + buf * 64 + c * 32, r);
+      tmem_ld_wait();
+#pragma unroll
+      for (int u = 0; u < 4; ++u) {
+        float bv[8];
+        if (a.has_bias) {
+          const uint4 raw = *reinterpret_cast<const uint4*>(bias_t + sw128_chunk1(tid, c * 4 + u));
+          unpack8<T>(raw, bv);
+        }
+        const float4 m0 = mb4[c * 8 + u * 2], m1 = mb4[c * 8 + u * 2 + 1];
+        const float mbv[8] = {m0.x, m0.y, m0.z, m0.w, m1.x, m1.y, m1.z, m1.w};
+#pragma unroll
+        for (int i = 0; i < 8; ++i) {
+          float v = __uint_as_float(r[u * 8 + i]) * a.scale;
+          if (a.has_bias) v += bv[i];
+          v += mbv[i];
+          x[c * 32 + u * 8 + i] = v;
+          mx4[i & 3] = fmaxf(mx4[i & 3], v);
+        }
+      }
+    }
+    const float m_new = fmaxf(m_run, fmaxf(fmaxf(mx4[0], mx4[1]), fmaxf(mx4[2], mx4[3])));
+    const float alpha = ex2_approx((m_run - m_new) * kLog2e);
+    if (j > 0) {   // finish tile j-1: its P V product is done by now, and P's buffer is free again
+      ok = mbar_wait(bar_pv, (j - 1) & 1, a.err, 15) && ok;
+      tc_fence_after_sync();
+      add_pv(alpha_prev);
+    }
+    float ps4[4] = {0.f, 0.f, 0.f, 0.f};
+#pragma unroll
+    for (int g = 0; g < 8; ++g) {
+      float p[8];
+#pragma unroll
+      for (int i = 0; i < 8; ++i) {
+        p[i] = ex2_approx((x[g * 8 + i] - m_new) * kLog2e);
+        ps4[i & 3] += p[i];
+      }
+      uint4 pk;
+      pk.x = pack2<T>(p[0], p[1]); pk.y = pack2<T>(p[2], p[3]);
+      pk.z = pack2<T>(p[4], p[5]); pk.w = pack2<T>(p[6], p[7]);
+      *reinterpret_cast<uint4*>(sP + sw128_chunk1(tid, g)) = pk;
+    }
+    l_run = l_run * alpha + ((ps4[0] + ps4[1]) + (ps4[2] + ps4[3]));
+    m_run = m_new;
+    alpha_prev = alpha;
+    fence_proxy_async_smem();
+    tc_fence_before_sync();
+    __syncthreads();
+    if (tid == 0) {
+      tc_fence_after_sync();
+      const uint32_t pa = smem_u32(sP), va = smem_u32(sV + (j & 3) * G::TK);
+#pragma unroll
+      for (int kk = 0; kk < 4; ++kk)
+        umma<KIND_F16>(tmem_base + COL_PV, make_smem_desc(pa + kk * 32, 16, 1024, 2),
+                       make_smem_desc(va + kk * 16 * G::RB, 64 * G::RB, G::SBO, G::LAYOUT), a.idesc_pv, kk > 0);
+      umma_commit(bar_pv);
+      if (j + 3 < nt) load_kv(j + 3);          // its stage held tile j-1, whose P V has completed
+      if (j + 2 < nt) {
+        if (a.has_bias) load_bias(j + 2);      // every thread is past its reads of bias(j)
+        issue_s(j + 2);                        // ... and of S(j): reuse both buffers
+      }
+    }
+    if (!ok) break;
+  }
+  ok = mbar_wait(bar_pv, (nt - 1) & 1, a.err, 15) && ok;
+  tc_fence_after_sync();
+  add_pv(alpha_prev);
+  const int qi = q0 + tid;
+  if (qi < a.N && ok) {
+    const float inv = 1.0f / l_run;
+    T* orow = reinterpret_cast<T*>(a.o) + b * a.o_st[0] + s * a.o_st[1] + qi * a.o_st[2] + h * a.o_st[3];
+#pragma unroll
+    for (int g = 0; g < HD / 8; ++g) {
+      uint4 pk;
+      pk.x = pack2<T>(o_acc[g * 8 + 0] * inv, o_acc[g * 8 + 1] * inv);
+      pk.y = pack2<T>(o_acc[g * 8 + 2] * inv, o_acc[g * 8 + 3] * inv);
+      pk.z = pack2<T>(o_acc[g * 8 + 4] * inv, o_acc[g * 8 + 5] * inv);
+      pk.w = pack2<T>(o_acc[g * 8 + 6] * inv, o_acc[g * 8 + 7] * inv);
+      reinterpret_cast<uint4*>(orow)[g] = pk;
+    }
+    const long long row = (((long long)b * a.S + s) * a.H + h) * a.N + qi;
+    a.stats[row] = m_run;
+    a.stats[(long long)a.B * a.S * a.H * a.N + row] = logf(l_run);
+  }
+  tc_fence_before_sync();
+  __syncthreads();
+  if (warp == 0) {
+    tc_fence_after_sync();
+    tmem_dealloc(tmem_base, 256);
+  }
+}
+
 
 bool forced_simt() {
   const char* e = getenv("TRI_B200_FORCE_SIMT");
@@ -962,16 +1200,34 @@ int fwd_launch(const TriAttnDesc* d, const void* q, const void* k, const void* v
   } else {
     tb = tq;
   }
-  auto kern = attn_fwd_tc_kernel<T, HD>;
-  static bool configured = false;
-  if (!configured) {
-    TRI_CUDA_OK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, Geo<HD>::SMEM));
-    configured = true;
-  }
   const long long blocks = (long long)((d->n_res + 127) / 128) * d->B * d->n_seq * d->H;
   const double pairs = (double)d->B * d->n_seq * d->H * d->n_res * (double)d->n_res;
   KernelTimer kt("tc_attn_fwd", st, 4.0 * pairs * d->D, 2.0 * 4.0 * d->B * d->n_seq * (double)d->n_res * d->H * d->D);
-  kern<<<(unsigned)blocks, 128, Geo<HD>::SMEM, st>>>(tq, tk, tv, tb, a);
+  // The pipelined 64-key-tile variant (TRI_B200_ATTN_FWD_PIPE=1) measures slower (1.70 vs 1.40 ms at N=768):
+  // the forward is bound by instruction issue in the softmax warps, not by MMA latency.
+  static const bool unpipelined = getenv("TRI_B200_ATTN_FWD_PIPE") == nullptr;
+  if (unpipelined) {
+    auto kern = attn_fwd_tc_kernel<T, HD>;
+    static bool configured = false;
+    if (!configured) {
+      TRI_CUDA_OK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, Geo<HD>::SMEM));
+      configured = true;
+    }
+    kern<<<(unsigned)blocks, 128, Geo<HD>::SMEM, st>>>(tq, tk, tv, tb, a);
+    TRI_LAUNCH_OK();
+    return 0;
+  }
+  TRI_TRY(qkv_map_rows(&tk, k, d, d->k_st, 64));
+  TRI_TRY(qkv_map_rows(&tv, v, d, d->v_st, 64));
+  a.idesc_s = make_idesc(kind, 128, 64, false, false);
+  auto kern = attn_fwd_pipe_kernel<T, HD>;
+  const int smem = GeoP<HD>::SMEM_BASE + ((d->n_res + 63) / 64) * 256;
+  static int configured = 0;
+  if (configured < smem) {
+    TRI_CUDA_OK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
+    configured = smem;
+  }
+  kern<<<(unsigned)blocks, 128, smem, st>>>(tq, tk, tv, tb, a);
   TRI_LAUNCH_OK();
   return 0;
 }
@@ -982,7 +1238,7 @@ bool attn_fwd_supported(const TriAttnDesc* d) {
   if (forced_simt()) return false;
   if (d->dtype != TRI_BF16 && d->dtype != TRI_F16) return false;
   if (d->D != 32 && d->D != 64) return false;
-  if (d->n_res % 8 != 0) return false;
+  if (d->n_res % 8 != 0 || d->n_res > 16384) return false;
   if (!strides_ok(d->q_st) || !strides_ok(d->k_st) || !strides_ok(d->v_st) || !strides_ok(d->o_st)) return false;
   if (d->bias_st[1] % 8 != 0 || d->bias_st[2] % 8 != 0 || d->bias_st[0] % 8 != 0) return false;
   if ((long long)((d->n_res + 127) / 128) * d->B * d->n_seq * d->H > 2147483647LL) return false;

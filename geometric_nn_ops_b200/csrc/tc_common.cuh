@@ -15,7 +15,11 @@ namespace tc {
 // ---------------------------------------------------------------------------------------------
 // device error word (one per launch, zeroed by the host before the launch)
 // ---------------------------------------------------------------------------------------------
-constexpr uint32_t kSpinLimit = 1u << 26;  // ~ a second or two of polling
+// A try_wait suspends the thread in hardware until the phase completes or kWaitHintNs elapse, so a waiting
+// warp issues almost no instructions (a bare polling loop took a third of all issue slots in the attention
+// kernels).  Every wait gives up after kWaitLimitCycles SM clocks (about two seconds).
+constexpr uint32_t kWaitHintNs = 1000000;
+constexpr long long kWaitLimitCycles = 4000000000LL;
 
 __device__ __forceinline__ void report_timeout(int* err, int code) {
   if (err != nullptr) atomicCAS(err, 0, code);
@@ -42,18 +46,23 @@ __device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity) {
   uint32_t ok;
   asm volatile(
       "{\n\t.reg .pred p;\n\t"
-      "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+      "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2, %3;\n\t"
       "selp.u32 %0, 1, 0, p;\n\t}"
       : "=r"(ok)
-      : "r"(smem_u32(bar)), "r"(parity)
+      : "r"(smem_u32(bar)), "r"(parity), "r"(kWaitHintNs)
       : "memory");
   return ok != 0;
 }
 // Returns false (and records `code`) if the phase did not complete within the poll limit.
 __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, int* err, int code) {
-  for (uint32_t i = 0; i < kSpinLimit; ++i) {
+  if (mbar_try_wait(bar, parity)) return true;
+  const long long t0 = clock64();
+  for (uint32_t i = 1;; ++i) {
     if (mbar_try_wait(bar, parity)) return true;
-    if ((i & 0xfff) == 0xfff && err != nullptr && *(volatile int*)err != 0) return false;  // someone else gave up
+    if ((i & 0xf) == 0) {
+      if (err != nullptr && *(volatile int*)err != 0) return false;  // someone else gave up
+      if (clock64() - t0 > kWaitLimitCycles) break;
+    }
   }
   report_timeout(err, code);
   return false;

@@ -155,27 +155,67 @@ __global__ void __launch_bounds__(256) ln_rows_bwd_kernel(const T* dz, const T* 
 // ---------------------------------------------------------------------------------------------
 constexpr int TP = 64;  // pixels per tile
 
+template <typename T> __device__ __forceinline__ void load8v(const T* p, float (&v)[8]) {
+  if constexpr (sizeof(T) == 4) {
+    const float4 a = reinterpret_cast<const float4*>(p)[0], b = reinterpret_cast<const float4*>(p)[1];
+    v[0] = a.x; v[1] = a.y; v[2] = a.z; v[3] = a.w; v[4] = b.x; v[5] = b.y; v[6] = b.z; v[7] = b.w;
+  } else {
+    union { uint4 u; T h[8]; } pk;
+    pk.u = *reinterpret_cast<const uint4*>(p);
+#pragma unroll
+    for (int e = 0; e < 8; ++e) v[e] = to_f32(pk.h[e]);
+  }
+}
+template <typename T> __device__ __forceinline__ void store8v(T* p, const float (&v)[8]) {
+  if constexpr (sizeof(T) == 4) {
+    reinterpret_cast<float4*>(p)[0] = make_float4(v[0], v[1], v[2], v[3]);
+    reinterpret_cast<float4*>(p)[1] = make_float4(v[4], v[5], v[6], v[7]);
+  } else {
+    union { uint4 u; T h[8]; } pk;
+#pragma unroll
+    for (int e = 0; e < 8; ++e) pk.h[e] = from_f32<T>(v[e]);
+    *reinterpret_cast<uint4*>(p) = pk.u;
+  }
+}
+
+// 64 pixels x 128 channels of a channel-major tensor -> smem tile[c][pixel] (fp32), 8 pixels per access.
+// The plane size is a multiple of 8 pixels, so a group of 8 never straddles two batch entries.
 template <typename T>
 __device__ __forceinline__ void load_cm_tile(float (*tile)[TP + 1], const T* src, long long m0, long long M,
                                              long long NN) {
-  const int pl = threadIdx.x & (TP - 1);
-  const long long m = m0 + pl;
-  const long long bb = m / NN, pix = m % NN;
-  for (int c = threadIdx.x / TP; c < CW; c += 256 / TP)
-    tile[c][pl] = m < M ? to_f32(src[(bb * CW + c) * NN + pix]) : 0.f;
+  for (int item = threadIdx.x; item < CW * (TP / 8); item += 256) {
+    const int c = item >> 3, pg = item & 7;
+    const long long m = m0 + pg * 8;
+    float v[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+    if (m < M) load8v<T>(src + ((m / NN) * CW + c) * NN + (m % NN), v);
+#pragma unroll
+    for (int e = 0; e < 8; ++e) tile[c][pg * 8 + e] = v[e];
+  }
+}
+template <typename T>
+__device__ __forceinline__ void store_cm_tile(const float (*tile)[TP + 1], T* dst, long long m0, long long M,
+                                              long long NN) {
+  for (int item = threadIdx.x; item < CW * (TP / 8); item += 256) {
+    const int c = item >> 3, pg = item & 7;
+    const long long m = m0 + pg * 8;
+    if (m >= M) continue;
+    float v[8];
+#pragma unroll
+    for (int e = 0; e < 8; ++e) v[e] = tile[c][pg * 8 + e];
+    store8v<T>(dst + ((m / NN) * CW + c) * NN + (m % NN), v);
+  }
 }
 
+// One warp per pixel; lane l owns channels 4l..4l+3, so the pixel-major side is read / written 8 or 16
+// bytes per lane (256 or 512 contiguous bytes per warp).
 template <typename T>
 __global__ void __launch_bounds__(256) ln_cm_kernel(const T* t_cm, const T* gamma, const T* beta, float eps,
                                                      long long M, long long NN, T* u, float* mean, float* rstd) {
   __shared__ float tile[CW][TP + 1];
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
-  float gm[4], bt[4];
-#pragma unroll
-  for (int k = 0; k < 4; ++k) {
-    gm[k] = gamma ? to_f32(gamma[lane + 32 * k]) : 1.f;
-    bt[k] = beta ? to_f32(beta[lane + 32 * k]) : 0.f;
-  }
+  float gm[4] = {1.f, 1.f, 1.f, 1.f}, bt[4] = {0.f, 0.f, 0.f, 0.f};
+  if (gamma) load4(gamma + lane * 4, gm);
+  if (beta) load4(beta + lane * 4, bt);
   const long long tiles = (M + TP - 1) / TP;
   for (long long tl = blockIdx.x; tl < tiles; tl += gridDim.x) {
     const long long m0 = tl * TP;
@@ -187,14 +227,15 @@ __global__ void __launch_bounds__(256) ln_cm_kernel(const T* t_cm, const T* gamm
       if (m >= M) break;
       float v[4];
 #pragma unroll
-      for (int k = 0; k < 4; ++k) v[k] = tile[lane + 32 * k][pl];
+      for (int k = 0; k < 4; ++k) v[k] = tile[lane * 4 + k][pl];
       const float mu = warp_sum(v[0] + v[1] + v[2] + v[3]) * (1.0f / CW);
       float q = 0.f;
 #pragma unroll
       for (int k = 0; k < 4; ++k) { v[k] -= mu; q += v[k] * v[k]; }
       const float rs = 1.0f / sqrtf(warp_sum(q) * (1.0f / CW) + eps);
 #pragma unroll
-      for (int k = 0; k < 4; ++k) u[m * CW + lane + 32 * k] = from_f32<T>(v[k] * rs * gm[k] + bt[k]);
+      for (int k = 0; k < 4; ++k) v[k] = v[k] * rs * gm[k] + bt[k];
+      store4(u + m * CW + lane * 4, v);
       if (lane == 0) { mean[m] = mu; rstd[m] = rs; }
     }
   }
@@ -207,9 +248,8 @@ __global__ void __launch_bounds__(256) ln_cm_bwd_kernel(const T* du, const T* t_
   __shared__ float tile[CW][TP + 1];
   __shared__ float sg[8][CW], sb[8][CW];
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
-  float gm[4], ag[4] = {}, ab[4] = {};
-#pragma unroll
-  for (int k = 0; k < 4; ++k) gm[k] = gamma ? to_f32(gamma[lane + 32 * k]) : 1.f;
+  float gm[4] = {1.f, 1.f, 1.f, 1.f}, ag[4] = {}, ab[4] = {};
+  if (gamma) load4(gamma + lane * 4, gm);
   const long long tiles = (M + TP - 1) / TP;
   for (long long tl = blockIdx.x; tl < tiles; tl += gridDim.x) {
     const long long m0 = tl * TP;
@@ -220,33 +260,27 @@ __global__ void __launch_bounds__(256) ln_cm_bwd_kernel(const T* du, const T* t_
       const long long m = m0 + pl;
       if (m >= M) break;
       const float mu = mean[m], rs = rstd[m];
-      float th[4], dh[4], s1 = 0.f, s2 = 0.f;
+      float d[4], th[4], dh[4], s1 = 0.f, s2 = 0.f;
+      load4(du + m * CW + lane * 4, d);
 #pragma unroll
       for (int k = 0; k < 4; ++k) {
-        th[k] = (tile[lane + 32 * k][pl] - mu) * rs;
-        const float d = to_f32(du[m * CW + lane + 32 * k]);
-        dh[k] = d * gm[k];
+        th[k] = (tile[lane * 4 + k][pl] - mu) * rs;
+        dh[k] = d[k] * gm[k];
         s1 += dh[k];
         s2 += dh[k] * th[k];
-        ag[k] += d * th[k];
-        ab[k] += d;
+        ag[k] += d[k] * th[k];
+        ab[k] += d[k];
       }
       s1 = warp_sum(s1) * (1.0f / CW);
       s2 = warp_sum(s2) * (1.0f / CW);
 #pragma unroll
-      for (int k = 0; k < 4; ++k) tile[lane + 32 * k][pl] = rs * (dh[k] - s1 - th[k] * s2);
+      for (int k = 0; k < 4; ++k) tile[lane * 4 + k][pl] = rs * (dh[k] - s1 - th[k] * s2);
     }
     __syncthreads();
-    {
-      const int pl = threadIdx.x & (TP - 1);
-      const long long m = m0 + pl;
-      const long long bb = m / NN, pix = m % NN;
-      if (m < M)
-        for (int c = threadIdx.x / TP; c < CW; c += 256 / TP) dt_cm[(bb * CW + c) * NN + pix] = from_f32<T>(tile[c][pl]);
-    }
+    store_cm_tile(tile, dt_cm, m0, M, NN);
   }
 #pragma unroll
-  for (int k = 0; k < 4; ++k) { sg[warp][lane + 32 * k] = ag[k]; sb[warp][lane + 32 * k] = ab[k]; }
+  for (int k = 0; k < 4; ++k) { sg[warp][lane * 4 + k] = ag[k]; sb[warp][lane * 4 + k] = ab[k]; }
   __syncthreads();
   if (threadIdx.x < CW) {
     float g = 0.f, b = 0.f;
