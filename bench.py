@@ -187,6 +187,18 @@ def cpu_reference(steps, warmup):
     }, dt
 
 
+def _finish(dist):
+    """Leave a multi-rank run without tearing NCCL down: a captured graph still references the communicator,
+    and destroying the process group under it has hung; the process is about to exit anyway."""
+    try:
+        dist.barrier()
+    except Exception:
+        pass
+    sys.stdout.flush()
+    sys.stderr.flush()
+    os._exit(0)
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -194,6 +206,7 @@ def main():
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
     ap.add_argument("--n-res", type=int, default=N_RES, help="pair side (default: the headline 768)")
+    ap.add_argument("--graph", action="store_true", help="replay the step from a CUDA graph on one GPU too")
     ap.add_argument("--quick", action="store_true",
                     help="timed region only: no end-to-end leg and no CPU baseline (for profiler captures)")
     args = ap.parse_args()
@@ -255,18 +268,59 @@ def main():
     barrier()
 
     # ---- timed region: device-resident inputs -------------------------------------------------
+    # On several GPUs each rank's shard is small enough for host launch latency to show, so the whole step
+    # (kernels and NCCL exchanges) is captured once in a CUDA graph and replayed; the per-kernel event
+    # brackets cannot live inside a graph, so there the kernel table comes from one extra eager step.
+    graph = None
+    if world > 1 or args.graph:
+        try:
+            side = torch.cuda.Stream()
+            side.wait_stream(torch.cuda.current_stream())
+            with torch.cuda.stream(side):
+                step_fn(dev_t, dev_w)
+            torch.cuda.current_stream().wait_stream(side)
+            barrier()
+            graph = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(graph):
+                graph_out = step_fn(dev_t, dev_w)   # noqa: F841  (keeps the captured outputs alive)
+            graph.replay()
+            barrier()
+        except Exception as exc:   # capture is an optimisation: fall back to eager launches
+            print(f"[bench] CUDA graph capture failed, running eagerly: {exc!r}", file=sys.stderr)
+            graph = None
+            barrier()
+    config["launch"] = "cuda graph replay" if graph is not None else "eager"
     _lib.reset_launch_count()
-    _lib.profile_enable(True)
+    if graph is None:
+        _lib.profile_enable(True)
     beg, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     with ClockSampler(local) as clocks:
         barrier()
         beg.record()
         for _ in range(args.steps):
-            step_fn(dev_t, dev_w)
+            if graph is not None:
+                graph.replay()
+            else:
+                step_fn(dev_t, dev_w)
         end.record()
         barrier()
     ms = beg.elapsed_time(end) / args.steps
     launches = _lib.launch_count()
+    prof_steps = args.steps
+    exchanges = None
+    if graph is not None:   # launches and per-kernel times from one eager step outside the timed region
+        _lib.reset_launch_count()
+        _lib.profile_enable(True)
+        if world > 1:
+            from geometric_nn_ops_b200 import sharded as _sh
+            _sh.TIMERS = {}
+        step_fn(dev_t, dev_w)
+        barrier()
+        if world > 1:
+            exchanges = {k_: {"calls": v_[0], "ms_per_step": v_[1]} for k_, v_ in _sh.timing_summary().items()}
+            _sh.TIMERS = None
+        launches = _lib.launch_count() * args.steps
+        prof_steps = 1
     prof = _lib.profile_summary()
     _lib.profile_enable(False)
 
@@ -322,7 +376,7 @@ def main():
         dist.all_reduce(times, op=dist.ReduceOp.MAX)
     ms, e2e_ms = times.tolist()
     if rank != 0:
-        dist.destroy_process_group()
+        _finish(dist)
         return
 
     flops = step_flops(n)
@@ -344,8 +398,8 @@ def main():
                 traffic = json.load(f).get(name)
         roofline = {"kernel": name, "bound": "tensor" if tensor_bound else "hbm", "achieved": ach, "peak": peak,
                     "unit": unit, "frac": ach / peak, "traffic": traffic, "peak_source": f"of {pk_kind}",
-                    "launches": cnt, "avg_launch_ms": tot_ms / cnt, "share_of_step": tot_ms / args.steps / ms}
-    kernels = {k_: {"launches": v_[0], "ms_per_step": v_[1] / args.steps} for k_, v_ in
+                    "launches": cnt, "avg_launch_ms": tot_ms / cnt, "share_of_step": tot_ms / prof_steps / ms}
+    kernels = {k_: {"launches": v_[0], "ms_per_step": v_[1] / prof_steps} for k_, v_ in
                sorted(prof.items(), key=lambda kv: -kv[1][1])}
     cpu, _ = cpu_reference(1, 1) if world == 1 and not args.quick else (None, None)
     line = dict(base, value=flops / (ms / 1e3) / 1e12, ms_per_step=ms,
@@ -354,10 +408,10 @@ def main():
                 e2e={"value": flops / (e2e_ms / 1e3) / 1e12, "unit": "TFLOP/s", "ms_per_step": e2e_ms,
                      "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h},
                 gpu_launches=launches, path=_lib.last_path(), clocks=clocks.summary(), roofline=roofline,
-                kernels=kernels, cpu_baseline=cpu)
-    print(json.dumps(line))
+                kernels=kernels, exchanges=exchanges, cpu_baseline=cpu)
+    print(json.dumps(line), flush=True)
     if dist is not None:
-        dist.destroy_process_group()
+        _finish(dist)
 
 
 if __name__ == "__main__":

@@ -306,12 +306,18 @@ __global__ void __launch_bounds__(256) colsum_kernel(const T* X, long long M, in
   }
 }
 
-__global__ void reduce_kernel(const float* partial, int nparts, int n, float* out) {
-  const int j = blockIdx.x * blockDim.x + threadIdx.x;
-  if (j >= n) return;
+// out[j] = sum_p partial[p][j].  64 outputs per block, four threads per output each summing every fourth
+// partial; the four sub-sums are added in a fixed order, so the result does not depend on scheduling.
+__global__ void __launch_bounds__(256) reduce_kernel(const float* partial, int nparts, int n, float* out) {
+  __shared__ float sub[4][64];
+  const int o = threadIdx.x & 63, lane4 = threadIdx.x >> 6;
+  const int j = blockIdx.x * 64 + o;
   float s = 0.f;
-  for (int p = 0; p < nparts; ++p) s += partial[(long long)p * n + j];
-  out[j] = s;
+  if (j < n)
+    for (int p = lane4; p < nparts; p += 4) s += partial[(long long)p * n + j];
+  sub[lane4][o] = s;
+  __syncthreads();
+  if (lane4 == 0 && j < n) out[j] = (sub[0][o] + sub[1][o]) + (sub[2][o] + sub[3][o]);
 }
 
 // Row sums of the channel-major dPG [512, M] scattered to the p_in / g_in bias gradients (one block per row,
@@ -487,7 +493,7 @@ int split_k_grad(cudaStream_t st, const Geom& gm, const void* lhs, int lhs_w, co
 
 int reduce_to(cudaStream_t st, const float* partial, int nparts, int n, float* out) {
   KernelTimer kt("tc_reduce", st, 0.0, 4.0 * (nparts + 1) * n);
-  reduce_kernel<<<cdiv(n, 256), 256, 0, st>>>(partial, nparts, n, out);
+  reduce_kernel<<<cdiv(n, 64), 256, 0, st>>>(partial, nparts, n, out);
   TRI_LAUNCH_OK();
   return 0;
 }

@@ -28,6 +28,33 @@ from .triangle._triattn import triangle_attention
 from .triangle._trimul import _DTYPES, _aligned, is_outgoing
 
 
+# Optional timing of the exchanges (bench.py turns it on for one eager step): name -> list of (start, end) events.
+TIMERS = None
+
+
+class _timed:
+    def __init__(self, name):
+        self.name = name
+
+    def __enter__(self):
+        if TIMERS is not None:
+            self.beg = torch.cuda.Event(enable_timing=True)
+            self.end = torch.cuda.Event(enable_timing=True)
+            self.beg.record()
+        return self
+
+    def __exit__(self, *exc):
+        if TIMERS is not None:
+            self.end.record()
+            TIMERS.setdefault(self.name, []).append((self.beg, self.end))
+
+
+def timing_summary():
+    """{name: (calls, total_ms)} of the exchanges recorded since ``TIMERS`` was set to a dict."""
+    torch.cuda.synchronize()
+    return {k: (len(v), sum(b.elapsed_time(e) for b, e in v)) for k, v in (TIMERS or {}).items()}
+
+
 def _world(group):
     return dist.get_world_size(group), dist.get_rank(group)
 
@@ -50,10 +77,13 @@ def rows_to_channels(t, group=None):
     if Ch % world != 0:
         raise ValueError(f"{Ch} channels are not divisible by {world} ranks")
     cs = Ch // world
-    send = t.reshape(L, world, cs, R * N).permute(1, 0, 2, 3).contiguous()
-    recv = torch.empty_like(send)
-    dist.all_to_all_single(recv, send, group=group)
-    return recv.reshape(world, L, cs, R, N).permute(1, 2, 0, 3, 4).reshape(L, cs, world * R, N)
+    with _timed("rows_to_channels.pack"):
+        send = t.reshape(L, world, cs, R * N).permute(1, 0, 2, 3).contiguous()
+        recv = torch.empty_like(send)
+    with _timed("rows_to_channels.all_to_all"):
+        dist.all_to_all_single(recv, send, group=group)
+    with _timed("rows_to_channels.unpack"):
+        return recv.reshape(world, L, cs, R, N).permute(1, 2, 0, 3, 4).reshape(L, cs, world * R, N)
 
 
 def channels_to_rows(t, group=None):
@@ -63,10 +93,13 @@ def channels_to_rows(t, group=None):
     if rows % world != 0:
         raise ValueError(f"{rows} rows are not divisible by {world} ranks")
     R = rows // world
-    send = t.reshape(L, cs, world, R * N).permute(2, 0, 1, 3).contiguous()
-    recv = torch.empty_like(send)
-    dist.all_to_all_single(recv, send, group=group)
-    return recv.permute(1, 0, 2, 3).reshape(L, world * cs, R, N)
+    with _timed("channels_to_rows.pack"):
+        send = t.reshape(L, cs, world, R * N).permute(2, 0, 1, 3).contiguous()
+        recv = torch.empty_like(send)
+    with _timed("channels_to_rows.all_to_all"):
+        dist.all_to_all_single(recv, send, group=group)
+    with _timed("channels_to_rows.unpack"):
+        return recv.permute(1, 0, 2, 3).reshape(L, world * cs, R, N)
 
 
 class _Transpose(torch.autograd.Function):
@@ -111,7 +144,8 @@ class _SumGradOverRanks(torch.autograd.Function):
     @staticmethod
     def backward(ctx, g):
         g = g.contiguous()
-        dist.all_reduce(g, op=dist.ReduceOp.SUM, group=ctx.group)
+        with _timed("bias_grad.all_reduce"):
+            dist.all_reduce(g, op=dist.ReduceOp.SUM, group=ctx.group)
         return g, None
 
 
@@ -231,7 +265,8 @@ class _ShardedTriMul(torch.autograd.Function):
         dx = torch.empty_like(xc)
         bufs.a_cm, bufs.b_cm, bufs.dx = dab[0].data_ptr(), dab[1].data_ptr(), dx.data_ptr()
         _phase(lib, d, _lib.PHASE_PROJECT_BWD, bufs, dev)
-        dist.all_reduce(flat, op=dist.ReduceOp.SUM, group=group)
+        with _timed("weight_grads.all_reduce"):
+            dist.all_reduce(flat, op=dist.ReduceOp.SUM, group=group)
         out = [dx if ctx.needs_input_grad[0] else None, None, None, None, None]
         for i, (n, dt) in enumerate(zip(_lib.WEIGHT_NAMES, ctx.weight_dtypes)):
             out.append(grads[n].to(dt) if n in grads and ctx.needs_input_grad[5 + i] else None)
