@@ -318,7 +318,8 @@ template <int HD, int TKV, int MODE> struct GeoR {
   static constexpr int OFF_V = OFF_K + 2 * TB;
   static constexpr int OFF_DS = OFF_V + 2 * TB;                              // [128 x 64] SW128 (MODE_DQ)
   static constexpr int OFF_BIAS = OFF_DS + (MODE == MODE_DQ ? 16384 : 0);    // [128 x TKV], 64-column blocks
-  static constexpr int OFF_MB = OFF_BIAS + 128 * TKV * 2;
+  static constexpr int NBIAS = MODE == MODE_DQ ? 2 : 1;                       // dQ: bias tiles two steps ahead
+  static constexpr int OFF_MB = OFF_BIAS + NBIAS * 128 * TKV * 2;
   static constexpr int OFF_BAR = OFF_MB + 512;
   static constexpr int SMEM = OFF_BAR + 128 + 1024;
 };
@@ -341,10 +342,10 @@ attn_bwd_rows_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_const
   float* sMb = reinterpret_cast<float*>(smem + G::OFF_MB);
   uint64_t* bar_once = reinterpret_cast<uint64_t*>(smem + G::OFF_BAR);  // Q+dO (DQ) or bias (DBIAS)
   uint64_t* bar_in = bar_once + 1;   // [2] per-step operand stages
-  uint64_t* bar_bias = bar_once + 3; // per-step bias (DQ)
-  uint64_t* bar_s = bar_once + 4;
-  uint64_t* bar_dq = bar_once + 5;
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bar_once + 6);
+  uint64_t* bar_bias = bar_once + 3; // [2] per-step bias (DQ)
+  uint64_t* bar_s = bar_once + 5;
+  uint64_t* bar_dq = bar_once + 6;
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bar_once + 7);
 
   // 128 * HALVES threads: thread (r, hh) owns row r of the tile and, with HALVES == 2, the column half hh,
   // so an SM holds twice the warps for the same shared memory and TMEM.  That pays for the dQ pass
@@ -372,7 +373,7 @@ attn_bwd_rows_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_const
 
   if (tid == 0) {
     mbar_init(bar_once, 1); mbar_init(&bar_in[0], 1); mbar_init(&bar_in[1], 1);
-    mbar_init(bar_bias, 1); mbar_init(bar_s, 1); mbar_init(bar_dq, 1);
+    mbar_init(&bar_bias[0], 1); mbar_init(&bar_bias[1], 1); mbar_init(bar_s, 1); mbar_init(bar_dq, 1);
     mbar_fence_init();
   }
   if (warp == 0) tmem_alloc(tmem_slot, 256);
@@ -385,10 +386,12 @@ attn_bwd_rows_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_const
   constexpr int CPT = TKV / 32 / HALVES;   // 32-column chunks per thread
   constexpr int COLS = TKV / HALVES;       // columns per thread
 
-  auto load_bias = [&](int k0) {
+  auto load_bias = [&](int k0, int buf) {   // buf: which of the dQ pass's two bias buffers (0 for dbias)
+    if constexpr (MODE == MODE_DQ) mbar_expect_tx(&bar_bias[buf], 128 * TKV * 2);
 #pragma unroll
     for (int blk = 0; blk < TKV / 64; ++blk)
-      tma_load_4d(sBias + blk * 16384, &tmBias, MODE == MODE_DQ ? bar_bias : bar_once, k0 + blk * 64, q0, h, bias_b);
+      tma_load_4d(sBias + buf * (128 * TKV * 2) + blk * 16384, &tmBias, MODE == MODE_DQ ? &bar_bias[buf] : bar_once,
+                  k0 + blk * 64, q0, h, bias_b);
   };
   auto load_step = [&](int step, int stg) {
     if constexpr (MODE == MODE_DQ) {
@@ -409,10 +412,10 @@ attn_bwd_rows_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_const
       mbar_expect_tx(bar_once, 2 * G::TA);
       tma_load_5d(sQ, &tmQ, bar_once, 0, h, q0, s, b);
       tma_load_5d(sDO, &tmDO, bar_once, 0, h, q0, s, b);
-      if (a.has_bias) { mbar_expect_tx(bar_bias, 128 * TKV * 2); load_bias(0); }
+      if (a.has_bias) for (int st = 0; st < 2 && st < nsteps; ++st) load_bias(st * TKV, st);
     } else if (a.has_bias) {
       mbar_expect_tx(bar_once, 128 * TKV * 2);
-      load_bias(kvb * TKV);
+      load_bias(kvb * TKV, 0);
     }
     for (int st = 0; st < 2 && st < nsteps; ++st) load_step(st, st);
   }
@@ -420,14 +423,22 @@ attn_bwd_rows_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_const
   const int qi = q0 + r;
   const bool q_ok = qi < a.N;
   const long long plane = (long long)a.B * a.S * a.H * a.N;
-  float m_row = 0.f, l_row = 0.f, d_row = 0.f;
-  auto load_stats = [&](int ss) {
+  float m_row = 0.f, l_row = 0.f, d_row = 0.f, m_nx = 0.f, l_nx = 0.f, d_nx = 0.f;
+  auto load_stats = [&](int ss, float& m, float& l, float& dl) {
     if (q_ok) {
       const long long row = (((long long)b * a.S + ss) * a.H + h) * a.N + qi;
-      m_row = a.stats[row]; l_row = a.stats[plane + row]; d_row = a.delta[row];
+      m = a.stats[row]; l = a.stats[plane + row]; dl = a.delta[row];
     }
   };
-  if constexpr (MODE == MODE_DQ) load_stats(s);
+  auto mask_term = [&](int row, int kj) -> float {
+    if (kj >= a.N) return -INFINITY;
+    if (a.mask == nullptr) return 0.f;
+    return kMaskSentinel * ((a.mask[b * a.mask_st[0] + row * a.mask_st[1] + kj] ? 1.0f : 0.0f) - 1.0f);
+  };
+  float mb_next = 0.f;
+  if (tid < TKV && nsteps > 0) mb_next = MODE == MODE_DQ ? mask_term(s, tid) : mask_term(s_lo, kvb * TKV + tid);
+  if (nsteps > 0) load_stats(MODE == MODE_DQ ? s : s_lo, m_nx, l_nx, d_nx);
+  if constexpr (MODE == MODE_DQ) { m_row = m_nx; l_row = l_nx; d_row = d_nx; }
   float acc[MODE == MODE_DBIAS ? TKV / HALVES : 1];
   if constexpr (MODE == MODE_DBIAS) {
 #pragma unroll
@@ -441,7 +452,7 @@ attn_bwd_rows_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_const
     const uint32_t par = j & 1, in_par = (j >> 1) & 1;
     const int row_s = MODE == MODE_DQ ? s : s_lo + j;
     const int k0 = MODE == MODE_DQ ? j * TKV : kvb * TKV;
-    if constexpr (MODE == MODE_DBIAS) load_stats(s_lo + j);
+    if constexpr (MODE == MODE_DBIAS) { m_row = m_nx; l_row = l_nx; d_row = d_nx; }   // loaded a step ahead
     if (tid == 0) {
       if (MODE == MODE_DQ && j == 0) ok = mbar_wait(bar_once, 0, a.err, 22);
       ok = mbar_wait(&bar_in[stg], in_par, a.err, 23) && ok;
@@ -459,17 +470,18 @@ attn_bwd_rows_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_const
                        make_smem_desc(va + ks * 32, 16, G::SBO, G::LAYOUT), a.idesc_a, ks > 0);
       umma_commit(bar_s);
     }
-    if (tid < TKV) {
-      const int kj = k0 + tid;
-      float mb = 0.f;
-      if (kj >= a.N) mb = -INFINITY;
-      else if (a.mask != nullptr) mb = kMaskSentinel * ((a.mask[b * a.mask_st[0] + row_s * a.mask_st[1] + kj] ? 1.0f : 0.0f) - 1.0f);
-      sMb[tid] = mb;
+    if (tid < TKV) {   // this step's mask terms were loaded a step ahead; fetch the next step's now
+      sMb[tid] = mb_next;
+      if (j + 1 < nsteps)
+        mb_next = MODE == MODE_DQ ? mask_term(s, (j + 1) * TKV + tid) : mask_term(s_lo + j + 1, kvb * TKV + tid);
+    }
+    if constexpr (MODE == MODE_DBIAS) {
+      if (j + 1 < nsteps) load_stats(s_lo + j + 1, m_nx, l_nx, d_nx);
     }
     __syncthreads();
     ok = mbar_wait(bar_s, par, a.err, 24) && ok;
     tc_fence_after_sync();
-    if (MODE == MODE_DQ && a.has_bias) ok = mbar_wait(bar_bias, par, a.err, 25) && ok;
+    if (MODE == MODE_DQ && a.has_bias) ok = mbar_wait(&bar_bias[stg], in_par, a.err, 25) && ok;
     if (MODE == MODE_DQ && j > 0) ok = mbar_wait(bar_dq, (j - 1) & 1, a.err, 26) && ok;  // dS buffer and K/V stage free
     if (MODE == MODE_DQ && tid == 0 && j > 0 && j + 1 < nsteps) load_step(j + 1, (j + 1) & 1);
 
@@ -485,7 +497,8 @@ attn_bwd_rows_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_const
         float bv[8], ds[8];
         if (a.has_bias) {
           const int g = c * 4 + u;
-          const uint4 raw = *reinterpret_cast<const uint4*>(sBias + (g >> 3) * 16384 + sw128_chunk1(r, g & 7));
+          const uint4 raw = *reinterpret_cast<const uint4*>(sBias + (MODE == MODE_DQ ? stg * (128 * TKV * 2) : 0) +
+                                                            (g >> 3) * 16384 + sw128_chunk1(r, g & 7));
           unpack8<T>(raw, bv);
         }
 #pragma unroll
@@ -519,7 +532,7 @@ attn_bwd_rows_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_const
                          make_smem_desc(ka + kk * 16 * G::RB, TKV * G::RB, G::SBO, G::LAYOUT), a.idesc_b,
                          (j > 0 || kk > 0) ? 1u : 0u);
         umma_commit(bar_dq);
-        if (a.has_bias && j + 1 < nsteps) { mbar_expect_tx(bar_bias, 128 * TKV * 2); load_bias((j + 1) * TKV); }
+        if (a.has_bias && j + 2 < nsteps) load_bias((j + 2) * TKV, stg);   // all reads of this buffer are done
       } else {
         if (j + 2 < nsteps) load_step(j + 2, stg);  // this step's MMAs have completed (bar_s), all reads are done
       }
@@ -591,8 +604,8 @@ template <int HD> struct GeoC {
   static constexpr int OFF_DO = OFF_Q + 2 * TQ;     // [2]
   static constexpr int OFF_PT = OFF_DO + 2 * TQ;    // [128 keys x 64 queries] SW128
   static constexpr int OFF_DST = OFF_PT + 16384;
-  static constexpr int OFF_BIAS = OFF_DST + 16384;  // [64 queries x 128 keys] as two [64 x 64] SW128 blocks
-  static constexpr int OFF_ST = OFF_BIAS + 16384;   // m[64], log l[64], delta[64]
+  static constexpr int OFF_BIAS = OFF_DST + 16384;  // 2 buffers of [64 queries x 128 keys] (two [64 x 64] SW128 blocks)
+  static constexpr int OFF_ST = OFF_BIAS + 2 * 16384;   // m[64], log l[64], delta[64]
   static constexpr int OFF_BAR = OFF_ST + 1024;
   static constexpr int SMEM = OFF_BAR + 128 + 1024;
 };
@@ -617,10 +630,10 @@ attn_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_const
   float* sD = sM + 128;
   uint64_t* bar_kv = reinterpret_cast<uint64_t*>(smem + G::OFF_BAR);
   uint64_t* bar_in = bar_kv + 1;  // [2]
-  uint64_t* bar_bias = bar_kv + 3;
-  uint64_t* bar_s = bar_kv + 4;
-  uint64_t* bar_acc = bar_kv + 5;
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bar_kv + 6);
+  uint64_t* bar_bias = bar_kv + 3;   // [2]: bias tiles are fetched two steps ahead
+  uint64_t* bar_s = bar_kv + 5;
+  uint64_t* bar_acc = bar_kv + 6;
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bar_kv + 7);
 
   // 256 threads: thread (r, hh) owns key r of the block and query half hh of each 64-query tile
   const int tid = threadIdx.x, warp = tid >> 5, r = tid & 127, hh = tid >> 7;
@@ -636,7 +649,7 @@ attn_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_const
 
   if (tid == 0) {
     mbar_init(bar_kv, 1); mbar_init(&bar_in[0], 1); mbar_init(&bar_in[1], 1);
-    mbar_init(bar_bias, 1); mbar_init(bar_s, 1); mbar_init(bar_acc, 1);
+    mbar_init(&bar_bias[0], 1); mbar_init(&bar_bias[1], 1); mbar_init(bar_s, 1); mbar_init(bar_acc, 1);
     mbar_fence_init();
   }
   if (warp == 0) tmem_alloc(tmem_slot, 256);
@@ -653,16 +666,18 @@ attn_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_const
     tma_load_5d(sDO + stg * G::TQ, &tmDO, &bar_in[stg], 0, h, step * 64, s, b);
   };
   auto load_bias = [&](int step) {
-    mbar_expect_tx(bar_bias, 16384);
-    tma_load_4d(sBias, &tmBias, bar_bias, k0, step * 64, h, bias_b);
-    tma_load_4d(sBias + 8192, &tmBias, bar_bias, k0 + 64, step * 64, h, bias_b);
+    uint64_t* bb = &bar_bias[step & 1];
+    uint8_t* dst = sBias + (step & 1) * 16384;
+    mbar_expect_tx(bb, 16384);
+    tma_load_4d(dst, &tmBias, bb, k0, step * 64, h, bias_b);
+    tma_load_4d(dst + 8192, &tmBias, bb, k0 + 64, step * 64, h, bias_b);
   };
   if (tid == 0) {
     mbar_expect_tx(bar_kv, 2 * G::TK);
     tma_load_5d(sK, &tmK, bar_kv, 0, h, k0, s, b);
     tma_load_5d(sV, &tmV, bar_kv, 0, h, k0, s, b);
     for (int st = 0; st < 2 && st < nsteps; ++st) load_step(st, st);
-    if (a.has_bias) load_bias(0);
+    if (a.has_bias) for (int st = 0; st < 2 && st < nsteps; ++st) load_bias(st);
   }
   const int kj = k0 + r;
   float mb = 0.f;
@@ -671,6 +686,10 @@ attn_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_const
   const long long plane = (long long)a.B * a.S * a.H * a.N;
   const long long row_base = (((long long)b * a.S + s) * a.H + h) * a.N;
   bool ok = true;
+  float st_m = 0.f, st_l = 0.f, st_d = 0.f;
+  if (tid < 64 && tid < a.N) {
+    st_m = a.stats[row_base + tid]; st_l = a.stats[plane + row_base + tid]; st_d = a.delta[row_base + tid];
+  }
 
   for (int j = 0; j < nsteps; ++j) {
     const int stg = j & 1, q0 = j * 64;
@@ -691,21 +710,24 @@ attn_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_const
                        make_smem_desc(da + ks * 32, 16, G::SBO, G::LAYOUT), a.idesc_a, ks > 0);
       umma_commit(bar_s);
     }
-    if (tid < 64) {
-      const int qi = q0 + tid;
-      const bool v = qi < a.N;
-      sM[tid] = v ? a.stats[row_base + qi] : 0.f;
-      sL[tid] = v ? a.stats[plane + row_base + qi] : 0.f;
-      sD[tid] = v ? a.delta[row_base + qi] : 0.f;
+    if (tid < 64) {   // this tile's query statistics were loaded a step ahead; fetch the next tile's now
+      sM[tid] = st_m; sL[tid] = st_l; sD[tid] = st_d;
+      const int qn = q0 + 64 + tid;
+      if (j + 1 < nsteps) {
+        const bool v = qn < a.N;
+        st_m = v ? a.stats[row_base + qn] : 0.f;
+        st_l = v ? a.stats[plane + row_base + qn] : 0.f;
+        st_d = v ? a.delta[row_base + qn] : 0.f;
+      }
     }
     __syncthreads();
     ok = mbar_wait(bar_s, par, a.err, 33) && ok;
     tc_fence_after_sync();
-    if (a.has_bias) ok = mbar_wait(bar_bias, par, a.err, 34) && ok;
+    if (a.has_bias) ok = mbar_wait(&bar_bias[stg], in_par, a.err, 34) && ok;
     if (j > 0) ok = mbar_wait(bar_acc, (j - 1) & 1, a.err, 35) && ok;   // P^T / dS^T buffers and the other stage are free
     if (tid == 0 && j > 0 && j + 1 < nsteps) load_step(j + 1, (j + 1) & 1);
 
-    const uint8_t* bias_col = sBias + (r >> 6) * 8192 + (r & 7) * 2;  // element (q, key r): + q*128 + swizzled chunk
+    const uint8_t* bias_col = sBias + stg * 16384 + (r >> 6) * 8192 + (r & 7) * 2;  // element (q, key r): + q*128 + swizzled chunk
     const int key_chunk = (r & 63) >> 3;
     {
       const int c = hh;
@@ -752,7 +774,7 @@ attn_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_const
                        make_smem_desc(qa + kk * 16 * G::RB, 64 * G::RB, G::SBO, G::LAYOUT), a.idesc_b,
                        (j > 0 || kk > 0) ? 1u : 0u);
       umma_commit(bar_acc);
-      if (a.has_bias && j + 1 < nsteps) load_bias(j + 1);
+      if (a.has_bias && j + 2 < nsteps) load_bias(j + 2);   // every thread is past its reads of this buffer
     }
     if (!ok) break;
   }
