@@ -68,6 +68,23 @@ template <> __device__ __forceinline__ uint32_t pack2<__half>(float a, float b) 
   __half2 v = __floats2half2_rn(a, b);
   return *reinterpret_cast<uint32_t*>(&v);
 }
+// one packed pair of 16-bit values -> two fp32
+template <typename T> __device__ __forceinline__ float2 unpack2(uint32_t w);
+template <> __device__ __forceinline__ float2 unpack2<__nv_bfloat16>(uint32_t w) {
+  return make_float2(__uint_as_float(w << 16), __uint_as_float(w & 0xffff0000u));
+}
+template <> __device__ __forceinline__ float2 unpack2<__half>(uint32_t w) {
+  return __half22float2(*reinterpret_cast<const __half2*>(&w));
+}
+// three-input maximum (one instruction on sm_100)
+__device__ __forceinline__ float fmax3(float a, float b, float c) {
+  float d;
+  asm("max.f32 %0, %1, %2, %3;" : "=f"(d) : "f"(a), "f"(b), "f"(c));
+  return d;
+}
+__device__ __forceinline__ float2 pair(uint32_t lo, uint32_t hi) { return make_float2(__uint_as_float(lo), __uint_as_float(hi)); }
+__device__ __forceinline__ float2 splat(float v) { return make_float2(v, v); }
+
 template <typename T>
 __device__ __forceinline__ void unpack8(const uint4& v, float (&f)[8]) {
   union { uint4 u; T h[8]; } pk;
@@ -76,7 +93,7 @@ __device__ __forceinline__ void unpack8(const uint4& v, float (&f)[8]) {
   for (int i = 0; i < 8; ++i) f[i] = to_f32(pk.h[i]);
 }
 
-template <typename T, int HD>
+template <typename T, int HD, bool HB>
 __global__ void __launch_bounds__(128, 2)
 attn_fwd_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmK,
                    const __grid_constant__ CUtensorMap tmV, const __grid_constant__ CUtensorMap tmBias,
@@ -166,9 +183,11 @@ attn_fwd_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
     tc_fence_after_sync();
     if (a.has_bias) ok = mbar_wait(bar_bias, par, a.err, 14) && ok;
 
-    // ---- logits into registers, running max --------------------------------------------------
-    float x[128];
+    // ---- logits into registers, running max (packed fp32x2 arithmetic) ---------------------------
+    float2 x2[64];
     float mx4[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};   // independent chains: no 128-long dependency
+    const float2 sc2 = splat(a.scale);
+    const float4* sMb4 = reinterpret_cast<const float4*>(sMb);
 #pragma unroll
     for (int c = 0; c < 4; ++c) {
       uint32_t r[32];
@@ -176,39 +195,39 @@ attn_fwd_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
       tmem_ld_wait();
 #pragma unroll
       for (int u = 0; u < 4; ++u) {
-        float bv[8];
-        if (a.has_bias) {
-          const uint4 raw = *reinterpret_cast<const uint4*>(sBias + sw128_chunk(tid, c * 4 + u));
-          unpack8<T>(raw, bv);
-        }
+        uint4 raw = make_uint4(0, 0, 0, 0);
+        if constexpr (HB) raw = *reinterpret_cast<const uint4*>(sBias + sw128_chunk(tid, c * 4 + u));
+        const uint32_t bw[4] = {raw.x, raw.y, raw.z, raw.w};
+        const float4 mA = sMb4[c * 8 + u * 2], mB = sMb4[c * 8 + u * 2 + 1];
+        const float2 mk[4] = {make_float2(mA.x, mA.y), make_float2(mA.z, mA.w), make_float2(mB.x, mB.y),
+                              make_float2(mB.z, mB.w)};
 #pragma unroll
-        for (int i = 0; i < 8; ++i) {
-          const int col = c * 32 + u * 8 + i;
-          float v = __uint_as_float(r[u * 8 + i]) * a.scale;
-          if (a.has_bias) v += bv[i];
-          v += sMb[col];
-          x[col] = v;
-          mx4[i & 3] = fmaxf(mx4[i & 3], v);
+        for (int i = 0; i < 4; ++i) {
+          float2 v = __ffma2_rn(pair(r[u * 8 + 2 * i], r[u * 8 + 2 * i + 1]), sc2, mk[i]);
+          if constexpr (HB) v = __fadd2_rn(v, unpack2<T>(bw[i]));
+          x2[c * 16 + u * 4 + i] = v;
+          mx4[i] = fmax3(mx4[i], v.x, v.y);
         }
       }
     }
     const float mx = fmaxf(fmaxf(mx4[0], mx4[1]), fmaxf(mx4[2], mx4[3]));
     const float m_new = fmaxf(m_run, mx);
     const float alpha = ex2_approx((m_run - m_new) * kLog2e);
-    float ps4[4] = {0.f, 0.f, 0.f, 0.f};
+    const float2 nm2 = splat(-m_new), l2e2 = splat(kLog2e);
+    float2 ps2[2] = {make_float2(0.f, 0.f), make_float2(0.f, 0.f)};
 #pragma unroll
     for (int g = 0; g < 16; ++g) {
-      float p[8];
+      uint32_t pw[4];
 #pragma unroll
-      for (int i = 0; i < 8; ++i) {
-        p[i] = ex2_approx((x[g * 8 + i] - m_new) * kLog2e);
-        ps4[i & 3] += p[i];
+      for (int i = 0; i < 4; ++i) {
+        const float2 e = __fmul2_rn(__fadd2_rn(x2[g * 4 + i], nm2), l2e2);
+        const float2 pp = make_float2(ex2_approx(e.x), ex2_approx(e.y));
+        ps2[i & 1] = __fadd2_rn(ps2[i & 1], pp);
+        pw[i] = pack2<T>(pp.x, pp.y);
       }
-      uint4 pk;
-      pk.x = pack2<T>(p[0], p[1]); pk.y = pack2<T>(p[2], p[3]);
-      pk.z = pack2<T>(p[4], p[5]); pk.w = pack2<T>(p[6], p[7]);
-      *reinterpret_cast<uint4*>(sP + sw128_chunk(tid, g)) = pk;
+      *reinterpret_cast<uint4*>(sP + sw128_chunk(tid, g)) = make_uint4(pw[0], pw[1], pw[2], pw[3]);
     }
+    const float ps4[4] = {ps2[0].x, ps2[0].y, ps2[1].x, ps2[1].y};
     l_run = l_run * alpha + ((ps4[0] + ps4[1]) + (ps4[2] + ps4[3]));
     m_run = m_new;
     fence_proxy_async_smem();
@@ -314,17 +333,18 @@ template <int HD, int TKV, int MODE> struct GeoR {
   static constexpr uint32_t SBO = 8 * RB;
   static constexpr int OFF_Q = 0;
   static constexpr int OFF_DO = OFF_Q + NA * TA;
+  static constexpr int NS = MODE == MODE_DQ ? 3 : 2;     // operand stages (dQ: K/V tiles are fetched two steps ahead)
   static constexpr int OFF_K = OFF_DO + NA * TA;
-  static constexpr int OFF_V = OFF_K + 2 * TB;
-  static constexpr int OFF_DS = OFF_V + 2 * TB;                              // [128 x 64] SW128 (MODE_DQ)
+  static constexpr int OFF_V = OFF_K + NS * TB;
+  static constexpr int OFF_DS = OFF_V + NS * TB;                             // [128 x 64] SW128 (MODE_DQ)
   static constexpr int OFF_BIAS = OFF_DS + (MODE == MODE_DQ ? 16384 : 0);    // [128 x TKV], 64-column blocks
   static constexpr int NBIAS = MODE == MODE_DQ ? 2 : 1;                       // dQ: bias tiles two steps ahead
-  static constexpr int OFF_MB = OFF_BIAS + NBIAS * 128 * TKV * 2;
-  static constexpr int OFF_BAR = OFF_MB + 512;
+  static constexpr int OFF_MB = OFF_BIAS + NBIAS * 128 * TKV * 2;             // 2 buffers of TKV mask terms
+  static constexpr int OFF_BAR = OFF_MB + 1024;
   static constexpr int SMEM = OFF_BAR + 128 + 1024;
 };
 
-template <typename T, int HD, int TKV, int MODE, int HALVES>
+template <typename T, int HD, int TKV, int MODE, int HALVES, bool HB>
 __global__ void __launch_bounds__(128 * HALVES, 2)
 attn_bwd_rows_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmDO,
                      const __grid_constant__ CUtensorMap tmK, const __grid_constant__ CUtensorMap tmV,
@@ -341,11 +361,11 @@ attn_bwd_rows_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_const
   uint8_t* sBias = smem + G::OFF_BIAS;
   float* sMb = reinterpret_cast<float*>(smem + G::OFF_MB);
   uint64_t* bar_once = reinterpret_cast<uint64_t*>(smem + G::OFF_BAR);  // Q+dO (DQ) or bias (DBIAS)
-  uint64_t* bar_in = bar_once + 1;   // [2] per-step operand stages
-  uint64_t* bar_bias = bar_once + 3; // [2] per-step bias (DQ)
-  uint64_t* bar_s = bar_once + 5;
-  uint64_t* bar_dq = bar_once + 6;
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bar_once + 7);
+  uint64_t* bar_in = bar_once + 1;   // [NS] per-step operand stages
+  uint64_t* bar_bias = bar_once + 4; // [2] per-step bias (DQ)
+  uint64_t* bar_s = bar_once + 6;
+  uint64_t* bar_dq = bar_once + 7;
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bar_once + 8);
 
   // 128 * HALVES threads: thread (r, hh) owns row r of the tile and, with HALVES == 2, the column half hh,
   // so an SM holds twice the warps for the same shared memory and TMEM.  That pays for the dQ pass
@@ -372,7 +392,8 @@ attn_bwd_rows_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_const
   const int bias_b = b * a.bias_b_mul;
 
   if (tid == 0) {
-    mbar_init(bar_once, 1); mbar_init(&bar_in[0], 1); mbar_init(&bar_in[1], 1);
+    mbar_init(bar_once, 1);
+    for (int i = 0; i < G::NS; ++i) mbar_init(&bar_in[i], 1);
     mbar_init(&bar_bias[0], 1); mbar_init(&bar_bias[1], 1); mbar_init(bar_s, 1); mbar_init(bar_dq, 1);
     mbar_fence_init();
   }
@@ -393,7 +414,8 @@ attn_bwd_rows_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_const
       tma_load_4d(sBias + buf * (128 * TKV * 2) + blk * 16384, &tmBias, MODE == MODE_DQ ? &bar_bias[buf] : bar_once,
                   k0 + blk * 64, q0, h, bias_b);
   };
-  auto load_step = [&](int step, int stg) {
+  auto load_step = [&](int step) {
+    const int stg = step % G::NS;
     if constexpr (MODE == MODE_DQ) {
       mbar_expect_tx(&bar_in[stg], 2 * G::TB);
       tma_load_5d(sK + stg * G::TB, &tmK, &bar_in[stg], 0, h, step * TKV, s, b);
@@ -406,18 +428,39 @@ attn_bwd_rows_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_const
       tma_load_5d(sV + stg * G::TB, &tmV, &bar_in[stg], 0, h, kvb * TKV, s_lo + step, b);
     }
   };
+  bool ok = true;
+  // S = Q K^T and dP = dO V^T of one step; issued one step ahead of the threads that consume the accumulators
+  auto issue_scores = [&](int step) {
+    const int stg = step % G::NS;
+    if (MODE == MODE_DQ && step == 0) ok = mbar_wait(bar_once, 0, a.err, 22);
+    ok = mbar_wait(&bar_in[stg], (step / G::NS) & 1, a.err, 23) && ok;
+    tc_fence_after_sync();
+    const int sa = MODE == MODE_DQ ? 0 : stg;
+    const uint32_t qa = smem_u32(sQ + sa * G::TA), da = smem_u32(sDO + sa * G::TA);
+    const uint32_t ka = smem_u32(sK + stg * G::TB), va = smem_u32(sV + stg * G::TB);
+#pragma unroll
+    for (int ks = 0; ks < HD / 16; ++ks)
+      umma<KIND_F16>(tmem_base, make_smem_desc(qa + ks * 32, 16, G::SBO, G::LAYOUT),
+                     make_smem_desc(ka + ks * 32, 16, G::SBO, G::LAYOUT), a.idesc_a, ks > 0);
+#pragma unroll
+    for (int ks = 0; ks < HD / 16; ++ks)
+      umma<KIND_F16>(tmem_base + COL_DP, make_smem_desc(da + ks * 32, 16, G::SBO, G::LAYOUT),
+                     make_smem_desc(va + ks * 32, 16, G::SBO, G::LAYOUT), a.idesc_a, ks > 0);
+    umma_commit(bar_s);
+  };
 
   if (tid == 0) {
     if constexpr (MODE == MODE_DQ) {
       mbar_expect_tx(bar_once, 2 * G::TA);
       tma_load_5d(sQ, &tmQ, bar_once, 0, h, q0, s, b);
       tma_load_5d(sDO, &tmDO, bar_once, 0, h, q0, s, b);
-      if (a.has_bias) for (int st = 0; st < 2 && st < nsteps; ++st) load_bias(st * TKV, st);
-    } else if (a.has_bias) {
+      if (HB) for (int st = 0; st < 2 && st < nsteps; ++st) load_bias(st * TKV, st);
+    } else if (HB) {
       mbar_expect_tx(bar_once, 128 * TKV * 2);
       load_bias(kvb * TKV, 0);
     }
-    for (int st = 0; st < 2 && st < nsteps; ++st) load_step(st, st);
+    for (int st = 0; st < 2 && st < nsteps; ++st) load_step(st);
+    if (nsteps > 0) issue_scores(0);
   }
 
   const int qi = q0 + r;
@@ -435,8 +478,15 @@ attn_bwd_rows_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_const
     if (a.mask == nullptr) return 0.f;
     return kMaskSentinel * ((a.mask[b * a.mask_st[0] + row * a.mask_st[1] + kj] ? 1.0f : 0.0f) - 1.0f);
   };
+  auto step_mask = [&](int step) -> float {   // additive mask term of key column `tid` at a step
+    if (step >= nsteps) return 0.f;
+    return MODE == MODE_DQ ? mask_term(s, step * TKV + tid) : mask_term(s_lo + step, kvb * TKV + tid);
+  };
   float mb_next = 0.f;
-  if (tid < TKV && nsteps > 0) mb_next = MODE == MODE_DQ ? mask_term(s, tid) : mask_term(s_lo, kvb * TKV + tid);
+  if (tid < TKV) {
+    sMb[tid] = step_mask(0);
+    mb_next = step_mask(1);
+  }
   if (nsteps > 0) load_stats(MODE == MODE_DQ ? s : s_lo, m_nx, l_nx, d_nx);
   if constexpr (MODE == MODE_DQ) { m_row = m_nx; l_row = l_nx; d_row = d_nx; }
   float acc[MODE == MODE_DBIAS ? TKV / HALVES : 1];
@@ -444,79 +494,95 @@ attn_bwd_rows_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_const
 #pragma unroll
     for (int i = 0; i < TKV / HALVES; ++i) acc[i] = 0.f;
   }
-  bool ok = true;
-  if (MODE == MODE_DBIAS && a.has_bias) ok = mbar_wait(bar_once, 0, a.err, 21);
+  if (MODE == MODE_DBIAS && HB) ok = mbar_wait(bar_once, 0, a.err, 21) && ok;
+  __syncthreads();
 
   for (int j = 0; j < nsteps; ++j) {
-    const int stg = j & 1;
+    const int stg = j & 1, kstg = j % G::NS;
     const uint32_t par = j & 1, in_par = (j >> 1) & 1;
-    const int row_s = MODE == MODE_DQ ? s : s_lo + j;
-    const int k0 = MODE == MODE_DQ ? j * TKV : kvb * TKV;
     if constexpr (MODE == MODE_DBIAS) { m_row = m_nx; l_row = l_nx; d_row = d_nx; }   // loaded a step ahead
-    if (tid == 0) {
-      if (MODE == MODE_DQ && j == 0) ok = mbar_wait(bar_once, 0, a.err, 22);
-      ok = mbar_wait(&bar_in[stg], in_par, a.err, 23) && ok;
-      tc_fence_after_sync();
-      const int sa = MODE == MODE_DQ ? 0 : stg;
-      const uint32_t qa = smem_u32(sQ + sa * G::TA), da = smem_u32(sDO + sa * G::TA);
-      const uint32_t ka = smem_u32(sK + stg * G::TB), va = smem_u32(sV + stg * G::TB);
-#pragma unroll
-      for (int ks = 0; ks < HD / 16; ++ks)
-        umma<KIND_F16>(tmem_base, make_smem_desc(qa + ks * 32, 16, G::SBO, G::LAYOUT),
-                       make_smem_desc(ka + ks * 32, 16, G::SBO, G::LAYOUT), a.idesc_a, ks > 0);
-#pragma unroll
-      for (int ks = 0; ks < HD / 16; ++ks)
-        umma<KIND_F16>(tmem_base + COL_DP, make_smem_desc(da + ks * 32, 16, G::SBO, G::LAYOUT),
-                       make_smem_desc(va + ks * 32, 16, G::SBO, G::LAYOUT), a.idesc_a, ks > 0);
-      umma_commit(bar_s);
-    }
-    if (tid < TKV) {   // this step's mask terms were loaded a step ahead; fetch the next step's now
-      sMb[tid] = mb_next;
-      if (j + 1 < nsteps)
-        mb_next = MODE == MODE_DQ ? mask_term(s, (j + 1) * TKV + tid) : mask_term(s_lo + j + 1, kvb * TKV + tid);
-    }
-    if constexpr (MODE == MODE_DBIAS) {
-      if (j + 1 < nsteps) load_stats(s_lo + j + 1, m_nx, l_nx, d_nx);
-    }
-    __syncthreads();
     ok = mbar_wait(bar_s, par, a.err, 24) && ok;
     tc_fence_after_sync();
-    if (MODE == MODE_DQ && a.has_bias) ok = mbar_wait(&bar_bias[stg], in_par, a.err, 25) && ok;
-    if (MODE == MODE_DQ && j > 0) ok = mbar_wait(bar_dq, (j - 1) & 1, a.err, 26) && ok;  // dS buffer and K/V stage free
-    if (MODE == MODE_DQ && tid == 0 && j > 0 && j + 1 < nsteps) load_step(j + 1, (j + 1) & 1);
+    if constexpr (MODE == MODE_DBIAS) {   // this step's operands have been consumed: fetch the step after next
+      if (tid == 0 && j + 2 < nsteps) load_step(j + 2);
+      if (j + 1 < nsteps) load_stats(s_lo + j + 1, m_nx, l_nx, d_nx);
+    }
+    // dQ: a thread's share of the logits fits in registers, so the accumulators are released before the
+    // arithmetic and the next step's products run under it.  dbias keeps its sums in registers instead and
+    // reads the accumulators chunk by chunk.
+    constexpr bool EARLY = MODE == MODE_DQ;
+    uint32_t rs[EARLY ? CPT : 1][32], rp[EARLY ? CPT : 1][32];
+    if constexpr (EARLY) {
+#pragma unroll
+      for (int cc = 0; cc < CPT; ++cc) {
+        tmem_ld_32x32(t_row + (hh * CPT + cc) * 32, rs[cc]);
+        tmem_ld_32x32(t_row + COL_DP + (hh * CPT + cc) * 32, rp[cc]);
+      }
+      tmem_ld_wait();
+      tc_fence_before_sync();
+      __syncthreads();   // every thread holds its logits: the accumulators can take the next step
+      if (tid == 0 && j + 1 < nsteps) issue_scores(j + 1);
+      if (tid < TKV) {   // next step's mask terms into the other buffer (its readers finished a step ago)
+        sMb[((j + 1) & 1) * TKV + tid] = mb_next;
+        mb_next = step_mask(j + 2);
+      }
+      if (HB) ok = mbar_wait(&bar_bias[stg], in_par, a.err, 25) && ok;
+      if (j > 0) {   // dS buffer and the K/V stage of step j-1 are free
+        ok = mbar_wait(bar_dq, (j - 1) & 1, a.err, 26) && ok;
+        if (tid == 0 && j + 2 < nsteps) load_step(j + 2);
+      } else if (tid == 0 && 2 < nsteps) {
+        load_step(2);
+      }
+    } else {
+      if (tid < TKV) {   // next step's mask terms; the barrier at the end of this step publishes them
+        sMb[((j + 1) & 1) * TKV + tid] = mb_next;
+        mb_next = step_mask(j + 2);
+      }
+    }
 
+    // packed fp32x2 arithmetic: P = 2^((x - m) log2e - log l log2e), dS = P (dP - delta)
+    const float2 sc2 = splat(a.scale), nm2 = splat(-m_row), nl2 = splat(-l_row * kLog2e), l2e2 = splat(kLog2e),
+                 nd2 = splat(-d_row);
+    const float4* sMb4 = reinterpret_cast<const float4*>(sMb + stg * TKV);
 #pragma unroll
     for (int cc = 0; cc < CPT; ++cc) {
       const int c = hh * CPT + cc;
-      uint32_t rs[32], rp[32];
-      tmem_ld_32x32(t_row + c * 32, rs);
-      tmem_ld_32x32(t_row + COL_DP + c * 32, rp);
-      tmem_ld_wait();
+      const int rc_ = EARLY ? cc : 0;
+      if constexpr (!EARLY) {
+        tmem_ld_32x32(t_row + c * 32, rs[0]);
+        tmem_ld_32x32(t_row + COL_DP + c * 32, rp[0]);
+        tmem_ld_wait();
+      }
 #pragma unroll
       for (int u = 0; u < 4; ++u) {
-        float bv[8], ds[8];
-        if (a.has_bias) {
+        uint4 raw = make_uint4(0, 0, 0, 0);
+        if constexpr (HB) {
           const int g = c * 4 + u;
-          const uint4 raw = *reinterpret_cast<const uint4*>(sBias + (MODE == MODE_DQ ? stg * (128 * TKV * 2) : 0) +
-                                                            (g >> 3) * 16384 + sw128_chunk1(r, g & 7));
-          unpack8<T>(raw, bv);
+          raw = *reinterpret_cast<const uint4*>(sBias + (MODE == MODE_DQ ? stg * (128 * TKV * 2) : 0) +
+                                                (g >> 3) * 16384 + sw128_chunk1(r, g & 7));
         }
+        const uint32_t bw[4] = {raw.x, raw.y, raw.z, raw.w};
+        const float4 mA = sMb4[c * 8 + u * 2], mB = sMb4[c * 8 + u * 2 + 1];
+        const float2 mk[4] = {make_float2(mA.x, mA.y), make_float2(mA.z, mA.w), make_float2(mB.x, mB.y),
+                              make_float2(mB.z, mB.w)};
+        uint32_t dw[4];
 #pragma unroll
-        for (int i = 0; i < 8; ++i) {
-          const int col = c * 32 + u * 8 + i;
-          float x = __uint_as_float(rs[u * 8 + i]) * a.scale;
-          if (a.has_bias) x += bv[i];
-          x += sMb[col];
-          const float p = ex2_approx(((x - m_row) - l_row) * kLog2e);
-          ds[i] = p * (__uint_as_float(rp[u * 8 + i]) - d_row);
-          if constexpr (MODE == MODE_DBIAS) acc[cc * 32 + u * 8 + i] += ds[i];
+        for (int i = 0; i < 4; ++i) {
+          float2 x = __ffma2_rn(pair(rs[rc_][u * 8 + 2 * i], rs[rc_][u * 8 + 2 * i + 1]), sc2, mk[i]);
+          if constexpr (HB) x = __fadd2_rn(x, unpack2<T>(bw[i]));
+          const float2 e = __ffma2_rn(__fadd2_rn(x, nm2), l2e2, nl2);
+          const float2 p = make_float2(ex2_approx(e.x), ex2_approx(e.y));
+          const float2 ds = __fmul2_rn(p, __fadd2_rn(pair(rp[rc_][u * 8 + 2 * i], rp[rc_][u * 8 + 2 * i + 1]), nd2));
+          if constexpr (MODE == MODE_DBIAS) {
+            const float2 t = __fadd2_rn(make_float2(acc[cc * 32 + u * 8 + 2 * i], acc[cc * 32 + u * 8 + 2 * i + 1]), ds);
+            acc[cc * 32 + u * 8 + 2 * i] = t.x;
+            acc[cc * 32 + u * 8 + 2 * i + 1] = t.y;
+          } else {
+            dw[i] = pack2<T>(ds.x, ds.y);
+          }
         }
-        if constexpr (MODE == MODE_DQ) {
-          uint4 pk;
-          pk.x = pack2<T>(ds[0], ds[1]); pk.y = pack2<T>(ds[2], ds[3]);
-          pk.z = pack2<T>(ds[4], ds[5]); pk.w = pack2<T>(ds[6], ds[7]);
-          *reinterpret_cast<uint4*>(sDS + sw128_chunk1(r, c * 4 + u)) = pk;
-        }
+        if constexpr (MODE == MODE_DQ)
+          *reinterpret_cast<uint4*>(sDS + sw128_chunk1(r, c * 4 + u)) = make_uint4(dw[0], dw[1], dw[2], dw[3]);
       }
     }
     if constexpr (MODE == MODE_DQ) fence_proxy_async_smem();
@@ -525,16 +591,16 @@ attn_bwd_rows_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_const
     if (tid == 0) {
       tc_fence_after_sync();
       if constexpr (MODE == MODE_DQ) {
-        const uint32_t dsa = smem_u32(sDS), ka = smem_u32(sK + stg * G::TB);
+        const uint32_t dsa = smem_u32(sDS), ka = smem_u32(sK + kstg * G::TB);
 #pragma unroll
         for (int kk = 0; kk < TKV / 16; ++kk)
           umma<KIND_F16>(tmem_base + COL_DQ, make_smem_desc(dsa + kk * 32, 16, 1024, 2),
                          make_smem_desc(ka + kk * 16 * G::RB, TKV * G::RB, G::SBO, G::LAYOUT), a.idesc_b,
                          (j > 0 || kk > 0) ? 1u : 0u);
         umma_commit(bar_dq);
-        if (a.has_bias && j + 2 < nsteps) load_bias((j + 2) * TKV, stg);   // all reads of this buffer are done
+        if (HB && j + 2 < nsteps) load_bias((j + 2) * TKV, stg);   // all reads of this buffer are done
       } else {
-        if (j + 2 < nsteps) load_step(j + 2, stg);  // this step's MMAs have completed (bar_s), all reads are done
+        if (j + 1 < nsteps) issue_scores(j + 1);   // every thread has read this step's accumulators
       }
     }
     if (!ok) break;
@@ -600,17 +666,18 @@ template <int HD> struct GeoC {
   static constexpr uint32_t SBO = 8 * RB;
   static constexpr int OFF_K = 0;
   static constexpr int OFF_V = OFF_K + TK;
-  static constexpr int OFF_Q = OFF_V + TK;          // [2]
-  static constexpr int OFF_DO = OFF_Q + 2 * TQ;     // [2]
-  static constexpr int OFF_PT = OFF_DO + 2 * TQ;    // [128 keys x 64 queries] SW128
+  static constexpr int NQ = 3;                      // Q / dO stages: tiles are fetched two steps ahead
+  static constexpr int OFF_Q = OFF_V + TK;          // [NQ]
+  static constexpr int OFF_DO = OFF_Q + NQ * TQ;    // [NQ]
+  static constexpr int OFF_PT = OFF_DO + NQ * TQ;   // [128 keys x 64 queries] SW128
   static constexpr int OFF_DST = OFF_PT + 16384;
-  static constexpr int OFF_BIAS = OFF_DST + 16384;  // 2 buffers of [64 queries x 128 keys] (two [64 x 64] SW128 blocks)
-  static constexpr int OFF_ST = OFF_BIAS + 2 * 16384;   // m[64], log l[64], delta[64]
-  static constexpr int OFF_BAR = OFF_ST + 1024;
+  static constexpr int OFF_BIAS = OFF_DST + 16384;  // 2 buffers of transposed bias [128 keys x 64 queries] SW128
+  static constexpr int OFF_ST = OFF_BIAS + 2 * 16384;   // 2 buffers of -m[64], -log l log2e[64], -delta[64]
+  static constexpr int OFF_BAR = OFF_ST + 2048;
   static constexpr int SMEM = OFF_BAR + 128 + 1024;
 };
 
-template <typename T, int HD>
+template <typename T, int HD, bool HB>
 __global__ void __launch_bounds__(256, 2)
 attn_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmDO,
                      const __grid_constant__ CUtensorMap tmK, const __grid_constant__ CUtensorMap tmV,
@@ -625,15 +692,13 @@ attn_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_const
   uint8_t* sPT = smem + G::OFF_PT;
   uint8_t* sDST = smem + G::OFF_DST;
   uint8_t* sBias = smem + G::OFF_BIAS;
-  float* sM = reinterpret_cast<float*>(smem + G::OFF_ST);
-  float* sL = sM + 64;
-  float* sD = sM + 128;
+  float* sStats = reinterpret_cast<float*>(smem + G::OFF_ST);   // [2][3][64]
   uint64_t* bar_kv = reinterpret_cast<uint64_t*>(smem + G::OFF_BAR);
-  uint64_t* bar_in = bar_kv + 1;  // [2]
-  uint64_t* bar_bias = bar_kv + 3;   // [2]: bias tiles are fetched two steps ahead
-  uint64_t* bar_s = bar_kv + 5;
-  uint64_t* bar_acc = bar_kv + 6;
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bar_kv + 7);
+  uint64_t* bar_in = bar_kv + 1;     // [3]
+  uint64_t* bar_bias = bar_kv + 4;   // [2]: bias tiles are fetched two steps ahead
+  uint64_t* bar_s = bar_kv + 6;
+  uint64_t* bar_acc = bar_kv + 7;
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bar_kv + 8);
 
   // 256 threads: thread (r, hh) owns key r of the block and query half hh of each 64-query tile
   const int tid = threadIdx.x, warp = tid >> 5, r = tid & 127, hh = tid >> 7;
@@ -648,7 +713,8 @@ attn_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_const
   const int bias_b = b * a.bias_b_mul;
 
   if (tid == 0) {
-    mbar_init(bar_kv, 1); mbar_init(&bar_in[0], 1); mbar_init(&bar_in[1], 1);
+    mbar_init(bar_kv, 1);
+    for (int i = 0; i < G::NQ; ++i) mbar_init(&bar_in[i], 1);
     mbar_init(&bar_bias[0], 1); mbar_init(&bar_bias[1], 1); mbar_init(bar_s, 1); mbar_init(bar_acc, 1);
     mbar_fence_init();
   }
@@ -660,7 +726,8 @@ attn_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_const
   const uint32_t t_row = tmem_base + ((uint32_t)((warp & 3) * 32) << 16);
   constexpr uint32_t COL_DP = 64, COL_DV = 128, COL_DK = 128 + HD;
 
-  auto load_step = [&](int step, int stg) {
+  auto load_step = [&](int step) {
+    const int stg = step % G::NQ;
     mbar_expect_tx(&bar_in[stg], 2 * G::TQ);
     tma_load_5d(sQ + stg * G::TQ, &tmQ, &bar_in[stg], 0, h, step * 64, s, b);
     tma_load_5d(sDO + stg * G::TQ, &tmDO, &bar_in[stg], 0, h, step * 64, s, b);
@@ -669,15 +736,34 @@ attn_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_const
     uint64_t* bb = &bar_bias[step & 1];
     uint8_t* dst = sBias + (step & 1) * 16384;
     mbar_expect_tx(bb, 16384);
-    tma_load_4d(dst, &tmBias, bb, k0, step * 64, h, bias_b);
-    tma_load_4d(dst + 8192, &tmBias, bb, k0 + 64, step * 64, h, bias_b);
+    tma_load_4d(dst, &tmBias, bb, step * 64, k0, h, bias_b);   // transposed copy: queries are the inner dimension
+  };
+  bool ok = true;
+  // S^T = K Q^T and dP^T = V dO^T of one 64-query tile; issued one step ahead of the threads that consume it
+  auto issue_scores = [&](int step) {
+    const int stg = step % G::NQ;
+    if (step == 0) ok = mbar_wait(bar_kv, 0, a.err, 31);
+    ok = mbar_wait(&bar_in[stg], (step / G::NQ) & 1, a.err, 32) && ok;
+    tc_fence_after_sync();
+    const uint32_t ka = smem_u32(sK), va = smem_u32(sV);
+    const uint32_t qa = smem_u32(sQ + stg * G::TQ), da = smem_u32(sDO + stg * G::TQ);
+#pragma unroll
+    for (int ks = 0; ks < HD / 16; ++ks)
+      umma<KIND_F16>(tmem_base, make_smem_desc(ka + ks * 32, 16, G::SBO, G::LAYOUT),
+                     make_smem_desc(qa + ks * 32, 16, G::SBO, G::LAYOUT), a.idesc_a, ks > 0);
+#pragma unroll
+    for (int ks = 0; ks < HD / 16; ++ks)
+      umma<KIND_F16>(tmem_base + COL_DP, make_smem_desc(va + ks * 32, 16, G::SBO, G::LAYOUT),
+                     make_smem_desc(da + ks * 32, 16, G::SBO, G::LAYOUT), a.idesc_a, ks > 0);
+    umma_commit(bar_s);
   };
   if (tid == 0) {
     mbar_expect_tx(bar_kv, 2 * G::TK);
     tma_load_5d(sK, &tmK, bar_kv, 0, h, k0, s, b);
     tma_load_5d(sV, &tmV, bar_kv, 0, h, k0, s, b);
-    for (int st = 0; st < 2 && st < nsteps; ++st) load_step(st, st);
-    if (a.has_bias) for (int st = 0; st < 2 && st < nsteps; ++st) load_bias(st);
+    for (int st = 0; st < 2 && st < nsteps; ++st) load_step(st);
+    if (HB) for (int st = 0; st < 2 && st < nsteps; ++st) load_bias(st);
+    issue_scores(0);
   }
   const int kj = k0 + r;
   float mb = 0.f;
@@ -685,75 +771,79 @@ attn_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_const
   else if (a.mask != nullptr) mb = kMaskSentinel * ((a.mask[b * a.mask_st[0] + s * a.mask_st[1] + kj] ? 1.0f : 0.0f) - 1.0f);
   const long long plane = (long long)a.B * a.S * a.H * a.N;
   const long long row_base = (((long long)b * a.S + s) * a.H + h) * a.N;
-  bool ok = true;
+  // per-query statistics live in shared memory in the form the packed arithmetic adds: -m, -log l log2e, -delta
+  auto fetch_stats = [&](int step, float& m, float& l, float& dl) {
+    const int qn = step * 64 + tid;
+    const bool v = step < nsteps && qn < a.N;
+    m = v ? a.stats[row_base + qn] : 0.f;
+    l = v ? a.stats[plane + row_base + qn] : 0.f;
+    dl = v ? a.delta[row_base + qn] : 0.f;
+  };
   float st_m = 0.f, st_l = 0.f, st_d = 0.f;
-  if (tid < 64 && tid < a.N) {
-    st_m = a.stats[row_base + tid]; st_l = a.stats[plane + row_base + tid]; st_d = a.delta[row_base + tid];
+  if (tid < 64) {
+    fetch_stats(0, st_m, st_l, st_d);
+    sStats[tid] = -st_m; sStats[64 + tid] = -st_l * kLog2e; sStats[128 + tid] = -st_d;
+    fetch_stats(1, st_m, st_l, st_d);
   }
+  __syncthreads();
 
   for (int j = 0; j < nsteps; ++j) {
-    const int stg = j & 1, q0 = j * 64;
+    const int stg = j & 1, qstg = j % G::NQ;
     const uint32_t par = j & 1, in_par = (j >> 1) & 1;
-    if (tid == 0) {
-      if (j == 0) ok = mbar_wait(bar_kv, 0, a.err, 31);
-      ok = mbar_wait(&bar_in[stg], in_par, a.err, 32) && ok;
-      tc_fence_after_sync();
-      const uint32_t ka = smem_u32(sK), va = smem_u32(sV);
-      const uint32_t qa = smem_u32(sQ + stg * G::TQ), da = smem_u32(sDO + stg * G::TQ);
-#pragma unroll
-      for (int ks = 0; ks < HD / 16; ++ks)   // S^T = K Q^T
-        umma<KIND_F16>(tmem_base, make_smem_desc(ka + ks * 32, 16, G::SBO, G::LAYOUT),
-                       make_smem_desc(qa + ks * 32, 16, G::SBO, G::LAYOUT), a.idesc_a, ks > 0);
-#pragma unroll
-      for (int ks = 0; ks < HD / 16; ++ks)   // dP^T = V dO^T
-        umma<KIND_F16>(tmem_base + COL_DP, make_smem_desc(va + ks * 32, 16, G::SBO, G::LAYOUT),
-                       make_smem_desc(da + ks * 32, 16, G::SBO, G::LAYOUT), a.idesc_a, ks > 0);
-      umma_commit(bar_s);
-    }
-    if (tid < 64) {   // this tile's query statistics were loaded a step ahead; fetch the next tile's now
-      sM[tid] = st_m; sL[tid] = st_l; sD[tid] = st_d;
-      const int qn = q0 + 64 + tid;
-      if (j + 1 < nsteps) {
-        const bool v = qn < a.N;
-        st_m = v ? a.stats[row_base + qn] : 0.f;
-        st_l = v ? a.stats[plane + row_base + qn] : 0.f;
-        st_d = v ? a.delta[row_base + qn] : 0.f;
-      }
-    }
-    __syncthreads();
     ok = mbar_wait(bar_s, par, a.err, 33) && ok;
     tc_fence_after_sync();
-    if (a.has_bias) ok = mbar_wait(&bar_bias[stg], in_par, a.err, 34) && ok;
-    if (j > 0) ok = mbar_wait(bar_acc, (j - 1) & 1, a.err, 35) && ok;   // P^T / dS^T buffers and the other stage are free
-    if (tid == 0 && j > 0 && j + 1 < nsteps) load_step(j + 1, (j + 1) & 1);
+    uint32_t rs[32], rp[32];
+    tmem_ld_32x32(t_row + hh * 32, rs);
+    tmem_ld_32x32(t_row + COL_DP + hh * 32, rp);
+    tmem_ld_wait();
+    tc_fence_before_sync();
+    __syncthreads();   // every thread holds its logits: the accumulators can take the next tile
+    if (tid == 0 && j + 1 < nsteps) issue_scores(j + 1);
+    if (tid < 64) {    // next tile's statistics into the other buffer (its readers finished a step ago)
+      float* nx = sStats + ((j + 1) & 1) * 192;
+      nx[tid] = -st_m; nx[64 + tid] = -st_l * kLog2e; nx[128 + tid] = -st_d;
+      fetch_stats(j + 2, st_m, st_l, st_d);
+    }
+    if (HB) ok = mbar_wait(&bar_bias[stg], in_par, a.err, 34) && ok;
+    if (j > 0) {       // P^T / dS^T buffers and the Q / dO stage of tile j-1 are free
+      ok = mbar_wait(bar_acc, (j - 1) & 1, a.err, 35) && ok;
+      if (tid == 0 && j + 2 < nsteps) load_step(j + 2);
+    } else if (tid == 0 && 2 < nsteps) {
+      load_step(2);
+    }
 
-    const uint8_t* bias_col = sBias + stg * 16384 + (r >> 6) * 8192 + (r & 7) * 2;  // element (q, key r): + q*128 + swizzled chunk
-    const int key_chunk = (r & 63) >> 3;
+    // packed fp32x2 arithmetic: P = 2^((x - m) log2e - log l log2e), dS = P (dP - delta); thread = key, columns = queries
+    const uint8_t* bias_row = sBias + stg * 16384;
+    const float2 sc2 = splat(a.scale), mk2 = splat(mb), l2e2 = splat(kLog2e);
+    const float4* sM4 = reinterpret_cast<const float4*>(sStats + stg * 192);
+    const float4* sL4 = sM4 + 16;
+    const float4* sD4 = sM4 + 32;
     {
       const int c = hh;
-      uint32_t rs[32], rp[32];
-      tmem_ld_32x32(t_row + c * 32, rs);
-      tmem_ld_32x32(t_row + COL_DP + c * 32, rp);
-      tmem_ld_wait();
 #pragma unroll
       for (int u = 0; u < 4; ++u) {
-        float pv[8], ds[8];
+        uint4 raw = make_uint4(0, 0, 0, 0);
+        if constexpr (HB) raw = *reinterpret_cast<const uint4*>(bias_row + sw128_chunk1(r, c * 4 + u));
+        const uint32_t bw[4] = {raw.x, raw.y, raw.z, raw.w};
+        const float4 m0 = sM4[c * 8 + u * 2], m1 = sM4[c * 8 + u * 2 + 1];
+        const float4 l0 = sL4[c * 8 + u * 2], l1 = sL4[c * 8 + u * 2 + 1];
+        const float4 d0 = sD4[c * 8 + u * 2], d1 = sD4[c * 8 + u * 2 + 1];
+        const float2 nm[4] = {make_float2(m0.x, m0.y), make_float2(m0.z, m0.w), make_float2(m1.x, m1.y), make_float2(m1.z, m1.w)};
+        const float2 nl[4] = {make_float2(l0.x, l0.y), make_float2(l0.z, l0.w), make_float2(l1.x, l1.y), make_float2(l1.z, l1.w)};
+        const float2 nd[4] = {make_float2(d0.x, d0.y), make_float2(d0.z, d0.w), make_float2(d1.x, d1.y), make_float2(d1.z, d1.w)};
+        uint32_t pw[4], dw[4];
 #pragma unroll
-        for (int i = 0; i < 8; ++i) {
-          const int q = c * 32 + u * 8 + i;
-          float x = __uint_as_float(rs[u * 8 + i]) * a.scale;
-          if (a.has_bias) x += to_f32(*reinterpret_cast<const T*>(bias_col + q * 128 + ((key_chunk ^ (q & 7)) << 4)));
-          x += mb;
-          pv[i] = ex2_approx(((x - sM[q]) - sL[q]) * kLog2e);
-          ds[i] = pv[i] * (__uint_as_float(rp[u * 8 + i]) - sD[q]);
+        for (int i = 0; i < 4; ++i) {
+          float2 x = __ffma2_rn(pair(rs[u * 8 + 2 * i], rs[u * 8 + 2 * i + 1]), sc2, mk2);
+          if constexpr (HB) x = __fadd2_rn(x, unpack2<T>(bw[i]));
+          const float2 e = __ffma2_rn(__fadd2_rn(x, nm[i]), l2e2, nl[i]);
+          const float2 pp = make_float2(ex2_approx(e.x), ex2_approx(e.y));
+          const float2 ds = __fmul2_rn(pp, __fadd2_rn(pair(rp[u * 8 + 2 * i], rp[u * 8 + 2 * i + 1]), nd[i]));
+          pw[i] = pack2<T>(pp.x, pp.y);
+          dw[i] = pack2<T>(ds.x, ds.y);
         }
-        uint4 pk;
-        pk.x = pack2<T>(pv[0], pv[1]); pk.y = pack2<T>(pv[2], pv[3]);
-        pk.z = pack2<T>(pv[4], pv[5]); pk.w = pack2<T>(pv[6], pv[7]);
-        *reinterpret_cast<uint4*>(sPT + sw128_chunk1(r, c * 4 + u)) = pk;
-        pk.x = pack2<T>(ds[0], ds[1]); pk.y = pack2<T>(ds[2], ds[3]);
-        pk.z = pack2<T>(ds[4], ds[5]); pk.w = pack2<T>(ds[6], ds[7]);
-        *reinterpret_cast<uint4*>(sDST + sw128_chunk1(r, c * 4 + u)) = pk;
+        *reinterpret_cast<uint4*>(sPT + sw128_chunk1(r, c * 4 + u)) = make_uint4(pw[0], pw[1], pw[2], pw[3]);
+        *reinterpret_cast<uint4*>(sDST + sw128_chunk1(r, c * 4 + u)) = make_uint4(dw[0], dw[1], dw[2], dw[3]);
       }
     }
     fence_proxy_async_smem();
@@ -762,7 +852,7 @@ attn_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_const
     if (tid == 0) {
       tc_fence_after_sync();
       const uint32_t pa = smem_u32(sPT), dsa = smem_u32(sDST);
-      const uint32_t qa = smem_u32(sQ + stg * G::TQ), da = smem_u32(sDO + stg * G::TQ);
+      const uint32_t qa = smem_u32(sQ + qstg * G::TQ), da = smem_u32(sDO + qstg * G::TQ);
 #pragma unroll
       for (int kk = 0; kk < 4; ++kk)   // dV += P^T dO   (B = dO as [n = d, k = query]: MN-major)
         umma<KIND_F16>(tmem_base + COL_DV, make_smem_desc(pa + kk * 32, 16, 1024, 2),
@@ -774,7 +864,7 @@ attn_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_const
                        make_smem_desc(qa + kk * 16 * G::RB, 64 * G::RB, G::SBO, G::LAYOUT), a.idesc_b,
                        (j > 0 || kk > 0) ? 1u : 0u);
       umma_commit(bar_acc);
-      if (a.has_bias && j + 2 < nsteps) load_bias(j + 2);   // every thread is past its reads of this buffer
+      if (HB && j + 2 < nsteps) load_bias(j + 2);   // every thread is past its reads of this buffer
     }
     if (!ok) break;
   }
@@ -864,6 +954,31 @@ int bias_map(CUtensorMap* out, const void* bias, const TriAttnDesc* d, int rows)
   return make_tmap(out, bias, d->dtype, 4, dims, str, box, 128);
 }
 
+// out[b][h][k][q] = bias[b][h][q][k] for 16-bit elements (the dK/dV pass reads keys as rows)
+__global__ void transpose_bias_kernel(const uint16_t* __restrict__ in, int64_t st_b, int64_t st_h, int64_t st_q, int n, int H,
+                                      uint16_t* __restrict__ out) {
+  __shared__ uint16_t tile[64][66];
+  const int bh = blockIdx.z, b = bh / H, h = bh % H;
+  const uint16_t* src = in + b * st_b + h * st_h;
+  uint16_t* dst = out + (int64_t)bh * n * n;
+  const int q0 = blockIdx.y * 64, k0 = blockIdx.x * 64;
+  for (int i = threadIdx.y; i < 64; i += blockDim.y) {
+    const int q = q0 + i;
+    for (int jj = threadIdx.x; jj < 64; jj += 32) {
+      const int k = k0 + jj;
+      tile[i][jj] = (q < n && k < n) ? src[q * st_q + k] : (uint16_t)0;
+    }
+  }
+  __syncthreads();
+  for (int i = threadIdx.y; i < 64; i += blockDim.y) {
+    const int k = k0 + i;
+    for (int jj = threadIdx.x; jj < 64; jj += 32) {
+      const int q = q0 + jj;
+      if (k < n && q < n) dst[(int64_t)k * n + q] = tile[jj][i];
+    }
+  }
+}
+
 template <typename KernelT>
 int set_dyn_smem(KernelT kern, int bytes) {
   TRI_CUDA_OK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, bytes));
@@ -873,7 +988,7 @@ int set_dyn_smem(KernelT kern, int bytes) {
 template <typename T, int HD>
 int bwd_launch(const TriAttnDesc* d, const void* q, const void* k, const void* v, const void* bias,
                const uint8_t* mask, const void* o, const float* stats, const void* d_o, void* dq, void* dk, void* dv,
-               float* dbias, int* err, float* delta, float* dbias_partial, cudaStream_t st) {
+               float* dbias, int* err, float* delta, float* dbias_partial, void* bias_t, cudaStream_t st) {
   const long long rows = (long long)d->B * d->n_seq * d->H * d->n_res;
   const double pairs = (double)rows * d->n_res;
   const double tensor_bytes = 2.0 * d->B * d->n_seq * (double)d->n_res * d->H * d->D;
@@ -896,15 +1011,27 @@ int bwd_launch(const TriAttnDesc* d, const void* q, const void* k, const void* v
   TRI_TRY(qkv_map_rows(&tdo, d_o, d, d->do_st, 64));
   TRI_TRY(qkv_map_rows(&tk, k, d, d->k_st, 128));
   TRI_TRY(qkv_map_rows(&tv, v, d, d->v_st, 128));
-  if (bias) TRI_TRY(bias_map(&tb, bias, d, 64)); else tb = tq;
+  if (bias) {   // the dK/dV pass (thread = key) reads a transposed copy of the bias: [b][h][key][query]
+    const int nb = d->bias_st[0] != 0 ? d->B : 1;
+    transpose_bias_kernel<<<dim3(cdiv(d->n_res, 64), cdiv(d->n_res, 64), nb * d->H), dim3(32, 8), 0, st>>>(
+        static_cast<const uint16_t*>(bias), d->bias_st[0], d->bias_st[1], d->bias_st[2], d->n_res, d->H,
+        static_cast<uint16_t*>(bias_t));
+    TRI_LAUNCH_OK();
+    const uint64_t dims[4] = {(uint64_t)d->n_res, (uint64_t)d->n_res, (uint64_t)d->H, (uint64_t)nb};
+    const uint64_t str[3] = {(uint64_t)d->n_res, (uint64_t)d->n_res * d->n_res, nb > 1 ? (uint64_t)d->H * d->n_res * d->n_res : 0};
+    const uint32_t box[4] = {64, 128, 1, 1};
+    TRI_TRY(make_tmap(&tb, bias_t, d->dtype, 4, dims, str, box, 128));
+  } else {
+    tb = tq;
+  }
   a.out0 = dk; a.out1 = dv;
   for (int i = 0; i < 4; ++i) { a.out0_st[i] = d->dk_st[i]; a.out1_st[i] = d->dv_st[i]; }
   a.idesc_a = make_idesc(kind, 128, 64, false, false);
   a.idesc_b = make_idesc(kind, 128, HD, false, true);
   {
-    auto kern = attn_bwd_dkdv_kernel<T, HD>;
-    static bool configured = false;
-    if (!configured) { TRI_TRY(set_dyn_smem(kern, GeoC<HD>::SMEM)); configured = true; }
+    auto kern = bias ? attn_bwd_dkdv_kernel<T, HD, true> : attn_bwd_dkdv_kernel<T, HD, false>;
+    static bool configured[2] = {false, false};
+    if (!configured[bias != nullptr]) { TRI_TRY(set_dyn_smem(kern, GeoC<HD>::SMEM)); configured[bias != nullptr] = true; }
     KernelTimer kt("tc_attn_bwd_dkdv", st, 8.0 * pairs * d->D, 6.0 * tensor_bytes);
     kern<<<(unsigned)((long long)qblocks * d->B * d->n_seq * d->H), 256, GeoC<HD>::SMEM, st>>>(tq, tdo, tk, tv, tb, a);
     TRI_LAUNCH_OK();
@@ -920,9 +1047,9 @@ int bwd_launch(const TriAttnDesc* d, const void* q, const void* k, const void* v
   a.idesc_a = make_idesc(kind, 128, 64, false, false);
   a.idesc_b = make_idesc(kind, 128, HD, false, true);
   {
-    auto kern = attn_bwd_rows_kernel<T, HD, 64, MODE_DQ, 2>;
-    static bool configured = false;
-    if (!configured) { TRI_TRY(set_dyn_smem(kern, GeoR<HD, 64, MODE_DQ>::SMEM)); configured = true; }
+    auto kern = bias ? attn_bwd_rows_kernel<T, HD, 64, MODE_DQ, 2, true> : attn_bwd_rows_kernel<T, HD, 64, MODE_DQ, 2, false>;
+    static bool configured[2] = {false, false};
+    if (!configured[bias != nullptr]) { TRI_TRY(set_dyn_smem(kern, GeoR<HD, 64, MODE_DQ>::SMEM)); configured[bias != nullptr] = true; }
     KernelTimer kt("tc_attn_bwd_dq", st, 2.0 * pairs * d->D, 5.0 * tensor_bytes);
     kern<<<(unsigned)((long long)qblocks * d->B * d->n_seq * d->H), 256, GeoR<HD, 64, MODE_DQ>::SMEM, st>>>(tq, tdo, tk, tv, tb, a);
     TRI_LAUNCH_OK();
@@ -936,7 +1063,7 @@ int bwd_launch(const TriAttnDesc* d, const void* q, const void* k, const void* v
     a.row_chunks = chunks;
     a.out0 = chunks > 1 ? dbias_partial : dbias;
     a.idesc_a = make_idesc(kind, 128, 128, false, false);
-    auto kern = attn_bwd_rows_kernel<T, HD, 128, MODE_DBIAS, 1>;
+    auto kern = attn_bwd_rows_kernel<T, HD, 128, MODE_DBIAS, 1, true>;   // a bias gradient implies a bias
     static bool configured = false;
     if (!configured) { TRI_TRY(set_dyn_smem(kern, GeoR<HD, 128, MODE_DBIAS>::SMEM)); configured = true; }
     KernelTimer kt("tc_attn_bwd_dbias", st, 0.0, 4.0 * tensor_bytes);
@@ -1229,11 +1356,11 @@ int fwd_launch(const TriAttnDesc* d, const void* q, const void* k, const void* v
   // the forward is bound by instruction issue in the softmax warps, not by MMA latency.
   static const bool unpipelined = getenv("TRI_B200_ATTN_FWD_PIPE") == nullptr;
   if (unpipelined) {
-    auto kern = attn_fwd_tc_kernel<T, HD>;
-    static bool configured = false;
-    if (!configured) {
+    auto kern = bias != nullptr ? attn_fwd_tc_kernel<T, HD, true> : attn_fwd_tc_kernel<T, HD, false>;
+    static bool configured[2] = {false, false};
+    if (!configured[bias != nullptr]) {
       TRI_CUDA_OK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, Geo<HD>::SMEM));
-      configured = true;
+      configured[bias != nullptr] = true;
     }
     kern<<<(unsigned)blocks, 128, Geo<HD>::SMEM, st>>>(tq, tk, tv, tb, a);
     TRI_LAUNCH_OK();
@@ -1275,7 +1402,8 @@ bool attn_bwd_supported(const TriAttnDesc* d) {
 size_t attn_ws_bytes(const TriAttnDesc* d, int is_bwd) {
   if (!is_bwd) return 512;
   return 512 + align_up((size_t)d->B * d->n_seq * d->H * d->n_res * sizeof(float)) +
-         align_up((size_t)kDbiasRowChunks * d->B * d->H * d->n_res * d->n_res * sizeof(float));
+         align_up((size_t)kDbiasRowChunks * d->B * d->H * d->n_res * d->n_res * sizeof(float)) +
+         align_up((size_t)d->B * d->H * d->n_res * d->n_res * 2);   // transposed 16-bit copy of the bias
 }
 
 int attn_forward(const TriAttnDesc* d, const void* q, const void* k, const void* v, const void* bias,
@@ -1300,12 +1428,13 @@ int attn_backward(const TriAttnDesc* d, const void* q, const void* k, const void
   float* delta = reinterpret_cast<float*>(static_cast<char*>(ws) + 512);
   float* part = reinterpret_cast<float*>(static_cast<char*>(ws) + 512 +
                                          align_up((size_t)d->B * d->n_seq * d->H * d->n_res * sizeof(float)));
+  void* bias_t = reinterpret_cast<char*>(part) + align_up((size_t)kDbiasRowChunks * d->B * d->H * d->n_res * d->n_res * sizeof(float));
   if (d->dtype == TRI_BF16) {
-    if (d->D == 32) return bwd_launch<__nv_bfloat16, 32>(d, q, k, v, bias, mask, o, lse, d_o, dq, dk, dv, dbias, err, delta, part, st);
-    return bwd_launch<__nv_bfloat16, 64>(d, q, k, v, bias, mask, o, lse, d_o, dq, dk, dv, dbias, err, delta, part, st);
+    if (d->D == 32) return bwd_launch<__nv_bfloat16, 32>(d, q, k, v, bias, mask, o, lse, d_o, dq, dk, dv, dbias, err, delta, part, bias_t, st);
+    return bwd_launch<__nv_bfloat16, 64>(d, q, k, v, bias, mask, o, lse, d_o, dq, dk, dv, dbias, err, delta, part, bias_t, st);
   }
-  if (d->D == 32) return bwd_launch<__half, 32>(d, q, k, v, bias, mask, o, lse, d_o, dq, dk, dv, dbias, err, delta, part, st);
-  return bwd_launch<__half, 64>(d, q, k, v, bias, mask, o, lse, d_o, dq, dk, dv, dbias, err, delta, part, st);
+  if (d->D == 32) return bwd_launch<__half, 32>(d, q, k, v, bias, mask, o, lse, d_o, dq, dk, dv, dbias, err, delta, part, bias_t, st);
+  return bwd_launch<__half, 64>(d, q, k, v, bias, mask, o, lse, d_o, dq, dk, dv, dbias, err, delta, part, bias_t, st);
 }
 
 }  // namespace tc
