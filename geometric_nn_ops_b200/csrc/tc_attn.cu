@@ -30,8 +30,8 @@ struct AttnArgs {
   void* o;
   int64_t o_st[4];
   float* stats;          // [2][B][S][H][N]: row max, log row sum
-  const uint8_t* mask;   // nullable
-  int64_t mask_st[2];
+  const float* mask_terms;   // [B][S][npad] additive key-mask terms (0, -1e9, or -inf beyond N)
+  int npad;                  // N rounded up to 128
   int has_bias;
   int bias_b_mul;        // 0 when the bias is broadcast over the batch
   uint32_t idesc_s, idesc_pv;
@@ -44,13 +44,13 @@ template <int HD> struct Geo {
   static constexpr uint32_t LAYOUT = RB == 128 ? 2 : 4;  // SWIZZLE_128B or SWIZZLE_64B
   static constexpr uint32_t SBO = 8 * RB;                // 8-row group
   static constexpr int OFF_Q = 0;
-  static constexpr int OFF_K = OFF_Q + TILE;
-  static constexpr int OFF_V = OFF_K + 2 * TILE;
+  static constexpr int OFF_K = OFF_Q + TILE;             // [2]
+  static constexpr int OFF_V = OFF_K + 2 * TILE;         // [2]
   static constexpr int OFF_P = OFF_V + 2 * TILE;         // [128 x 128] as two SW128 blocks of 64 keys
   static constexpr int OFF_BIAS = OFF_P + 32768;         // same shape
-  static constexpr int OFF_MB = OFF_BIAS + 32768;        // 128 floats
-  static constexpr int OFF_BAR = OFF_MB + 512;
-  static constexpr int SMEM = OFF_BAR + 128 + 1024;      // + alignment slack
+  static constexpr int OFF_MB = OFF_BIAS + 32768;        // [2] x 128 additive key-mask terms
+  static constexpr int OFF_BAR = OFF_MB + 1024;
+  static constexpr int SMEM = OFF_BAR + 256 + 1024;      // + alignment slack
 };
 
 // byte offset of 16-byte chunk `g` (0..15, 8 elements each) of row r inside a [128 x 128] two-block SW128 tile
@@ -93,8 +93,33 @@ __device__ __forceinline__ void unpack8(const uint4& v, float (&f)[8]) {
   for (int i = 0; i < 8; ++i) f[i] = to_f32(pk.h[i]);
 }
 
+// additive key-mask terms of every (batch, row): 0 for a kept key, -1e9 for a masked key, -inf beyond N; rows of npad
+__global__ void mask_terms_kernel(const uint8_t* __restrict__ mask, int64_t st_b, int64_t st_s, int B, int S, int N, int npad,
+                                  float* __restrict__ out) {
+  const long long idx = blockIdx.x * (long long)blockDim.x + threadIdx.x;
+  if (idx >= (long long)B * S * npad) return;
+  const int k = idx % npad;
+  const long long bs = idx / npad;
+  const int s = bs % S, b = bs / S;
+  float v = 0.f;
+  if (k >= N) v = -INFINITY;
+  else if (mask != nullptr) v = kMaskSentinel * ((mask[b * st_b + s * st_s + k] ? 1.0f : 0.0f) - 1.0f);
+  out[idx] = v;
+}
+
+// 288 threads.  Warps 0-7 do the softmax arithmetic: thread (r, hh) owns query row r and the 64-key half hh of each
+// 128-key tile, with its own running maximum and sum and its own output accumulator O_hh in TMEM; the halves are
+// merged once at the end.  Warp 8 issues every TMA copy and every MMA.  The two sides meet on mbarriers:
+//   bar_s    issuer -> threads   S = Q K^T of a tile is in TMEM
+//   bar_free threads -> issuer   every warp has its logits in registers (next tile's S, bias and mask terms may load)
+//   bar_p    threads -> issuer   P of the tile is in shared memory and O has its final scale (P V may start)
+//   bar_pv   issuer -> threads   P V is done: P's buffer is free and O is current
+// O stays in TMEM across tiles.  It is rescaled only when a row's maximum grows by more than kRescale, so the
+// stored maximum may be stale by up to that much: P <= e^kRescale = 256, and the row sum uses the same maximum.
+constexpr float kRescale = 5.545177444f;   // 8 ln 2
+
 template <typename T, int HD, bool HB>
-__global__ void __launch_bounds__(128, 2)
+__global__ void __launch_bounds__(288, 2)
 attn_fwd_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmK,
                    const __grid_constant__ CUtensorMap tmV, const __grid_constant__ CUtensorMap tmBias,
                    const AttnArgs a) {
@@ -108,13 +133,16 @@ attn_fwd_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
   uint8_t* sBias = smem + G::OFF_BIAS;
   float* sMb = reinterpret_cast<float*>(smem + G::OFF_MB);
   uint64_t* bar_q = reinterpret_cast<uint64_t*>(smem + G::OFF_BAR);
-  uint64_t* bar_kv = bar_q + 1;  // [2]
-  uint64_t* bar_bias = bar_q + 3;
-  uint64_t* bar_s = bar_q + 4;
-  uint64_t* bar_pv = bar_q + 5;
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bar_q + 6);
+  uint64_t* bar_k = bar_q + 1;   // [2] K tile + mask terms
+  uint64_t* bar_v = bar_q + 3;   // [2]
+  uint64_t* bar_bias = bar_q + 5;
+  uint64_t* bar_s = bar_q + 6;
+  uint64_t* bar_pv = bar_q + 7;
+  uint64_t* bar_free = bar_q + 8;
+  uint64_t* bar_p = bar_q + 9;
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bar_q + 10);
 
-  const int tid = threadIdx.x, warp = tid >> 5;
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31, r = tid & 127, hh = (tid >> 7) & 1;
   const int qblocks = (a.N + 127) / 128;
   int z = blockIdx.x;
   const int qb = z % qblocks; z /= qblocks;
@@ -122,11 +150,11 @@ attn_fwd_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
   const int s = z % a.S;
   const int b = z / a.S;
   const int q0 = qb * 128;
-  const int ntiles = (a.N + 127) / 128;
+  const int nt = (a.N + 127) / 128;
 
   if (tid == 0) {
-    mbar_init(bar_q, 1); mbar_init(&bar_kv[0], 1); mbar_init(&bar_kv[1], 1);
-    mbar_init(bar_bias, 1); mbar_init(bar_s, 1); mbar_init(bar_pv, 1);
+    mbar_init(bar_q, 1); mbar_init(&bar_k[0], 1); mbar_init(&bar_k[1], 1); mbar_init(&bar_v[0], 1); mbar_init(&bar_v[1], 1);
+    mbar_init(bar_bias, 1); mbar_init(bar_s, 1); mbar_init(bar_pv, 1); mbar_init(bar_free, 8); mbar_init(bar_p, 8);
     mbar_fence_init();
   }
   if (warp == 0) tmem_alloc(tmem_slot, 256);
@@ -134,155 +162,205 @@ attn_fwd_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
   __syncthreads();
   tc_fence_after_sync();
   const uint32_t tmem_base = *tmem_slot;
-  const uint32_t t_row = tmem_base + ((uint32_t)(warp * 32) << 16);
-
-  if (tid == 0) {
-    mbar_expect_tx(bar_q, G::TILE);
-    tma_load_5d(sQ, &tmQ, bar_q, 0, h, q0, s, b);
-    for (int st = 0; st < 2 && st < ntiles; ++st) {
-      mbar_expect_tx(&bar_kv[st], 2 * G::TILE);
-      tma_load_5d(sK + st * G::TILE, &tmK, &bar_kv[st], 0, h, st * 128, s, b);
-      tma_load_5d(sV + st * G::TILE, &tmV, &bar_kv[st], 0, h, st * 128, s, b);
-    }
-    if (a.has_bias) {
-      mbar_expect_tx(bar_bias, 32768);
-      tma_load_4d(sBias, &tmBias, bar_bias, 0, q0, h, b * a.bias_b_mul);
-      tma_load_4d(sBias + 16384, &tmBias, bar_bias, 64, q0, h, b * a.bias_b_mul);
-    }
-  }
-
-  float m_run = -INFINITY, l_run = 0.f;
-  float o_acc[HD];
-#pragma unroll
-  for (int i = 0; i < HD; ++i) o_acc[i] = 0.f;
+  const uint32_t t_row = tmem_base + ((uint32_t)((warp & 3) * 32) << 16);
+  constexpr uint32_t COL_O = 128;   // O_0 at [128, 128 + HD), O_1 at [128 + HD, 128 + 2 HD)
   bool ok = true;
 
-  for (int j = 0; j < ntiles; ++j) {
-    const int stg = j & 1, k0 = j * 128;
-    const uint32_t par = j & 1, kv_par = (j >> 1) & 1;
-    if (tid == 0) {
-      if (j == 0) ok = mbar_wait(bar_q, 0, a.err, 11);
-      ok = ok && mbar_wait(&bar_kv[stg], kv_par, a.err, 12);
-      tc_fence_after_sync();
-      const uint32_t qa = smem_u32(sQ), ka = smem_u32(sK + stg * G::TILE);
+  if (warp == 8) {
+    if (lane == 0) {
+      // ---------------------------------- issuer -------------------------------------------------
+      const float* mrow = a.mask_terms + ((long long)b * a.S + s) * a.npad;
+      auto load_k = [&](int t) {
+        const int stg = t & 1;
+        mbar_expect_tx(&bar_k[stg], G::TILE + 512);
+        tma_load_5d(sK + stg * G::TILE, &tmK, &bar_k[stg], 0, h, t * 128, s, b);
+        bulk_load(sMb + stg * 128, mrow + t * 128, 512, &bar_k[stg]);
+      };
+      auto load_v = [&](int t) {
+        const int stg = t & 1;
+        mbar_expect_tx(&bar_v[stg], G::TILE);
+        tma_load_5d(sV + stg * G::TILE, &tmV, &bar_v[stg], 0, h, t * 128, s, b);
+      };
+      auto load_bias = [&](int t) {
+        mbar_expect_tx(bar_bias, 32768);
+        tma_load_4d(sBias, &tmBias, bar_bias, t * 128, q0, h, b * a.bias_b_mul);
+        tma_load_4d(sBias + 16384, &tmBias, bar_bias, t * 128 + 64, q0, h, b * a.bias_b_mul);
+      };
+      constexpr uint32_t HI_KMAJ = desc_hi(G::SBO, G::LAYOUT);
+      constexpr uint32_t HI_P = desc_hi(1024, 2);
+      const uint32_t q_lo = desc_lo(smem_u32(sQ), 16), k_lo = desc_lo(smem_u32(sK), 16);
+      const uint32_t p_lo = desc_lo(smem_u32(sP), 16), vmn_lo = desc_lo(smem_u32(sV), 128 * G::RB);   // V as [n = d, k = key]
+      auto issue_s = [&](int t) {
+        ok = mbar_wait(&bar_k[t & 1], (t >> 1) & 1, a.err, 12) && ok;
+        tc_fence_after_sync();
+        const uint32_t so = (t & 1) * (G::TILE >> 4);
 #pragma unroll
-      for (int ks = 0; ks < HD / 16; ++ks)
-        umma<KIND_F16>(tmem_base, make_smem_desc(qa + ks * 32, 16, G::SBO, G::LAYOUT),
-                       make_smem_desc(ka + ks * 32, 16, G::SBO, G::LAYOUT), a.idesc_s, ks > 0);
-      umma_commit(bar_s);
+        for (int ks = 0; ks < HD / 16; ++ks)
+          umma<KIND_F16>(tmem_base, desc_join(q_lo + ks * 2, HI_KMAJ), desc_join(k_lo + so + ks * 2, HI_KMAJ), a.idesc_s, ks > 0);
+        umma_commit(bar_s);
+      };
+      mbar_expect_tx(bar_q, G::TILE);
+      tma_load_5d(sQ, &tmQ, bar_q, 0, h, q0, s, b);
+      for (int t = 0; t < 2 && t < nt; ++t) { load_k(t); load_v(t); }
+      if (HB) load_bias(0);
+      ok = mbar_wait(bar_q, 0, a.err, 11);
+      issue_s(0);
+      for (int j = 0; j < nt && ok; ++j) {
+        const int stg = j & 1;
+        ok = mbar_wait(bar_free, j & 1, a.err, 16) && ok;   // logits, bias and mask terms of tile j are in registers
+        if (j + 1 < nt) {
+          issue_s(j + 1);
+          if (HB) load_bias(j + 1);
+        }
+        if (j + 2 < nt) load_k(j + 2);                      // S(j) has completed: its K stage is free
+        ok = mbar_wait(bar_p, j & 1, a.err, 17) && ok;
+        if (j >= 1) {                                       // (complete: the threads waited for it before writing P)
+          ok = mbar_wait(bar_pv, (j - 1) & 1, a.err, 15) && ok;
+          if (j + 1 < nt) load_v(j + 1);                    // P V(j-1) is done: its V stage is free
+        }
+        ok = mbar_wait(&bar_v[stg], (j >> 1) & 1, a.err, 18) && ok;
+        tc_fence_after_sync();
+        const uint32_t so = stg * (G::TILE >> 4);
+#pragma unroll
+        for (int kk = 0; kk < 8; ++kk)   // O_half += P[:, half] V[half]: keys 64 * (kk >> 2) + 16 * (kk & 3) ...
+          umma<KIND_F16>(tmem_base + COL_O + (kk >> 2) * HD, desc_join(p_lo + (kk >> 2) * 1024 + (kk & 3) * 2, HI_P),
+                         desc_join(vmn_lo + so + kk * G::RB, HI_KMAJ), a.idesc_pv, (j > 0 || (kk & 3) > 0) ? 1u : 0u);
+        umma_commit(bar_pv);
+      }
     }
-    {  // additive key-mask term for this tile's 128 keys (thread t handles key t)
-      const int kj = k0 + tid;
-      float mb = 0.f;
-      if (kj >= a.N) mb = -INFINITY;
-      else if (a.mask != nullptr) mb = kMaskSentinel * ((a.mask[b * a.mask_st[0] + s * a.mask_st[1] + kj] ? 1.0f : 0.0f) - 1.0f);
-      sMb[tid] = mb;
-    }
-    __syncthreads();
-    ok = mbar_wait(bar_s, par, a.err, 13) && ok;
-    tc_fence_after_sync();
-    if (a.has_bias) ok = mbar_wait(bar_bias, par, a.err, 14) && ok;
+  } else {
+    // ------------------------------------ softmax warps ------------------------------------------
+    float m_run = -INFINITY, l_run = 0.f;
+    const float2 sc2 = splat(a.scale), l2e2 = splat(kLog2e);
+    const uint32_t t_o = t_row + COL_O + hh * HD;   // this thread's output accumulator row
 
-    // ---- logits into registers, running max (packed fp32x2 arithmetic) ---------------------------
-    float2 x2[64];
-    float mx4[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};   // independent chains: no 128-long dependency
-    const float2 sc2 = splat(a.scale);
-    const float4* sMb4 = reinterpret_cast<const float4*>(sMb);
+    for (int j = 0; j < nt; ++j) {
+      const int stg = j & 1;
+      ok = mbar_wait(bar_s, j & 1, a.err, 13) && ok;
+      tc_fence_after_sync();
+      ok = mbar_wait(&bar_k[stg], (j >> 1) & 1, a.err, 12) && ok;   // the tile's mask terms
+      if (HB) ok = mbar_wait(bar_bias, j & 1, a.err, 14) && ok;
+
+      // ---- logits of this thread's 64 keys into registers, their maximum ----------------------------
+      float2 x2[32];
+      float mx4[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};   // independent chains
+      const float4* sMb4 = reinterpret_cast<const float4*>(sMb + stg * 128 + hh * 64);
 #pragma unroll
-    for (int c = 0; c < 4; ++c) {
-      uint32_t r[32];
-      tmem_ld_32x32(t_row + c * 32, r);
-      tmem_ld_wait();
+      for (int c = 0; c < 2; ++c) {
+        uint32_t rr[32];
+        tmem_ld_32x32(t_row + hh * 64 + c * 32, rr);
+        tmem_ld_wait();
 #pragma unroll
-      for (int u = 0; u < 4; ++u) {
-        uint4 raw = make_uint4(0, 0, 0, 0);
-        if constexpr (HB) raw = *reinterpret_cast<const uint4*>(sBias + sw128_chunk(tid, c * 4 + u));
-        const uint32_t bw[4] = {raw.x, raw.y, raw.z, raw.w};
-        const float4 mA = sMb4[c * 8 + u * 2], mB = sMb4[c * 8 + u * 2 + 1];
-        const float2 mk[4] = {make_float2(mA.x, mA.y), make_float2(mA.z, mA.w), make_float2(mB.x, mB.y),
-                              make_float2(mB.z, mB.w)};
+        for (int u = 0; u < 4; ++u) {
+          uint4 raw = make_uint4(0, 0, 0, 0);
+          if constexpr (HB) raw = *reinterpret_cast<const uint4*>(sBias + sw128_chunk(r, hh * 8 + c * 4 + u));
+          const uint32_t bw[4] = {raw.x, raw.y, raw.z, raw.w};
+          const float4 mA = sMb4[c * 8 + u * 2], mB = sMb4[c * 8 + u * 2 + 1];
+          const float2 mk[4] = {make_float2(mA.x, mA.y), make_float2(mA.z, mA.w), make_float2(mB.x, mB.y),
+                                make_float2(mB.z, mB.w)};
 #pragma unroll
-        for (int i = 0; i < 4; ++i) {
-          float2 v = __ffma2_rn(pair(r[u * 8 + 2 * i], r[u * 8 + 2 * i + 1]), sc2, mk[i]);
-          if constexpr (HB) v = __fadd2_rn(v, unpack2<T>(bw[i]));
-          x2[c * 16 + u * 4 + i] = v;
-          mx4[i] = fmax3(mx4[i], v.x, v.y);
+          for (int i = 0; i < 4; ++i) {
+            float2 v = __ffma2_rn(pair(rr[u * 8 + 2 * i], rr[u * 8 + 2 * i + 1]), sc2, mk[i]);
+            if constexpr (HB) v = __fadd2_rn(v, unpack2<T>(bw[i]));
+            x2[c * 16 + u * 4 + i] = v;
+            mx4[i] = fmax3(mx4[i], v.x, v.y);
+          }
         }
       }
-    }
-    const float mx = fmaxf(fmaxf(mx4[0], mx4[1]), fmaxf(mx4[2], mx4[3]));
-    const float m_new = fmaxf(m_run, mx);
-    const float alpha = ex2_approx((m_run - m_new) * kLog2e);
-    const float2 nm2 = splat(-m_new), l2e2 = splat(kLog2e);
-    float2 ps2[2] = {make_float2(0.f, 0.f), make_float2(0.f, 0.f)};
-#pragma unroll
-    for (int g = 0; g < 16; ++g) {
-      uint32_t pw[4];
-#pragma unroll
-      for (int i = 0; i < 4; ++i) {
-        const float2 e = __fmul2_rn(__fadd2_rn(x2[g * 4 + i], nm2), l2e2);
-        const float2 pp = make_float2(ex2_approx(e.x), ex2_approx(e.y));
-        ps2[i & 1] = __fadd2_rn(ps2[i & 1], pp);
-        pw[i] = pack2<T>(pp.x, pp.y);
-      }
-      *reinterpret_cast<uint4*>(sP + sw128_chunk(tid, g)) = make_uint4(pw[0], pw[1], pw[2], pw[3]);
-    }
-    const float ps4[4] = {ps2[0].x, ps2[0].y, ps2[1].x, ps2[1].y};
-    l_run = l_run * alpha + ((ps4[0] + ps4[1]) + (ps4[2] + ps4[3]));
-    m_run = m_new;
-    fence_proxy_async_smem();
-    tc_fence_before_sync();
-    __syncthreads();
+      tc_fence_before_sync();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(bar_free);
 
-    if (tid == 0) {
-      tc_fence_after_sync();
-      const uint32_t pa = smem_u32(sP), va = smem_u32(sV + stg * G::TILE);
+      const float mx = fmaxf(fmaxf(mx4[0], mx4[1]), fmaxf(mx4[2], mx4[3]));
+      const bool grow = mx > m_run + kRescale;          // (always true on the first tile with a key in range)
+      const float m_new = grow ? mx : m_run;
+      if (j > 0) {
+        ok = mbar_wait(bar_pv, (j - 1) & 1, a.err, 15) && ok;   // P's buffer is free, O is current
+        tc_fence_after_sync();
+        if (__any_sync(0xffffffffu, grow)) {            // tcgen05.ld / st are warp-wide: rows that keep their maximum scale by 1
+          const float alpha = grow ? ex2_approx((m_run - m_new) * kLog2e) : 1.0f;   // m_run = -inf gives 0 (O_hh is 0 then)
+          l_run *= alpha;
 #pragma unroll
-      for (int kk = 0; kk < 8; ++kk)
-        umma<KIND_F16>(tmem_base + 128, make_smem_desc(pa + (kk >> 2) * 16384 + (kk & 3) * 32, 16, 1024, 2),
-                       make_smem_desc(va + kk * 16 * G::RB, 128 * G::RB, G::SBO, G::LAYOUT), a.idesc_pv, kk > 0);
-      umma_commit(bar_pv);
-      if (a.has_bias && j + 1 < ntiles) {  // every thread has finished reading this tile's bias
-        mbar_expect_tx(bar_bias, 32768);
-        tma_load_4d(sBias, &tmBias, bar_bias, k0 + 128, q0, h, b * a.bias_b_mul);
-        tma_load_4d(sBias + 16384, &tmBias, bar_bias, k0 + 192, q0, h, b * a.bias_b_mul);
+          for (int c = 0; c < HD / 16; ++c) {
+            uint32_t o[16];
+            tmem_ld_32x16(t_o + c * 16, o);
+            tmem_ld_wait();
+#pragma unroll
+            for (int i = 0; i < 16; ++i) o[i] = __float_as_uint(__uint_as_float(o[i]) * alpha);
+            tmem_st_32x16(t_o + c * 16, o);
+          }
+          tmem_st_wait();
+        }
       }
-    }
-    ok = mbar_wait(bar_pv, par, a.err, 15) && ok;
-    tc_fence_after_sync();
-    if (tid == 0 && j + 2 < ntiles) {  // the PV product has consumed this K/V stage
-      mbar_expect_tx(&bar_kv[stg], 2 * G::TILE);
-      tma_load_5d(sK + stg * G::TILE, &tmK, &bar_kv[stg], 0, h, k0 + 256, s, b);
-      tma_load_5d(sV + stg * G::TILE, &tmV, &bar_kv[stg], 0, h, k0 + 256, s, b);
-    }
+      m_run = m_new;
+
+      // ---- P = 2^((x - m) log2e), its row sum; P rounded to the input dtype into shared memory ---------
+      const float2 nm2 = splat(m_new == -INFINITY ? 0.f : -m_new);   // a half with no key in range yet: P = 2^-inf = 0
+      float2 ps2[2] = {make_float2(0.f, 0.f), make_float2(0.f, 0.f)};
 #pragma unroll
-    for (int c = 0; c < HD / 32; ++c) {
-      uint32_t r[32];
-      tmem_ld_32x32(t_row + 128 + c * 32, r);
+      for (int g = 0; g < 8; ++g) {
+        uint32_t pw[4];
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+          const float2 e = __fmul2_rn(__fadd2_rn(x2[g * 4 + i], nm2), l2e2);
+          const float2 pp = make_float2(ex2_approx(e.x), ex2_approx(e.y));
+          ps2[i & 1] = __fadd2_rn(ps2[i & 1], pp);
+          pw[i] = pack2<T>(pp.x, pp.y);
+        }
+        *reinterpret_cast<uint4*>(sP + sw128_chunk(r, hh * 8 + g)) = make_uint4(pw[0], pw[1], pw[2], pw[3]);
+      }
+      l_run += (ps2[0].x + ps2[0].y) + (ps2[1].x + ps2[1].y);
+      fence_proxy_async_smem();
+      tc_fence_before_sync();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(bar_p);
+      if (!ok) break;
+    }
+
+    // ---- merge the two key halves of each row and write O, the row maximum and log row sum -------------
+    ok = mbar_wait(bar_pv, (nt - 1) & 1, a.err, 15) && ok;
+    tc_fence_after_sync();
+    float* xch = reinterpret_cast<float*>(sP);   // [128 rows][HD + 2] floats, free now that the last P V is done
+    constexpr int XS = HD + 2;
+    float o_acc[HD];
+#pragma unroll
+    for (int c = 0; c < HD / 16; ++c) {
+      uint32_t o[16];
+      tmem_ld_32x16(t_o + c * 16, o);
       tmem_ld_wait();
 #pragma unroll
-      for (int i = 0; i < 32; ++i) o_acc[c * 32 + i] = o_acc[c * 32 + i] * alpha + __uint_as_float(r[i]);
+      for (int i = 0; i < 16; ++i) o_acc[c * 16 + i] = __uint_as_float(o[i]);
     }
-    tc_fence_before_sync();
-    if (!ok) break;
-  }
-
-  const int qi = q0 + tid;
-  if (qi < a.N && ok) {
-    const float inv = 1.0f / l_run;
-    T* orow = reinterpret_cast<T*>(a.o) + b * a.o_st[0] + s * a.o_st[1] + qi * a.o_st[2] + h * a.o_st[3];
+    if (hh == 1) {
+      float* row = xch + r * XS;
+      row[0] = m_run; row[1] = l_run;
 #pragma unroll
-    for (int g = 0; g < HD / 8; ++g) {
-      uint4 pk;
-      pk.x = pack2<T>(o_acc[g * 8 + 0] * inv, o_acc[g * 8 + 1] * inv);
-      pk.y = pack2<T>(o_acc[g * 8 + 2] * inv, o_acc[g * 8 + 3] * inv);
-      pk.z = pack2<T>(o_acc[g * 8 + 4] * inv, o_acc[g * 8 + 5] * inv);
-      pk.w = pack2<T>(o_acc[g * 8 + 6] * inv, o_acc[g * 8 + 7] * inv);
-      reinterpret_cast<uint4*>(orow)[g] = pk;
+      for (int i = 0; i < HD; ++i) row[2 + i] = o_acc[i];
     }
-    const long long row = (((long long)b * a.S + s) * a.H + h) * a.N + qi;
-    a.stats[row] = m_run;
-    a.stats[(long long)a.B * a.S * a.H * a.N + row] = logf(l_run);
+    named_barrier(1, 256);
+    const int qi = q0 + r;
+    if (hh == 0 && qi < a.N && ok) {
+      const float* row = xch + r * XS;
+      const float m1 = row[0], l1 = row[1];
+      const float m = fmaxf(m_run, m1);   // finite: key 0 is in range and belongs to half 0
+      const float a0 = ex2_approx((m_run - m) * kLog2e), a1 = ex2_approx((m1 - m) * kLog2e);
+      const float l = l_run * a0 + l1 * a1;
+      const float inv = 1.0f / l, w0 = a0 * inv, w1 = a1 * inv;
+      T* orow = reinterpret_cast<T*>(a.o) + b * a.o_st[0] + s * a.o_st[1] + qi * a.o_st[2] + h * a.o_st[3];
+#pragma unroll
+      for (int g = 0; g < HD / 8; ++g) {
+        float f[8];
+#pragma unroll
+        for (int i = 0; i < 8; ++i) f[i] = o_acc[g * 8 + i] * w0 + row[2 + g * 8 + i] * w1;
+        uint4 pk;
+        pk.x = pack2<T>(f[0], f[1]); pk.y = pack2<T>(f[2], f[3]);
+        pk.z = pack2<T>(f[4], f[5]); pk.w = pack2<T>(f[6], f[7]);
+        reinterpret_cast<uint4*>(orow)[g] = pk;
+      }
+      const long long srow = (((long long)b * a.S + s) * a.H + h) * a.N + qi;
+      a.stats[srow] = m;
+      a.stats[(long long)a.B * a.S * a.H * a.N + srow] = logf(l);
+    }
   }
   tc_fence_before_sync();
   __syncthreads();
@@ -308,6 +386,9 @@ struct AttnBwdArgs {
   float scale;
   const float* stats;    // [2][B][S][H][N]
   const float* delta;    // [B][S][H][N]
+  const float* prep;     // [3][B][S][H][npad]: -m, -log l * log2e, -delta, zero in the padding
+  long long prep_plane;  // B*S*H*npad
+  int npad;              // N rounded up to 128
   const uint8_t* mask;
   int64_t mask_st[2];
   int has_bias, bias_b_mul;
@@ -664,21 +745,29 @@ template <int HD> struct GeoC {
   static constexpr int TQ = 64 * RB;    // Q / dO tile
   static constexpr uint32_t LAYOUT = RB == 128 ? 2 : 4;
   static constexpr uint32_t SBO = 8 * RB;
+  static constexpr int NQ = 3;                      // query-tile stages: tiles are fetched two steps ahead
+  static constexpr int ST = 3 * 64 * 4;             // one stage of row statistics: -m, -log l log2e, -delta for 64 queries
   static constexpr int OFF_K = 0;
   static constexpr int OFF_V = OFF_K + TK;
-  static constexpr int NQ = 3;                      // Q / dO stages: tiles are fetched two steps ahead
   static constexpr int OFF_Q = OFF_V + TK;          // [NQ]
   static constexpr int OFF_DO = OFF_Q + NQ * TQ;    // [NQ]
   static constexpr int OFF_PT = OFF_DO + NQ * TQ;   // [128 keys x 64 queries] SW128
   static constexpr int OFF_DST = OFF_PT + 16384;
   static constexpr int OFF_BIAS = OFF_DST + 16384;  // 2 buffers of transposed bias [128 keys x 64 queries] SW128
-  static constexpr int OFF_ST = OFF_BIAS + 2 * 16384;   // 2 buffers of -m[64], -log l log2e[64], -delta[64]
-  static constexpr int OFF_BAR = OFF_ST + 2048;
-  static constexpr int SMEM = OFF_BAR + 128 + 1024;
+  static constexpr int OFF_ST = OFF_BIAS + 2 * 16384;   // [NQ] statistics stages
+  static constexpr int OFF_BAR = OFF_ST + NQ * ST;
+  static constexpr int SMEM = OFF_BAR + 256 + 1024;
 };
 
+// 288 threads.  Warps 0-7 do the arithmetic: thread (r, hh) owns key r of the block and query half hh of each
+// 64-query tile.  Warp 8 issues every TMA copy and every MMA, so none of that serial code sits between the
+// arithmetic warps' steps; the two sides meet only on mbarriers:
+//   bar_s    issuer -> threads   S^T and dP^T of a tile are in TMEM
+//   bar_free threads -> issuer   every warp has read them into registers (the next tile's products may start)
+//   bar_p    threads -> issuer   P^T and dS^T of the tile are in shared memory (dV, dK products may start)
+//   bar_acc  issuer -> threads   those products are done: the P^T / dS^T buffers and the tile's stage are free
 template <typename T, int HD, bool HB>
-__global__ void __launch_bounds__(256, 2)
+__global__ void __launch_bounds__(288, 2)
 attn_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmDO,
                      const __grid_constant__ CUtensorMap tmK, const __grid_constant__ CUtensorMap tmV,
                      const __grid_constant__ CUtensorMap tmBias, const AttnBwdArgs a) {
@@ -692,16 +781,17 @@ attn_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_const
   uint8_t* sPT = smem + G::OFF_PT;
   uint8_t* sDST = smem + G::OFF_DST;
   uint8_t* sBias = smem + G::OFF_BIAS;
-  float* sStats = reinterpret_cast<float*>(smem + G::OFF_ST);   // [2][3][64]
+  float* sStats = reinterpret_cast<float*>(smem + G::OFF_ST);   // [NQ][3][64]
   uint64_t* bar_kv = reinterpret_cast<uint64_t*>(smem + G::OFF_BAR);
-  uint64_t* bar_in = bar_kv + 1;     // [3]
-  uint64_t* bar_bias = bar_kv + 4;   // [2]: bias tiles are fetched two steps ahead
+  uint64_t* bar_in = bar_kv + 1;     // [NQ]
+  uint64_t* bar_bias = bar_kv + 4;   // [2]
   uint64_t* bar_s = bar_kv + 6;
   uint64_t* bar_acc = bar_kv + 7;
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bar_kv + 8);
+  uint64_t* bar_free = bar_kv + 8;
+  uint64_t* bar_p = bar_kv + 9;
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bar_kv + 10);
 
-  // 256 threads: thread (r, hh) owns key r of the block and query half hh of each 64-query tile
-  const int tid = threadIdx.x, warp = tid >> 5, r = tid & 127, hh = tid >> 7;
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31, r = tid & 127, hh = (tid >> 7) & 1;
   const int kblocks = (a.N + 127) / 128;
   int z = blockIdx.x;
   const int kvb = z % kblocks; z /= kblocks;
@@ -716,6 +806,7 @@ attn_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_const
     mbar_init(bar_kv, 1);
     for (int i = 0; i < G::NQ; ++i) mbar_init(&bar_in[i], 1);
     mbar_init(&bar_bias[0], 1); mbar_init(&bar_bias[1], 1); mbar_init(bar_s, 1); mbar_init(bar_acc, 1);
+    mbar_init(bar_free, 8); mbar_init(bar_p, 8);
     mbar_fence_init();
   }
   if (warp == 0) tmem_alloc(tmem_slot, 256);
@@ -725,100 +816,105 @@ attn_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_const
   const uint32_t tmem_base = *tmem_slot;
   const uint32_t t_row = tmem_base + ((uint32_t)((warp & 3) * 32) << 16);
   constexpr uint32_t COL_DP = 64, COL_DV = 128, COL_DK = 128 + HD;
-
-  auto load_step = [&](int step) {
-    const int stg = step % G::NQ;
-    mbar_expect_tx(&bar_in[stg], 2 * G::TQ);
-    tma_load_5d(sQ + stg * G::TQ, &tmQ, &bar_in[stg], 0, h, step * 64, s, b);
-    tma_load_5d(sDO + stg * G::TQ, &tmDO, &bar_in[stg], 0, h, step * 64, s, b);
-  };
-  auto load_bias = [&](int step) {
-    uint64_t* bb = &bar_bias[step & 1];
-    uint8_t* dst = sBias + (step & 1) * 16384;
-    mbar_expect_tx(bb, 16384);
-    tma_load_4d(dst, &tmBias, bb, step * 64, k0, h, bias_b);   // transposed copy: queries are the inner dimension
-  };
   bool ok = true;
-  // S^T = K Q^T and dP^T = V dO^T of one 64-query tile; issued one step ahead of the threads that consume it
-  auto issue_scores = [&](int step) {
-    const int stg = step % G::NQ;
-    if (step == 0) ok = mbar_wait(bar_kv, 0, a.err, 31);
-    ok = mbar_wait(&bar_in[stg], (step / G::NQ) & 1, a.err, 32) && ok;
-    tc_fence_after_sync();
-    const uint32_t ka = smem_u32(sK), va = smem_u32(sV);
-    const uint32_t qa = smem_u32(sQ + stg * G::TQ), da = smem_u32(sDO + stg * G::TQ);
-#pragma unroll
-    for (int ks = 0; ks < HD / 16; ++ks)
-      umma<KIND_F16>(tmem_base, make_smem_desc(ka + ks * 32, 16, G::SBO, G::LAYOUT),
-                     make_smem_desc(qa + ks * 32, 16, G::SBO, G::LAYOUT), a.idesc_a, ks > 0);
-#pragma unroll
-    for (int ks = 0; ks < HD / 16; ++ks)
-      umma<KIND_F16>(tmem_base + COL_DP, make_smem_desc(va + ks * 32, 16, G::SBO, G::LAYOUT),
-                     make_smem_desc(da + ks * 32, 16, G::SBO, G::LAYOUT), a.idesc_a, ks > 0);
-    umma_commit(bar_s);
-  };
-  if (tid == 0) {
-    mbar_expect_tx(bar_kv, 2 * G::TK);
-    tma_load_5d(sK, &tmK, bar_kv, 0, h, k0, s, b);
-    tma_load_5d(sV, &tmV, bar_kv, 0, h, k0, s, b);
-    for (int st = 0; st < 2 && st < nsteps; ++st) load_step(st);
-    if (HB) for (int st = 0; st < 2 && st < nsteps; ++st) load_bias(st);
-    issue_scores(0);
-  }
-  const int kj = k0 + r;
-  float mb = 0.f;
-  if (kj >= a.N) mb = -INFINITY;
-  else if (a.mask != nullptr) mb = kMaskSentinel * ((a.mask[b * a.mask_st[0] + s * a.mask_st[1] + kj] ? 1.0f : 0.0f) - 1.0f);
-  const long long plane = (long long)a.B * a.S * a.H * a.N;
-  const long long row_base = (((long long)b * a.S + s) * a.H + h) * a.N;
-  // per-query statistics live in shared memory in the form the packed arithmetic adds: -m, -log l log2e, -delta
-  auto fetch_stats = [&](int step, float& m, float& l, float& dl) {
-    const int qn = step * 64 + tid;
-    const bool v = step < nsteps && qn < a.N;
-    m = v ? a.stats[row_base + qn] : 0.f;
-    l = v ? a.stats[plane + row_base + qn] : 0.f;
-    dl = v ? a.delta[row_base + qn] : 0.f;
-  };
-  float st_m = 0.f, st_l = 0.f, st_d = 0.f;
-  if (tid < 64) {
-    fetch_stats(0, st_m, st_l, st_d);
-    sStats[tid] = -st_m; sStats[64 + tid] = -st_l * kLog2e; sStats[128 + tid] = -st_d;
-    fetch_stats(1, st_m, st_l, st_d);
-  }
-  __syncthreads();
 
-  for (int j = 0; j < nsteps; ++j) {
-    const int stg = j & 1, qstg = j % G::NQ;
-    const uint32_t par = j & 1, in_par = (j >> 1) & 1;
-    ok = mbar_wait(bar_s, par, a.err, 33) && ok;
-    tc_fence_after_sync();
-    uint32_t rs[32], rp[32];
-    tmem_ld_32x32(t_row + hh * 32, rs);
-    tmem_ld_32x32(t_row + COL_DP + hh * 32, rp);
-    tmem_ld_wait();
-    tc_fence_before_sync();
-    __syncthreads();   // every thread holds its logits: the accumulators can take the next tile
-    if (tid == 0 && j + 1 < nsteps) issue_scores(j + 1);
-    if (tid < 64) {    // next tile's statistics into the other buffer (its readers finished a step ago)
-      float* nx = sStats + ((j + 1) & 1) * 192;
-      nx[tid] = -st_m; nx[64 + tid] = -st_l * kLog2e; nx[128 + tid] = -st_d;
-      fetch_stats(j + 2, st_m, st_l, st_d);
+  if (warp == 8) {
+    if (lane == 0) {
+      // ---------------------------------- issuer -------------------------------------------------
+      const float* prep_row = a.prep + ((((long long)b * a.S + s) * a.H + h) * (long long)a.npad);
+      auto load_step = [&](int step) {
+        const int stg = step % G::NQ;
+        float* st = sStats + stg * 192;
+        mbar_expect_tx(&bar_in[stg], 2 * G::TQ + G::ST);
+        tma_load_5d(sQ + stg * G::TQ, &tmQ, &bar_in[stg], 0, h, step * 64, s, b);
+        tma_load_5d(sDO + stg * G::TQ, &tmDO, &bar_in[stg], 0, h, step * 64, s, b);
+        bulk_load(st, prep_row + step * 64, 256, &bar_in[stg]);
+        bulk_load(st + 64, prep_row + a.prep_plane + step * 64, 256, &bar_in[stg]);
+        bulk_load(st + 128, prep_row + 2 * a.prep_plane + step * 64, 256, &bar_in[stg]);
+      };
+      auto load_bias = [&](int step) {
+        uint64_t* bb = &bar_bias[step & 1];
+        mbar_expect_tx(bb, 16384);
+        tma_load_4d(sBias + (step & 1) * 16384, &tmBias, bb, step * 64, k0, h, bias_b);   // transposed copy: queries inner
+      };
+      // Descriptors are built once: the high word is a constant per operand kind, the low word is
+      // (address >> 4) plus the leading-dimension field, so a k-step or a stage only adds to it.
+      constexpr uint32_t HI_KMAJ = desc_hi(G::SBO, G::LAYOUT);   // K, V, Q, dO as K-major rows of RB bytes
+      constexpr uint32_t HI_PT = desc_hi(1024, 2);               // P^T, dS^T: [128 x 64] SW128
+      const uint32_t k_lo = desc_lo(smem_u32(sK), 16), v_lo = desc_lo(smem_u32(sV), 16);
+      const uint32_t q_lo = desc_lo(smem_u32(sQ), 16), do_lo = desc_lo(smem_u32(sDO), 16);
+      const uint32_t qmn_lo = desc_lo(smem_u32(sQ), 64 * G::RB), domn_lo = desc_lo(smem_u32(sDO), 64 * G::RB);   // MN-major view
+      const uint32_t pt_lo = desc_lo(smem_u32(sPT), 16), dst_lo = desc_lo(smem_u32(sDST), 16);
+      // S^T = K Q^T and dP^T = V dO^T of one 64-query tile
+      auto issue_scores = [&](int step) {
+        const int stg = step % G::NQ;
+        ok = mbar_wait(&bar_in[stg], (step / G::NQ) & 1, a.err, 32) && ok;
+        tc_fence_after_sync();
+        const uint32_t so = stg * (G::TQ >> 4);
+#pragma unroll
+        for (int ks = 0; ks < HD / 16; ++ks)
+          umma<KIND_F16>(tmem_base, desc_join(k_lo + ks * 2, HI_KMAJ), desc_join(q_lo + so + ks * 2, HI_KMAJ), a.idesc_a, ks > 0);
+#pragma unroll
+        for (int ks = 0; ks < HD / 16; ++ks)
+          umma<KIND_F16>(tmem_base + COL_DP, desc_join(v_lo + ks * 2, HI_KMAJ), desc_join(do_lo + so + ks * 2, HI_KMAJ), a.idesc_a, ks > 0);
+        umma_commit(bar_s);
+      };
+      mbar_expect_tx(bar_kv, 2 * G::TK);
+      tma_load_5d(sK, &tmK, bar_kv, 0, h, k0, s, b);
+      tma_load_5d(sV, &tmV, bar_kv, 0, h, k0, s, b);
+      for (int st = 0; st < G::NQ && st < nsteps; ++st) load_step(st);
+      if (HB) for (int st = 0; st < 2 && st < nsteps; ++st) load_bias(st);
+      ok = mbar_wait(bar_kv, 0, a.err, 31);
+      issue_scores(0);
+      for (int j = 0; j < nsteps && ok; ++j) {
+        const int qstg = j % G::NQ;
+        ok = mbar_wait(bar_free, j & 1, a.err, 37) && ok;
+        if (j + 1 < nsteps) issue_scores(j + 1);
+        ok = mbar_wait(bar_p, j & 1, a.err, 38) && ok;
+        if (j >= 1) ok = mbar_wait(bar_acc, (j - 1) & 1, a.err, 39) && ok;   // (complete: the threads waited for it too)
+        tc_fence_after_sync();
+        const uint32_t so = qstg * (G::TQ >> 4);
+#pragma unroll
+        for (int kk = 0; kk < 4; ++kk)   // dV += P^T dO   (B = dO as [n = d, k = query]: MN-major)
+          umma<KIND_F16>(tmem_base + COL_DV, desc_join(pt_lo + kk * 2, HI_PT), desc_join(domn_lo + so + kk * G::RB, HI_KMAJ),
+                         a.idesc_b, (j > 0 || kk > 0) ? 1u : 0u);
+#pragma unroll
+        for (int kk = 0; kk < 4; ++kk)   // dK += dS^T Q
+          umma<KIND_F16>(tmem_base + COL_DK, desc_join(dst_lo + kk * 2, HI_PT), desc_join(qmn_lo + so + kk * G::RB, HI_KMAJ),
+                         a.idesc_b, (j > 0 || kk > 0) ? 1u : 0u);
+        umma_commit(bar_acc);
+        if (HB && j + 2 < nsteps) load_bias(j + 2);         // bar_p: every thread is past its reads of this buffer
+        if (j >= 1 && j + 2 < nsteps) load_step(j + 2);     // tile j-1's stage is free: its dV / dK products are done
+      }
     }
-    if (HB) ok = mbar_wait(&bar_bias[stg], in_par, a.err, 34) && ok;
-    if (j > 0) {       // P^T / dS^T buffers and the Q / dO stage of tile j-1 are free
-      ok = mbar_wait(bar_acc, (j - 1) & 1, a.err, 35) && ok;
-      if (tid == 0 && j + 2 < nsteps) load_step(j + 2);
-    } else if (tid == 0 && 2 < nsteps) {
-      load_step(2);
-    }
-
-    // packed fp32x2 arithmetic: P = 2^((x - m) log2e - log l log2e), dS = P (dP - delta); thread = key, columns = queries
-    const uint8_t* bias_row = sBias + stg * 16384;
+  } else {
+    // ------------------------------------ arithmetic warps ---------------------------------------
+    const int kj = k0 + r;
+    float mb = 0.f;
+    if (kj >= a.N) mb = -INFINITY;
+    else if (a.mask != nullptr) mb = kMaskSentinel * ((a.mask[b * a.mask_st[0] + s * a.mask_st[1] + kj] ? 1.0f : 0.0f) - 1.0f);
     const float2 sc2 = splat(a.scale), mk2 = splat(mb), l2e2 = splat(kLog2e);
-    const float4* sM4 = reinterpret_cast<const float4*>(sStats + stg * 192);
-    const float4* sL4 = sM4 + 16;
-    const float4* sD4 = sM4 + 32;
-    {
+
+    for (int j = 0; j < nsteps; ++j) {
+      const int stg = j & 1, qstg = j % G::NQ;
+      ok = mbar_wait(bar_s, j & 1, a.err, 33) && ok;
+      tc_fence_after_sync();
+      uint32_t rs[32], rp[32];
+      tmem_ld_32x32(t_row + hh * 32, rs);
+      tmem_ld_32x32(t_row + COL_DP + hh * 32, rp);
+      tmem_ld_wait();
+      tc_fence_before_sync();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(bar_free);   // this warp holds its logits: the accumulators can take the next tile
+      ok = mbar_wait(&bar_in[qstg], (j / G::NQ) & 1, a.err, 32) && ok;   // the tile's row statistics
+      if (HB) ok = mbar_wait(&bar_bias[stg], (j >> 1) & 1, a.err, 34) && ok;
+      if (j > 0) ok = mbar_wait(bar_acc, (j - 1) & 1, a.err, 35) && ok;   // P^T / dS^T buffers are free
+
+      // packed fp32x2 arithmetic: P = 2^((x - m) log2e - log l log2e), dS = P (dP - delta); thread = key, columns = queries
+      const uint8_t* bias_row = sBias + stg * 16384;
+      const float4* sM4 = reinterpret_cast<const float4*>(sStats + qstg * 192);
+      const float4* sL4 = sM4 + 16;
+      const float4* sD4 = sM4 + 32;
       const int c = hh;
 #pragma unroll
       for (int u = 0; u < 4; ++u) {
@@ -845,55 +941,39 @@ attn_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_const
         *reinterpret_cast<uint4*>(sPT + sw128_chunk1(r, c * 4 + u)) = make_uint4(pw[0], pw[1], pw[2], pw[3]);
         *reinterpret_cast<uint4*>(sDST + sw128_chunk1(r, c * 4 + u)) = make_uint4(dw[0], dw[1], dw[2], dw[3]);
       }
+      fence_proxy_async_smem();
+      tc_fence_before_sync();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(bar_p);
+      if (!ok) break;
     }
-    fence_proxy_async_smem();
-    tc_fence_before_sync();
-    __syncthreads();
-    if (tid == 0) {
-      tc_fence_after_sync();
-      const uint32_t pa = smem_u32(sPT), dsa = smem_u32(sDST);
-      const uint32_t qa = smem_u32(sQ + qstg * G::TQ), da = smem_u32(sDO + qstg * G::TQ);
+    ok = mbar_wait(bar_acc, (nsteps - 1) & 1, a.err, 36) && ok;
+    tc_fence_after_sync();
+    {
+      const bool st_ok = kj < a.N && ok && hh == 0;
+      T* krow = reinterpret_cast<T*>(a.out0) + b * a.out0_st[0] + s * a.out0_st[1] + kj * a.out0_st[2] + h * a.out0_st[3];
+      T* vrow = reinterpret_cast<T*>(a.out1) + b * a.out1_st[0] + s * a.out1_st[1] + kj * a.out1_st[2] + h * a.out1_st[3];
 #pragma unroll
-      for (int kk = 0; kk < 4; ++kk)   // dV += P^T dO   (B = dO as [n = d, k = query]: MN-major)
-        umma<KIND_F16>(tmem_base + COL_DV, make_smem_desc(pa + kk * 32, 16, 1024, 2),
-                       make_smem_desc(da + kk * 16 * G::RB, 64 * G::RB, G::SBO, G::LAYOUT), a.idesc_b,
-                       (j > 0 || kk > 0) ? 1u : 0u);
+      for (int c = 0; c < HD / 32; ++c) {
+        uint32_t rk[32], rv[32];
+        tmem_ld_32x32(t_row + COL_DK + c * 32, rk);
+        tmem_ld_32x32(t_row + COL_DV + c * 32, rv);
+        tmem_ld_wait();
+        if (st_ok) {
 #pragma unroll
-      for (int kk = 0; kk < 4; ++kk)   // dK += dS^T Q
-        umma<KIND_F16>(tmem_base + COL_DK, make_smem_desc(dsa + kk * 32, 16, 1024, 2),
-                       make_smem_desc(qa + kk * 16 * G::RB, 64 * G::RB, G::SBO, G::LAYOUT), a.idesc_b,
-                       (j > 0 || kk > 0) ? 1u : 0u);
-      umma_commit(bar_acc);
-      if (HB && j + 2 < nsteps) load_bias(j + 2);   // every thread is past its reads of this buffer
-    }
-    if (!ok) break;
-  }
-  ok = mbar_wait(bar_acc, (nsteps - 1) & 1, a.err, 36) && ok;
-  tc_fence_after_sync();
-  {
-    const bool st_ok = kj < a.N && ok && hh == 0;
-    T* krow = reinterpret_cast<T*>(a.out0) + b * a.out0_st[0] + s * a.out0_st[1] + kj * a.out0_st[2] + h * a.out0_st[3];
-    T* vrow = reinterpret_cast<T*>(a.out1) + b * a.out1_st[0] + s * a.out1_st[1] + kj * a.out1_st[2] + h * a.out1_st[3];
-#pragma unroll
-    for (int c = 0; c < HD / 32; ++c) {
-      uint32_t rk[32], rv[32];
-      tmem_ld_32x32(t_row + COL_DK + c * 32, rk);
-      tmem_ld_32x32(t_row + COL_DV + c * 32, rv);
-      tmem_ld_wait();
-      if (st_ok) {
-#pragma unroll
-        for (int g = 0; g < 4; ++g) {
-          uint4 pk;
-          pk.x = pack2<T>(__uint_as_float(rk[g * 8 + 0]) * a.scale, __uint_as_float(rk[g * 8 + 1]) * a.scale);
-          pk.y = pack2<T>(__uint_as_float(rk[g * 8 + 2]) * a.scale, __uint_as_float(rk[g * 8 + 3]) * a.scale);
-          pk.z = pack2<T>(__uint_as_float(rk[g * 8 + 4]) * a.scale, __uint_as_float(rk[g * 8 + 5]) * a.scale);
-          pk.w = pack2<T>(__uint_as_float(rk[g * 8 + 6]) * a.scale, __uint_as_float(rk[g * 8 + 7]) * a.scale);
-          reinterpret_cast<uint4*>(krow)[c * 4 + g] = pk;
-          pk.x = pack2<T>(__uint_as_float(rv[g * 8 + 0]), __uint_as_float(rv[g * 8 + 1]));
-          pk.y = pack2<T>(__uint_as_float(rv[g * 8 + 2]), __uint_as_float(rv[g * 8 + 3]));
-          pk.z = pack2<T>(__uint_as_float(rv[g * 8 + 4]), __uint_as_float(rv[g * 8 + 5]));
-          pk.w = pack2<T>(__uint_as_float(rv[g * 8 + 6]), __uint_as_float(rv[g * 8 + 7]));
-          reinterpret_cast<uint4*>(vrow)[c * 4 + g] = pk;
+          for (int g = 0; g < 4; ++g) {
+            uint4 pk;
+            pk.x = pack2<T>(__uint_as_float(rk[g * 8 + 0]) * a.scale, __uint_as_float(rk[g * 8 + 1]) * a.scale);
+            pk.y = pack2<T>(__uint_as_float(rk[g * 8 + 2]) * a.scale, __uint_as_float(rk[g * 8 + 3]) * a.scale);
+            pk.z = pack2<T>(__uint_as_float(rk[g * 8 + 4]) * a.scale, __uint_as_float(rk[g * 8 + 5]) * a.scale);
+            pk.w = pack2<T>(__uint_as_float(rk[g * 8 + 6]) * a.scale, __uint_as_float(rk[g * 8 + 7]) * a.scale);
+            reinterpret_cast<uint4*>(krow)[c * 4 + g] = pk;
+            pk.x = pack2<T>(__uint_as_float(rv[g * 8 + 0]), __uint_as_float(rv[g * 8 + 1]));
+            pk.y = pack2<T>(__uint_as_float(rv[g * 8 + 2]), __uint_as_float(rv[g * 8 + 3]));
+            pk.z = pack2<T>(__uint_as_float(rv[g * 8 + 4]), __uint_as_float(rv[g * 8 + 5]));
+            pk.w = pack2<T>(__uint_as_float(rv[g * 8 + 6]), __uint_as_float(rv[g * 8 + 7]));
+            reinterpret_cast<uint4*>(vrow)[c * 4 + g] = pk;
+          }
         }
       }
     }
@@ -906,9 +986,11 @@ attn_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_const
   }
 }
 
-// delta[b,s,h,i] = sum_d dO * O
+// delta[b,s,h,i] = sum_d dO * O; also the per-row constants of the backward passes in the form their packed
+// arithmetic adds (prep[0] = -m, prep[1] = -log l * log2e, prep[2] = -delta), rows padded to npad entries.
 template <typename T>
-__global__ void attn_delta_tc_kernel(TriAttnDesc d, const T* o, const T* d_o, float* delta) {
+__global__ void attn_delta_tc_kernel(TriAttnDesc d, const T* o, const T* d_o, const float* stats, float* delta,
+                                     float* prep, int npad) {
   const long long idx = blockIdx.x * (long long)blockDim.x + threadIdx.x;
   const long long total = (long long)d.B * d.n_seq * d.H * d.n_res;
   if (idx >= total) return;
@@ -926,6 +1008,10 @@ __global__ void attn_delta_tc_kernel(TriAttnDesc d, const T* o, const T* d_o, fl
     for (int e = 0; e < 8; ++e) acc = fmaf(x[e], y[e], acc);
   }
   delta[idx] = acc;
+  const long long pi = (idx / d.n_res) * npad + i, plane = (total / d.n_res) * npad;
+  prep[pi] = -stats[idx];
+  prep[plane + pi] = -stats[total + idx] * kLog2e;
+  prep[2 * plane + pi] = -acc;
 }
 
 __global__ void sum_partials_kernel(const float* partial, int nparts, long long n, float* out) {
@@ -988,19 +1074,22 @@ int set_dyn_smem(KernelT kern, int bytes) {
 template <typename T, int HD>
 int bwd_launch(const TriAttnDesc* d, const void* q, const void* k, const void* v, const void* bias,
                const uint8_t* mask, const void* o, const float* stats, const void* d_o, void* dq, void* dk, void* dv,
-               float* dbias, int* err, float* delta, float* dbias_partial, void* bias_t, cudaStream_t st) {
+               float* dbias, int* err, float* delta, float* dbias_partial, void* bias_t, float* prep, cudaStream_t st) {
   const long long rows = (long long)d->B * d->n_seq * d->H * d->n_res;
   const double pairs = (double)rows * d->n_res;
   const double tensor_bytes = 2.0 * d->B * d->n_seq * (double)d->n_res * d->H * d->D;
+  const int npad = (d->n_res + 127) / 128 * 128;
+  const long long prep_plane = (long long)d->B * d->n_seq * d->H * npad;
   {
     KernelTimer kt("tc_attn_delta", st, 0.0, 2.0 * tensor_bytes);
-    attn_delta_tc_kernel<T><<<cdiv(rows, 256), 256, 0, st>>>(*d, (const T*)o, (const T*)d_o, delta);
+    if (npad != d->n_res) TRI_CUDA_OK(cudaMemsetAsync(prep, 0, 3 * prep_plane * sizeof(float), st));
+    attn_delta_tc_kernel<T><<<cdiv(rows, 256), 256, 0, st>>>(*d, (const T*)o, (const T*)d_o, stats, delta, prep, npad);
     TRI_LAUNCH_OK();
   }
   const int kind = d->dtype == TRI_BF16 ? KIND_BF16 : KIND_F16;
   AttnBwdArgs a;
   a.B = d->B; a.S = d->n_seq; a.N = d->n_res; a.H = d->H; a.scale = d->scale;
-  a.stats = stats; a.delta = delta; a.mask = mask; a.mask_st[0] = d->mask_st[0]; a.mask_st[1] = d->mask_st[1];
+  a.stats = stats; a.delta = delta; a.prep = prep; a.prep_plane = prep_plane; a.npad = npad; a.mask = mask; a.mask_st[0] = d->mask_st[0]; a.mask_st[1] = d->mask_st[1];
   a.has_bias = bias != nullptr; a.bias_b_mul = d->bias_st[0] != 0 ? 1 : 0; a.err = err;
   a.row_chunks = 1;
   const int qblocks = (d->n_res + 127) / 128;
@@ -1033,7 +1122,7 @@ int bwd_launch(const TriAttnDesc* d, const void* q, const void* k, const void* v
     static bool configured[2] = {false, false};
     if (!configured[bias != nullptr]) { TRI_TRY(set_dyn_smem(kern, GeoC<HD>::SMEM)); configured[bias != nullptr] = true; }
     KernelTimer kt("tc_attn_bwd_dkdv", st, 8.0 * pairs * d->D, 6.0 * tensor_bytes);
-    kern<<<(unsigned)((long long)qblocks * d->B * d->n_seq * d->H), 256, GeoC<HD>::SMEM, st>>>(tq, tdo, tk, tv, tb, a);
+    kern<<<(unsigned)((long long)qblocks * d->B * d->n_seq * d->H), 288, GeoC<HD>::SMEM, st>>>(tq, tdo, tk, tv, tb, a);
     TRI_LAUNCH_OK();
   }
   // ---- dQ ------------------------------------------------------------------------------------
@@ -1077,234 +1166,6 @@ int bwd_launch(const TriAttnDesc* d, const void* q, const void* k, const void* v
   return 0;
 }
 
-// ------------------------------------------------------------------------------------------------
-// Forward, pipelined form: 64-key tiles, the logit accumulator S double buffered in TMEM so that
-// S(j+1) and S(j+2) are computed while the threads exponentiate tile j, P V(j) applied one step late,
-// bias tiles double buffered, K/V in a 4-stage ring.  One __syncthreads per tile.
-// ------------------------------------------------------------------------------------------------
-template <int HD> struct GeoP {
-  static constexpr int RB = HD * 2;
-  static constexpr int TQ = 128 * RB;                    // Q tile
-  static constexpr int TK = 64 * RB;                     // K or V tile (64 keys)
-  static constexpr uint32_t LAYOUT = RB == 128 ? 2 : 4;
-  static constexpr uint32_t SBO = 8 * RB;
-  static constexpr int NST = 4;                          // K/V stages
-  static constexpr int OFF_Q = 0;
-  static constexpr int OFF_K = OFF_Q + TQ;
-  static constexpr int OFF_V = OFF_K + NST * TK;
-  static constexpr int OFF_P = OFF_V + NST * TK;         // [128 x 64] SW128
-  static constexpr int OFF_BIAS = OFF_P + 16384;         // 2 x [128 x 64] SW128
-  static constexpr int OFF_BAR = OFF_BIAS + 2 * 16384;
-  static constexpr int OFF_MB = OFF_BAR + 128;           // additive mask term of the whole key row
-  static constexpr int SMEM_BASE = OFF_MB + 1024;        // + alignment slack; the mask row is added at launch
-};
-
-template <typename T, int HD>
-__global__ void __launch_bounds__(128, 2)
-attn_fwd_pipe_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmK,
-                     const __grid_constant__ CUtensorMap tmV, const __grid_constant__ CUtensorMap tmBias,
-                     const AttnArgs a) {
-  using G = GeoP<HD>;
-  extern __shared__ uint8_t smem_raw[];
-  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
-  uint8_t* sQ = smem + G::OFF_Q;
-  uint8_t* sK = smem + G::OFF_K;
-  uint8_t* sV = smem + G::OFF_V;
-  uint8_t* sP = smem + G::OFF_P;
-  uint8_t* sBias = smem + G::OFF_BIAS;
-  uint64_t* bar_q = reinterpret_cast<uint64_t*>(smem + G::OFF_BAR);
-  uint64_t* bar_kv = bar_q + 1;    // [4]
-  uint64_t* bar_bias = bar_q + 5;  // [2]
-  uint64_t* bar_s = bar_q + 7;     // [2]
-  uint64_t* bar_pv = bar_q + 9;
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bar_q + 10);
-  float* sMb = reinterpret_cast<float*>(smem + G::OFF_MB);
-
-  const int tid = threadIdx.x, warp = tid >> 5;
-  const int qblocks = (a.N + 127) / 128;
-  int z = blockIdx.x;
-  const int qb = z % qblocks; z /= qblocks;
-  const int h = z % a.H; z /= a.H;
-  const int s = z % a.S;
-  const int b = z / a.S;
-  const int q0 = qb * 128;
-  const int nt = (a.N + 63) / 64;
-  const int bias_b = b * a.bias_b_mul;
-
-  if (tid == 0) {
-    mbar_init(bar_q, 1);
-    for (int i = 0; i < 4; ++i) mbar_init(&bar_kv[i], 1);
-    for (int i = 0; i < 2; ++i) { mbar_init(&bar_bias[i], 1); mbar_init(&bar_s[i], 1); }
-    mbar_init(bar_pv, 1);
-    mbar_fence_init();
-  }
-  if (warp == 0) tmem_alloc(tmem_slot, 256);
-  for (int kj = tid; kj < nt * 64; kj += 128) {
-    float mb = 0.f;
-    if (kj >= a.N) mb = -INFINITY;
-    else if (a.mask != nullptr) mb = kMaskSentinel * ((a.mask[b * a.mask_st[0] + s * a.mask_st[1] + kj] ? 1.0f : 0.0f) - 1.0f);
-    sMb[kj] = mb;
-  }
-  tc_fence_before_sync();
-  __syncthreads();
-  tc_fence_after_sync();
-  const uint32_t tmem_base = *tmem_slot;
-  const uint32_t t_row = tmem_base + ((uint32_t)(warp * 32) << 16);
-  constexpr uint32_t COL_PV = 128;
-  bool ok = true;
-
-  auto load_kv = [&](int j) {
-    const int st = j & 3;
-    mbar_expect_tx(&bar_kv[st], 2 * G::TK);
-    tma_load_5d(sK + st * G::TK, &tmK, &bar_kv[st], 0, h, j * 64, s, b);
-    tma_load_5d(sV + st * G::TK, &tmV, &bar_kv[st], 0, h, j * 64, s, b);
-  };
-  auto load_bias = [&](int j) {
-    mbar_expect_tx(&bar_bias[j & 1], 16384);
-    tma_load_4d(sBias + (j & 1) * 16384, &tmBias, &bar_bias[j & 1], j * 64, q0, h, bias_b);
-  };
-  auto issue_s = [&](int j) {   // S(j) = Q K_j^T into TMEM buffer j & 1
-    ok = mbar_wait(&bar_kv[j & 3], (j >> 2) & 1, a.err, 12) && ok;
-    tc_fence_after_sync();
-    const uint32_t qa = smem_u32(sQ), ka = smem_u32(sK + (j & 3) * G::TK);
-#pragma unroll
-    for (int ks = 0; ks < HD / 16; ++ks)
-      umma<KIND_F16>(tmem_base + (j & 1) * 64, make_smem_desc(qa + ks * 32, 16, G::SBO, G::LAYOUT),
-                     make_smem_desc(ka + ks * 32, 16, G::SBO, G::LAYOUT), a.idesc_s, ks > 0);
-    umma_commit(&bar_s[j & 1]);
-  };
-
-  if (tid == 0) {
-    mbar_expect_tx(bar_q, G::TQ);
-    tma_load_5d(sQ, &tmQ, bar_q, 0, h, q0, s, b);
-    for (int j = 0; j < 3 && j < nt; ++j) load_kv(j);
-    if (a.has_bias) for (int j = 0; j < 2 && j < nt; ++j) load_bias(j);
-    ok = mbar_wait(bar_q, 0, a.err, 11);
-    issue_s(0);
-    if (nt > 1) issue_s(1);
-  }
-
-  float m_run = -INFINITY, l_run = 0.f, alpha_prev = 0.f;
-  float o_acc[HD];
-#pragma unroll
-  for (int i = 0; i < HD; ++i) o_acc[i] = 0.f;
-  auto add_pv = [&](float alpha) {
-#pragma unroll
-    for (int c = 0; c < HD / 32; ++c) {
-      uint32_t r[32];
-      tmem_ld_32x32(t_row + COL_PV + c * 32, r);
-      tmem_ld_wait();
-#pragma unroll
-      for (int i = 0; i < 32; ++i) o_acc[c * 32 + i] = o_acc[c * 32 + i] * alpha + __uint_as_float(r[i]);
-    }
-  };
-
-  for (int j = 0; j < nt; ++j) {
-    const int buf = j & 1;
-    const uint32_t par2 = (j >> 1) & 1;
-    ok = mbar_wait(&bar_s[buf], par2, a.err, 13) && ok;
-    if (a.has_bias) ok = mbar_wait(&bar_bias[buf], par2, a.err, 14) && ok;
-    tc_fence_after_sync();
-    float x[64];
-    float mx4[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
-    const float4* mb4 = reinterpret_cast<const float4*>(sMb + j * 64);
-    const uint8_t* bias_t = sBias + buf * 16384;
-#pragma unroll
-    for (int c = 0; c < 2; ++c) {
-      uint32_t r[32];
-      tmem_ld_32x32(t_row + buf * 64 + c * 32, r);
-      tmem_ld_wait();
-#pragma unroll
-      for (int u = 0; u < 4; ++u) {
-        float bv[8];
-        if (a.has_bias) {
-          const uint4 raw = *reinterpret_cast<const uint4*>(bias_t + sw128_chunk1(tid, c * 4 + u));
-          unpack8<T>(raw, bv);
-        }
-        const float4 m0 = mb4[c * 8 + u * 2], m1 = mb4[c * 8 + u * 2 + 1];
-        const float mbv[8] = {m0.x, m0.y, m0.z, m0.w, m1.x, m1.y, m1.z, m1.w};
-#pragma unroll
-        for (int i = 0; i < 8; ++i) {
-          float v = __uint_as_float(r[u * 8 + i]) * a.scale;
-          if (a.has_bias) v += bv[i];
-          v += mbv[i];
-          x[c * 32 + u * 8 + i] = v;
-          mx4[i & 3] = fmaxf(mx4[i & 3], v);
-        }
-      }
-    }
-    const float m_new = fmaxf(m_run, fmaxf(fmaxf(mx4[0], mx4[1]), fmaxf(mx4[2], mx4[3])));
-    const float alpha = ex2_approx((m_run - m_new) * kLog2e);
-    if (j > 0) {   // finish tile j-1: its P V product is done by now, and P's buffer is free again
-      ok = mbar_wait(bar_pv, (j - 1) & 1, a.err, 15) && ok;
-      tc_fence_after_sync();
-      add_pv(alpha_prev);
-    }
-    float ps4[4] = {0.f, 0.f, 0.f, 0.f};
-#pragma unroll
-    for (int g = 0; g < 8; ++g) {
-      float p[8];
-#pragma unroll
-      for (int i = 0; i < 8; ++i) {
-        p[i] = ex2_approx((x[g * 8 + i] - m_new) * kLog2e);
-        ps4[i & 3] += p[i];
-      }
-      uint4 pk;
-      pk.x = pack2<T>(p[0], p[1]); pk.y = pack2<T>(p[2], p[3]);
-      pk.z = pack2<T>(p[4], p[5]); pk.w = pack2<T>(p[6], p[7]);
-      *reinterpret_cast<uint4*>(sP + sw128_chunk1(tid, g)) = pk;
-    }
-    l_run = l_run * alpha + ((ps4[0] + ps4[1]) + (ps4[2] + ps4[3]));
-    m_run = m_new;
-    alpha_prev = alpha;
-    fence_proxy_async_smem();
-    tc_fence_before_sync();
-    __syncthreads();
-    if (tid == 0) {
-      tc_fence_after_sync();
-      const uint32_t pa = smem_u32(sP), va = smem_u32(sV + (j & 3) * G::TK);
-#pragma unroll
-      for (int kk = 0; kk < 4; ++kk)
-        umma<KIND_F16>(tmem_base + COL_PV, make_smem_desc(pa + kk * 32, 16, 1024, 2),
-                       make_smem_desc(va + kk * 16 * G::RB, 64 * G::RB, G::SBO, G::LAYOUT), a.idesc_pv, kk > 0);
-      umma_commit(bar_pv);
-      if (j + 3 < nt) load_kv(j + 3);          // its stage held tile j-1, whose P V has completed
-      if (j + 2 < nt) {
-        if (a.has_bias) load_bias(j + 2);      // every thread is past its reads of bias(j)
-        issue_s(j + 2);                        // ... and of S(j): reuse both buffers
-      }
-    }
-    if (!ok) break;
-  }
-  ok = mbar_wait(bar_pv, (nt - 1) & 1, a.err, 15) && ok;
-  tc_fence_after_sync();
-  add_pv(alpha_prev);
-  const int qi = q0 + tid;
-  if (qi < a.N && ok) {
-    const float inv = 1.0f / l_run;
-    T* orow = reinterpret_cast<T*>(a.o) + b * a.o_st[0] + s * a.o_st[1] + qi * a.o_st[2] + h * a.o_st[3];
-#pragma unroll
-    for (int g = 0; g < HD / 8; ++g) {
-      uint4 pk;
-      pk.x = pack2<T>(o_acc[g * 8 + 0] * inv, o_acc[g * 8 + 1] * inv);
-      pk.y = pack2<T>(o_acc[g * 8 + 2] * inv, o_acc[g * 8 + 3] * inv);
-      pk.z = pack2<T>(o_acc[g * 8 + 4] * inv, o_acc[g * 8 + 5] * inv);
-      pk.w = pack2<T>(o_acc[g * 8 + 6] * inv, o_acc[g * 8 + 7] * inv);
-      reinterpret_cast<uint4*>(orow)[g] = pk;
-    }
-    const long long row = (((long long)b * a.S + s) * a.H + h) * a.N + qi;
-    a.stats[row] = m_run;
-    a.stats[(long long)a.B * a.S * a.H * a.N + row] = logf(l_run);
-  }
-  tc_fence_before_sync();
-  __syncthreads();
-  if (warp == 0) {
-    tc_fence_after_sync();
-    tmem_dealloc(tmem_base, 256);
-  }
-}
-
-
 bool forced_simt() {
   const char* e = getenv("TRI_B200_FORCE_SIMT");
   return e != nullptr && e[0] == '1';
@@ -1326,7 +1187,7 @@ int qkv_map(CUtensorMap* out, const void* p, const TriAttnDesc* d, const int64_t
 
 template <typename T, int HD>
 int fwd_launch(const TriAttnDesc* d, const void* q, const void* k, const void* v, const void* bias,
-               const uint8_t* mask, void* o, float* stats, int* err, cudaStream_t st) {
+               const uint8_t* mask, void* o, float* stats, int* err, float* mask_terms, cudaStream_t st) {
   CUtensorMap tq, tk, tv, tb;
   TRI_TRY(qkv_map(&tq, q, d, d->q_st));
   TRI_TRY(qkv_map(&tk, k, d, d->k_st));
@@ -1334,8 +1195,13 @@ int fwd_launch(const TriAttnDesc* d, const void* q, const void* k, const void* v
   AttnArgs a;
   a.B = d->B; a.S = d->n_seq; a.N = d->n_res; a.H = d->H; a.scale = d->scale;
   a.o = o; for (int i = 0; i < 4; ++i) a.o_st[i] = d->o_st[i];
-  a.stats = stats; a.mask = mask; a.mask_st[0] = d->mask_st[0]; a.mask_st[1] = d->mask_st[1];
+  a.stats = stats; a.mask_terms = mask_terms; a.npad = (d->n_res + 127) / 128 * 128;
   a.has_bias = bias != nullptr; a.bias_b_mul = d->bias_st[0] != 0 ? 1 : 0;
+  {
+    const long long n = (long long)d->B * d->n_seq * a.npad;
+    mask_terms_kernel<<<cdiv(n, 256), 256, 0, st>>>(mask, d->mask_st[0], d->mask_st[1], d->B, d->n_seq, d->n_res, a.npad, mask_terms);
+    TRI_LAUNCH_OK();
+  }
   const int kind = d->dtype == TRI_BF16 ? KIND_BF16 : KIND_F16;
   a.idesc_s = make_idesc(kind, 128, 128, false, false);
   a.idesc_pv = make_idesc(kind, 128, HD, false, true);
@@ -1352,31 +1218,13 @@ int fwd_launch(const TriAttnDesc* d, const void* q, const void* k, const void* v
   const long long blocks = (long long)((d->n_res + 127) / 128) * d->B * d->n_seq * d->H;
   const double pairs = (double)d->B * d->n_seq * d->H * d->n_res * (double)d->n_res;
   KernelTimer kt("tc_attn_fwd", st, 4.0 * pairs * d->D, 2.0 * 4.0 * d->B * d->n_seq * (double)d->n_res * d->H * d->D);
-  // The pipelined 64-key-tile variant (TRI_B200_ATTN_FWD_PIPE=1) measures slower (1.70 vs 1.40 ms at N=768):
-  // the forward is bound by instruction issue in the softmax warps, not by MMA latency.
-  static const bool unpipelined = getenv("TRI_B200_ATTN_FWD_PIPE") == nullptr;
-  if (unpipelined) {
-    auto kern = bias != nullptr ? attn_fwd_tc_kernel<T, HD, true> : attn_fwd_tc_kernel<T, HD, false>;
-    static bool configured[2] = {false, false};
-    if (!configured[bias != nullptr]) {
-      TRI_CUDA_OK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, Geo<HD>::SMEM));
-      configured[bias != nullptr] = true;
-    }
-    kern<<<(unsigned)blocks, 128, Geo<HD>::SMEM, st>>>(tq, tk, tv, tb, a);
-    TRI_LAUNCH_OK();
-    return 0;
+  auto kern = bias != nullptr ? attn_fwd_tc_kernel<T, HD, true> : attn_fwd_tc_kernel<T, HD, false>;
+  static bool configured[2] = {false, false};
+  if (!configured[bias != nullptr]) {
+    TRI_CUDA_OK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, Geo<HD>::SMEM));
+    configured[bias != nullptr] = true;
   }
-  TRI_TRY(qkv_map_rows(&tk, k, d, d->k_st, 64));
-  TRI_TRY(qkv_map_rows(&tv, v, d, d->v_st, 64));
-  a.idesc_s = make_idesc(kind, 128, 64, false, false);
-  auto kern = attn_fwd_pipe_kernel<T, HD>;
-  const int smem = GeoP<HD>::SMEM_BASE + ((d->n_res + 63) / 64) * 256;
-  static int configured = 0;
-  if (configured < smem) {
-    TRI_CUDA_OK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
-    configured = smem;
-  }
-  kern<<<(unsigned)blocks, 128, smem, st>>>(tq, tk, tv, tb, a);
+  kern<<<(unsigned)blocks, 288, Geo<HD>::SMEM, st>>>(tq, tk, tv, tb, a);
   TRI_LAUNCH_OK();
   return 0;
 }
@@ -1399,24 +1247,28 @@ bool attn_bwd_supported(const TriAttnDesc* d) {
          strides_ok(d->dv_st) && d->n_seq <= 65535;
 }
 
+static size_t attn_npad(const TriAttnDesc* d) { return ((size_t)d->n_res + 127) / 128 * 128; }
+
 size_t attn_ws_bytes(const TriAttnDesc* d, int is_bwd) {
-  if (!is_bwd) return 512;
+  if (!is_bwd) return 512 + align_up((size_t)d->B * d->n_seq * attn_npad(d) * sizeof(float));   // additive key-mask terms
   return 512 + align_up((size_t)d->B * d->n_seq * d->H * d->n_res * sizeof(float)) +
          align_up((size_t)kDbiasRowChunks * d->B * d->H * d->n_res * d->n_res * sizeof(float)) +
-         align_up((size_t)d->B * d->H * d->n_res * d->n_res * 2);   // transposed 16-bit copy of the bias
+         align_up((size_t)d->B * d->H * d->n_res * d->n_res * 2) +   // transposed 16-bit copy of the bias
+         align_up(3 * (size_t)d->B * d->n_seq * d->H * attn_npad(d) * sizeof(float));   // padded per-row constants
 }
 
 int attn_forward(const TriAttnDesc* d, const void* q, const void* k, const void* v, const void* bias,
                  const uint8_t* mask, void* o, float* lse, void* ws, size_t ws_size, cudaStream_t st) {
-  if (ws == nullptr || ws_size < 256) return fail(TRI_ERR_WORKSPACE, "attention forward needs a 256-byte workspace");
+  if (ws == nullptr || ws_size < attn_ws_bytes(d, 0)) return fail(TRI_ERR_WORKSPACE, "attention forward workspace too small");
   TRI_CUDA_OK(cudaMemsetAsync(ws, 0, 256, st));
   int* err = static_cast<int*>(ws);
+  float* mt = reinterpret_cast<float*>(static_cast<char*>(ws) + 512);
   if (d->dtype == TRI_BF16) {
-    if (d->D == 32) return fwd_launch<__nv_bfloat16, 32>(d, q, k, v, bias, mask, o, lse, err, st);
-    return fwd_launch<__nv_bfloat16, 64>(d, q, k, v, bias, mask, o, lse, err, st);
+    if (d->D == 32) return fwd_launch<__nv_bfloat16, 32>(d, q, k, v, bias, mask, o, lse, err, mt, st);
+    return fwd_launch<__nv_bfloat16, 64>(d, q, k, v, bias, mask, o, lse, err, mt, st);
   }
-  if (d->D == 32) return fwd_launch<__half, 32>(d, q, k, v, bias, mask, o, lse, err, st);
-  return fwd_launch<__half, 64>(d, q, k, v, bias, mask, o, lse, err, st);
+  if (d->D == 32) return fwd_launch<__half, 32>(d, q, k, v, bias, mask, o, lse, err, mt, st);
+  return fwd_launch<__half, 64>(d, q, k, v, bias, mask, o, lse, err, mt, st);
 }
 
 int attn_backward(const TriAttnDesc* d, const void* q, const void* k, const void* v, const void* bias,
@@ -1429,12 +1281,13 @@ int attn_backward(const TriAttnDesc* d, const void* q, const void* k, const void
   float* part = reinterpret_cast<float*>(static_cast<char*>(ws) + 512 +
                                          align_up((size_t)d->B * d->n_seq * d->H * d->n_res * sizeof(float)));
   void* bias_t = reinterpret_cast<char*>(part) + align_up((size_t)kDbiasRowChunks * d->B * d->H * d->n_res * d->n_res * sizeof(float));
+  float* prep = reinterpret_cast<float*>(static_cast<char*>(bias_t) + align_up((size_t)d->B * d->H * d->n_res * d->n_res * 2));
   if (d->dtype == TRI_BF16) {
-    if (d->D == 32) return bwd_launch<__nv_bfloat16, 32>(d, q, k, v, bias, mask, o, lse, d_o, dq, dk, dv, dbias, err, delta, part, bias_t, st);
-    return bwd_launch<__nv_bfloat16, 64>(d, q, k, v, bias, mask, o, lse, d_o, dq, dk, dv, dbias, err, delta, part, bias_t, st);
+    if (d->D == 32) return bwd_launch<__nv_bfloat16, 32>(d, q, k, v, bias, mask, o, lse, d_o, dq, dk, dv, dbias, err, delta, part, bias_t, prep, st);
+    return bwd_launch<__nv_bfloat16, 64>(d, q, k, v, bias, mask, o, lse, d_o, dq, dk, dv, dbias, err, delta, part, bias_t, prep, st);
   }
-  if (d->D == 32) return bwd_launch<__half, 32>(d, q, k, v, bias, mask, o, lse, d_o, dq, dk, dv, dbias, err, delta, part, bias_t, st);
-  return bwd_launch<__half, 64>(d, q, k, v, bias, mask, o, lse, d_o, dq, dk, dv, dbias, err, delta, part, bias_t, st);
+  if (d->D == 32) return bwd_launch<__half, 32>(d, q, k, v, bias, mask, o, lse, d_o, dq, dk, dv, dbias, err, delta, part, bias_t, prep, st);
+  return bwd_launch<__half, 64>(d, q, k, v, bias, mask, o, lse, d_o, dq, dk, dv, dbias, err, delta, part, bias_t, prep, st);
 }
 
 }  // namespace tc
