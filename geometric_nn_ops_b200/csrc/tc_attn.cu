@@ -46,9 +46,9 @@ template <int HD> struct Geo {
   static constexpr int OFF_Q = 0;
   static constexpr int OFF_K = OFF_Q + TILE;             // [2]
   static constexpr int OFF_V = OFF_K + 2 * TILE;         // [2]
-  static constexpr int OFF_P = OFF_V + 2 * TILE;         // [128 x 128] as two SW128 blocks of 64 keys
-  static constexpr int OFF_BIAS = OFF_P + 32768;         // same shape
-  static constexpr int OFF_MB = OFF_BIAS + 32768;        // [2] x 128 additive key-mask terms
+  static constexpr int OFF_P = OFF_V + 2 * TILE;         // [2] x [128 x 128] (two SW128 blocks of 64 keys): the bias tile
+                                                         // arrives here and each thread overwrites it with its P values
+  static constexpr int OFF_MB = OFF_P + 2 * 32768;       // [2] x 128 additive key-mask terms
   static constexpr int OFF_BAR = OFF_MB + 1024;
   static constexpr int SMEM = OFF_BAR + 256 + 1024;      // + alignment slack
 };
@@ -107,19 +107,21 @@ __global__ void mask_terms_kernel(const uint8_t* __restrict__ mask, int64_t st_b
   out[idx] = v;
 }
 
-// 288 threads.  Warps 0-7 do the softmax arithmetic: thread (r, hh) owns query row r and the 64-key half hh of each
+// 320 threads.  Warps 0-7 do the softmax arithmetic: thread (r, hh) owns query row r and the 64-key half hh of each
 // 128-key tile, with its own running maximum and sum and its own output accumulator O_hh in TMEM; the halves are
-// merged once at the end.  Warp 8 issues every TMA copy and every MMA.  The two sides meet on mbarriers:
-//   bar_s    issuer -> threads   S = Q K^T of a tile is in TMEM
-//   bar_free threads -> issuer   every warp has its logits in registers (next tile's S, bias and mask terms may load)
-//   bar_p    threads -> issuer   P of the tile is in shared memory and O has its final scale (P V may start)
-//   bar_pv   issuer -> threads   P V is done: P's buffer is free and O is current
+// merged once at the end.  Warp 8 issues the MMAs, warp 9 the TMA copies.  The sides meet on mbarriers:
+//   bar_s    MMA -> threads      S = Q K^T of a tile is in TMEM
+//   bar_free threads -> MMA, TMA every warp has its logits in registers (next tile's S and K may follow)
+//   bar_p    threads -> MMA      P of the tile is in shared memory and O has its final scale (P V may start)
+//   bar_pv   MMA -> TMA, threads P V is done: its V stage and P buffer are free and O is current
+// The bias tile of step j lands in buffer j & 1 and each thread overwrites its own part with P, so P is double
+// buffered at no cost and the threads never wait for P V except to rescale O.
 // O stays in TMEM across tiles.  It is rescaled only when a row's maximum grows by more than kRescale, so the
 // stored maximum may be stale by up to that much: P <= e^kRescale = 256, and the row sum uses the same maximum.
 constexpr float kRescale = 5.545177444f;   // 8 ln 2
 
 template <typename T, int HD, bool HB>
-__global__ void __launch_bounds__(288, 2)
+__global__ void __launch_bounds__(320, 2)
 attn_fwd_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmK,
                    const __grid_constant__ CUtensorMap tmV, const __grid_constant__ CUtensorMap tmBias,
                    const AttnArgs a) {
@@ -130,17 +132,16 @@ attn_fwd_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
   uint8_t* sK = smem + G::OFF_K;
   uint8_t* sV = smem + G::OFF_V;
   uint8_t* sP = smem + G::OFF_P;
-  uint8_t* sBias = smem + G::OFF_BIAS;
   float* sMb = reinterpret_cast<float*>(smem + G::OFF_MB);
   uint64_t* bar_q = reinterpret_cast<uint64_t*>(smem + G::OFF_BAR);
-  uint64_t* bar_k = bar_q + 1;   // [2] K tile + mask terms
-  uint64_t* bar_v = bar_q + 3;   // [2]
-  uint64_t* bar_bias = bar_q + 5;
-  uint64_t* bar_s = bar_q + 6;
-  uint64_t* bar_pv = bar_q + 7;
-  uint64_t* bar_free = bar_q + 8;
-  uint64_t* bar_p = bar_q + 9;
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bar_q + 10);
+  uint64_t* bar_k = bar_q + 1;      // [2] K tile + mask terms
+  uint64_t* bar_v = bar_q + 3;      // [2]
+  uint64_t* bar_bias = bar_q + 5;   // [2]
+  uint64_t* bar_s = bar_q + 7;
+  uint64_t* bar_pv = bar_q + 8;     // [2]: tile j commits to bar_pv[j & 1]
+  uint64_t* bar_free = bar_q + 10;
+  uint64_t* bar_p = bar_q + 11;
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bar_q + 12);
 
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31, r = tid & 127, hh = (tid >> 7) & 1;
   const int qblocks = (a.N + 127) / 128;
@@ -153,8 +154,9 @@ attn_fwd_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
   const int nt = (a.N + 127) / 128;
 
   if (tid == 0) {
-    mbar_init(bar_q, 1); mbar_init(&bar_k[0], 1); mbar_init(&bar_k[1], 1); mbar_init(&bar_v[0], 1); mbar_init(&bar_v[1], 1);
-    mbar_init(bar_bias, 1); mbar_init(bar_s, 1); mbar_init(bar_pv, 1); mbar_init(bar_free, 8); mbar_init(bar_p, 8);
+    mbar_init(bar_q, 1);
+    for (int i = 0; i < 2; ++i) { mbar_init(&bar_k[i], 1); mbar_init(&bar_v[i], 1); mbar_init(&bar_bias[i], 1); mbar_init(&bar_pv[i], 1); }
+    mbar_init(bar_s, 1); mbar_init(bar_free, 8); mbar_init(bar_p, 8);
     mbar_fence_init();
   }
   if (warp == 0) tmem_alloc(tmem_slot, 256);
@@ -166,9 +168,9 @@ attn_fwd_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
   constexpr uint32_t COL_O = 128;   // O_0 at [128, 128 + HD), O_1 at [128 + HD, 128 + 2 HD)
   bool ok = true;
 
-  if (warp == 8) {
+  if (warp == 9) {
     if (lane == 0) {
-      // ---------------------------------- issuer -------------------------------------------------
+      // ---------------------------------- TMA copies ---------------------------------------------
       const float* mrow = a.mask_terms + ((long long)b * a.S + s) * a.npad;
       auto load_k = [&](int t) {
         const int stg = t & 1;
@@ -182,10 +184,32 @@ attn_fwd_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
         tma_load_5d(sV + stg * G::TILE, &tmV, &bar_v[stg], 0, h, t * 128, s, b);
       };
       auto load_bias = [&](int t) {
-        mbar_expect_tx(bar_bias, 32768);
-        tma_load_4d(sBias, &tmBias, bar_bias, t * 128, q0, h, b * a.bias_b_mul);
-        tma_load_4d(sBias + 16384, &tmBias, bar_bias, t * 128 + 64, q0, h, b * a.bias_b_mul);
+        uint64_t* bb = &bar_bias[t & 1];
+        uint8_t* dst = sP + (t & 1) * 32768;
+        mbar_expect_tx(bb, 32768);
+        tma_load_4d(dst, &tmBias, bb, t * 128, q0, h, b * a.bias_b_mul);
+        tma_load_4d(dst + 16384, &tmBias, bb, t * 128 + 64, q0, h, b * a.bias_b_mul);
       };
+      mbar_expect_tx(bar_q, G::TILE);
+      tma_load_5d(sQ, &tmQ, bar_q, 0, h, q0, s, b);
+      for (int t = 0; t < 2 && t < nt; ++t) {
+        load_k(t);
+        if (HB) load_bias(t);
+        load_v(t);
+      }
+      for (int j = 0; j < nt && ok; ++j) {
+        ok = mbar_wait(bar_free, j & 1, a.err, 16) && ok;   // S(j) has been read: its K stage and mask terms are free
+        if (j + 2 < nt) load_k(j + 2);
+        if (j + 2 < nt) {                                    // P V(j) done: its V stage and bias / P buffer are free
+          ok = mbar_wait(&bar_pv[j & 1], (j >> 1) & 1, a.err, 15) && ok;
+          if (HB) load_bias(j + 2);
+          load_v(j + 2);
+        }
+      }
+    }
+  } else if (warp == 8) {
+    if (lane == 0) {
+      // ---------------------------------- MMA issue ----------------------------------------------
       constexpr uint32_t HI_KMAJ = desc_hi(G::SBO, G::LAYOUT);
       constexpr uint32_t HI_P = desc_hi(1024, 2);
       const uint32_t q_lo = desc_lo(smem_u32(sQ), 16), k_lo = desc_lo(smem_u32(sK), 16);
@@ -199,33 +223,21 @@ attn_fwd_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
           umma<KIND_F16>(tmem_base, desc_join(q_lo + ks * 2, HI_KMAJ), desc_join(k_lo + so + ks * 2, HI_KMAJ), a.idesc_s, ks > 0);
         umma_commit(bar_s);
       };
-      mbar_expect_tx(bar_q, G::TILE);
-      tma_load_5d(sQ, &tmQ, bar_q, 0, h, q0, s, b);
-      for (int t = 0; t < 2 && t < nt; ++t) { load_k(t); load_v(t); }
-      if (HB) load_bias(0);
       ok = mbar_wait(bar_q, 0, a.err, 11);
       issue_s(0);
       for (int j = 0; j < nt && ok; ++j) {
         const int stg = j & 1;
-        ok = mbar_wait(bar_free, j & 1, a.err, 16) && ok;   // logits, bias and mask terms of tile j are in registers
-        if (j + 1 < nt) {
-          issue_s(j + 1);
-          if (HB) load_bias(j + 1);
-        }
-        if (j + 2 < nt) load_k(j + 2);                      // S(j) has completed: its K stage is free
+        ok = mbar_wait(bar_free, j & 1, a.err, 16) && ok;   // logits of tile j are in registers
+        if (j + 1 < nt) issue_s(j + 1);
         ok = mbar_wait(bar_p, j & 1, a.err, 17) && ok;
-        if (j >= 1) {                                       // (complete: the threads waited for it before writing P)
-          ok = mbar_wait(bar_pv, (j - 1) & 1, a.err, 15) && ok;
-          if (j + 1 < nt) load_v(j + 1);                    // P V(j-1) is done: its V stage is free
-        }
         ok = mbar_wait(&bar_v[stg], (j >> 1) & 1, a.err, 18) && ok;
         tc_fence_after_sync();
-        const uint32_t so = stg * (G::TILE >> 4);
+        const uint32_t so = stg * (G::TILE >> 4), po = stg * (32768 >> 4);
 #pragma unroll
         for (int kk = 0; kk < 8; ++kk)   // O_half += P[:, half] V[half]: keys 64 * (kk >> 2) + 16 * (kk & 3) ...
-          umma<KIND_F16>(tmem_base + COL_O + (kk >> 2) * HD, desc_join(p_lo + (kk >> 2) * 1024 + (kk & 3) * 2, HI_P),
+          umma<KIND_F16>(tmem_base + COL_O + (kk >> 2) * HD, desc_join(p_lo + po + (kk >> 2) * 1024 + (kk & 3) * 2, HI_P),
                          desc_join(vmn_lo + so + kk * G::RB, HI_KMAJ), a.idesc_pv, (j > 0 || (kk & 3) > 0) ? 1u : 0u);
-        umma_commit(bar_pv);
+        umma_commit(&bar_pv[stg]);
       }
     }
   } else {
@@ -239,7 +251,8 @@ attn_fwd_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
       ok = mbar_wait(bar_s, j & 1, a.err, 13) && ok;
       tc_fence_after_sync();
       ok = mbar_wait(&bar_k[stg], (j >> 1) & 1, a.err, 12) && ok;   // the tile's mask terms
-      if (HB) ok = mbar_wait(bar_bias, j & 1, a.err, 14) && ok;
+      if (HB) ok = mbar_wait(&bar_bias[stg], (j >> 1) & 1, a.err, 14) && ok;
+      uint8_t* sPj = sP + stg * 32768;   // holds the bias tile now, P when this step is done
 
       // ---- logits of this thread's 64 keys into registers, their maximum ----------------------------
       float2 x2[32];
@@ -253,7 +266,7 @@ attn_fwd_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
 #pragma unroll
         for (int u = 0; u < 4; ++u) {
           uint4 raw = make_uint4(0, 0, 0, 0);
-          if constexpr (HB) raw = *reinterpret_cast<const uint4*>(sBias + sw128_chunk(r, hh * 8 + c * 4 + u));
+          if constexpr (HB) raw = *reinterpret_cast<const uint4*>(sPj + sw128_chunk(r, hh * 8 + c * 4 + u));
           const uint32_t bw[4] = {raw.x, raw.y, raw.z, raw.w};
           const float4 mA = sMb4[c * 8 + u * 2], mB = sMb4[c * 8 + u * 2 + 1];
           const float2 mk[4] = {make_float2(mA.x, mA.y), make_float2(mA.z, mA.w), make_float2(mB.x, mB.y),
@@ -274,23 +287,21 @@ attn_fwd_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
       const float mx = fmaxf(fmaxf(mx4[0], mx4[1]), fmaxf(mx4[2], mx4[3]));
       const bool grow = mx > m_run + kRescale;          // (always true on the first tile with a key in range)
       const float m_new = grow ? mx : m_run;
-      if (j > 0) {
-        ok = mbar_wait(bar_pv, (j - 1) & 1, a.err, 15) && ok;   // P's buffer is free, O is current
+      if (j > 0 && __any_sync(0xffffffffu, grow)) {     // tcgen05.ld / st are warp-wide: rows that keep their maximum scale by 1
+        ok = mbar_wait(&bar_pv[(j - 1) & 1], ((j - 1) >> 1) & 1, a.err, 15) && ok;   // O is current
         tc_fence_after_sync();
-        if (__any_sync(0xffffffffu, grow)) {            // tcgen05.ld / st are warp-wide: rows that keep their maximum scale by 1
-          const float alpha = grow ? ex2_approx((m_run - m_new) * kLog2e) : 1.0f;   // m_run = -inf gives 0 (O_hh is 0 then)
-          l_run *= alpha;
+        const float alpha = grow ? ex2_approx((m_run - m_new) * kLog2e) : 1.0f;   // m_run = -inf gives 0 (O_hh is 0 then)
+        l_run *= alpha;
 #pragma unroll
-          for (int c = 0; c < HD / 16; ++c) {
-            uint32_t o[16];
-            tmem_ld_32x16(t_o + c * 16, o);
-            tmem_ld_wait();
+        for (int c = 0; c < HD / 16; ++c) {
+          uint32_t o[16];
+          tmem_ld_32x16(t_o + c * 16, o);
+          tmem_ld_wait();
 #pragma unroll
-            for (int i = 0; i < 16; ++i) o[i] = __float_as_uint(__uint_as_float(o[i]) * alpha);
-            tmem_st_32x16(t_o + c * 16, o);
-          }
-          tmem_st_wait();
+          for (int i = 0; i < 16; ++i) o[i] = __float_as_uint(__uint_as_float(o[i]) * alpha);
+          tmem_st_32x16(t_o + c * 16, o);
         }
+        tmem_st_wait();
       }
       m_run = m_new;
 
@@ -307,7 +318,7 @@ attn_fwd_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
           ps2[i & 1] = __fadd2_rn(ps2[i & 1], pp);
           pw[i] = pack2<T>(pp.x, pp.y);
         }
-        *reinterpret_cast<uint4*>(sP + sw128_chunk(r, hh * 8 + g)) = make_uint4(pw[0], pw[1], pw[2], pw[3]);
+        *reinterpret_cast<uint4*>(sPj + sw128_chunk(r, hh * 8 + g)) = make_uint4(pw[0], pw[1], pw[2], pw[3]);
       }
       l_run += (ps2[0].x + ps2[0].y) + (ps2[1].x + ps2[1].y);
       fence_proxy_async_smem();
@@ -318,9 +329,10 @@ attn_fwd_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
     }
 
     // ---- merge the two key halves of each row and write O, the row maximum and log row sum -------------
-    ok = mbar_wait(bar_pv, (nt - 1) & 1, a.err, 15) && ok;
+    ok = mbar_wait(&bar_pv[(nt - 1) & 1], ((nt - 1) >> 1) & 1, a.err, 15) && ok;
+    if (nt > 1) ok = mbar_wait(&bar_pv[nt & 1], ((nt - 2) >> 1) & 1, a.err, 15) && ok;
     tc_fence_after_sync();
-    float* xch = reinterpret_cast<float*>(sP);   // [128 rows][HD + 2] floats, free now that the last P V is done
+    float* xch = reinterpret_cast<float*>(sP);   // [128 rows][HD + 2] floats, free now that every P V is done
     constexpr int XS = HD + 2;
     float o_acc[HD];
 #pragma unroll
@@ -751,23 +763,25 @@ template <int HD> struct GeoC {
   static constexpr int OFF_V = OFF_K + TK;
   static constexpr int OFF_Q = OFF_V + TK;          // [NQ]
   static constexpr int OFF_DO = OFF_Q + NQ * TQ;    // [NQ]
-  static constexpr int OFF_PT = OFF_DO + NQ * TQ;   // [128 keys x 64 queries] SW128
-  static constexpr int OFF_DST = OFF_PT + 16384;
-  static constexpr int OFF_BIAS = OFF_DST + 16384;  // 2 buffers of transposed bias [128 keys x 64 queries] SW128
-  static constexpr int OFF_ST = OFF_BIAS + 2 * 16384;   // [NQ] statistics stages
+  static constexpr int OFF_PT = OFF_DO + NQ * TQ;   // [2] x [128 keys x 64 queries] SW128: the transposed bias tile arrives
+                                                    // here and each thread overwrites its part with P^T
+  static constexpr int OFF_DST = OFF_PT + 2 * 16384;    // [2] x dS^T, same shape
+  static constexpr int OFF_ST = OFF_DST + 2 * 16384;    // [NQ] statistics stages
   static constexpr int OFF_BAR = OFF_ST + NQ * ST;
   static constexpr int SMEM = OFF_BAR + 256 + 1024;
 };
 
-// 288 threads.  Warps 0-7 do the arithmetic: thread (r, hh) owns key r of the block and query half hh of each
-// 64-query tile.  Warp 8 issues every TMA copy and every MMA, so none of that serial code sits between the
-// arithmetic warps' steps; the two sides meet only on mbarriers:
-//   bar_s    issuer -> threads   S^T and dP^T of a tile are in TMEM
-//   bar_free threads -> issuer   every warp has read them into registers (the next tile's products may start)
-//   bar_p    threads -> issuer   P^T and dS^T of the tile are in shared memory (dV, dK products may start)
-//   bar_acc  issuer -> threads   those products are done: the P^T / dS^T buffers and the tile's stage are free
+// 320 threads.  Warps 0-7 do the arithmetic: thread (r, hh) owns key r of the block and query half hh of each
+// 64-query tile.  Warp 8 issues the MMAs and warp 9 the TMA copies, so none of that serial code sits between the
+// arithmetic warps' steps; the sides meet only on mbarriers:
+//   bar_s    MMA -> threads      S^T and dP^T of a tile are in TMEM
+//   bar_free threads -> MMA      every warp has read them into registers (the next tile's products may start)
+//   bar_p    threads -> MMA      P^T and dS^T of the tile are in shared memory (dV, dK products may start)
+//   bar_acc  MMA -> TMA, threads those products are done: the tile's stage and its P^T / dS^T buffers are free
+// P^T and dS^T are double buffered (P^T over the bias tile it was computed from), so the threads do not wait for
+// the dV / dK products of one tile before the arithmetic of the next.
 template <typename T, int HD, bool HB>
-__global__ void __launch_bounds__(288, 2)
+__global__ void __launch_bounds__(320, 2)
 attn_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmDO,
                      const __grid_constant__ CUtensorMap tmK, const __grid_constant__ CUtensorMap tmV,
                      const __grid_constant__ CUtensorMap tmBias, const AttnBwdArgs a) {
@@ -780,16 +794,16 @@ attn_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_const
   uint8_t* sDO = smem + G::OFF_DO;
   uint8_t* sPT = smem + G::OFF_PT;
   uint8_t* sDST = smem + G::OFF_DST;
-  uint8_t* sBias = smem + G::OFF_BIAS;
   float* sStats = reinterpret_cast<float*>(smem + G::OFF_ST);   // [NQ][3][64]
   uint64_t* bar_kv = reinterpret_cast<uint64_t*>(smem + G::OFF_BAR);
   uint64_t* bar_in = bar_kv + 1;     // [NQ]
   uint64_t* bar_bias = bar_kv + 4;   // [2]
   uint64_t* bar_s = bar_kv + 6;
-  uint64_t* bar_acc = bar_kv + 7;
-  uint64_t* bar_free = bar_kv + 8;
-  uint64_t* bar_p = bar_kv + 9;
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bar_kv + 10);
+  uint64_t* bar_acc = bar_kv + 7;    // [4]: tile j commits to bar_acc[j & 3] (the copy warp may lag the MMA warp by up to
+                                     // three tiles, so two tiles that share a barrier are never both pending)
+  uint64_t* bar_free = bar_kv + 11;
+  uint64_t* bar_p = bar_kv + 12;
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bar_kv + 13);
 
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31, r = tid & 127, hh = (tid >> 7) & 1;
   const int kblocks = (a.N + 127) / 128;
@@ -805,7 +819,8 @@ attn_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_const
   if (tid == 0) {
     mbar_init(bar_kv, 1);
     for (int i = 0; i < G::NQ; ++i) mbar_init(&bar_in[i], 1);
-    mbar_init(&bar_bias[0], 1); mbar_init(&bar_bias[1], 1); mbar_init(bar_s, 1); mbar_init(bar_acc, 1);
+    mbar_init(&bar_bias[0], 1); mbar_init(&bar_bias[1], 1); mbar_init(bar_s, 1);
+    for (int i = 0; i < 4; ++i) mbar_init(&bar_acc[i], 1);
     mbar_init(bar_free, 8); mbar_init(bar_p, 8);
     mbar_fence_init();
   }
@@ -818,9 +833,9 @@ attn_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_const
   constexpr uint32_t COL_DP = 64, COL_DV = 128, COL_DK = 128 + HD;
   bool ok = true;
 
-  if (warp == 8) {
+  if (warp == 9) {
     if (lane == 0) {
-      // ---------------------------------- issuer -------------------------------------------------
+      // ---------------------------------- TMA copies ---------------------------------------------
       const float* prep_row = a.prep + ((((long long)b * a.S + s) * a.H + h) * (long long)a.npad);
       auto load_step = [&](int step) {
         const int stg = step % G::NQ;
@@ -835,8 +850,24 @@ attn_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_const
       auto load_bias = [&](int step) {
         uint64_t* bb = &bar_bias[step & 1];
         mbar_expect_tx(bb, 16384);
-        tma_load_4d(sBias + (step & 1) * 16384, &tmBias, bb, step * 64, k0, h, bias_b);   // transposed copy: queries inner
+        tma_load_4d(sPT + (step & 1) * 16384, &tmBias, bb, step * 64, k0, h, bias_b);   // transposed copy: queries inner
       };
+      mbar_expect_tx(bar_kv, 2 * G::TK);
+      tma_load_5d(sK, &tmK, bar_kv, 0, h, k0, s, b);
+      tma_load_5d(sV, &tmV, bar_kv, 0, h, k0, s, b);
+      for (int st = 0; st < G::NQ && st < nsteps; ++st) {
+        load_step(st);
+        if (HB && st < 2) load_bias(st);
+      }
+      for (int j = 0; j + 2 < nsteps && ok; ++j) {
+        ok = mbar_wait(&bar_acc[j & 3], (j >> 2) & 1, a.err, 39) && ok;   // tile j's dV / dK products are done
+        if (HB) load_bias(j + 2);                                         // its P^T buffer is free
+        if (j + 3 < nsteps) load_step(j + 3);                             // ... and its Q / dO / statistics stage
+      }
+    }
+  } else if (warp == 8) {
+    if (lane == 0) {
+      // ---------------------------------- MMA issue ----------------------------------------------
       // Descriptors are built once: the high word is a constant per operand kind, the low word is
       // (address >> 4) plus the leading-dimension field, so a k-step or a stage only adds to it.
       constexpr uint32_t HI_KMAJ = desc_hi(G::SBO, G::LAYOUT);   // K, V, Q, dO as K-major rows of RB bytes
@@ -859,11 +890,6 @@ attn_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_const
           umma<KIND_F16>(tmem_base + COL_DP, desc_join(v_lo + ks * 2, HI_KMAJ), desc_join(do_lo + so + ks * 2, HI_KMAJ), a.idesc_a, ks > 0);
         umma_commit(bar_s);
       };
-      mbar_expect_tx(bar_kv, 2 * G::TK);
-      tma_load_5d(sK, &tmK, bar_kv, 0, h, k0, s, b);
-      tma_load_5d(sV, &tmV, bar_kv, 0, h, k0, s, b);
-      for (int st = 0; st < G::NQ && st < nsteps; ++st) load_step(st);
-      if (HB) for (int st = 0; st < 2 && st < nsteps; ++st) load_bias(st);
       ok = mbar_wait(bar_kv, 0, a.err, 31);
       issue_scores(0);
       for (int j = 0; j < nsteps && ok; ++j) {
@@ -871,20 +897,17 @@ attn_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_const
         ok = mbar_wait(bar_free, j & 1, a.err, 37) && ok;
         if (j + 1 < nsteps) issue_scores(j + 1);
         ok = mbar_wait(bar_p, j & 1, a.err, 38) && ok;
-        if (j >= 1) ok = mbar_wait(bar_acc, (j - 1) & 1, a.err, 39) && ok;   // (complete: the threads waited for it too)
         tc_fence_after_sync();
-        const uint32_t so = qstg * (G::TQ >> 4);
+        const uint32_t so = qstg * (G::TQ >> 4), bo = (j & 1) * (16384 >> 4);
 #pragma unroll
         for (int kk = 0; kk < 4; ++kk)   // dV += P^T dO   (B = dO as [n = d, k = query]: MN-major)
-          umma<KIND_F16>(tmem_base + COL_DV, desc_join(pt_lo + kk * 2, HI_PT), desc_join(domn_lo + so + kk * G::RB, HI_KMAJ),
+          umma<KIND_F16>(tmem_base + COL_DV, desc_join(pt_lo + bo + kk * 2, HI_PT), desc_join(domn_lo + so + kk * G::RB, HI_KMAJ),
                          a.idesc_b, (j > 0 || kk > 0) ? 1u : 0u);
 #pragma unroll
         for (int kk = 0; kk < 4; ++kk)   // dK += dS^T Q
-          umma<KIND_F16>(tmem_base + COL_DK, desc_join(dst_lo + kk * 2, HI_PT), desc_join(qmn_lo + so + kk * G::RB, HI_KMAJ),
+          umma<KIND_F16>(tmem_base + COL_DK, desc_join(dst_lo + bo + kk * 2, HI_PT), desc_join(qmn_lo + so + kk * G::RB, HI_KMAJ),
                          a.idesc_b, (j > 0 || kk > 0) ? 1u : 0u);
-        umma_commit(bar_acc);
-        if (HB && j + 2 < nsteps) load_bias(j + 2);         // bar_p: every thread is past its reads of this buffer
-        if (j >= 1 && j + 2 < nsteps) load_step(j + 2);     // tile j-1's stage is free: its dV / dK products are done
+        umma_commit(&bar_acc[j & 3]);
       }
     }
   } else {
@@ -908,10 +931,10 @@ attn_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_const
       if (lane == 0) mbar_arrive(bar_free);   // this warp holds its logits: the accumulators can take the next tile
       ok = mbar_wait(&bar_in[qstg], (j / G::NQ) & 1, a.err, 32) && ok;   // the tile's row statistics
       if (HB) ok = mbar_wait(&bar_bias[stg], (j >> 1) & 1, a.err, 34) && ok;
-      if (j > 0) ok = mbar_wait(bar_acc, (j - 1) & 1, a.err, 35) && ok;   // P^T / dS^T buffers are free
 
       // packed fp32x2 arithmetic: P = 2^((x - m) log2e - log l log2e), dS = P (dP - delta); thread = key, columns = queries
-      const uint8_t* bias_row = sBias + stg * 16384;
+      uint8_t* sPTj = sPT + stg * 16384;     // holds the transposed bias tile now, P^T when this step is done
+      uint8_t* sDSTj = sDST + stg * 16384;   // (its last readers, tile j-2's products, finished before S^T(j) did)
       const float4* sM4 = reinterpret_cast<const float4*>(sStats + qstg * 192);
       const float4* sL4 = sM4 + 16;
       const float4* sD4 = sM4 + 32;
@@ -919,7 +942,7 @@ attn_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_const
 #pragma unroll
       for (int u = 0; u < 4; ++u) {
         uint4 raw = make_uint4(0, 0, 0, 0);
-        if constexpr (HB) raw = *reinterpret_cast<const uint4*>(bias_row + sw128_chunk1(r, c * 4 + u));
+        if constexpr (HB) raw = *reinterpret_cast<const uint4*>(sPTj + sw128_chunk1(r, c * 4 + u));
         const uint32_t bw[4] = {raw.x, raw.y, raw.z, raw.w};
         const float4 m0 = sM4[c * 8 + u * 2], m1 = sM4[c * 8 + u * 2 + 1];
         const float4 l0 = sL4[c * 8 + u * 2], l1 = sL4[c * 8 + u * 2 + 1];
@@ -938,8 +961,8 @@ attn_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_const
           pw[i] = pack2<T>(pp.x, pp.y);
           dw[i] = pack2<T>(ds.x, ds.y);
         }
-        *reinterpret_cast<uint4*>(sPT + sw128_chunk1(r, c * 4 + u)) = make_uint4(pw[0], pw[1], pw[2], pw[3]);
-        *reinterpret_cast<uint4*>(sDST + sw128_chunk1(r, c * 4 + u)) = make_uint4(dw[0], dw[1], dw[2], dw[3]);
+        *reinterpret_cast<uint4*>(sPTj + sw128_chunk1(r, c * 4 + u)) = make_uint4(pw[0], pw[1], pw[2], pw[3]);
+        *reinterpret_cast<uint4*>(sDSTj + sw128_chunk1(r, c * 4 + u)) = make_uint4(dw[0], dw[1], dw[2], dw[3]);
       }
       fence_proxy_async_smem();
       tc_fence_before_sync();
@@ -947,7 +970,7 @@ attn_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_const
       if (lane == 0) mbar_arrive(bar_p);
       if (!ok) break;
     }
-    ok = mbar_wait(bar_acc, (nsteps - 1) & 1, a.err, 36) && ok;
+    ok = mbar_wait(&bar_acc[(nsteps - 1) & 3], ((nsteps - 1) >> 2) & 1, a.err, 36) && ok;
     tc_fence_after_sync();
     {
       const bool st_ok = kj < a.N && ok && hh == 0;
@@ -1122,7 +1145,7 @@ int bwd_launch(const TriAttnDesc* d, const void* q, const void* k, const void* v
     static bool configured[2] = {false, false};
     if (!configured[bias != nullptr]) { TRI_TRY(set_dyn_smem(kern, GeoC<HD>::SMEM)); configured[bias != nullptr] = true; }
     KernelTimer kt("tc_attn_bwd_dkdv", st, 8.0 * pairs * d->D, 6.0 * tensor_bytes);
-    kern<<<(unsigned)((long long)qblocks * d->B * d->n_seq * d->H), 288, GeoC<HD>::SMEM, st>>>(tq, tdo, tk, tv, tb, a);
+    kern<<<(unsigned)((long long)qblocks * d->B * d->n_seq * d->H), 320, GeoC<HD>::SMEM, st>>>(tq, tdo, tk, tv, tb, a);
     TRI_LAUNCH_OK();
   }
   // ---- dQ ------------------------------------------------------------------------------------
@@ -1224,7 +1247,7 @@ int fwd_launch(const TriAttnDesc* d, const void* q, const void* k, const void* v
     TRI_CUDA_OK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, Geo<HD>::SMEM));
     configured[bias != nullptr] = true;
   }
-  kern<<<(unsigned)blocks, 288, Geo<HD>::SMEM, st>>>(tq, tk, tv, tb, a);
+  kern<<<(unsigned)blocks, 320, Geo<HD>::SMEM, st>>>(tq, tk, tv, tb, a);
   TRI_LAUNCH_OK();
   return 0;
 }

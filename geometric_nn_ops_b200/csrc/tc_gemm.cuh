@@ -96,6 +96,27 @@ template <typename T> __device__ __forceinline__ void store8(T* p, const float* 
   }
 }
 
+// The same 8 elements as raw 16-byte words: issued early, converted when used, so that a tile's global loads
+// are all in flight before its arithmetic (the epilogue warps are too few to hide one load after another).
+template <typename T> struct Raw8 { uint4 w[sizeof(T) == 4 ? 2 : 1]; };
+template <typename T> __device__ __forceinline__ Raw8<T> ldraw8(const T* p) {
+  Raw8<T> r;
+  r.w[0] = __ldg(reinterpret_cast<const uint4*>(p));
+  if constexpr (sizeof(T) == 4) r.w[1] = __ldg(reinterpret_cast<const uint4*>(p) + 1);
+  return r;
+}
+template <typename T> __device__ __forceinline__ void cvtraw8(const Raw8<T>& r, float (&v)[8]) {
+  if constexpr (sizeof(T) == 4) {
+    v[0] = __uint_as_float(r.w[0].x); v[1] = __uint_as_float(r.w[0].y); v[2] = __uint_as_float(r.w[0].z); v[3] = __uint_as_float(r.w[0].w);
+    v[4] = __uint_as_float(r.w[1].x); v[5] = __uint_as_float(r.w[1].y); v[6] = __uint_as_float(r.w[1].z); v[7] = __uint_as_float(r.w[1].w);
+  } else {
+    union { uint4 u; T h[8]; } pk;
+    pk.u = r.w[0];
+#pragma unroll
+    for (int i = 0; i < 8; ++i) v[i] = to_f32(pk.h[i]);
+  }
+}
+
 template <typename TOUT>
 __device__ __forceinline__ void store_row32(TOUT* dst, const float (&v)[32], int valid, bool vec_ok) {
   if (valid >= 32 && vec_ok) {
@@ -259,6 +280,32 @@ tc_gemm_kernel(const __grid_constant__ CUtensorMap tmA0, const __grid_constant__
     for (int tile = blockIdx.x; tile < total; tile += gridDim.x) {
       int tm, tn, bz;
       decode(tile, tm, tn, bz);
+      // the backward gate epilogues read a gradient tile from global memory: fetch it before waiting for the product
+      Raw8<TIN> dpre[2][4], mpre[2][4];
+      if constexpr (EPI == EPI_GATE_IN_BWD) {
+        const TIN* mask = reinterpret_cast<const TIN*>(g.aux);
+        const TIN* dplane = reinterpret_cast<const TIN*>(tm == 0 ? g.aux2 : g.aux3);
+#pragma unroll
+        for (int jj = 0; jj < 2; ++jj)
+#pragma unroll
+          for (int u = 0; u < 4; ++u) {
+            const long long m8 = (long long)tn * 128 + (grp * 2 + jj) * 32 + u * 8;
+            if (m8 < g.N) {
+              const long long bb = m8 / g.plane, pix = m8 % g.plane;
+              dpre[jj][u] = ldraw8<TIN>(dplane + (bb * 128 + row) * g.plane + pix);
+              if (mask != nullptr) mpre[jj][u] = ldraw8<TIN>(mask + m8);
+            }
+          }
+      } else if constexpr (EPI == EPI_GATE_OUT_BWD) {
+        const int m = tm * kBM + row;
+        const TIN* dout = reinterpret_cast<const TIN*>(g.aux) + (long long)m * 128;
+        if (m < g.M) {
+#pragma unroll
+          for (int jj = 0; jj < 2; ++jj)
+#pragma unroll
+            for (int u = 0; u < 4; ++u) dpre[jj][u] = ldraw8<TIN>(dout + (grp * 2 + jj) * 32 + u * 8);
+        }
+      }
       if (!mbar_wait(&tfull[acc], acc_phase, g.err, 4)) break;
       tc_fence_after_sync();
       const uint32_t t_row = tmem_base + ((uint32_t)(quarter * 32) << 16) + acc * BN;
@@ -285,7 +332,7 @@ tc_gemm_kernel(const __grid_constant__ CUtensorMap tmA0, const __grid_constant__
         const TIN* mask = reinterpret_cast<const TIN*>(g.aux);
         float bp = 0.f, bg = 0.f;
         if (g.bias0 != nullptr) { bp = g.bias0[tm * 256 + row]; bg = g.bias0[tm * 256 + 128 + row]; }
-#pragma unroll 1
+#pragma unroll
         for (int jj = 0; jj < 2; ++jj) {
           const int j = grp * 2 + jj;
           float p[32], gt[32];
@@ -296,7 +343,10 @@ tc_gemm_kernel(const __grid_constant__ CUtensorMap tmA0, const __grid_constant__
             if (m8 >= g.N) continue;
             const long long bb = m8 / g.plane, pix = m8 % g.plane;
             float mk[8];
-            if (mask != nullptr) load8<TIN>(mask + m8, mk);
+            if (mask != nullptr) {
+              if constexpr (EPI == EPI_GATE_IN_BWD) cvtraw8<TIN>(mpre[jj][u], mk);
+              else load8<TIN>(mask + m8, mk);
+            }
             if constexpr (EPI == EPI_GATE_IN) {
               float r[8];
 #pragma unroll
@@ -307,9 +357,8 @@ tc_gemm_kernel(const __grid_constant__ CUtensorMap tmA0, const __grid_constant__
               TOUT* plane = reinterpret_cast<TOUT*>(tm == 0 ? g.out0 : g.out1);
               store8<TOUT>(plane + (bb * 128 + row) * g.plane + pix, r);
             } else {
-              const TIN* dplane = reinterpret_cast<const TIN*>(tm == 0 ? g.aux2 : g.aux3);
               float d[8], dp[8], dg[8];
-              load8<TIN>(dplane + (bb * 128 + row) * g.plane + pix, d);
+              cvtraw8<TIN>(dpre[jj][u], d);
 #pragma unroll
               for (int i = 0; i < 8; ++i) {
                 const float dd = mask != nullptr ? d[i] * mk[i] : d[i];
@@ -328,8 +377,7 @@ tc_gemm_kernel(const __grid_constant__ CUtensorMap tmA0, const __grid_constant__
         const int m = tm * kBM + row;
         TOUT* o0 = reinterpret_cast<TOUT*>(g.out0) + (long long)m * 128;
         TOUT* o1 = reinterpret_cast<TOUT*>(g.out1) + (long long)m * 128;
-        const TIN* dout = reinterpret_cast<const TIN*>(g.aux) + (long long)m * 128;
-#pragma unroll 1
+#pragma unroll
         for (int jj = 0; jj < 2; ++jj) {
           const int j = grp * 2 + jj;
           float y[32], gt[32];
@@ -338,7 +386,7 @@ tc_gemm_kernel(const __grid_constant__ CUtensorMap tmA0, const __grid_constant__
 #pragma unroll
             for (int u = 0; u < 4; ++u) {
               float r0[8], r1[8], d[8];
-              if constexpr (EPI == EPI_GATE_OUT_BWD) load8<TIN>(dout + j * 32 + u * 8, d);
+              if constexpr (EPI == EPI_GATE_OUT_BWD) cvtraw8<TIN>(dpre[jj][u], d);
 #pragma unroll
               for (int i = 0; i < 8; ++i) {
                 const int c = j * 32 + u * 8 + i;
