@@ -831,6 +831,11 @@ attn_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_const
   const uint32_t tmem_base = *tmem_slot;
   const uint32_t t_row = tmem_base + ((uint32_t)((warp & 3) * 32) << 16);
   constexpr uint32_t COL_DP = 64, COL_DV = 128, COL_DK = 128 + HD;
+  // With head dim 32 the 256 TMEM columns have room for P^T and dS^T themselves (two 16-bit values per column), and
+  // the dV / dK products read them from there: half the shared-memory traffic of the step, which is what bounds it.
+  // They are single buffered, so a tile's values are stored once the previous tile's products are done.
+  constexpr bool TMEM_A = HD == 32;
+  constexpr uint32_t COL_PT = 192, COL_DST = 224;
   bool ok = true;
 
   if (warp == 9) {
@@ -900,13 +905,19 @@ attn_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_const
         tc_fence_after_sync();
         const uint32_t so = qstg * (G::TQ >> 4), bo = (j & 1) * (16384 >> 4);
 #pragma unroll
-        for (int kk = 0; kk < 4; ++kk)   // dV += P^T dO   (B = dO as [n = d, k = query]: MN-major)
-          umma<KIND_F16>(tmem_base + COL_DV, desc_join(pt_lo + bo + kk * 2, HI_PT), desc_join(domn_lo + so + kk * G::RB, HI_KMAJ),
-                         a.idesc_b, (j > 0 || kk > 0) ? 1u : 0u);
+        for (int kk = 0; kk < 4; ++kk) {   // dV += P^T dO   (B = dO as [n = d, k = query]: MN-major)
+          const uint64_t bd = desc_join(domn_lo + so + kk * G::RB, HI_KMAJ);
+          const uint32_t accf = (j > 0 || kk > 0) ? 1u : 0u;
+          if constexpr (TMEM_A) umma_ts_f16(tmem_base + COL_DV, tmem_base + COL_PT + kk * 8, bd, a.idesc_b, accf);
+          else umma<KIND_F16>(tmem_base + COL_DV, desc_join(pt_lo + bo + kk * 2, HI_PT), bd, a.idesc_b, accf);
+        }
 #pragma unroll
-        for (int kk = 0; kk < 4; ++kk)   // dK += dS^T Q
-          umma<KIND_F16>(tmem_base + COL_DK, desc_join(dst_lo + bo + kk * 2, HI_PT), desc_join(qmn_lo + so + kk * G::RB, HI_KMAJ),
-                         a.idesc_b, (j > 0 || kk > 0) ? 1u : 0u);
+        for (int kk = 0; kk < 4; ++kk) {   // dK += dS^T Q
+          const uint64_t bd = desc_join(qmn_lo + so + kk * G::RB, HI_KMAJ);
+          const uint32_t accf = (j > 0 || kk > 0) ? 1u : 0u;
+          if constexpr (TMEM_A) umma_ts_f16(tmem_base + COL_DK, tmem_base + COL_DST + kk * 8, bd, a.idesc_b, accf);
+          else umma<KIND_F16>(tmem_base + COL_DK, desc_join(dst_lo + bo + kk * 2, HI_PT), bd, a.idesc_b, accf);
+        }
         umma_commit(&bar_acc[j & 3]);
       }
     }
@@ -939,6 +950,7 @@ attn_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_const
       const float4* sL4 = sM4 + 16;
       const float4* sD4 = sM4 + 32;
       const int c = hh;
+      uint32_t pw[16], dw[16];
 #pragma unroll
       for (int u = 0; u < 4; ++u) {
         uint4 raw = make_uint4(0, 0, 0, 0);
@@ -950,7 +962,6 @@ attn_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_const
         const float2 nm[4] = {make_float2(m0.x, m0.y), make_float2(m0.z, m0.w), make_float2(m1.x, m1.y), make_float2(m1.z, m1.w)};
         const float2 nl[4] = {make_float2(l0.x, l0.y), make_float2(l0.z, l0.w), make_float2(l1.x, l1.y), make_float2(l1.z, l1.w)};
         const float2 nd[4] = {make_float2(d0.x, d0.y), make_float2(d0.z, d0.w), make_float2(d1.x, d1.y), make_float2(d1.z, d1.w)};
-        uint32_t pw[4], dw[4];
 #pragma unroll
         for (int i = 0; i < 4; ++i) {
           float2 x = __ffma2_rn(pair(rs[u * 8 + 2 * i], rs[u * 8 + 2 * i + 1]), sc2, mk2);
@@ -958,13 +969,23 @@ attn_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_const
           const float2 e = __ffma2_rn(__fadd2_rn(x, nm[i]), l2e2, nl[i]);
           const float2 pp = make_float2(ex2_approx(e.x), ex2_approx(e.y));
           const float2 ds = __fmul2_rn(pp, __fadd2_rn(pair(rp[u * 8 + 2 * i], rp[u * 8 + 2 * i + 1]), nd[i]));
-          pw[i] = pack2<T>(pp.x, pp.y);
-          dw[i] = pack2<T>(ds.x, ds.y);
+          pw[u * 4 + i] = pack2<T>(pp.x, pp.y);
+          dw[u * 4 + i] = pack2<T>(ds.x, ds.y);
         }
-        *reinterpret_cast<uint4*>(sPTj + sw128_chunk1(r, c * 4 + u)) = make_uint4(pw[0], pw[1], pw[2], pw[3]);
-        *reinterpret_cast<uint4*>(sDSTj + sw128_chunk1(r, c * 4 + u)) = make_uint4(dw[0], dw[1], dw[2], dw[3]);
+        if constexpr (!TMEM_A) {
+          *reinterpret_cast<uint4*>(sPTj + sw128_chunk1(r, c * 4 + u)) = make_uint4(pw[u * 4], pw[u * 4 + 1], pw[u * 4 + 2], pw[u * 4 + 3]);
+          *reinterpret_cast<uint4*>(sDSTj + sw128_chunk1(r, c * 4 + u)) = make_uint4(dw[u * 4], dw[u * 4 + 1], dw[u * 4 + 2], dw[u * 4 + 3]);
+        }
       }
-      fence_proxy_async_smem();
+      if constexpr (TMEM_A) {
+        if (j > 0) ok = mbar_wait(&bar_acc[(j - 1) & 3], ((j - 1) >> 2) & 1, a.err, 35) && ok;   // the previous tile's products have read theirs
+        tc_fence_after_sync();
+        tmem_st_32x16(t_row + COL_PT + hh * 16, pw);    // this thread's key row, its 32 queries as 16 packed columns
+        tmem_st_32x16(t_row + COL_DST + hh * 16, dw);
+        tmem_st_wait();
+      } else {
+        fence_proxy_async_smem();
+      }
       tc_fence_before_sync();
       __syncwarp();
       if (lane == 0) mbar_arrive(bar_p);
