@@ -166,6 +166,11 @@ attn_fwd_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
   const uint32_t tmem_base = *tmem_slot;
   const uint32_t t_row = tmem_base + ((uint32_t)((warp & 3) * 32) << 16);
   constexpr uint32_t COL_O = 128;   // O_0 at [128, 128 + HD), O_1 at [128 + HD, 128 + 2 HD)
+  // With head dim 32 the 256 TMEM columns have room for P itself (two 16-bit values per column) and P V reads it
+  // from there, which halves the step's shared-memory traffic.  P is single buffered then: a tile's values are
+  // stored once the previous tile's P V is done.
+  constexpr bool TMEM_P = HD == 32;
+  constexpr uint32_t COL_P = 192;
   bool ok = true;
 
   if (warp == 9) {
@@ -199,10 +204,11 @@ attn_fwd_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
       }
       for (int j = 0; j < nt && ok; ++j) {
         ok = mbar_wait(bar_free, j & 1, a.err, 16) && ok;   // S(j) has been read: its K stage and mask terms are free
-        if (j + 2 < nt) load_k(j + 2);
-        if (j + 2 < nt) {                                    // P V(j) done: its V stage and bias / P buffer are free
-          ok = mbar_wait(&bar_pv[j & 1], (j >> 1) & 1, a.err, 15) && ok;
-          if (HB) load_bias(j + 2);
+        if (j + 2 < nt) {
+          load_k(j + 2);
+          if (HB && TMEM_P) load_bias(j + 2);                // the bias tile has been read too and P does not replace it
+          ok = mbar_wait(&bar_pv[j & 1], (j >> 1) & 1, a.err, 15) && ok;   // P V(j) done: its V stage and P buffer are free
+          if (HB && !TMEM_P) load_bias(j + 2);
           load_v(j + 2);
         }
       }
@@ -234,9 +240,12 @@ attn_fwd_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
         tc_fence_after_sync();
         const uint32_t so = stg * (G::TILE >> 4), po = stg * (32768 >> 4);
 #pragma unroll
-        for (int kk = 0; kk < 8; ++kk)   // O_half += P[:, half] V[half]: keys 64 * (kk >> 2) + 16 * (kk & 3) ...
-          umma<KIND_F16>(tmem_base + COL_O + (kk >> 2) * HD, desc_join(p_lo + po + (kk >> 2) * 1024 + (kk & 3) * 2, HI_P),
-                         desc_join(vmn_lo + so + kk * G::RB, HI_KMAJ), a.idesc_pv, (j > 0 || (kk & 3) > 0) ? 1u : 0u);
+        for (int kk = 0; kk < 8; ++kk) {   // O_half += P[:, half] V[half]: keys 64 * (kk >> 2) + 16 * (kk & 3) ...
+          const uint64_t vd = desc_join(vmn_lo + so + kk * G::RB, HI_KMAJ);
+          const uint32_t accf = (j > 0 || (kk & 3) > 0) ? 1u : 0u;
+          if constexpr (TMEM_P) umma_ts_f16(tmem_base + COL_O + (kk >> 2) * HD, tmem_base + COL_P + kk * 8, vd, a.idesc_pv, accf);
+          else umma<KIND_F16>(tmem_base + COL_O + (kk >> 2) * HD, desc_join(p_lo + po + (kk >> 2) * 1024 + (kk & 3) * 2, HI_P), vd, a.idesc_pv, accf);
+        }
         umma_commit(&bar_pv[stg]);
       }
     }
@@ -308,20 +317,34 @@ attn_fwd_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
       // ---- P = 2^((x - m) log2e), its row sum; P rounded to the input dtype into shared memory ---------
       const float2 nm2 = splat(m_new == -INFINITY ? 0.f : -m_new);   // a half with no key in range yet: P = 2^-inf = 0
       float2 ps2[2] = {make_float2(0.f, 0.f), make_float2(0.f, 0.f)};
+      uint32_t pw[32];
 #pragma unroll
       for (int g = 0; g < 8; ++g) {
-        uint32_t pw[4];
 #pragma unroll
         for (int i = 0; i < 4; ++i) {
           const float2 e = __fmul2_rn(__fadd2_rn(x2[g * 4 + i], nm2), l2e2);
           const float2 pp = make_float2(ex2_approx(e.x), ex2_approx(e.y));
           ps2[i & 1] = __fadd2_rn(ps2[i & 1], pp);
-          pw[i] = pack2<T>(pp.x, pp.y);
+          pw[g * 4 + i] = pack2<T>(pp.x, pp.y);
         }
-        *reinterpret_cast<uint4*>(sPj + sw128_chunk(r, hh * 8 + g)) = make_uint4(pw[0], pw[1], pw[2], pw[3]);
+        if constexpr (!TMEM_P)
+          *reinterpret_cast<uint4*>(sPj + sw128_chunk(r, hh * 8 + g)) = make_uint4(pw[g * 4], pw[g * 4 + 1], pw[g * 4 + 2], pw[g * 4 + 3]);
       }
       l_run += (ps2[0].x + ps2[0].y) + (ps2[1].x + ps2[1].y);
-      fence_proxy_async_smem();
+      if constexpr (TMEM_P) {
+        if (j > 0) ok = mbar_wait(&bar_pv[(j - 1) & 1], ((j - 1) >> 1) & 1, a.err, 15) && ok;   // the previous P has been read
+        tc_fence_after_sync();
+#pragma unroll
+        for (int c = 0; c < 2; ++c) {   // this thread's query row, its 64 keys as 32 packed columns
+          uint32_t w[16];
+#pragma unroll
+          for (int i = 0; i < 16; ++i) w[i] = pw[c * 16 + i];
+          tmem_st_32x16(t_row + COL_P + hh * 32 + c * 16, w);
+        }
+        tmem_st_wait();
+      } else {
+        fence_proxy_async_smem();
+      }
       tc_fence_before_sync();
       __syncwarp();
       if (lane == 0) mbar_arrive(bar_p);
