@@ -1,15 +1,22 @@
 // Tensor-core triangle attention (tcgen05 + TMEM + TMA), bf16 / fp16, head dim 32 or 64.
 //
-// Forward: one CTA (128 threads, one query row per thread) per (batch, row, head, 128-query block).
-// Per 128-key tile:
-//   S   = Q K^T             tcgen05.mma, A/B from TMA-staged swizzled smem, accumulator in TMEM (128 cols)
-//   x   = scale*S + bias + mask_bias        tcgen05.ld to registers; bias tile TMA-staged in smem
-//   P   = exp2((x - m) log2e), online max / sum per row; P rounded to the input dtype into smem
-//   PV  = P V               tcgen05.mma (P K-major from smem, V MN-major), fresh TMEM accumulator (D cols)
-//   O   = O*alpha + PV      in registers (so no TMEM read-modify-write for the rescale)
-// Two CTAs per SM overlap each other's MMA / softmax phases.  K/V tiles are double buffered.
+// All four kernels share one shape: 320 threads, of which warps 0-7 do the elementwise arithmetic (two threads per
+// tile row, each owning half of the tile's columns), warp 8 issues every tcgen05.mma and warp 9 every TMA / bulk
+// copy.  The three sides meet only on mbarriers, so the serial issue code never sits between the arithmetic warps'
+// steps, and score products for the next tile are issued as soon as the accumulators have been read into registers.
+// The arithmetic is packed fp32x2 (fma.rn.f32x2 and friends); row constants arrive in the form it adds
+// (-m, -log l * log2e, -delta), and additive key-mask terms (0, -1e9, -inf beyond N) come from a small array
+// prepared once per call.  With head dim 32 the probabilities (forward) and dS / P^T / dS^T (backward) never touch
+// shared memory: they are stored packed into TMEM and read from there as the A operand of the next product, which
+// halves the shared-memory traffic that otherwise bounds these kernels.
+//
+// Forward, per (batch, row, head, 128-query block), per 128-key tile:
+//   S = Q K^T (TMEM) -> x = scale*S + mask + bias -> running maximum -> P = 2^((x - m) log2e) -> O_half += P V.
+//   Each half of the key tile keeps its own maximum, sum and O accumulator (merged at the end); O stays in TMEM
+//   and is rescaled only when a maximum grows by more than 8 ln 2.
+// Backward: three deterministic passes, each recomputing P from the saved statistics (see below).
 // Semantics follow triangle_attention_torch (geometric_nn_ops_torch/triangle/_reference/triangle_attention.py:28-44):
-// bias and the finite -1e9 key-mask sentinel are added in fp32 in that order; keys beyond N_res get -inf.
+// bias and the finite -1e9 key-mask sentinel are added in fp32; keys beyond N_res get -inf.
 #include <algorithm>
 #include <cstdlib>
 
@@ -409,11 +416,12 @@ attn_fwd_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
 // =================================================================================================
 // Backward.  Three deterministic passes, each recomputing P from the saved statistics:
 //   dK/dV : one CTA per (b, row, head, 128-key block), thread = key.  Per 64-query tile:
-//           S^T = K Q^T and dP^T = V dO^T (TMEM), P^T and dS^T to smem, dV += P^T dO, dK += dS^T Q (TMEM).
+//           S^T = K Q^T and dP^T = V dO^T (TMEM), P^T and dS^T packed (TMEM or smem), dV += P^T dO, dK += dS^T Q.
+//           The bias is read from a transposed copy so that a thread's queries are contiguous.
 //   dQ    : one CTA per (b, row, head, 128-query block), thread = query.  Per 64-key tile:
-//           S = Q K^T, dP = dO V^T, dS to smem, dQ += dS K (TMEM).
-//   dbias : one CTA per (b, head, 128-query block, 128-key block) looping over all rows in order and
-//           summing dS in registers (no atomics: the row reduction has a fixed order).
+//           S = Q K^T, dP = dO V^T, dS packed into TMEM, dQ += dS K.
+//   dbias : one CTA per (row chunk, b, head, 128-query block, 64-key block) looping over its rows in order and
+//           summing dS in registers (no atomics: fixed order), S / dP double buffered in TMEM.
 // P = exp((x - m) - log l), dS = P * (dP - delta), delta = sum_d dO*O (computed by a small kernel first).
 // =================================================================================================
 struct AttnBwdArgs {
@@ -424,6 +432,7 @@ struct AttnBwdArgs {
   const float* prep;     // [3][B][S][H][npad]: -m, -log l * log2e, -delta, zero in the padding
   long long prep_plane;  // B*S*H*npad
   int npad;              // N rounded up to 128
+  const float* mask_terms;   // [B][S][npad] additive key-mask terms (0, -1e9, or -inf beyond N)
   const uint8_t* mask;
   int64_t mask_st[2];
   int has_bias, bias_b_mul;
@@ -438,342 +447,6 @@ struct AttnBwdArgs {
 // byte offset of 16-byte chunk g (0..7) of row r inside a one-block SW128 tile (rows of 64 16-bit elements)
 __device__ __forceinline__ int sw128_chunk1(int r, int g) { return r * 128 + ((g ^ (r & 7)) << 4); }
 
-enum { MODE_DQ = 0, MODE_DBIAS = 1 };
-
-template <int HD, int TKV, int MODE> struct GeoR {
-  static constexpr int RB = HD * 2;
-  static constexpr int TA = 128 * RB;                    // Q / dO tile
-  static constexpr int TB = TKV * RB;                    // K / V tile
-  static constexpr int NA = MODE == MODE_DQ ? 1 : 2;     // buffers of the 128-row tiles
-  static constexpr uint32_t LAYOUT = RB == 128 ? 2 : 4;
-  static constexpr uint32_t SBO = 8 * RB;
-  static constexpr int OFF_Q = 0;
-  static constexpr int OFF_DO = OFF_Q + NA * TA;
-  static constexpr int NS = MODE == MODE_DQ ? 3 : 2;     // operand stages (dQ: K/V tiles are fetched two steps ahead)
-  static constexpr int OFF_K = OFF_DO + NA * TA;
-  static constexpr int OFF_V = OFF_K + NS * TB;
-  static constexpr int OFF_DS = OFF_V + NS * TB;                             // [128 x 64] SW128 (MODE_DQ)
-  static constexpr int OFF_BIAS = OFF_DS + (MODE == MODE_DQ ? 16384 : 0);    // [128 x TKV], 64-column blocks
-  static constexpr int NBIAS = MODE == MODE_DQ ? 2 : 1;                       // dQ: bias tiles two steps ahead
-  static constexpr int OFF_MB = OFF_BIAS + NBIAS * 128 * TKV * 2;             // 2 buffers of TKV mask terms
-  static constexpr int OFF_BAR = OFF_MB + 1024;
-  static constexpr int SMEM = OFF_BAR + 128 + 1024;
-};
-
-template <typename T, int HD, int TKV, int MODE, int HALVES, bool HB>
-__global__ void __launch_bounds__(128 * HALVES, 2)
-attn_bwd_rows_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmDO,
-                     const __grid_constant__ CUtensorMap tmK, const __grid_constant__ CUtensorMap tmV,
-                     const __grid_constant__ CUtensorMap tmBias, const AttnBwdArgs a) {
-  using G = GeoR<HD, TKV, MODE>;
-  static_assert(MODE == MODE_DBIAS || TKV == 64, "dQ pass uses 64-key tiles");
-  extern __shared__ uint8_t smem_raw[];
-  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
-  uint8_t* sQ = smem + G::OFF_Q;
-  uint8_t* sDO = smem + G::OFF_DO;
-  uint8_t* sK = smem + G::OFF_K;
-  uint8_t* sV = smem + G::OFF_V;
-  uint8_t* sDS = smem + G::OFF_DS;
-  uint8_t* sBias = smem + G::OFF_BIAS;
-  float* sMb = reinterpret_cast<float*>(smem + G::OFF_MB);
-  uint64_t* bar_once = reinterpret_cast<uint64_t*>(smem + G::OFF_BAR);  // Q+dO (DQ) or bias (DBIAS)
-  uint64_t* bar_in = bar_once + 1;   // [NS] per-step operand stages
-  uint64_t* bar_bias = bar_once + 4; // [2] per-step bias (DQ)
-  uint64_t* bar_s = bar_once + 6;
-  uint64_t* bar_dq = bar_once + 7;
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bar_once + 8);
-
-  // 128 * HALVES threads: thread (r, hh) owns row r of the tile and, with HALVES == 2, the column half hh,
-  // so an SM holds twice the warps for the same shared memory and TMEM.  That pays for the dQ pass
-  // (2.03 -> 1.81 ms at N=768); the dbias pass, with its register accumulators, is faster with one thread per row.
-  const int tid = threadIdx.x, warp = tid >> 5, r = tid & 127, hh = tid >> 7;
-  const int qblocks = (a.N + 127) / 128;
-  int z = blockIdx.x, b, h, s = 0, qb, kvb = 0, nsteps, s_lo = 0, rc = 0;
-  if constexpr (MODE == MODE_DQ) {
-    qb = z % qblocks; z /= qblocks;
-    h = z % a.H; z /= a.H;
-    s = z % a.S; b = z / a.S;
-    nsteps = (a.N + TKV - 1) / TKV;
-  } else {
-    const int kblocks = (a.N + TKV - 1) / TKV;
-    kvb = z % kblocks; z /= kblocks;
-    qb = z % qblocks; z /= qblocks;
-    h = z % a.H; z /= a.H;
-    b = z % a.B; rc = z / a.B;
-    const int per = (a.S + a.row_chunks - 1) / a.row_chunks;
-    s_lo = rc * per;
-    nsteps = max(0, min(a.S, s_lo + per) - s_lo);
-  }
-  const int q0 = qb * 128;
-  const int bias_b = b * a.bias_b_mul;
-
-  if (tid == 0) {
-    mbar_init(bar_once, 1);
-    for (int i = 0; i < G::NS; ++i) mbar_init(&bar_in[i], 1);
-    mbar_init(&bar_bias[0], 1); mbar_init(&bar_bias[1], 1); mbar_init(bar_s, 1); mbar_init(bar_dq, 1);
-    mbar_fence_init();
-  }
-  if (warp == 0) tmem_alloc(tmem_slot, 256);
-  tc_fence_before_sync();
-  __syncthreads();
-  tc_fence_after_sync();
-  const uint32_t tmem_base = *tmem_slot;
-  const uint32_t t_row = tmem_base + ((uint32_t)((warp & 3) * 32) << 16);
-  constexpr uint32_t COL_DP = TKV, COL_DQ = 2 * TKV;
-  constexpr int CPT = TKV / 32 / HALVES;   // 32-column chunks per thread
-  constexpr int COLS = TKV / HALVES;       // columns per thread
-
-  auto load_bias = [&](int k0, int buf) {   // buf: which of the dQ pass's two bias buffers (0 for dbias)
-    if constexpr (MODE == MODE_DQ) mbar_expect_tx(&bar_bias[buf], 128 * TKV * 2);
-#pragma unroll
-    for (int blk = 0; blk < TKV / 64; ++blk)
-      tma_load_4d(sBias + buf * (128 * TKV * 2) + blk * 16384, &tmBias, MODE == MODE_DQ ? &bar_bias[buf] : bar_once,
-                  k0 + blk * 64, q0, h, bias_b);
-  };
-  auto load_step = [&](int step) {
-    const int stg = step % G::NS;
-    if constexpr (MODE == MODE_DQ) {
-      mbar_expect_tx(&bar_in[stg], 2 * G::TB);
-      tma_load_5d(sK + stg * G::TB, &tmK, &bar_in[stg], 0, h, step * TKV, s, b);
-      tma_load_5d(sV + stg * G::TB, &tmV, &bar_in[stg], 0, h, step * TKV, s, b);
-    } else {
-      mbar_expect_tx(&bar_in[stg], 2 * G::TB + 2 * G::TA);
-      tma_load_5d(sQ + stg * G::TA, &tmQ, &bar_in[stg], 0, h, q0, s_lo + step, b);
-      tma_load_5d(sDO + stg * G::TA, &tmDO, &bar_in[stg], 0, h, q0, s_lo + step, b);
-      tma_load_5d(sK + stg * G::TB, &tmK, &bar_in[stg], 0, h, kvb * TKV, s_lo + step, b);
-      tma_load_5d(sV + stg * G::TB, &tmV, &bar_in[stg], 0, h, kvb * TKV, s_lo + step, b);
-    }
-  };
-  bool ok = true;
-  // S = Q K^T and dP = dO V^T of one step; issued one step ahead of the threads that consume the accumulators
-  auto issue_scores = [&](int step) {
-    const int stg = step % G::NS;
-    if (MODE == MODE_DQ && step == 0) ok = mbar_wait(bar_once, 0, a.err, 22);
-    ok = mbar_wait(&bar_in[stg], (step / G::NS) & 1, a.err, 23) && ok;
-    tc_fence_after_sync();
-    const int sa = MODE == MODE_DQ ? 0 : stg;
-    const uint32_t qa = smem_u32(sQ + sa * G::TA), da = smem_u32(sDO + sa * G::TA);
-    const uint32_t ka = smem_u32(sK + stg * G::TB), va = smem_u32(sV + stg * G::TB);
-#pragma unroll
-    for (int ks = 0; ks < HD / 16; ++ks)
-      umma<KIND_F16>(tmem_base, make_smem_desc(qa + ks * 32, 16, G::SBO, G::LAYOUT),
-                     make_smem_desc(ka + ks * 32, 16, G::SBO, G::LAYOUT), a.idesc_a, ks > 0);
-#pragma unroll
-    for (int ks = 0; ks < HD / 16; ++ks)
-      umma<KIND_F16>(tmem_base + COL_DP, make_smem_desc(da + ks * 32, 16, G::SBO, G::LAYOUT),
-                     make_smem_desc(va + ks * 32, 16, G::SBO, G::LAYOUT), a.idesc_a, ks > 0);
-    umma_commit(bar_s);
-  };
-
-  if (tid == 0) {
-    if constexpr (MODE == MODE_DQ) {
-      mbar_expect_tx(bar_once, 2 * G::TA);
-      tma_load_5d(sQ, &tmQ, bar_once, 0, h, q0, s, b);
-      tma_load_5d(sDO, &tmDO, bar_once, 0, h, q0, s, b);
-      if (HB) for (int st = 0; st < 2 && st < nsteps; ++st) load_bias(st * TKV, st);
-    } else if (HB) {
-      mbar_expect_tx(bar_once, 128 * TKV * 2);
-      load_bias(kvb * TKV, 0);
-    }
-    for (int st = 0; st < 2 && st < nsteps; ++st) load_step(st);
-    if (nsteps > 0) issue_scores(0);
-  }
-
-  const int qi = q0 + r;
-  const bool q_ok = qi < a.N;
-  const long long plane = (long long)a.B * a.S * a.H * a.N;
-  float m_row = 0.f, l_row = 0.f, d_row = 0.f, m_nx = 0.f, l_nx = 0.f, d_nx = 0.f;
-  auto load_stats = [&](int ss, float& m, float& l, float& dl) {
-    if (q_ok) {
-      const long long row = (((long long)b * a.S + ss) * a.H + h) * a.N + qi;
-      m = a.stats[row]; l = a.stats[plane + row]; dl = a.delta[row];
-    }
-  };
-  auto mask_term = [&](int row, int kj) -> float {
-    if (kj >= a.N) return -INFINITY;
-    if (a.mask == nullptr) return 0.f;
-    return kMaskSentinel * ((a.mask[b * a.mask_st[0] + row * a.mask_st[1] + kj] ? 1.0f : 0.0f) - 1.0f);
-  };
-  auto step_mask = [&](int step) -> float {   // additive mask term of key column `tid` at a step
-    if (step >= nsteps) return 0.f;
-    return MODE == MODE_DQ ? mask_term(s, step * TKV + tid) : mask_term(s_lo + step, kvb * TKV + tid);
-  };
-  float mb_next = 0.f;
-  if (tid < TKV) {
-    sMb[tid] = step_mask(0);
-    mb_next = step_mask(1);
-  }
-  if (nsteps > 0) load_stats(MODE == MODE_DQ ? s : s_lo, m_nx, l_nx, d_nx);
-  if constexpr (MODE == MODE_DQ) { m_row = m_nx; l_row = l_nx; d_row = d_nx; }
-  float acc[MODE == MODE_DBIAS ? TKV / HALVES : 1];
-  if constexpr (MODE == MODE_DBIAS) {
-#pragma unroll
-    for (int i = 0; i < TKV / HALVES; ++i) acc[i] = 0.f;
-  }
-  if (MODE == MODE_DBIAS && HB) ok = mbar_wait(bar_once, 0, a.err, 21) && ok;
-  __syncthreads();
-
-  for (int j = 0; j < nsteps; ++j) {
-    const int stg = j & 1, kstg = j % G::NS;
-    const uint32_t par = j & 1, in_par = (j >> 1) & 1;
-    if constexpr (MODE == MODE_DBIAS) { m_row = m_nx; l_row = l_nx; d_row = d_nx; }   // loaded a step ahead
-    ok = mbar_wait(bar_s, par, a.err, 24) && ok;
-    tc_fence_after_sync();
-    if constexpr (MODE == MODE_DBIAS) {   // this step's operands have been consumed: fetch the step after next
-      if (tid == 0 && j + 2 < nsteps) load_step(j + 2);
-      if (j + 1 < nsteps) load_stats(s_lo + j + 1, m_nx, l_nx, d_nx);
-    }
-    // dQ: a thread's share of the logits fits in registers, so the accumulators are released before the
-    // arithmetic and the next step's products run under it.  dbias keeps its sums in registers instead and
-    // reads the accumulators chunk by chunk.
-    constexpr bool EARLY = MODE == MODE_DQ;
-    uint32_t rs[EARLY ? CPT : 1][32], rp[EARLY ? CPT : 1][32];
-    if constexpr (EARLY) {
-#pragma unroll
-      for (int cc = 0; cc < CPT; ++cc) {
-        tmem_ld_32x32(t_row + (hh * CPT + cc) * 32, rs[cc]);
-        tmem_ld_32x32(t_row + COL_DP + (hh * CPT + cc) * 32, rp[cc]);
-      }
-      tmem_ld_wait();
-      tc_fence_before_sync();
-      __syncthreads();   // every thread holds its logits: the accumulators can take the next step
-      if (tid == 0 && j + 1 < nsteps) issue_scores(j + 1);
-      if (tid < TKV) {   // next step's mask terms into the other buffer (its readers finished a step ago)
-        sMb[((j + 1) & 1) * TKV + tid] = mb_next;
-        mb_next = step_mask(j + 2);
-      }
-      if (HB) ok = mbar_wait(&bar_bias[stg], in_par, a.err, 25) && ok;
-      if (j > 0) {   // dS buffer and the K/V stage of step j-1 are free
-        ok = mbar_wait(bar_dq, (j - 1) & 1, a.err, 26) && ok;
-        if (tid == 0 && j + 2 < nsteps) load_step(j + 2);
-      } else if (tid == 0 && 2 < nsteps) {
-        load_step(2);
-      }
-    } else {
-      if (tid < TKV) {   // next step's mask terms; the barrier at the end of this step publishes them
-        sMb[((j + 1) & 1) * TKV + tid] = mb_next;
-        mb_next = step_mask(j + 2);
-      }
-    }
-
-    // packed fp32x2 arithmetic: P = 2^((x - m) log2e - log l log2e), dS = P (dP - delta)
-    const float2 sc2 = splat(a.scale), nm2 = splat(-m_row), nl2 = splat(-l_row * kLog2e), l2e2 = splat(kLog2e),
-                 nd2 = splat(-d_row);
-    const float4* sMb4 = reinterpret_cast<const float4*>(sMb + stg * TKV);
-#pragma unroll
-    for (int cc = 0; cc < CPT; ++cc) {
-      const int c = hh * CPT + cc;
-      const int rc_ = EARLY ? cc : 0;
-      if constexpr (!EARLY) {
-        tmem_ld_32x32(t_row + c * 32, rs[0]);
-        tmem_ld_32x32(t_row + COL_DP + c * 32, rp[0]);
-        tmem_ld_wait();
-      }
-#pragma unroll
-      for (int u = 0; u < 4; ++u) {
-        uint4 raw = make_uint4(0, 0, 0, 0);
-        if constexpr (HB) {
-          const int g = c * 4 + u;
-          raw = *reinterpret_cast<const uint4*>(sBias + (MODE == MODE_DQ ? stg * (128 * TKV * 2) : 0) +
-                                                (g >> 3) * 16384 + sw128_chunk1(r, g & 7));
-        }
-        const uint32_t bw[4] = {raw.x, raw.y, raw.z, raw.w};
-        const float4 mA = sMb4[c * 8 + u * 2], mB = sMb4[c * 8 + u * 2 + 1];
-        const float2 mk[4] = {make_float2(mA.x, mA.y), make_float2(mA.z, mA.w), make_float2(mB.x, mB.y),
-                              make_float2(mB.z, mB.w)};
-        uint32_t dw[4];
-#pragma unroll
-        for (int i = 0; i < 4; ++i) {
-          float2 x = __ffma2_rn(pair(rs[rc_][u * 8 + 2 * i], rs[rc_][u * 8 + 2 * i + 1]), sc2, mk[i]);
-          if constexpr (HB) x = __fadd2_rn(x, unpack2<T>(bw[i]));
-          const float2 e = __ffma2_rn(__fadd2_rn(x, nm2), l2e2, nl2);
-          const float2 p = make_float2(ex2_approx(e.x), ex2_approx(e.y));
-          const float2 ds = __fmul2_rn(p, __fadd2_rn(pair(rp[rc_][u * 8 + 2 * i], rp[rc_][u * 8 + 2 * i + 1]), nd2));
-          if constexpr (MODE == MODE_DBIAS) {
-            const float2 t = __fadd2_rn(make_float2(acc[cc * 32 + u * 8 + 2 * i], acc[cc * 32 + u * 8 + 2 * i + 1]), ds);
-            acc[cc * 32 + u * 8 + 2 * i] = t.x;
-            acc[cc * 32 + u * 8 + 2 * i + 1] = t.y;
-          } else {
-            dw[i] = pack2<T>(ds.x, ds.y);
-          }
-        }
-        if constexpr (MODE == MODE_DQ)
-          *reinterpret_cast<uint4*>(sDS + sw128_chunk1(r, c * 4 + u)) = make_uint4(dw[0], dw[1], dw[2], dw[3]);
-      }
-    }
-    if constexpr (MODE == MODE_DQ) fence_proxy_async_smem();
-    tc_fence_before_sync();
-    __syncthreads();
-    if (tid == 0) {
-      tc_fence_after_sync();
-      if constexpr (MODE == MODE_DQ) {
-        const uint32_t dsa = smem_u32(sDS), ka = smem_u32(sK + kstg * G::TB);
-#pragma unroll
-        for (int kk = 0; kk < TKV / 16; ++kk)
-          umma<KIND_F16>(tmem_base + COL_DQ, make_smem_desc(dsa + kk * 32, 16, 1024, 2),
-                         make_smem_desc(ka + kk * 16 * G::RB, TKV * G::RB, G::SBO, G::LAYOUT), a.idesc_b,
-                         (j > 0 || kk > 0) ? 1u : 0u);
-        umma_commit(bar_dq);
-        if (HB && j + 2 < nsteps) load_bias((j + 2) * TKV, stg);   // all reads of this buffer are done
-      } else {
-        if (j + 1 < nsteps) issue_scores(j + 1);   // every thread has read this step's accumulators
-      }
-    }
-    if (!ok) break;
-  }
-
-  if constexpr (MODE == MODE_DQ) {
-    ok = mbar_wait(bar_dq, (nsteps - 1) & 1, a.err, 27) && ok;
-    tc_fence_after_sync();
-    {
-      // tcgen05.ld is warp-collective: every thread loads, only valid rows store
-      const bool st_ok = q_ok && ok && hh == 0;
-      T* row = reinterpret_cast<T*>(a.out0) + b * a.out0_st[0] + s * a.out0_st[1] + qi * a.out0_st[2] + h * a.out0_st[3];
-#pragma unroll
-      for (int c = 0; c < HD / 32; ++c) {
-        uint32_t r[32];
-        tmem_ld_32x32(t_row + COL_DQ + c * 32, r);
-        tmem_ld_wait();
-        if (st_ok) {
-#pragma unroll
-          for (int g = 0; g < 4; ++g) {
-            uint4 pk;
-            pk.x = pack2<T>(__uint_as_float(r[g * 8 + 0]) * a.scale, __uint_as_float(r[g * 8 + 1]) * a.scale);
-            pk.y = pack2<T>(__uint_as_float(r[g * 8 + 2]) * a.scale, __uint_as_float(r[g * 8 + 3]) * a.scale);
-            pk.z = pack2<T>(__uint_as_float(r[g * 8 + 4]) * a.scale, __uint_as_float(r[g * 8 + 5]) * a.scale);
-            pk.w = pack2<T>(__uint_as_float(r[g * 8 + 6]) * a.scale, __uint_as_float(r[g * 8 + 7]) * a.scale);
-            reinterpret_cast<uint4*>(row)[c * 4 + g] = pk;
-          }
-        }
-      }
-    }
-  } else {
-    if (q_ok && ok) {
-      float* row = reinterpret_cast<float*>(a.out0) + (long long)rc * a.B * a.H * a.N * a.N +
-                   (((long long)b * a.H + h) * a.N + qi) * a.N + kvb * TKV + hh * COLS;
-      const int valid = a.N - kvb * TKV - hh * COLS;
-      if (valid >= COLS && (a.N % 4) == 0) {
-#pragma unroll
-        for (int i = 0; i < COLS / 4; ++i)
-          reinterpret_cast<float4*>(row)[i] = make_float4(acc[4 * i], acc[4 * i + 1], acc[4 * i + 2], acc[4 * i + 3]);
-      } else {
-#pragma unroll
-        for (int i = 0; i < COLS; ++i)
-          if (i < valid) row[i] = acc[i];
-      }
-    }
-  }
-  tc_fence_before_sync();
-  __syncthreads();
-  if (warp == 0) {
-    tc_fence_after_sync();
-    tmem_dealloc(tmem_base, 256);
-  }
-}
-
-// ------------------------------------------------------------------------------------------------
-// dK / dV pass (thread = key, 64-query tiles)
-// ------------------------------------------------------------------------------------------------
 template <int HD> struct GeoC {
   static constexpr int RB = HD * 2;
   static constexpr int TK = 128 * RB;   // K / V tile
@@ -1053,6 +726,428 @@ attn_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_const
   }
 }
 
+// ------------------------------------------------------------------------------------------------
+// dQ pass: one CTA per (batch, row, head, 128-query block), 64-key tiles.  320 threads: warps 0-7 do the arithmetic
+// (thread (r, hh) owns query r and key half hh of each tile), warp 8 issues the MMAs, warp 9 the TMA copies.
+//   S = Q K^T, dP = dO V^T (TMEM) -> dS = P (dP - delta) packed into TMEM -> dQ += dS K (A operand read from TMEM).
+// Barriers as in the dK/dV pass: bar_s, bar_free, bar_p, and a ring bar_dq[4] for the dQ products.
+// ------------------------------------------------------------------------------------------------
+template <int HD> struct GeoQ {
+  static constexpr int RB = HD * 2;
+  static constexpr int TA = 128 * RB;                    // Q / dO tile
+  static constexpr int TB = 64 * RB;                     // K / V tile
+  static constexpr uint32_t LAYOUT = RB == 128 ? 2 : 4;
+  static constexpr uint32_t SBO = 8 * RB;
+  static constexpr int NS = 3;                           // K / V stages: tiles are fetched two steps ahead
+  static constexpr int OFF_Q = 0;
+  static constexpr int OFF_DO = OFF_Q + TA;
+  static constexpr int OFF_K = OFF_DO + TA;              // [NS]
+  static constexpr int OFF_V = OFF_K + NS * TB;          // [NS]
+  static constexpr int OFF_BIAS = OFF_V + NS * TB;       // [2] x [128 queries x 64 keys] SW128
+  static constexpr int OFF_MB = OFF_BIAS + 2 * 16384;    // [NS] x 64 additive key-mask terms
+  static constexpr int OFF_BAR = OFF_MB + NS * 256;
+  static constexpr int SMEM = OFF_BAR + 256 + 1024;
+};
+
+template <typename T, int HD, bool HB>
+__global__ void __launch_bounds__(320, 2)
+attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmDO,
+                   const __grid_constant__ CUtensorMap tmK, const __grid_constant__ CUtensorMap tmV,
+                   const __grid_constant__ CUtensorMap tmBias, const AttnBwdArgs a) {
+  using G = GeoQ<HD>;
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  uint8_t* sQ = smem + G::OFF_Q;
+  uint8_t* sDO = smem + G::OFF_DO;
+  uint8_t* sK = smem + G::OFF_K;
+  uint8_t* sV = smem + G::OFF_V;
+  uint8_t* sBias = smem + G::OFF_BIAS;
+  float* sMb = reinterpret_cast<float*>(smem + G::OFF_MB);
+  uint64_t* bar_once = reinterpret_cast<uint64_t*>(smem + G::OFF_BAR);   // Q + dO
+  uint64_t* bar_in = bar_once + 1;    // [NS] K, V and mask terms of a tile
+  uint64_t* bar_bias = bar_once + 4;  // [2]
+  uint64_t* bar_s = bar_once + 6;
+  uint64_t* bar_dq = bar_once + 7;    // [4]: tile j commits to bar_dq[j & 3]
+  uint64_t* bar_free = bar_once + 11;
+  uint64_t* bar_p = bar_once + 12;
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bar_once + 13);
+
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31, r = tid & 127, hh = (tid >> 7) & 1;
+  const int qblocks = (a.N + 127) / 128;
+  int z = blockIdx.x;
+  const int qb = z % qblocks; z /= qblocks;
+  const int h = z % a.H; z /= a.H;
+  const int s = z % a.S;
+  const int b = z / a.S;
+  const int q0 = qb * 128;
+  const int nsteps = (a.N + 63) / 64;
+  const int bias_b = b * a.bias_b_mul;
+
+  if (tid == 0) {
+    mbar_init(bar_once, 1);
+    for (int i = 0; i < G::NS; ++i) mbar_init(&bar_in[i], 1);
+    mbar_init(&bar_bias[0], 1); mbar_init(&bar_bias[1], 1); mbar_init(bar_s, 1);
+    for (int i = 0; i < 4; ++i) mbar_init(&bar_dq[i], 1);
+    mbar_init(bar_free, 8); mbar_init(bar_p, 8);
+    mbar_fence_init();
+  }
+  if (warp == 0) tmem_alloc(tmem_slot, 256);
+  tc_fence_before_sync();
+  __syncthreads();
+  tc_fence_after_sync();
+  const uint32_t tmem_base = *tmem_slot;
+  const uint32_t t_row = tmem_base + ((uint32_t)((warp & 3) * 32) << 16);
+  constexpr uint32_t COL_DP = 64, COL_DQ = 128, COL_DS = 128 + HD;   // dS: 64 keys as 32 packed columns
+  bool ok = true;
+
+  if (warp == 9) {
+    if (lane == 0) {
+      // ---------------------------------- TMA copies ---------------------------------------------
+      const float* mrow = a.mask_terms + ((long long)b * a.S + s) * a.npad;
+      auto load_step = [&](int step) {
+        const int stg = step % G::NS;
+        mbar_expect_tx(&bar_in[stg], 2 * G::TB + 256);
+        tma_load_5d(sK + stg * G::TB, &tmK, &bar_in[stg], 0, h, step * 64, s, b);
+        tma_load_5d(sV + stg * G::TB, &tmV, &bar_in[stg], 0, h, step * 64, s, b);
+        bulk_load(sMb + stg * 64, mrow + step * 64, 256, &bar_in[stg]);
+      };
+      auto load_bias = [&](int step) {
+        uint64_t* bb = &bar_bias[step & 1];
+        mbar_expect_tx(bb, 16384);
+        tma_load_4d(sBias + (step & 1) * 16384, &tmBias, bb, step * 64, q0, h, bias_b);
+      };
+      mbar_expect_tx(bar_once, 2 * G::TA);
+      tma_load_5d(sQ, &tmQ, bar_once, 0, h, q0, s, b);
+      tma_load_5d(sDO, &tmDO, bar_once, 0, h, q0, s, b);
+      for (int st = 0; st < G::NS && st < nsteps; ++st) {
+        load_step(st);
+        if (HB && st < 2) load_bias(st);
+      }
+      for (int j = 0; j + 2 < nsteps && ok; ++j) {
+        ok = mbar_wait(&bar_dq[j & 3], (j >> 2) & 1, a.err, 26) && ok;   // tile j's dQ product is done
+        if (HB) load_bias(j + 2);                                        // (its bias tile was read before that)
+        if (j + 3 < nsteps) load_step(j + 3);                            // its K / V stage is free
+      }
+    }
+  } else if (warp == 8) {
+    if (lane == 0) {
+      // ---------------------------------- MMA issue ----------------------------------------------
+      constexpr uint32_t HI_KMAJ = desc_hi(G::SBO, G::LAYOUT);
+      const uint32_t q_lo = desc_lo(smem_u32(sQ), 16), do_lo = desc_lo(smem_u32(sDO), 16);
+      const uint32_t k_lo = desc_lo(smem_u32(sK), 16), v_lo = desc_lo(smem_u32(sV), 16);
+      const uint32_t kmn_lo = desc_lo(smem_u32(sK), 64 * G::RB);   // K as [n = d, k = key]
+      auto issue_scores = [&](int step) {
+        const int stg = step % G::NS;
+        ok = mbar_wait(&bar_in[stg], (step / G::NS) & 1, a.err, 23) && ok;
+        tc_fence_after_sync();
+        const uint32_t so = stg * (G::TB >> 4);
+#pragma unroll
+        for (int ks = 0; ks < HD / 16; ++ks)
+          umma<KIND_F16>(tmem_base, desc_join(q_lo + ks * 2, HI_KMAJ), desc_join(k_lo + so + ks * 2, HI_KMAJ), a.idesc_a, ks > 0);
+#pragma unroll
+        for (int ks = 0; ks < HD / 16; ++ks)
+          umma<KIND_F16>(tmem_base + COL_DP, desc_join(do_lo + ks * 2, HI_KMAJ), desc_join(v_lo + so + ks * 2, HI_KMAJ), a.idesc_a, ks > 0);
+        umma_commit(bar_s);
+      };
+      ok = mbar_wait(bar_once, 0, a.err, 22);
+      issue_scores(0);
+      for (int j = 0; j < nsteps && ok; ++j) {
+        ok = mbar_wait(bar_free, j & 1, a.err, 28) && ok;
+        if (j + 1 < nsteps) issue_scores(j + 1);
+        ok = mbar_wait(bar_p, j & 1, a.err, 29) && ok;
+        tc_fence_after_sync();
+        const uint32_t so = (j % G::NS) * (G::TB >> 4);
+#pragma unroll
+        for (int kk = 0; kk < 4; ++kk)   // dQ += dS K   (A = dS from TMEM, B = K as [n = d, k = key]: MN-major)
+          umma_ts_f16(tmem_base + COL_DQ, tmem_base + COL_DS + kk * 8, desc_join(kmn_lo + so + kk * G::RB, HI_KMAJ), a.idesc_b,
+                      (j > 0 || kk > 0) ? 1u : 0u);
+        umma_commit(&bar_dq[j & 3]);
+      }
+    }
+  } else {
+    // ------------------------------------ arithmetic warps ---------------------------------------
+    const int qi = q0 + r;
+    const bool q_ok = qi < a.N;
+    float m_row = 0.f, l_row = 0.f, d_row = 0.f;
+    if (q_ok) {
+      const long long plane = (long long)a.B * a.S * a.H * a.N;
+      const long long row = (((long long)b * a.S + s) * a.H + h) * a.N + qi;
+      m_row = a.stats[row]; l_row = a.stats[plane + row]; d_row = a.delta[row];
+    }
+    // packed fp32x2 arithmetic: P = 2^((x - m) log2e - log l log2e), dS = P (dP - delta)
+    const float2 sc2 = splat(a.scale), nm2 = splat(-m_row), nl2 = splat(-l_row * kLog2e), l2e2 = splat(kLog2e),
+                 nd2 = splat(-d_row);
+
+    for (int j = 0; j < nsteps; ++j) {
+      const int stg = j & 1, kstg = j % G::NS;
+      ok = mbar_wait(bar_s, j & 1, a.err, 24) && ok;
+      tc_fence_after_sync();
+      uint32_t rs[32], rp[32];
+      tmem_ld_32x32(t_row + hh * 32, rs);
+      tmem_ld_32x32(t_row + COL_DP + hh * 32, rp);
+      tmem_ld_wait();
+      tc_fence_before_sync();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(bar_free);   // this warp holds its logits: the accumulators can take the next tile
+      ok = mbar_wait(&bar_in[kstg], (j / G::NS) & 1, a.err, 23) && ok;   // the tile's mask terms
+      if (HB) ok = mbar_wait(&bar_bias[stg], (j >> 1) & 1, a.err, 25) && ok;
+
+      const float4* sMb4 = reinterpret_cast<const float4*>(sMb + kstg * 64 + hh * 32);
+      const uint8_t* bias_t = sBias + stg * 16384;
+      uint32_t dw[16];
+#pragma unroll
+      for (int u = 0; u < 4; ++u) {
+        uint4 raw = make_uint4(0, 0, 0, 0);
+        if constexpr (HB) raw = *reinterpret_cast<const uint4*>(bias_t + sw128_chunk1(r, hh * 4 + u));
+        const uint32_t bw[4] = {raw.x, raw.y, raw.z, raw.w};
+        const float4 mA = sMb4[u * 2], mB = sMb4[u * 2 + 1];
+        const float2 mk[4] = {make_float2(mA.x, mA.y), make_float2(mA.z, mA.w), make_float2(mB.x, mB.y),
+                              make_float2(mB.z, mB.w)};
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+          float2 x = __ffma2_rn(pair(rs[u * 8 + 2 * i], rs[u * 8 + 2 * i + 1]), sc2, mk[i]);
+          if constexpr (HB) x = __fadd2_rn(x, unpack2<T>(bw[i]));
+          const float2 e = __ffma2_rn(__fadd2_rn(x, nm2), l2e2, nl2);
+          const float2 p = make_float2(ex2_approx(e.x), ex2_approx(e.y));
+          const float2 ds = __fmul2_rn(p, __fadd2_rn(pair(rp[u * 8 + 2 * i], rp[u * 8 + 2 * i + 1]), nd2));
+          dw[u * 4 + i] = pack2<T>(ds.x, ds.y);
+        }
+      }
+      if (j > 0) ok = mbar_wait(&bar_dq[(j - 1) & 3], ((j - 1) >> 2) & 1, a.err, 26) && ok;   // the previous dS has been read
+      tc_fence_after_sync();
+      tmem_st_32x16(t_row + COL_DS + hh * 16, dw);   // this thread's query row, its 32 keys as 16 packed columns
+      tmem_st_wait();
+      tc_fence_before_sync();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(bar_p);
+      if (!ok) break;
+    }
+    ok = mbar_wait(&bar_dq[(nsteps - 1) & 3], ((nsteps - 1) >> 2) & 1, a.err, 27) && ok;
+    tc_fence_after_sync();
+    {
+      // tcgen05.ld is warp-collective: every thread loads, only valid rows store; the halves split the head dim
+      const bool st_ok = q_ok && ok;
+      T* row = reinterpret_cast<T*>(a.out0) + b * a.out0_st[0] + s * a.out0_st[1] + qi * a.out0_st[2] + h * a.out0_st[3];
+#pragma unroll
+      for (int c = 0; c < HD / 32; ++c) {
+        uint32_t v[16];
+        tmem_ld_32x16(t_row + COL_DQ + hh * (HD / 2) + c * 16, v);
+        tmem_ld_wait();
+        if (st_ok) {
+#pragma unroll
+          for (int g = 0; g < 2; ++g) {
+            uint4 pk;
+            pk.x = pack2<T>(__uint_as_float(v[g * 8 + 0]) * a.scale, __uint_as_float(v[g * 8 + 1]) * a.scale);
+            pk.y = pack2<T>(__uint_as_float(v[g * 8 + 2]) * a.scale, __uint_as_float(v[g * 8 + 3]) * a.scale);
+            pk.z = pack2<T>(__uint_as_float(v[g * 8 + 4]) * a.scale, __uint_as_float(v[g * 8 + 5]) * a.scale);
+            pk.w = pack2<T>(__uint_as_float(v[g * 8 + 6]) * a.scale, __uint_as_float(v[g * 8 + 7]) * a.scale);
+            reinterpret_cast<uint4*>(row)[(hh * (HD / 2) + c * 16) / 8 + g] = pk;
+          }
+        }
+      }
+    }
+  }
+  tc_fence_before_sync();
+  __syncthreads();
+  if (warp == 0) {
+    tc_fence_after_sync();
+    tmem_dealloc(tmem_base, 256);
+  }
+}
+
+// ------------------------------------------------------------------------------------------------
+// dbias pass: one CTA per (row chunk, batch, head, 128-query block, 64-key block) looping over the rows of its chunk
+// in order and summing dS = P (dP - delta) in registers (no atomics: the sum over rows has a fixed order; the chunks'
+// partial sums are added by sum_partials_kernel).  320 threads: warps 0-7 do the arithmetic (thread (r, hh) owns
+// query r and key half hh), warp 8 issues the MMAs, warp 9 the TMA copies.  S and dP are double buffered in TMEM,
+// so the products of the next two rows run under the arithmetic of this one.
+//   bar_s[2]    MMA -> threads        S, dP of a row are in TMEM buffer (row & 1)
+//   bar_free[4] threads -> MMA, TMA   the row's accumulators, statistics and mask terms have been read
+// ------------------------------------------------------------------------------------------------
+template <int HD> struct GeoB {
+  static constexpr int RB = HD * 2;
+  static constexpr int TA = 128 * RB;                    // Q / dO tile
+  static constexpr int TB = 64 * RB;                     // K / V tile
+  static constexpr uint32_t LAYOUT = RB == 128 ? 2 : 4;
+  static constexpr uint32_t SBO = 8 * RB;
+  static constexpr int NS = 3;                           // row stages
+  static constexpr int STAT = 2048;                      // -m, -log l log2e, -delta of 128 queries; 64 mask terms; padding
+                                                         // (stages stay 1024-byte aligned for the swizzled tiles)
+  static constexpr int STAGE = 2 * TA + 2 * TB + STAT;
+  static constexpr int OFF_BIAS = NS * STAGE;            // [128 queries x 64 keys] SW128, loaded once
+  static constexpr int OFF_BAR = OFF_BIAS + 16384;
+  static constexpr int SMEM = OFF_BAR + 256 + 1024;
+};
+
+template <typename T, int HD>
+__global__ void __launch_bounds__(320, HD == 32 ? 2 : 1)
+attn_bwd_dbias_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmDO,
+                      const __grid_constant__ CUtensorMap tmK, const __grid_constant__ CUtensorMap tmV,
+                      const __grid_constant__ CUtensorMap tmBias, const AttnBwdArgs a) {
+  using G = GeoB<HD>;
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  uint8_t* sBias = smem + G::OFF_BIAS;
+  uint64_t* bar_once = reinterpret_cast<uint64_t*>(smem + G::OFF_BAR);   // bias tile
+  uint64_t* bar_in = bar_once + 1;     // [NS]
+  uint64_t* bar_s = bar_once + 4;      // [2]
+  uint64_t* bar_free = bar_once + 6;   // [4]: row j arrives on bar_free[j & 3]
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bar_once + 10);
+  auto stage_q = [&](int stg) { return smem + stg * G::STAGE; };
+  auto stage_do = [&](int stg) { return smem + stg * G::STAGE + G::TA; };
+  auto stage_k = [&](int stg) { return smem + stg * G::STAGE + 2 * G::TA; };
+  auto stage_v = [&](int stg) { return smem + stg * G::STAGE + 2 * G::TA + G::TB; };
+  auto stage_stat = [&](int stg) { return reinterpret_cast<float*>(smem + stg * G::STAGE + 2 * G::TA + 2 * G::TB); };
+
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31, r = tid & 127, hh = (tid >> 7) & 1;
+  const int qblocks = (a.N + 127) / 128, kblocks = (a.N + 63) / 64;
+  int z = blockIdx.x;
+  const int kvb = z % kblocks; z /= kblocks;
+  const int qb = z % qblocks; z /= qblocks;
+  const int h = z % a.H; z /= a.H;
+  const int b = z % a.B;
+  const int rc = z / a.B;
+  const int per = (a.S + a.row_chunks - 1) / a.row_chunks;
+  const int s_lo = rc * per;
+  const int nsteps = max(0, min(a.S, s_lo + per) - s_lo);
+  const int q0 = qb * 128, k0 = kvb * 64;
+
+  if (tid == 0) {
+    mbar_init(bar_once, 1);
+    for (int i = 0; i < G::NS; ++i) mbar_init(&bar_in[i], 1);
+    mbar_init(&bar_s[0], 1); mbar_init(&bar_s[1], 1);
+    for (int i = 0; i < 4; ++i) mbar_init(&bar_free[i], 8);
+    mbar_fence_init();
+  }
+  if (warp == 0) tmem_alloc(tmem_slot, 256);
+  tc_fence_before_sync();
+  __syncthreads();
+  tc_fence_after_sync();
+  const uint32_t tmem_base = *tmem_slot;
+  const uint32_t t_row = tmem_base + ((uint32_t)((warp & 3) * 32) << 16);
+  bool ok = true;
+
+  if (warp == 9) {
+    if (lane == 0) {
+      // ---------------------------------- TMA copies ---------------------------------------------
+      auto load_step = [&](int step) {
+        const int stg = step % G::NS, s = s_lo + step;
+        const float* prow = a.prep + ((((long long)b * a.S + s) * a.H + h) * (long long)a.npad) + q0;
+        float* st = stage_stat(stg);
+        mbar_expect_tx(&bar_in[stg], 2 * G::TA + 2 * G::TB + 3 * 512 + 256);
+        tma_load_5d(stage_q(stg), &tmQ, &bar_in[stg], 0, h, q0, s, b);
+        tma_load_5d(stage_do(stg), &tmDO, &bar_in[stg], 0, h, q0, s, b);
+        tma_load_5d(stage_k(stg), &tmK, &bar_in[stg], 0, h, k0, s, b);
+        tma_load_5d(stage_v(stg), &tmV, &bar_in[stg], 0, h, k0, s, b);
+        bulk_load(st, prow, 512, &bar_in[stg]);
+        bulk_load(st + 128, prow + a.prep_plane, 512, &bar_in[stg]);
+        bulk_load(st + 256, prow + 2 * a.prep_plane, 512, &bar_in[stg]);
+        bulk_load(st + 384, a.mask_terms + ((long long)b * a.S + s) * a.npad + k0, 256, &bar_in[stg]);
+      };
+      if (nsteps > 0) {   // (a CTA with no rows must not leave a copy in flight)
+        mbar_expect_tx(bar_once, 16384);
+        tma_load_4d(sBias, &tmBias, bar_once, k0, q0, h, b * a.bias_b_mul);
+      }
+      for (int st = 0; st < G::NS && st < nsteps; ++st) load_step(st);
+      for (int j = 0; j + G::NS < nsteps && ok; ++j) {
+        ok = mbar_wait(&bar_free[j & 3], (j >> 2) & 1, a.err, 41) && ok;   // row j has been consumed: its stage is free
+        load_step(j + G::NS);
+      }
+    }
+  } else if (warp == 8) {
+    if (lane == 0) {
+      // ---------------------------------- MMA issue ----------------------------------------------
+      constexpr uint32_t HI_KMAJ = desc_hi(G::SBO, G::LAYOUT);
+      const uint32_t base_lo = desc_lo(smem_u32(smem), 16);
+      for (int j = 0; j < nsteps && ok; ++j) {
+        const int stg = j % G::NS, buf = j & 1;
+        if (j >= 2) ok = mbar_wait(&bar_free[(j - 2) & 3], ((j - 2) >> 2) & 1, a.err, 42) && ok;   // TMEM buffer is free
+        ok = mbar_wait(&bar_in[stg], (j / G::NS) & 1, a.err, 43) && ok;
+        tc_fence_after_sync();
+        const uint32_t q_lo = base_lo + stg * (G::STAGE >> 4), do_lo = q_lo + (G::TA >> 4), k_lo = do_lo + (G::TA >> 4),
+                       v_lo = k_lo + (G::TB >> 4);
+#pragma unroll
+        for (int ks = 0; ks < HD / 16; ++ks)
+          umma<KIND_F16>(tmem_base + buf * 128, desc_join(q_lo + ks * 2, HI_KMAJ), desc_join(k_lo + ks * 2, HI_KMAJ), a.idesc_a, ks > 0);
+#pragma unroll
+        for (int ks = 0; ks < HD / 16; ++ks)
+          umma<KIND_F16>(tmem_base + buf * 128 + 64, desc_join(do_lo + ks * 2, HI_KMAJ), desc_join(v_lo + ks * 2, HI_KMAJ), a.idesc_a, ks > 0);
+        umma_commit(&bar_s[buf]);
+      }
+    }
+  } else {
+    // ------------------------------------ arithmetic warps ---------------------------------------
+    float acc[32];
+#pragma unroll
+    for (int i = 0; i < 32; ++i) acc[i] = 0.f;
+    const float2 sc2 = splat(a.scale), l2e2 = splat(kLog2e);
+    if (nsteps > 0) ok = mbar_wait(bar_once, 0, a.err, 21);
+
+    for (int j = 0; j < nsteps; ++j) {
+      const int stg = j % G::NS, buf = j & 1;
+      ok = mbar_wait(&bar_in[stg], (j / G::NS) & 1, a.err, 43) && ok;   // statistics and mask terms of the row
+      const float* st = stage_stat(stg);
+      const float2 nm2 = splat(st[r]), nl2 = splat(st[128 + r]), nd2 = splat(st[256 + r]);
+      const float4* sMb4 = reinterpret_cast<const float4*>(st + 384 + hh * 32);
+      ok = mbar_wait(&bar_s[buf], (j >> 1) & 1, a.err, 24) && ok;
+      tc_fence_after_sync();
+#pragma unroll
+      for (int c = 0; c < 2; ++c) {
+        uint32_t rs[16], rp[16];
+        tmem_ld_32x16(t_row + buf * 128 + hh * 32 + c * 16, rs);
+        tmem_ld_32x16(t_row + buf * 128 + 64 + hh * 32 + c * 16, rp);
+        tmem_ld_wait();
+#pragma unroll
+        for (int u = 0; u < 2; ++u) {
+          const uint4 raw = *reinterpret_cast<const uint4*>(sBias + sw128_chunk1(r, hh * 4 + c * 2 + u));   // same tile for every row
+          const uint32_t bw[4] = {raw.x, raw.y, raw.z, raw.w};
+          const float4 mA = sMb4[c * 4 + u * 2], mB = sMb4[c * 4 + u * 2 + 1];
+          const float2 mk[4] = {make_float2(mA.x, mA.y), make_float2(mA.z, mA.w), make_float2(mB.x, mB.y),
+                                make_float2(mB.z, mB.w)};
+#pragma unroll
+          for (int i = 0; i < 4; ++i) {
+            float2 x = __ffma2_rn(pair(rs[u * 8 + 2 * i], rs[u * 8 + 2 * i + 1]), sc2, mk[i]);
+            x = __fadd2_rn(x, unpack2<T>(bw[i]));
+            const float2 e = __ffma2_rn(__fadd2_rn(x, nm2), l2e2, nl2);
+            const float2 p = make_float2(ex2_approx(e.x), ex2_approx(e.y));
+            const float2 ds = __fmul2_rn(p, __fadd2_rn(pair(rp[u * 8 + 2 * i], rp[u * 8 + 2 * i + 1]), nd2));
+            const int k = c * 16 + u * 8 + 2 * i;
+            const float2 t = __fadd2_rn(make_float2(acc[k], acc[k + 1]), ds);
+            acc[k] = t.x;
+            acc[k + 1] = t.y;
+          }
+        }
+      }
+      tc_fence_before_sync();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(&bar_free[j & 3]);   // accumulators, statistics and mask terms of the row are consumed
+      if (!ok) break;
+    }
+
+    const int qi = q0 + r;
+    if (qi < a.N && ok) {
+      float* row = reinterpret_cast<float*>(a.out0) + (long long)rc * a.B * a.H * a.N * a.N +
+                   (((long long)b * a.H + h) * a.N + qi) * a.N + k0 + hh * 32;
+      const int valid = a.N - k0 - hh * 32;
+      if (valid >= 32 && (a.N % 4) == 0) {
+#pragma unroll
+        for (int i = 0; i < 8; ++i)
+          reinterpret_cast<float4*>(row)[i] = make_float4(acc[4 * i], acc[4 * i + 1], acc[4 * i + 2], acc[4 * i + 3]);
+      } else {
+#pragma unroll
+        for (int i = 0; i < 32; ++i)
+          if (i < valid) row[i] = acc[i];
+      }
+    }
+  }
+  tc_fence_before_sync();
+  __syncthreads();
+  if (warp == 0) {
+    tc_fence_after_sync();
+    tmem_dealloc(tmem_base, 256);
+  }
+}
+
 // delta[b,s,h,i] = sum_d dO * O; also the per-row constants of the backward passes in the form their packed
 // arithmetic adds (prep[0] = -m, prep[1] = -log l * log2e, prep[2] = -delta), rows padded to npad entries.
 template <typename T>
@@ -1141,7 +1236,8 @@ int set_dyn_smem(KernelT kern, int bytes) {
 template <typename T, int HD>
 int bwd_launch(const TriAttnDesc* d, const void* q, const void* k, const void* v, const void* bias,
                const uint8_t* mask, const void* o, const float* stats, const void* d_o, void* dq, void* dk, void* dv,
-               float* dbias, int* err, float* delta, float* dbias_partial, void* bias_t, float* prep, cudaStream_t st) {
+               float* dbias, int* err, float* delta, float* dbias_partial, void* bias_t, float* prep, float* mask_terms,
+               cudaStream_t st) {
   const long long rows = (long long)d->B * d->n_seq * d->H * d->n_res;
   const double pairs = (double)rows * d->n_res;
   const double tensor_bytes = 2.0 * d->B * d->n_seq * (double)d->n_res * d->H * d->D;
@@ -1149,6 +1245,11 @@ int bwd_launch(const TriAttnDesc* d, const void* q, const void* k, const void* v
   const long long prep_plane = (long long)d->B * d->n_seq * d->H * npad;
   {
     KernelTimer kt("tc_attn_delta", st, 0.0, 2.0 * tensor_bytes);
+    {
+      const long long n = (long long)d->B * d->n_seq * npad;
+      mask_terms_kernel<<<cdiv(n, 256), 256, 0, st>>>(mask, d->mask_st[0], d->mask_st[1], d->B, d->n_seq, d->n_res, npad, mask_terms);
+      TRI_LAUNCH_OK();
+    }
     if (npad != d->n_res) TRI_CUDA_OK(cudaMemsetAsync(prep, 0, 3 * prep_plane * sizeof(float), st));
     attn_delta_tc_kernel<T><<<cdiv(rows, 256), 256, 0, st>>>(*d, (const T*)o, (const T*)d_o, stats, delta, prep, npad);
     TRI_LAUNCH_OK();
@@ -1156,7 +1257,7 @@ int bwd_launch(const TriAttnDesc* d, const void* q, const void* k, const void* v
   const int kind = d->dtype == TRI_BF16 ? KIND_BF16 : KIND_F16;
   AttnBwdArgs a;
   a.B = d->B; a.S = d->n_seq; a.N = d->n_res; a.H = d->H; a.scale = d->scale;
-  a.stats = stats; a.delta = delta; a.prep = prep; a.prep_plane = prep_plane; a.npad = npad; a.mask = mask; a.mask_st[0] = d->mask_st[0]; a.mask_st[1] = d->mask_st[1];
+  a.stats = stats; a.delta = delta; a.prep = prep; a.prep_plane = prep_plane; a.npad = npad; a.mask_terms = mask_terms; a.mask = mask; a.mask_st[0] = d->mask_st[0]; a.mask_st[1] = d->mask_st[1];
   a.has_bias = bias != nullptr; a.bias_b_mul = d->bias_st[0] != 0 ? 1 : 0; a.err = err;
   a.row_chunks = 1;
   const int qblocks = (d->n_res + 127) / 128;
@@ -1203,27 +1304,26 @@ int bwd_launch(const TriAttnDesc* d, const void* q, const void* k, const void* v
   a.idesc_a = make_idesc(kind, 128, 64, false, false);
   a.idesc_b = make_idesc(kind, 128, HD, false, true);
   {
-    auto kern = bias ? attn_bwd_rows_kernel<T, HD, 64, MODE_DQ, 2, true> : attn_bwd_rows_kernel<T, HD, 64, MODE_DQ, 2, false>;
+    auto kern = bias ? attn_bwd_dq_kernel<T, HD, true> : attn_bwd_dq_kernel<T, HD, false>;
     static bool configured[2] = {false, false};
-    if (!configured[bias != nullptr]) { TRI_TRY(set_dyn_smem(kern, GeoR<HD, 64, MODE_DQ>::SMEM)); configured[bias != nullptr] = true; }
+    if (!configured[bias != nullptr]) { TRI_TRY(set_dyn_smem(kern, GeoQ<HD>::SMEM)); configured[bias != nullptr] = true; }
     KernelTimer kt("tc_attn_bwd_dq", st, 2.0 * pairs * d->D, 5.0 * tensor_bytes);
-    kern<<<(unsigned)((long long)qblocks * d->B * d->n_seq * d->H), 256, GeoR<HD, 64, MODE_DQ>::SMEM, st>>>(tq, tdo, tk, tv, tb, a);
+    kern<<<(unsigned)((long long)qblocks * d->B * d->n_seq * d->H), 320, GeoQ<HD>::SMEM, st>>>(tq, tdo, tk, tv, tb, a);
     TRI_LAUNCH_OK();
   }
   // ---- dbias ---------------------------------------------------------------------------------
   if (dbias != nullptr) {
-    TRI_TRY(qkv_map_rows(&tk, k, d, d->k_st, 128));
-    TRI_TRY(qkv_map_rows(&tv, v, d, d->v_st, 128));
     const int chunks = d->n_seq >= 2 * kDbiasRowChunks ? kDbiasRowChunks : 1;
     const long long nb = (long long)d->B * d->H * d->n_res * d->n_res;
+    const int kblocks = (d->n_res + 63) / 64;
     a.row_chunks = chunks;
     a.out0 = chunks > 1 ? dbias_partial : dbias;
-    a.idesc_a = make_idesc(kind, 128, 128, false, false);
-    auto kern = attn_bwd_rows_kernel<T, HD, 128, MODE_DBIAS, 1, true>;   // a bias gradient implies a bias
+    a.idesc_a = make_idesc(kind, 128, 64, false, false);
+    auto kern = attn_bwd_dbias_kernel<T, HD>;   // (K / V maps with 64-key boxes and the bias map are those of the dQ pass)
     static bool configured = false;
-    if (!configured) { TRI_TRY(set_dyn_smem(kern, GeoR<HD, 128, MODE_DBIAS>::SMEM)); configured = true; }
+    if (!configured) { TRI_TRY(set_dyn_smem(kern, GeoB<HD>::SMEM)); configured = true; }
     KernelTimer kt("tc_attn_bwd_dbias", st, 0.0, 4.0 * tensor_bytes);
-    kern<<<(unsigned)((long long)qblocks * qblocks * d->B * d->H * chunks), 128, GeoR<HD, 128, MODE_DBIAS>::SMEM, st>>>(tq, tdo, tk, tv, tb, a);
+    kern<<<(unsigned)((long long)qblocks * kblocks * d->B * d->H * chunks), 320, GeoB<HD>::SMEM, st>>>(tq, tdo, tk, tv, tb, a);
     TRI_LAUNCH_OK();
     if (chunks > 1) {   // fixed-order sum of the row-chunk partials
       sum_partials_kernel<<<cdiv(nb, 256), 256, 0, st>>>(dbias_partial, chunks, nb, dbias);
@@ -1321,7 +1421,8 @@ size_t attn_ws_bytes(const TriAttnDesc* d, int is_bwd) {
   return 512 + align_up((size_t)d->B * d->n_seq * d->H * d->n_res * sizeof(float)) +
          align_up((size_t)kDbiasRowChunks * d->B * d->H * d->n_res * d->n_res * sizeof(float)) +
          align_up((size_t)d->B * d->H * d->n_res * d->n_res * 2) +   // transposed 16-bit copy of the bias
-         align_up(3 * (size_t)d->B * d->n_seq * d->H * attn_npad(d) * sizeof(float));   // padded per-row constants
+         align_up(3 * (size_t)d->B * d->n_seq * d->H * attn_npad(d) * sizeof(float)) +   // padded per-row constants
+         align_up((size_t)d->B * d->n_seq * attn_npad(d) * sizeof(float));               // additive key-mask terms
 }
 
 int attn_forward(const TriAttnDesc* d, const void* q, const void* k, const void* v, const void* bias,
@@ -1349,12 +1450,13 @@ int attn_backward(const TriAttnDesc* d, const void* q, const void* k, const void
                                          align_up((size_t)d->B * d->n_seq * d->H * d->n_res * sizeof(float)));
   void* bias_t = reinterpret_cast<char*>(part) + align_up((size_t)kDbiasRowChunks * d->B * d->H * d->n_res * d->n_res * sizeof(float));
   float* prep = reinterpret_cast<float*>(static_cast<char*>(bias_t) + align_up((size_t)d->B * d->H * d->n_res * d->n_res * 2));
+  float* mterms = reinterpret_cast<float*>(reinterpret_cast<char*>(prep) + align_up(3 * (size_t)d->B * d->n_seq * d->H * attn_npad(d) * sizeof(float)));
   if (d->dtype == TRI_BF16) {
-    if (d->D == 32) return bwd_launch<__nv_bfloat16, 32>(d, q, k, v, bias, mask, o, lse, d_o, dq, dk, dv, dbias, err, delta, part, bias_t, prep, st);
-    return bwd_launch<__nv_bfloat16, 64>(d, q, k, v, bias, mask, o, lse, d_o, dq, dk, dv, dbias, err, delta, part, bias_t, prep, st);
+    if (d->D == 32) return bwd_launch<__nv_bfloat16, 32>(d, q, k, v, bias, mask, o, lse, d_o, dq, dk, dv, dbias, err, delta, part, bias_t, prep, mterms, st);
+    return bwd_launch<__nv_bfloat16, 64>(d, q, k, v, bias, mask, o, lse, d_o, dq, dk, dv, dbias, err, delta, part, bias_t, prep, mterms, st);
   }
-  if (d->D == 32) return bwd_launch<__half, 32>(d, q, k, v, bias, mask, o, lse, d_o, dq, dk, dv, dbias, err, delta, part, bias_t, prep, st);
-  return bwd_launch<__half, 64>(d, q, k, v, bias, mask, o, lse, d_o, dq, dk, dv, dbias, err, delta, part, bias_t, prep, st);
+  if (d->D == 32) return bwd_launch<__half, 32>(d, q, k, v, bias, mask, o, lse, d_o, dq, dk, dv, dbias, err, delta, part, bias_t, prep, mterms, st);
+  return bwd_launch<__half, 64>(d, q, k, v, bias, mask, o, lse, d_o, dq, dk, dv, dbias, err, delta, part, bias_t, prep, mterms, st);
 }
 
 }  // namespace tc
