@@ -51,7 +51,9 @@ def test_golden_fp32_ieee(ta, path):
 
 
 SHAPES = [(1, 8, 8, 2, 8), (2, 5, 37, 3, 16), (1, 16, 100, 4, 32), (1, 3, 130, 2, 64), (1, 4, 65, 1, 48),
-          (1, 4, 64, 4, 32), (1, 6, 136, 4, 32), (2, 3, 256, 2, 64), (1, 2, 384, 4, 32)]
+          (1, 4, 64, 4, 32), (1, 6, 136, 4, 32), (2, 3, 256, 2, 64), (1, 2, 384, 4, 32),
+          (1, 9, 72, 2, 32),     # 9 rows: the bias gradient is summed over four row chunks, the last one empty
+          (1, 3, 200, 2, 64)]    # head dim 64 with a ragged second key tile
 MODES = [(torch.float32, "ieee"), (torch.float32, "tf32"), (torch.bfloat16, "ieee"), (torch.float16, "ieee")]
 
 
