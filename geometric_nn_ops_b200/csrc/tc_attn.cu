@@ -56,7 +56,8 @@ template <int HD> struct Geo {
   static constexpr int OFF_P = OFF_V + 2 * TILE;         // [2] x [128 x 128] (two SW128 blocks of 64 keys): the bias tile
                                                          // arrives here and each thread overwrites it with its P values
   static constexpr int OFF_MB = OFF_P + 2 * 32768;       // [2] x 128 additive key-mask terms
-  static constexpr int OFF_BAR = OFF_MB + 1024;
+  static constexpr int OFF_X = OFF_MB + 1024;            // [128][2] floats exchanged when the key halves are merged
+  static constexpr int OFF_BAR = OFF_X + 1024;
   static constexpr int SMEM = OFF_BAR + 256 + 1024;      // + alignment slack
 };
 
@@ -140,25 +141,36 @@ attn_fwd_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
   uint8_t* sV = smem + G::OFF_V;
   uint8_t* sP = smem + G::OFF_P;
   float* sMb = reinterpret_cast<float*>(smem + G::OFF_MB);
+  float* sX = reinterpret_cast<float*>(smem + G::OFF_X);   // [128][2]: maximum and sum of key half 1, for the merge
   uint64_t* bar_q = reinterpret_cast<uint64_t*>(smem + G::OFF_BAR);
   uint64_t* bar_k = bar_q + 1;      // [2] K tile + mask terms
   uint64_t* bar_v = bar_q + 3;      // [2]
   uint64_t* bar_bias = bar_q + 5;   // [2]
   uint64_t* bar_s = bar_q + 7;
-  uint64_t* bar_pv = bar_q + 8;     // [2]: tile j commits to bar_pv[j & 1]
+  uint64_t* bar_pv = bar_q + 8;     // [2]: tile c commits to bar_pv[c & 1]
   uint64_t* bar_free = bar_q + 10;
   uint64_t* bar_p = bar_q + 11;
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bar_q + 12);
 
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31, r = tid & 127, hh = (tid >> 7) & 1;
   const int qblocks = (a.N + 127) / 128;
-  int z = blockIdx.x;
-  const int qb = z % qblocks; z /= qblocks;
-  const int h = z % a.H; z /= a.H;
-  const int s = z % a.S;
-  const int b = z / a.S;
-  const int q0 = qb * 128;
   const int nt = (a.N + 127) / 128;
+  // Persistent: this CTA takes work items blockIdx.x, blockIdx.x + gridDim.x, ... (an item = one (batch, row, head,
+  // 128-query block)) and treats their key tiles as one stream c = 0, 1, ...: the copy warp runs two tiles ahead
+  // across item boundaries, and TMEM, barriers and the pipeline survive from one item to the next.
+  const long long items = (long long)qblocks * a.H * a.S * a.B;
+  const int my_items = blockIdx.x < items ? (int)((items - blockIdx.x + gridDim.x - 1) / gridDim.x) : 0;
+  const int total = my_items * nt;
+  struct Item { int q0, h, s, b; };
+  auto item_of = [&](int n) {   // (the item count fits 31 bits: 32-bit divisions)
+    unsigned z = blockIdx.x + (unsigned)n * gridDim.x;
+    Item it;
+    it.q0 = (int)(z % (unsigned)qblocks) * 128; z /= (unsigned)qblocks;
+    it.h = (int)(z % (unsigned)a.H); z /= (unsigned)a.H;
+    it.s = (int)(z % (unsigned)a.S);
+    it.b = (int)(z / (unsigned)a.S);
+    return it;
+  };
 
   if (tid == 0) {
     mbar_init(bar_q, 1);
@@ -183,40 +195,57 @@ attn_fwd_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
   if (warp == 9) {
     if (lane == 0) {
       // ---------------------------------- TMA copies ---------------------------------------------
-      const float* mrow = a.mask_terms + ((long long)b * a.S + s) * a.npad;
-      auto load_k = [&](int t) {
-        const int stg = t & 1;
+      auto load_q = [&](int n) {
+        const Item it = item_of(n);
+        mbar_expect_tx(bar_q, G::TILE);
+        tma_load_5d(sQ, &tmQ, bar_q, 0, it.h, it.q0, it.s, it.b);
+      };
+      // tile c of the stream: item `it`, key tile t of that item
+      auto load_k = [&](int c, const Item& it, int t) {
+        const int stg = c & 1;
         mbar_expect_tx(&bar_k[stg], G::TILE + 512);
-        tma_load_5d(sK + stg * G::TILE, &tmK, &bar_k[stg], 0, h, t * 128, s, b);
-        bulk_load(sMb + stg * 128, mrow + t * 128, 512, &bar_k[stg]);
+        tma_load_5d(sK + stg * G::TILE, &tmK, &bar_k[stg], 0, it.h, t * 128, it.s, it.b);
+        bulk_load(sMb + stg * 128, a.mask_terms + ((long long)it.b * a.S + it.s) * a.npad + t * 128, 512, &bar_k[stg]);
       };
-      auto load_v = [&](int t) {
-        const int stg = t & 1;
+      auto load_v = [&](int c, const Item& it, int t) {
+        const int stg = c & 1;
         mbar_expect_tx(&bar_v[stg], G::TILE);
-        tma_load_5d(sV + stg * G::TILE, &tmV, &bar_v[stg], 0, h, t * 128, s, b);
+        tma_load_5d(sV + stg * G::TILE, &tmV, &bar_v[stg], 0, it.h, t * 128, it.s, it.b);
       };
-      auto load_bias = [&](int t) {
-        uint64_t* bb = &bar_bias[t & 1];
-        uint8_t* dst = sP + (t & 1) * 32768;
+      auto load_bias = [&](int c, const Item& it, int t) {
+        uint64_t* bb = &bar_bias[c & 1];
+        uint8_t* dst = sP + (c & 1) * 32768;
         mbar_expect_tx(bb, 32768);
-        tma_load_4d(dst, &tmBias, bb, t * 128, q0, h, b * a.bias_b_mul);
-        tma_load_4d(dst + 16384, &tmBias, bb, t * 128 + 64, q0, h, b * a.bias_b_mul);
+        tma_load_4d(dst, &tmBias, bb, t * 128, it.q0, it.h, it.b * a.bias_b_mul);
+        tma_load_4d(dst + 16384, &tmBias, bb, t * 128 + 64, it.q0, it.h, it.b * a.bias_b_mul);
       };
-      mbar_expect_tx(bar_q, G::TILE);
-      tma_load_5d(sQ, &tmQ, bar_q, 0, h, q0, s, b);
-      for (int t = 0; t < 2 && t < nt; ++t) {
-        load_k(t);
-        if (HB) load_bias(t);
-        load_v(t);
+      // (la_n, la_t): item and key tile of the stream position being loaded, two tiles ahead of the consumers
+      int la_n = 0, la_t = 0;
+      Item la = item_of(0);
+      auto advance = [&]() {
+        if (++la_t == nt) { la_t = 0; ++la_n; if (la_n < my_items) la = item_of(la_n); }
+      };
+      if (total > 0) load_q(0);
+      for (int c = 0; c < 2 && c < total; ++c) {
+        load_k(c, la, la_t);
+        if (HB) load_bias(c, la, la_t);
+        load_v(c, la, la_t);
+        advance();
       }
-      for (int j = 0; j < nt && ok; ++j) {
-        ok = mbar_wait(bar_free, j & 1, a.err, 16) && ok;   // S(j) has been read: its K stage and mask terms are free
-        if (j + 2 < nt) {
-          load_k(j + 2);
-          if (HB && TMEM_P) load_bias(j + 2);                // the bias tile has been read too and P does not replace it
-          ok = mbar_wait(&bar_pv[j & 1], (j >> 1) & 1, a.err, 15) && ok;   // P V(j) done: its V stage and P buffer are free
-          if (HB && !TMEM_P) load_bias(j + 2);
-          load_v(j + 2);
+      int jt = 0, n_cur = 0;   // key tile and item of stream position c
+      for (int c = 0; c < total && ok; ++c) {
+        ok = mbar_wait(bar_free, c & 1, a.err, 16) && ok;   // S(c) has been read: its K stage and mask terms are free
+        if (++jt == nt) {                                    // ... and it was the item's last use of Q
+          jt = 0;
+          if (++n_cur < my_items) load_q(n_cur);
+        }
+        if (c + 2 < total) {
+          load_k(c + 2, la, la_t);
+          if (HB && TMEM_P) load_bias(c + 2, la, la_t);      // the bias tile has been read too and P does not replace it
+          ok = mbar_wait(&bar_pv[c & 1], (c >> 1) & 1, a.err, 15) && ok;   // P V(c) done: its V stage and P buffer are free
+          if (HB && !TMEM_P) load_bias(c + 2, la, la_t);
+          load_v(c + 2, la, la_t);
+          advance();
         }
       }
     }
@@ -227,23 +256,26 @@ attn_fwd_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
       constexpr uint32_t HI_P = desc_hi(1024, 2);
       const uint32_t q_lo = desc_lo(smem_u32(sQ), 16), k_lo = desc_lo(smem_u32(sK), 16);
       const uint32_t p_lo = desc_lo(smem_u32(sP), 16), vmn_lo = desc_lo(smem_u32(sV), 128 * G::RB);   // V as [n = d, k = key]
-      auto issue_s = [&](int t) {
-        ok = mbar_wait(&bar_k[t & 1], (t >> 1) & 1, a.err, 12) && ok;
+      int s_t = 0, s_n = 0;   // key tile and item of the next S product
+      auto issue_s = [&](int c) {
+        if (s_t == 0) ok = mbar_wait(bar_q, s_n & 1, a.err, 11) && ok;   // first tile of an item: its Q
+        if (++s_t == nt) { s_t = 0; ++s_n; }
+        ok = mbar_wait(&bar_k[c & 1], (c >> 1) & 1, a.err, 12) && ok;
         tc_fence_after_sync();
-        const uint32_t so = (t & 1) * (G::TILE >> 4);
+        const uint32_t so = (c & 1) * (G::TILE >> 4);
 #pragma unroll
         for (int ks = 0; ks < HD / 16; ++ks)
           umma<KIND_F16>(tmem_base, desc_join(q_lo + ks * 2, HI_KMAJ), desc_join(k_lo + so + ks * 2, HI_KMAJ), a.idesc_s, ks > 0);
         umma_commit(bar_s);
       };
-      ok = mbar_wait(bar_q, 0, a.err, 11);
-      issue_s(0);
-      for (int j = 0; j < nt && ok; ++j) {
-        const int stg = j & 1;
-        ok = mbar_wait(bar_free, j & 1, a.err, 16) && ok;   // logits of tile j are in registers
-        if (j + 1 < nt) issue_s(j + 1);
-        ok = mbar_wait(bar_p, j & 1, a.err, 17) && ok;
-        ok = mbar_wait(&bar_v[stg], (j >> 1) & 1, a.err, 18) && ok;
+      if (total > 0) issue_s(0);
+      int j = 0;
+      for (int c = 0; c < total && ok; ++c, j = (j + 1 == nt ? 0 : j + 1)) {
+        const int stg = c & 1;
+        ok = mbar_wait(bar_free, c & 1, a.err, 16) && ok;   // logits of tile c are in registers
+        if (c + 1 < total) issue_s(c + 1);
+        ok = mbar_wait(bar_p, c & 1, a.err, 17) && ok;
+        ok = mbar_wait(&bar_v[stg], (c >> 1) & 1, a.err, 18) && ok;
         tc_fence_after_sync();
         const uint32_t so = stg * (G::TILE >> 4), po = stg * (32768 >> 4);
 #pragma unroll
@@ -258,150 +290,152 @@ attn_fwd_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
     }
   } else {
     // ------------------------------------ softmax warps ------------------------------------------
-    float m_run = -INFINITY, l_run = 0.f;
     const float2 sc2 = splat(a.scale), l2e2 = splat(kLog2e);
     const uint32_t t_o = t_row + COL_O + hh * HD;   // this thread's output accumulator row
-
-    for (int j = 0; j < nt; ++j) {
-      const int stg = j & 1;
-      ok = mbar_wait(bar_s, j & 1, a.err, 13) && ok;
-      tc_fence_after_sync();
-      ok = mbar_wait(&bar_k[stg], (j >> 1) & 1, a.err, 12) && ok;   // the tile's mask terms
-      if (HB) ok = mbar_wait(&bar_bias[stg], (j >> 1) & 1, a.err, 14) && ok;
-      uint8_t* sPj = sP + stg * 32768;   // holds the bias tile now, P when this step is done
-
-      // ---- logits of this thread's 64 keys into registers, their maximum ----------------------------
-      float2 x2[32];
-      float mx4[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};   // independent chains
-      const float4* sMb4 = reinterpret_cast<const float4*>(sMb + stg * 128 + hh * 64);
-#pragma unroll
-      for (int c = 0; c < 2; ++c) {
-        uint32_t rr[32];
-        tmem_ld_32x32(t_row + hh * 64 + c * 32, rr);
-        tmem_ld_wait();
-#pragma unroll
-        for (int u = 0; u < 4; ++u) {
-          uint4 raw = make_uint4(0, 0, 0, 0);
-          if constexpr (HB) raw = *reinterpret_cast<const uint4*>(sPj + sw128_chunk(r, hh * 8 + c * 4 + u));
-          const uint32_t bw[4] = {raw.x, raw.y, raw.z, raw.w};
-          const float4 mA = sMb4[c * 8 + u * 2], mB = sMb4[c * 8 + u * 2 + 1];
-          const float2 mk[4] = {make_float2(mA.x, mA.y), make_float2(mA.z, mA.w), make_float2(mB.x, mB.y),
-                                make_float2(mB.z, mB.w)};
-#pragma unroll
-          for (int i = 0; i < 4; ++i) {
-            float2 v = __ffma2_rn(pair(rr[u * 8 + 2 * i], rr[u * 8 + 2 * i + 1]), sc2, mk[i]);
-            if constexpr (HB) v = __fadd2_rn(v, unpack2<T>(bw[i]));
-            x2[c * 16 + u * 4 + i] = v;
-            mx4[i] = fmax3(mx4[i], v.x, v.y);
-          }
-        }
-      }
-      tc_fence_before_sync();
-      __syncwarp();
-      if (lane == 0) mbar_arrive(bar_free);
-
-      const float mx = fmaxf(fmaxf(mx4[0], mx4[1]), fmaxf(mx4[2], mx4[3]));
-      const bool grow = mx > m_run + kRescale;          // (always true on the first tile with a key in range)
-      const float m_new = grow ? mx : m_run;
-      if (j > 0 && __any_sync(0xffffffffu, grow)) {     // tcgen05.ld / st are warp-wide: rows that keep their maximum scale by 1
-        ok = mbar_wait(&bar_pv[(j - 1) & 1], ((j - 1) >> 1) & 1, a.err, 15) && ok;   // O is current
+    for (int n = 0; n < my_items; ++n) {
+      const Item it = item_of(n);
+      float m_run = -INFINITY, l_run = 0.f;
+      for (int j = 0; j < nt; ++j) {
+        const int c = n * nt + j, stg = c & 1;
+        ok = mbar_wait(bar_s, c & 1, a.err, 13) && ok;
         tc_fence_after_sync();
-        const float alpha = grow ? ex2_approx((m_run - m_new) * kLog2e) : 1.0f;   // m_run = -inf gives 0 (O_hh is 0 then)
-        l_run *= alpha;
+        ok = mbar_wait(&bar_k[stg], (c >> 1) & 1, a.err, 12) && ok;   // the tile's mask terms
+        if (HB) ok = mbar_wait(&bar_bias[stg], (c >> 1) & 1, a.err, 14) && ok;
+        uint8_t* sPj = sP + stg * 32768;   // holds the bias tile; with P in shared memory, P when this step is done
+
+        // ---- logits of this thread's 64 keys into registers, their maximum ----------------------------
+        float2 x2[32];
+        float mx4[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};   // independent chains
+        const float4* sMb4 = reinterpret_cast<const float4*>(sMb + stg * 128 + hh * 64);
 #pragma unroll
-        for (int c = 0; c < HD / 16; ++c) {
-          uint32_t o[16];
-          tmem_ld_32x16(t_o + c * 16, o);
+        for (int cc = 0; cc < 2; ++cc) {
+          uint32_t rr[32];
+          tmem_ld_32x32(t_row + hh * 64 + cc * 32, rr);
           tmem_ld_wait();
 #pragma unroll
-          for (int i = 0; i < 16; ++i) o[i] = __float_as_uint(__uint_as_float(o[i]) * alpha);
-          tmem_st_32x16(t_o + c * 16, o);
+          for (int u = 0; u < 4; ++u) {
+            uint4 raw = make_uint4(0, 0, 0, 0);
+            if constexpr (HB) raw = *reinterpret_cast<const uint4*>(sPj + sw128_chunk(r, hh * 8 + cc * 4 + u));
+            const uint32_t bw[4] = {raw.x, raw.y, raw.z, raw.w};
+            const float4 mA = sMb4[cc * 8 + u * 2], mB = sMb4[cc * 8 + u * 2 + 1];
+            const float2 mk[4] = {make_float2(mA.x, mA.y), make_float2(mA.z, mA.w), make_float2(mB.x, mB.y),
+                                  make_float2(mB.z, mB.w)};
+#pragma unroll
+            for (int i = 0; i < 4; ++i) {
+              float2 v = __ffma2_rn(pair(rr[u * 8 + 2 * i], rr[u * 8 + 2 * i + 1]), sc2, mk[i]);
+              if constexpr (HB) v = __fadd2_rn(v, unpack2<T>(bw[i]));
+              x2[cc * 16 + u * 4 + i] = v;
+              mx4[i] = fmax3(mx4[i], v.x, v.y);
+            }
+          }
         }
-        tmem_st_wait();
-      }
-      m_run = m_new;
+        tc_fence_before_sync();
+        __syncwarp();
+        if (lane == 0) mbar_arrive(bar_free);
 
-      // ---- P = 2^((x - m) log2e), its row sum; P rounded to the input dtype into shared memory ---------
-      const float2 nm2 = splat(m_new == -INFINITY ? 0.f : -m_new);   // a half with no key in range yet: P = 2^-inf = 0
-      float2 ps2[2] = {make_float2(0.f, 0.f), make_float2(0.f, 0.f)};
-      uint32_t pw[32];
+        const float mx = fmaxf(fmaxf(mx4[0], mx4[1]), fmaxf(mx4[2], mx4[3]));
+        const bool grow = mx > m_run + kRescale;          // (always true on the first tile with a key in range)
+        const float m_new = grow ? mx : m_run;
+        if (j > 0 && __any_sync(0xffffffffu, grow)) {     // tcgen05.ld / st are warp-wide: rows that keep their maximum scale by 1
+          ok = mbar_wait(&bar_pv[(c - 1) & 1], ((c - 1) >> 1) & 1, a.err, 15) && ok;   // O is current
+          tc_fence_after_sync();
+          const float alpha = grow ? ex2_approx((m_run - m_new) * kLog2e) : 1.0f;   // m_run = -inf gives 0 (O_hh is 0 then)
+          l_run *= alpha;
 #pragma unroll
-      for (int g = 0; g < 8; ++g) {
+          for (int cc = 0; cc < HD / 16; ++cc) {
+            uint32_t o[16];
+            tmem_ld_32x16(t_o + cc * 16, o);
+            tmem_ld_wait();
 #pragma unroll
-        for (int i = 0; i < 4; ++i) {
-          const float2 e = __fmul2_rn(__fadd2_rn(x2[g * 4 + i], nm2), l2e2);
-          const float2 pp = make_float2(ex2_approx(e.x), ex2_approx(e.y));
-          ps2[i & 1] = __fadd2_rn(ps2[i & 1], pp);
-          pw[g * 4 + i] = pack2<T>(pp.x, pp.y);
+            for (int i = 0; i < 16; ++i) o[i] = __float_as_uint(__uint_as_float(o[i]) * alpha);
+            tmem_st_32x16(t_o + cc * 16, o);
+          }
+          tmem_st_wait();
         }
-        if constexpr (!TMEM_P)
-          *reinterpret_cast<uint4*>(sPj + sw128_chunk(r, hh * 8 + g)) = make_uint4(pw[g * 4], pw[g * 4 + 1], pw[g * 4 + 2], pw[g * 4 + 3]);
-      }
-      l_run += (ps2[0].x + ps2[0].y) + (ps2[1].x + ps2[1].y);
-      if constexpr (TMEM_P) {
-        if (j > 0) ok = mbar_wait(&bar_pv[(j - 1) & 1], ((j - 1) >> 1) & 1, a.err, 15) && ok;   // the previous P has been read
-        tc_fence_after_sync();
+        m_run = m_new;
+
+        // ---- P = 2^((x - m) log2e), its row sum; P rounded to the input dtype -----------------------------
+        const float2 nm2 = splat(m_new == -INFINITY ? 0.f : -m_new);   // a half with no key in range yet: P = 2^-inf = 0
+        float2 ps2[2] = {make_float2(0.f, 0.f), make_float2(0.f, 0.f)};
+        uint32_t pw[32];
 #pragma unroll
-        for (int c = 0; c < 2; ++c) {   // this thread's query row, its 64 keys as 32 packed columns
-          uint32_t w[16];
+        for (int g = 0; g < 8; ++g) {
 #pragma unroll
-          for (int i = 0; i < 16; ++i) w[i] = pw[c * 16 + i];
-          tmem_st_32x16(t_row + COL_P + hh * 32 + c * 16, w);
+          for (int i = 0; i < 4; ++i) {
+            const float2 e = __fmul2_rn(__fadd2_rn(x2[g * 4 + i], nm2), l2e2);
+            const float2 pp = make_float2(ex2_approx(e.x), ex2_approx(e.y));
+            ps2[i & 1] = __fadd2_rn(ps2[i & 1], pp);
+            pw[g * 4 + i] = pack2<T>(pp.x, pp.y);
+          }
+          if constexpr (!TMEM_P)
+            *reinterpret_cast<uint4*>(sPj + sw128_chunk(r, hh * 8 + g)) = make_uint4(pw[g * 4], pw[g * 4 + 1], pw[g * 4 + 2], pw[g * 4 + 3]);
         }
-        tmem_st_wait();
-      } else {
-        fence_proxy_async_smem();
+        l_run += (ps2[0].x + ps2[0].y) + (ps2[1].x + ps2[1].y);
+        if constexpr (TMEM_P) {
+          if (c > 0) ok = mbar_wait(&bar_pv[(c - 1) & 1], ((c - 1) >> 1) & 1, a.err, 15) && ok;   // the previous P has been read
+          tc_fence_after_sync();
+#pragma unroll
+          for (int cc = 0; cc < 2; ++cc) {   // this thread's query row, its 64 keys as 32 packed columns
+            uint32_t w[16];
+#pragma unroll
+            for (int i = 0; i < 16; ++i) w[i] = pw[cc * 16 + i];
+            tmem_st_32x16(t_row + COL_P + hh * 32 + cc * 16, w);
+          }
+          tmem_st_wait();
+        } else {
+          fence_proxy_async_smem();
+        }
+        tc_fence_before_sync();
+        __syncwarp();
+        if (lane == 0) mbar_arrive(bar_p);
+        if (!ok) break;
       }
-      tc_fence_before_sync();
-      __syncwarp();
-      if (lane == 0) mbar_arrive(bar_p);
       if (!ok) break;
-    }
 
-    // ---- merge the two key halves of each row and write O, the row maximum and log row sum -------------
-    ok = mbar_wait(&bar_pv[(nt - 1) & 1], ((nt - 1) >> 1) & 1, a.err, 15) && ok;
-    if (nt > 1) ok = mbar_wait(&bar_pv[nt & 1], ((nt - 2) >> 1) & 1, a.err, 15) && ok;
-    tc_fence_after_sync();
-    float* xch = reinterpret_cast<float*>(sP);   // [128 rows][HD + 2] floats, free now that every P V is done
-    constexpr int XS = HD + 2;
-    float o_acc[HD];
+      // ---- merge the two key halves of each row and write O, the row maximum and log row sum -------------
+      // Both halves' accumulators sit in this row's TMEM lane; only the maximum and sum of half 1 cross threads.
+      // The next item's first P V, which overwrites O, is issued only after every warp has arrived on bar_p
+      // for that tile, hence after this.
+      const int cl = n * nt + nt - 1;
+      ok = mbar_wait(&bar_pv[cl & 1], (cl >> 1) & 1, a.err, 15) && ok;
+      tc_fence_after_sync();
+      if (hh == 1) { sX[2 * r] = m_run; sX[2 * r + 1] = l_run; }
+      named_barrier(1, 256);
+      if (hh == 0) {
+        const float m1 = sX[2 * r], l1 = sX[2 * r + 1];
+        const float m = fmaxf(m_run, m1);   // finite: key 0 is in range and belongs to half 0
+        const float a0 = ex2_approx((m_run - m) * kLog2e), a1 = ex2_approx((m1 - m) * kLog2e);
+        const float l = l_run * a0 + l1 * a1;
+        const float inv = 1.0f / l, w0 = a0 * inv, w1 = a1 * inv;
+        const int qi = it.q0 + r;
+        const bool st_ok = qi < a.N && ok;
+        T* orow = reinterpret_cast<T*>(a.o) + it.b * a.o_st[0] + it.s * a.o_st[1] + qi * a.o_st[2] + it.h * a.o_st[3];
 #pragma unroll
-    for (int c = 0; c < HD / 16; ++c) {
-      uint32_t o[16];
-      tmem_ld_32x16(t_o + c * 16, o);
-      tmem_ld_wait();
+        for (int cc = 0; cc < HD / 16; ++cc) {   // tcgen05.ld is warp-wide: every row loads, valid rows store
+          uint32_t o0[16], o1[16];
+          tmem_ld_32x16(t_row + COL_O + cc * 16, o0);
+          tmem_ld_32x16(t_row + COL_O + HD + cc * 16, o1);
+          tmem_ld_wait();
+          if (st_ok) {
 #pragma unroll
-      for (int i = 0; i < 16; ++i) o_acc[c * 16 + i] = __uint_as_float(o[i]);
-    }
-    if (hh == 1) {
-      float* row = xch + r * XS;
-      row[0] = m_run; row[1] = l_run;
+            for (int g = 0; g < 2; ++g) {
+              float f[8];
 #pragma unroll
-      for (int i = 0; i < HD; ++i) row[2 + i] = o_acc[i];
-    }
-    named_barrier(1, 256);
-    const int qi = q0 + r;
-    if (hh == 0 && qi < a.N && ok) {
-      const float* row = xch + r * XS;
-      const float m1 = row[0], l1 = row[1];
-      const float m = fmaxf(m_run, m1);   // finite: key 0 is in range and belongs to half 0
-      const float a0 = ex2_approx((m_run - m) * kLog2e), a1 = ex2_approx((m1 - m) * kLog2e);
-      const float l = l_run * a0 + l1 * a1;
-      const float inv = 1.0f / l, w0 = a0 * inv, w1 = a1 * inv;
-      T* orow = reinterpret_cast<T*>(a.o) + b * a.o_st[0] + s * a.o_st[1] + qi * a.o_st[2] + h * a.o_st[3];
-#pragma unroll
-      for (int g = 0; g < HD / 8; ++g) {
-        float f[8];
-#pragma unroll
-        for (int i = 0; i < 8; ++i) f[i] = o_acc[g * 8 + i] * w0 + row[2 + g * 8 + i] * w1;
-        uint4 pk;
-        pk.x = pack2<T>(f[0], f[1]); pk.y = pack2<T>(f[2], f[3]);
-        pk.z = pack2<T>(f[4], f[5]); pk.w = pack2<T>(f[6], f[7]);
-        reinterpret_cast<uint4*>(orow)[g] = pk;
+              for (int i = 0; i < 8; ++i) f[i] = __uint_as_float(o0[g * 8 + i]) * w0 + __uint_as_float(o1[g * 8 + i]) * w1;
+              uint4 pk;
+              pk.x = pack2<T>(f[0], f[1]); pk.y = pack2<T>(f[2], f[3]);
+              pk.z = pack2<T>(f[4], f[5]); pk.w = pack2<T>(f[6], f[7]);
+              reinterpret_cast<uint4*>(orow)[cc * 2 + g] = pk;
+            }
+          }
+        }
+        if (st_ok) {
+          const long long srow = (((long long)it.b * a.S + it.s) * a.H + it.h) * a.N + qi;
+          a.stats[srow] = m;
+          a.stats[(long long)a.B * a.S * a.H * a.N + srow] = logf(l);
+        }
       }
-      const long long srow = (((long long)b * a.S + s) * a.H + h) * a.N + qi;
-      a.stats[srow] = m;
-      a.stats[(long long)a.B * a.S * a.H * a.N + srow] = logf(l);
+      tc_fence_before_sync();   // orders this item's TMEM reads before the arrivals that let the next item overwrite O
     }
   }
   tc_fence_before_sync();
@@ -411,7 +445,6 @@ attn_fwd_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
     tmem_dealloc(tmem_base, 256);
   }
 }
-
 
 // =================================================================================================
 // Backward.  Three deterministic passes, each recomputing P from the saved statistics:
@@ -1333,6 +1366,17 @@ int bwd_launch(const TriAttnDesc* d, const void* q, const void* k, const void* v
   return 0;
 }
 
+// multiprocessors of the current device (persistent kernels launch two CTAs per SM)
+int sm_count() {
+  static int n = 0;
+  if (n == 0) {
+    int dev = 0;
+    cudaGetDevice(&dev);
+    cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev);
+  }
+  return n;
+}
+
 bool forced_simt() {
   const char* e = getenv("TRI_B200_FORCE_SIMT");
   return e != nullptr && e[0] == '1';
@@ -1391,7 +1435,7 @@ int fwd_launch(const TriAttnDesc* d, const void* q, const void* k, const void* v
     TRI_CUDA_OK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, Geo<HD>::SMEM));
     configured[bias != nullptr] = true;
   }
-  kern<<<(unsigned)blocks, 320, Geo<HD>::SMEM, st>>>(tq, tk, tv, tb, a);
+  kern<<<(unsigned)std::min<long long>(blocks, 2LL * sm_count()), 320, Geo<HD>::SMEM, st>>>(tq, tk, tv, tb, a);
   TRI_LAUNCH_OK();
   return 0;
 }
