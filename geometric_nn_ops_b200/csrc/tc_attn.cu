@@ -148,9 +148,10 @@ attn_fwd_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
   uint64_t* bar_bias = bar_q + 5;   // [2]
   uint64_t* bar_s = bar_q + 7;
   uint64_t* bar_pv = bar_q + 8;     // [2]: tile c commits to bar_pv[c & 1]
-  uint64_t* bar_free = bar_q + 10;
-  uint64_t* bar_p = bar_q + 11;
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bar_q + 12);
+  uint64_t* bar_free = bar_q + 10;  // [4]: tile c arrives on bar_free[c & 3] (the copy warp may lag the threads by up to
+                                    // two tiles, so two tiles that share a barrier are never both pending)
+  uint64_t* bar_p = bar_q + 14;
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bar_q + 15);
 
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31, r = tid & 127, hh = (tid >> 7) & 1;
   const int qblocks = (a.N + 127) / 128;
@@ -175,7 +176,8 @@ attn_fwd_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
   if (tid == 0) {
     mbar_init(bar_q, 1);
     for (int i = 0; i < 2; ++i) { mbar_init(&bar_k[i], 1); mbar_init(&bar_v[i], 1); mbar_init(&bar_bias[i], 1); mbar_init(&bar_pv[i], 1); }
-    mbar_init(bar_s, 1); mbar_init(bar_free, 8); mbar_init(bar_p, 8);
+    mbar_init(bar_s, 1); mbar_init(bar_p, 8);
+    for (int i = 0; i < 4; ++i) mbar_init(&bar_free[i], 8);
     mbar_fence_init();
   }
   if (warp == 0) tmem_alloc(tmem_slot, 256);
@@ -234,7 +236,7 @@ attn_fwd_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
       }
       int jt = 0, n_cur = 0;   // key tile and item of stream position c
       for (int c = 0; c < total && ok; ++c) {
-        ok = mbar_wait(bar_free, c & 1, a.err, 16) && ok;   // S(c) has been read: its K stage and mask terms are free
+        ok = mbar_wait(&bar_free[c & 3], (c >> 2) & 1, a.err, 16) && ok;   // S(c) has been read: its K stage and mask terms are free
         if (++jt == nt) {                                    // ... and it was the item's last use of Q
           jt = 0;
           if (++n_cur < my_items) load_q(n_cur);
@@ -272,7 +274,7 @@ attn_fwd_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
       int j = 0;
       for (int c = 0; c < total && ok; ++c, j = (j + 1 == nt ? 0 : j + 1)) {
         const int stg = c & 1;
-        ok = mbar_wait(bar_free, c & 1, a.err, 16) && ok;   // logits of tile c are in registers
+        ok = mbar_wait(&bar_free[c & 3], (c >> 2) & 1, a.err, 16) && ok;   // logits of tile c are in registers
         if (c + 1 < total) issue_s(c + 1);
         ok = mbar_wait(bar_p, c & 1, a.err, 17) && ok;
         ok = mbar_wait(&bar_v[stg], (c >> 1) & 1, a.err, 18) && ok;
@@ -331,7 +333,7 @@ attn_fwd_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
         }
         tc_fence_before_sync();
         __syncwarp();
-        if (lane == 0) mbar_arrive(bar_free);
+        if (lane == 0) mbar_arrive(&bar_free[c & 3]);
 
         const float mx = fmaxf(fmaxf(mx4[0], mx4[1]), fmaxf(mx4[2], mx4[3]));
         const bool grow = mx > m_run + kRescale;          // (always true on the first tile with a key in range)
@@ -1217,6 +1219,17 @@ __global__ void sum_partials_kernel(const float* partial, int nparts, long long 
   out[i] = s;
 }
 
+// multiprocessors of the current device (persistent kernels launch two CTAs per SM)
+int sm_count() {
+  static int n = 0;
+  if (n == 0) {
+    int dev = 0;
+    cudaGetDevice(&dev);
+    cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev);
+  }
+  return n;
+}
+
 constexpr int kDbiasRowChunks = 4;
 
 // rank-5 map with a caller-chosen number of residues per box
@@ -1364,17 +1377,6 @@ int bwd_launch(const TriAttnDesc* d, const void* q, const void* k, const void* v
     }
   }
   return 0;
-}
-
-// multiprocessors of the current device (persistent kernels launch two CTAs per SM)
-int sm_count() {
-  static int n = 0;
-  if (n == 0) {
-    int dev = 0;
-    cudaGetDevice(&dev);
-    cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev);
-  }
-  return n;
 }
 
 bool forced_simt() {

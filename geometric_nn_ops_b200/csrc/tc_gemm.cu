@@ -115,7 +115,7 @@ static int launch_t(cudaStream_t st, const CUtensorMap* maps, const GemmArgs& g,
   const int total = g.batches * g.tiles_m * g.tiles_n;
   const int grid = std::min(total, sm_count());
   KernelTimer kt(p.name, st, p.flops, p.bytes);
-  kern<<<grid, kGemmThreads, smem, st>>>(maps[0], maps[1], maps[2], maps[3], g);
+  kern<<<grid, gemm_threads(EPI), smem, st>>>(maps[0], maps[1], maps[2], maps[3], g);
   TRI_LAUNCH_OK();
   return 0;
 }

@@ -38,7 +38,10 @@ enum Epilogue {
 
 constexpr int kBM = 128;
 constexpr int kStageA = kBM * 128;  // bytes
-constexpr int kGemmThreads = 320;
+// warp 0 producer, warp 1 MMA, then the epilogue warps: 8 for the plain store, 16 for the gate epilogues, whose
+// per-element arithmetic (sigmoid, products) is latency-bound with fewer warps per scheduler
+constexpr int gemm_epi_warps(int epi) { return epi == 0 ? 8 : 16; }
+constexpr int gemm_threads(int epi) { return 64 + 32 * gemm_epi_warps(epi); }
 
 struct GemmArgs {
   int M, N;                  // output extent of one batch entry
@@ -138,6 +141,15 @@ __device__ __forceinline__ void ld32x2_f(uint32_t t0, uint32_t t1, float (&a)[32
 #pragma unroll
   for (int i = 0; i < 32; ++i) { a[i] = __uint_as_float(ra[i]); b[i] = __uint_as_float(rb[i]); }
 }
+// two 16-column loads with one wait
+__device__ __forceinline__ void ld16x2_f(uint32_t t0, uint32_t t1, float (&a)[16], float (&b)[16]) {
+  uint32_t ra[16], rb[16];
+  tmem_ld_32x16(t0, ra);
+  tmem_ld_32x16(t1, rb);
+  tmem_ld_wait();
+#pragma unroll
+  for (int i = 0; i < 16; ++i) { a[i] = __uint_as_float(ra[i]); b[i] = __uint_as_float(rb[i]); }
+}
 __device__ __forceinline__ void ld32_f(uint32_t taddr, float (&v)[32]) {
   uint32_t r[32];
   tmem_ld_32x32(taddr, r);
@@ -147,7 +159,7 @@ __device__ __forceinline__ void ld32_f(uint32_t taddr, float (&v)[32]) {
 }
 
 template <typename TIN, typename TOUT, int BN, int EPI, int STAGES>
-__global__ void __launch_bounds__(kGemmThreads, 1)
+__global__ void __launch_bounds__(gemm_threads(EPI), 1)
 tc_gemm_kernel(const __grid_constant__ CUtensorMap tmA0, const __grid_constant__ CUtensorMap tmB0,
                const __grid_constant__ CUtensorMap tmA1, const __grid_constant__ CUtensorMap tmB1, const GemmArgs g) {
   constexpr int ES = sizeof(TIN);
@@ -174,7 +186,7 @@ tc_gemm_kernel(const __grid_constant__ CUtensorMap tmA0, const __grid_constant__
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   if (threadIdx.x == 0) {
     for (int s = 0; s < STAGES; ++s) { mbar_init(&full[s], 1); mbar_init(&empty[s], 1); }
-    for (int a = 0; a < 2; ++a) { mbar_init(&tfull[a], 1); mbar_init(&tempty[a], 8); }
+    for (int a = 0; a < 2; ++a) { mbar_init(&tfull[a], 1); mbar_init(&tempty[a], gemm_epi_warps(EPI)); }
     mbar_fence_init();
     tma_prefetch_desc(&tmA0);
     tma_prefetch_desc(&tmB0);
@@ -271,9 +283,11 @@ tc_gemm_kernel(const __grid_constant__ CUtensorMap tmA0, const __grid_constant__
     }
     __syncwarp();
   } else {
-    // ------------------------------------------------------------------ epilogue: 2 groups x 4 warps
+    // ------------------------------------------------------------------ epilogue: groups of 4 warps
     const int quarter = warp & 3;            // the TMEM lane quarter this warp may read
-    const int grp = (warp - 2) >> 2;         // column half this warp's group takes
+    const int grp = (warp - 2) >> 2;         // column share this warp's group takes (2 or 4 groups)
+    constexpr int NGRP = gemm_epi_warps(EPI) / 4;
+    constexpr int CPG = 4 / NGRP;            // gate epilogues: 32-pixel (or channel) chunks per group
     const int row = quarter * 32 + lane;
     int acc = 0;
     uint32_t acc_phase = 0;
@@ -281,19 +295,19 @@ tc_gemm_kernel(const __grid_constant__ CUtensorMap tmA0, const __grid_constant__
       int tm, tn, bz;
       decode(tile, tm, tn, bz);
       // the backward gate epilogues read a gradient tile from global memory: fetch it before waiting for the product
-      Raw8<TIN> dpre[2][4], mpre[2][4];
+      Raw8<TIN> dpre[CPG][4];
       if constexpr (EPI == EPI_GATE_IN_BWD) {
-        const TIN* mask = reinterpret_cast<const TIN*>(g.aux);
         const TIN* dplane = reinterpret_cast<const TIN*>(tm == 0 ? g.aux2 : g.aux3);
+        const long long t0 = (long long)tn * 128, tb0 = t0 / g.plane, tp0 = t0 - tb0 * g.plane;   // one division per tile
 #pragma unroll
-        for (int jj = 0; jj < 2; ++jj)
+        for (int jj = 0; jj < CPG; ++jj)
 #pragma unroll
           for (int u = 0; u < 4; ++u) {
-            const long long m8 = (long long)tn * 128 + (grp * 2 + jj) * 32 + u * 8;
-            if (m8 < g.N) {
-              const long long bb = m8 / g.plane, pix = m8 % g.plane;
+            const int off = (grp * CPG + jj) * 32 + u * 8;
+            if (t0 + off < g.N) {
+              long long bb = tb0, pix = tp0 + off;
+              while (pix >= g.plane) { pix -= g.plane; ++bb; }
               dpre[jj][u] = ldraw8<TIN>(dplane + (bb * 128 + row) * g.plane + pix);
-              if (mask != nullptr) mpre[jj][u] = ldraw8<TIN>(mask + m8);
             }
           }
       } else if constexpr (EPI == EPI_GATE_OUT_BWD) {
@@ -301,9 +315,9 @@ tc_gemm_kernel(const __grid_constant__ CUtensorMap tmA0, const __grid_constant__
         const TIN* dout = reinterpret_cast<const TIN*>(g.aux) + (long long)m * 128;
         if (m < g.M) {
 #pragma unroll
-          for (int jj = 0; jj < 2; ++jj)
+          for (int jj = 0; jj < CPG; ++jj)
 #pragma unroll
-            for (int u = 0; u < 4; ++u) dpre[jj][u] = ldraw8<TIN>(dout + (grp * 2 + jj) * 32 + u * 8);
+            for (int u = 0; u < 4; ++u) dpre[jj][u] = ldraw8<TIN>(dout + (grp * CPG + jj) * 32 + u * 8);
         }
       }
       if (!mbar_wait(&tfull[acc], acc_phase, g.err, 4)) break;
@@ -313,7 +327,7 @@ tc_gemm_kernel(const __grid_constant__ CUtensorMap tmA0, const __grid_constant__
         const int m = tm * kBM + row, n0 = tn * BN;
         TOUT* out = reinterpret_cast<TOUT*>(g.out0) + bz * g.batch_out + (long long)m * g.ld_out;
         const bool vec_ok = (g.ld_out * sizeof(TOUT)) % 16 == 0 && (g.batch_out * sizeof(TOUT)) % 16 == 0;
-        constexpr int CH = BN / 64;  // 32-column chunks per group
+        constexpr int CH = BN / 32 / NGRP;  // 32-column chunks per group
 #pragma unroll 1
         for (int jj = 0; jj < CH; ++jj) {
           const int j = grp * CH + jj;
@@ -329,46 +343,49 @@ tc_gemm_kernel(const __grid_constant__ CUtensorMap tmA0, const __grid_constant__
       } else if constexpr (EPI == EPI_GATE_IN || EPI == EPI_GATE_IN_BWD) {
         // row = channel of half tm; columns: P for pixels n0..n0+127, then G for the same pixels
         const long long n0 = (long long)tn * 128;
+        const long long nb0 = n0 / g.plane, np0 = n0 - nb0 * g.plane;   // one division per tile
         const TIN* mask = reinterpret_cast<const TIN*>(g.aux);
         float bp = 0.f, bg = 0.f;
         if (g.bias0 != nullptr) { bp = g.bias0[tm * 256 + row]; bg = g.bias0[tm * 256 + 128 + row]; }
 #pragma unroll
-        for (int jj = 0; jj < 2; ++jj) {
-          const int j = grp * 2 + jj;
-          float p[32], gt[32];
-          ld32x2_f(t_row + j * 32, t_row + 128 + j * 32, p, gt);
+        for (int jj = 0; jj < CPG; ++jj) {
+          const int j = grp * CPG + jj;
 #pragma unroll
-          for (int u = 0; u < 4; ++u) {
-            const long long m8 = n0 + j * 32 + u * 8;   // 8 pixels: same batch entry, all valid or none
-            if (m8 >= g.N) continue;
-            const long long bb = m8 / g.plane, pix = m8 % g.plane;
-            float mk[8];
-            if (mask != nullptr) {
-              if constexpr (EPI == EPI_GATE_IN_BWD) cvtraw8<TIN>(mpre[jj][u], mk);
-              else load8<TIN>(mask + m8, mk);
-            }
-            if constexpr (EPI == EPI_GATE_IN) {
-              float r[8];
+          for (int hf = 0; hf < 2; ++hf) {   // 16 pixels at a time keeps the registers of 576 threads within budget
+            float p[16], gt[16];
+            ld16x2_f(t_row + j * 32 + hf * 16, t_row + 128 + j * 32 + hf * 16, p, gt);
 #pragma unroll
-              for (int i = 0; i < 8; ++i) {
-                r[i] = (p[u * 8 + i] + bp) * fast_sigmoid(gt[u * 8 + i] + bg);
-                if (mask != nullptr) r[i] *= mk[i];
+            for (int uu = 0; uu < 2; ++uu) {
+              const int u = hf * 2 + uu;
+              const long long m8 = n0 + j * 32 + u * 8;   // 8 pixels: same batch entry, all valid or none
+              if (m8 >= g.N) continue;
+              long long bb = nb0, pix = np0 + j * 32 + u * 8;
+              while (pix >= g.plane) { pix -= g.plane; ++bb; }
+              float mk[8];
+              if (mask != nullptr) load8<TIN>(mask + m8, mk);
+              if constexpr (EPI == EPI_GATE_IN) {
+                float r[8];
+#pragma unroll
+                for (int i = 0; i < 8; ++i) {
+                  r[i] = (p[uu * 8 + i] + bp) * fast_sigmoid(gt[uu * 8 + i] + bg);
+                  if (mask != nullptr) r[i] *= mk[i];
+                }
+                TOUT* plane = reinterpret_cast<TOUT*>(tm == 0 ? g.out0 : g.out1);
+                store8<TOUT>(plane + (bb * 128 + row) * g.plane + pix, r);
+              } else {
+                float d[8], dp[8], dg[8];
+                cvtraw8<TIN>(dpre[jj][u], d);
+#pragma unroll
+                for (int i = 0; i < 8; ++i) {
+                  const float dd = mask != nullptr ? d[i] * mk[i] : d[i];
+                  const float sg = fast_sigmoid(gt[uu * 8 + i] + bg);
+                  dp[i] = dd * sg;
+                  dg[i] = dd * (p[uu * 8 + i] + bp) * sg * (1.0f - sg);
+                }
+                TOUT* o = reinterpret_cast<TOUT*>(g.out0);
+                store8<TOUT>(o + (long long)(tm * 256 + row) * g.ld_out + m8, dp);
+                store8<TOUT>(o + (long long)(tm * 256 + 128 + row) * g.ld_out + m8, dg);
               }
-              TOUT* plane = reinterpret_cast<TOUT*>(tm == 0 ? g.out0 : g.out1);
-              store8<TOUT>(plane + (bb * 128 + row) * g.plane + pix, r);
-            } else {
-              float d[8], dp[8], dg[8];
-              cvtraw8<TIN>(dpre[jj][u], d);
-#pragma unroll
-              for (int i = 0; i < 8; ++i) {
-                const float dd = mask != nullptr ? d[i] * mk[i] : d[i];
-                const float sg = fast_sigmoid(gt[u * 8 + i] + bg);
-                dp[i] = dd * sg;
-                dg[i] = dd * (p[u * 8 + i] + bp) * sg * (1.0f - sg);
-              }
-              TOUT* o = reinterpret_cast<TOUT*>(g.out0);
-              store8<TOUT>(o + (long long)(tm * 256 + row) * g.ld_out + m8, dp);
-              store8<TOUT>(o + (long long)(tm * 256 + 128 + row) * g.ld_out + m8, dg);
             }
           }
         }
@@ -378,30 +395,34 @@ tc_gemm_kernel(const __grid_constant__ CUtensorMap tmA0, const __grid_constant__
         TOUT* o0 = reinterpret_cast<TOUT*>(g.out0) + (long long)m * 128;
         TOUT* o1 = reinterpret_cast<TOUT*>(g.out1) + (long long)m * 128;
 #pragma unroll
-        for (int jj = 0; jj < 2; ++jj) {
-          const int j = grp * 2 + jj;
-          float y[32], gt[32];
-          ld32x2_f(t_row + j * 32, t_row + 128 + j * 32, y, gt);
-          if (m < g.M) {
+        for (int jj = 0; jj < CPG; ++jj) {
+          const int j = grp * CPG + jj;
 #pragma unroll
-            for (int u = 0; u < 4; ++u) {
-              float r0[8], r1[8], d[8];
-              if constexpr (EPI == EPI_GATE_OUT_BWD) cvtraw8<TIN>(dpre[jj][u], d);
+          for (int hf = 0; hf < 2; ++hf) {
+            float y[16], gt[16];
+            ld16x2_f(t_row + j * 32 + hf * 16, t_row + 128 + j * 32 + hf * 16, y, gt);
+            if (m < g.M) {
 #pragma unroll
-              for (int i = 0; i < 8; ++i) {
-                const int c = j * 32 + u * 8 + i;
-                float yv = y[u * 8 + i], gv = gt[u * 8 + i];
-                if (g.bias0 != nullptr) { yv += g.bias0[c]; gv += g.bias0[128 + c]; }
-                const float sg = fast_sigmoid(gv);
-                if constexpr (EPI == EPI_GATE_OUT) {
-                  r0[i] = yv * sg;
-                } else {
-                  r0[i] = d[i] * sg;
-                  r1[i] = d[i] * yv * sg * (1.0f - sg);
+              for (int uu = 0; uu < 2; ++uu) {
+                const int u = hf * 2 + uu;
+                float r0[8], r1[8], d[8];
+                if constexpr (EPI == EPI_GATE_OUT_BWD) cvtraw8<TIN>(dpre[jj][u], d);
+#pragma unroll
+                for (int i = 0; i < 8; ++i) {
+                  const int c = j * 32 + u * 8 + i;
+                  float yv = y[uu * 8 + i], gv = gt[uu * 8 + i];
+                  if (g.bias0 != nullptr) { yv += g.bias0[c]; gv += g.bias0[128 + c]; }
+                  const float sg = fast_sigmoid(gv);
+                  if constexpr (EPI == EPI_GATE_OUT) {
+                    r0[i] = yv * sg;
+                  } else {
+                    r0[i] = d[i] * sg;
+                    r1[i] = d[i] * yv * sg * (1.0f - sg);
+                  }
                 }
+                store8<TOUT>(o0 + j * 32 + u * 8, r0);
+                if constexpr (EPI == EPI_GATE_OUT_BWD) store8<TOUT>(o1 + j * 32 + u * 8, r1);
               }
-              store8<TOUT>(o0 + j * 32 + u * 8, r0);
-              if constexpr (EPI == EPI_GATE_OUT_BWD) store8<TOUT>(o1 + j * 32 + u * 8, r1);
             }
           }
         }
