@@ -120,9 +120,35 @@ template <typename T> __device__ __forceinline__ void cvtraw8(const Raw8<T>& r, 
   }
 }
 
+// 32-byte accesses (16 values of a 16-bit type) for the channel-major tensors of the transposed gate GEMMs: a lane
+// then reads or writes whole 32-byte sectors of its channel row instead of two half sectors in two requests.
+template <typename T> __device__ __forceinline__ void ldraw16(const T* p, Raw8<T>& lo, Raw8<T>& hi) {
+  static_assert(sizeof(T) == 2, "16-bit types");
+  asm volatile("ld.global.nc.v8.b32 {%0,%1,%2,%3,%4,%5,%6,%7}, [%8];"
+               : "=r"(lo.w[0].x), "=r"(lo.w[0].y), "=r"(lo.w[0].z), "=r"(lo.w[0].w), "=r"(hi.w[0].x), "=r"(hi.w[0].y),
+                 "=r"(hi.w[0].z), "=r"(hi.w[0].w)
+               : "l"(p));
+}
+template <typename T> __device__ __forceinline__ void store16(T* p, const float* v) {
+  static_assert(sizeof(T) == 2, "16-bit types");
+  union { uint4 u[2]; T h[16]; } pk;
+#pragma unroll
+  for (int i = 0; i < 16; ++i) pk.h[i] = from_f32<T>(v[i]);
+  asm volatile("st.global.v8.b32 [%0], {%1,%2,%3,%4,%5,%6,%7,%8};" ::"l"(p), "r"(pk.u[0].x), "r"(pk.u[0].y), "r"(pk.u[0].z),
+               "r"(pk.u[0].w), "r"(pk.u[1].x), "r"(pk.u[1].y), "r"(pk.u[1].z), "r"(pk.u[1].w)
+               : "memory");
+}
+
 template <typename TOUT>
 __device__ __forceinline__ void store_row32(TOUT* dst, const float (&v)[32], int valid, bool vec_ok) {
   if (valid >= 32 && vec_ok) {
+    if constexpr (sizeof(TOUT) == 2) {
+      if ((reinterpret_cast<uintptr_t>(dst) & 31) == 0) {   // whole 32-byte sectors per request
+        store16<TOUT>(dst, &v[0]);
+        store16<TOUT>(dst + 16, &v[16]);
+        return;
+      }
+    }
 #pragma unroll
     for (int i = 0; i < 4; ++i) store8<TOUT>(dst + 8 * i, &v[8 * i]);
   } else {
@@ -299,6 +325,7 @@ tc_gemm_kernel(const __grid_constant__ CUtensorMap tmA0, const __grid_constant__
       if constexpr (EPI == EPI_GATE_IN_BWD) {
         const TIN* dplane = reinterpret_cast<const TIN*>(tm == 0 ? g.aux2 : g.aux3);
         const long long t0 = (long long)tn * 128, tb0 = t0 / g.plane, tp0 = t0 - tb0 * g.plane;   // one division per tile
+        const bool wide = sizeof(TIN) == 2 && (g.plane & 15) == 0 && (g.N & 15) == 0;   // 16-pixel groups: aligned, never split
 #pragma unroll
         for (int jj = 0; jj < CPG; ++jj)
 #pragma unroll
@@ -307,7 +334,13 @@ tc_gemm_kernel(const __grid_constant__ CUtensorMap tmA0, const __grid_constant__
             if (t0 + off < g.N) {
               long long bb = tb0, pix = tp0 + off;
               while (pix >= g.plane) { pix -= g.plane; ++bb; }
-              dpre[jj][u] = ldraw8<TIN>(dplane + (bb * 128 + row) * g.plane + pix);
+              const TIN* src = dplane + (bb * 128 + row) * g.plane + pix;
+              if constexpr (sizeof(TIN) == 2) {
+                if (wide) { if ((u & 1) == 0) ldraw16<TIN>(src, dpre[jj][u], dpre[jj][u + 1]); }
+                else dpre[jj][u] = ldraw8<TIN>(src);
+              } else {
+                dpre[jj][u] = ldraw8<TIN>(src);
+              }
             }
           }
       } else if constexpr (EPI == EPI_GATE_OUT_BWD) {
@@ -317,7 +350,14 @@ tc_gemm_kernel(const __grid_constant__ CUtensorMap tmA0, const __grid_constant__
 #pragma unroll
           for (int jj = 0; jj < CPG; ++jj)
 #pragma unroll
-            for (int u = 0; u < 4; ++u) dpre[jj][u] = ldraw8<TIN>(dout + (grp * CPG + jj) * 32 + u * 8);
+            for (int u = 0; u < 4; u += 2) {
+              if constexpr (sizeof(TIN) == 2) {   // rows of 256 bytes: 32-byte loads are aligned
+                ldraw16<TIN>(dout + (grp * CPG + jj) * 32 + u * 8, dpre[jj][u], dpre[jj][u + 1]);
+              } else {
+                dpre[jj][u] = ldraw8<TIN>(dout + (grp * CPG + jj) * 32 + u * 8);
+                dpre[jj][u + 1] = ldraw8<TIN>(dout + (grp * CPG + jj) * 32 + u * 8 + 8);
+              }
+            }
         }
       }
       if (!mbar_wait(&tfull[acc], acc_phase, g.err, 4)) break;
@@ -344,6 +384,7 @@ tc_gemm_kernel(const __grid_constant__ CUtensorMap tmA0, const __grid_constant__
         // row = channel of half tm; columns: P for pixels n0..n0+127, then G for the same pixels
         const long long n0 = (long long)tn * 128;
         const long long nb0 = n0 / g.plane, np0 = n0 - nb0 * g.plane;   // one division per tile
+        const bool wide16 = sizeof(TOUT) == 2 && (g.plane & 15) == 0 && (g.N & 15) == 0 && (g.ld_out & 15) == 0;
         const TIN* mask = reinterpret_cast<const TIN*>(g.aux);
         float bp = 0.f, bg = 0.f;
         if (g.bias0 != nullptr) { bp = g.bias0[tm * 256 + row]; bg = g.bias0[tm * 256 + 128 + row]; }
@@ -354,6 +395,8 @@ tc_gemm_kernel(const __grid_constant__ CUtensorMap tmA0, const __grid_constant__
           for (int hf = 0; hf < 2; ++hf) {   // 16 pixels at a time keeps the registers of 576 threads within budget
             float p[16], gt[16];
             ld16x2_f(t_row + j * 32 + hf * 16, t_row + 128 + j * 32 + hf * 16, p, gt);
+            float o0[16], o1[16];   // GATE_IN: gated value; GATE_IN_BWD: dP and dG
+            long long bb16 = 0, pix16 = 0;
 #pragma unroll
             for (int uu = 0; uu < 2; ++uu) {
               const int u = hf * 2 + uu;
@@ -361,30 +404,47 @@ tc_gemm_kernel(const __grid_constant__ CUtensorMap tmA0, const __grid_constant__
               if (m8 >= g.N) continue;
               long long bb = nb0, pix = np0 + j * 32 + u * 8;
               while (pix >= g.plane) { pix -= g.plane; ++bb; }
+              if (uu == 0) { bb16 = bb; pix16 = pix; }
               float mk[8];
               if (mask != nullptr) load8<TIN>(mask + m8, mk);
               if constexpr (EPI == EPI_GATE_IN) {
-                float r[8];
 #pragma unroll
                 for (int i = 0; i < 8; ++i) {
-                  r[i] = (p[uu * 8 + i] + bp) * fast_sigmoid(gt[uu * 8 + i] + bg);
-                  if (mask != nullptr) r[i] *= mk[i];
+                  o0[uu * 8 + i] = (p[uu * 8 + i] + bp) * fast_sigmoid(gt[uu * 8 + i] + bg);
+                  if (mask != nullptr) o0[uu * 8 + i] *= mk[i];
                 }
-                TOUT* plane = reinterpret_cast<TOUT*>(tm == 0 ? g.out0 : g.out1);
-                store8<TOUT>(plane + (bb * 128 + row) * g.plane + pix, r);
+                if (!wide16) {
+                  TOUT* plane = reinterpret_cast<TOUT*>(tm == 0 ? g.out0 : g.out1);
+                  store8<TOUT>(plane + (bb * 128 + row) * g.plane + pix, &o0[uu * 8]);
+                }
               } else {
-                float d[8], dp[8], dg[8];
+                float d[8];
                 cvtraw8<TIN>(dpre[jj][u], d);
 #pragma unroll
                 for (int i = 0; i < 8; ++i) {
                   const float dd = mask != nullptr ? d[i] * mk[i] : d[i];
                   const float sg = fast_sigmoid(gt[uu * 8 + i] + bg);
-                  dp[i] = dd * sg;
-                  dg[i] = dd * (p[uu * 8 + i] + bp) * sg * (1.0f - sg);
+                  o0[uu * 8 + i] = dd * sg;
+                  o1[uu * 8 + i] = dd * (p[uu * 8 + i] + bp) * sg * (1.0f - sg);
                 }
-                TOUT* o = reinterpret_cast<TOUT*>(g.out0);
-                store8<TOUT>(o + (long long)(tm * 256 + row) * g.ld_out + m8, dp);
-                store8<TOUT>(o + (long long)(tm * 256 + 128 + row) * g.ld_out + m8, dg);
+                if (!wide16) {
+                  TOUT* o = reinterpret_cast<TOUT*>(g.out0);
+                  store8<TOUT>(o + (long long)(tm * 256 + row) * g.ld_out + m8, &o0[uu * 8]);
+                  store8<TOUT>(o + (long long)(tm * 256 + 128 + row) * g.ld_out + m8, &o1[uu * 8]);
+                }
+              }
+            }
+            if constexpr (sizeof(TOUT) == 2) {
+              const long long m16 = n0 + j * 32 + hf * 16;
+              if (wide16 && m16 < g.N) {   // one 32-byte store per output row
+                if constexpr (EPI == EPI_GATE_IN) {
+                  TOUT* plane = reinterpret_cast<TOUT*>(tm == 0 ? g.out0 : g.out1);
+                  store16<TOUT>(plane + (bb16 * 128 + row) * g.plane + pix16, o0);
+                } else {
+                  TOUT* o = reinterpret_cast<TOUT*>(g.out0);
+                  store16<TOUT>(o + (long long)(tm * 256 + row) * g.ld_out + m16, o0);
+                  store16<TOUT>(o + (long long)(tm * 256 + 128 + row) * g.ld_out + m16, o1);
+                }
               }
             }
           }
@@ -402,10 +462,11 @@ tc_gemm_kernel(const __grid_constant__ CUtensorMap tmA0, const __grid_constant__
             float y[16], gt[16];
             ld16x2_f(t_row + j * 32 + hf * 16, t_row + 128 + j * 32 + hf * 16, y, gt);
             if (m < g.M) {
+              float r0[16], r1[16];
 #pragma unroll
               for (int uu = 0; uu < 2; ++uu) {
                 const int u = hf * 2 + uu;
-                float r0[8], r1[8], d[8];
+                float d[8];
                 if constexpr (EPI == EPI_GATE_OUT_BWD) cvtraw8<TIN>(dpre[jj][u], d);
 #pragma unroll
                 for (int i = 0; i < 8; ++i) {
@@ -414,14 +475,24 @@ tc_gemm_kernel(const __grid_constant__ CUtensorMap tmA0, const __grid_constant__
                   if (g.bias0 != nullptr) { yv += g.bias0[c]; gv += g.bias0[128 + c]; }
                   const float sg = fast_sigmoid(gv);
                   if constexpr (EPI == EPI_GATE_OUT) {
-                    r0[i] = yv * sg;
+                    r0[uu * 8 + i] = yv * sg;
                   } else {
-                    r0[i] = d[i] * sg;
-                    r1[i] = d[i] * yv * sg * (1.0f - sg);
+                    r0[uu * 8 + i] = d[i] * sg;
+                    r1[uu * 8 + i] = d[i] * yv * sg * (1.0f - sg);
                   }
                 }
-                store8<TOUT>(o0 + j * 32 + u * 8, r0);
-                if constexpr (EPI == EPI_GATE_OUT_BWD) store8<TOUT>(o1 + j * 32 + u * 8, r1);
+              }
+              // 16 channels of this pixel: one 32-byte store for 16-bit outputs (rows are 256 bytes, so it is aligned)
+              if constexpr (sizeof(TOUT) == 2) {
+                store16<TOUT>(o0 + j * 32 + hf * 16, r0);
+                if constexpr (EPI == EPI_GATE_OUT_BWD) store16<TOUT>(o1 + j * 32 + hf * 16, r1);
+              } else {
+                store8<TOUT>(o0 + j * 32 + hf * 16, r0);
+                store8<TOUT>(o0 + j * 32 + hf * 16 + 8, r0 + 8);
+                if constexpr (EPI == EPI_GATE_OUT_BWD) {
+                  store8<TOUT>(o1 + j * 32 + hf * 16, r1);
+                  store8<TOUT>(o1 + j * 32 + hf * 16 + 8, r1 + 8);
+                }
               }
             }
           }

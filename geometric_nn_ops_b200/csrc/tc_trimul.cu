@@ -85,76 +85,6 @@ __global__ void prep_weights_kernel(const T* wp, const T* wg, const T* bp, const
 // ---------------------------------------------------------------------------------------------
 // LayerNorm over pixel-major rows (x -> z)
 // ---------------------------------------------------------------------------------------------
-template <typename T>
-__global__ void __launch_bounds__(256) ln_rows_kernel(const T* x, const T* gamma, const T* beta, float eps,
-                                                       long long M, T* z, float* mean, float* rstd) {
-  const int lane = threadIdx.x & 31;
-  const long long row = blockIdx.x * 8LL + (threadIdx.x >> 5);
-  if (row >= M) return;
-  float v[4];
-  load4(x + row * CW + lane * 4, v);
-  const float mu = warp_sum(v[0] + v[1] + v[2] + v[3]) * (1.0f / CW);
-  float q = 0.f;
-#pragma unroll
-  for (int i = 0; i < 4; ++i) { v[i] -= mu; q += v[i] * v[i]; }
-  const float rs = 1.0f / sqrtf(warp_sum(q) * (1.0f / CW) + eps);
-  float gm[4] = {1.f, 1.f, 1.f, 1.f}, bt[4] = {0.f, 0.f, 0.f, 0.f};
-  if (gamma) load4(gamma + lane * 4, gm);
-  if (beta) load4(beta + lane * 4, bt);
-#pragma unroll
-  for (int i = 0; i < 4; ++i) v[i] = v[i] * rs * gm[i] + bt[i];
-  store4(z + row * CW + lane * 4, v);
-  if (lane == 0) { mean[row] = mu; rstd[row] = rs; }
-}
-
-// dx = rstd * (dhat - mean(dhat) - xhat * mean(dhat*xhat)); per-block partial dgamma / dbeta
-template <typename T>
-__global__ void __launch_bounds__(256) ln_rows_bwd_kernel(const T* dz, const T* x, const float* mean,
-                                                           const float* rstd, const T* gamma, long long M, T* dx,
-                                                           float* pg, float* pb) {
-  __shared__ float sg[8][CW], sb[8][CW];
-  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
-  float gm[4] = {1.f, 1.f, 1.f, 1.f};
-  if (gamma) load4(gamma + lane * 4, gm);
-  float ag[4] = {}, ab[4] = {};
-  for (long long row = blockIdx.x * 8LL + warp; row < M; row += gridDim.x * 8LL) {
-    float xv[4], dv[4];
-    load4(x + row * CW + lane * 4, xv);
-    load4(dz + row * CW + lane * 4, dv);
-    const float mu = mean[row], rs = rstd[row];
-    float s1 = 0.f, s2 = 0.f, dh[4];
-#pragma unroll
-    for (int i = 0; i < 4; ++i) {
-      xv[i] = (xv[i] - mu) * rs;
-      dh[i] = dv[i] * gm[i];
-      s1 += dh[i];
-      s2 += dh[i] * xv[i];
-      ag[i] += dv[i] * xv[i];
-      ab[i] += dv[i];
-    }
-    s1 = warp_sum(s1) * (1.0f / CW);
-    s2 = warp_sum(s2) * (1.0f / CW);
-#pragma unroll
-    for (int i = 0; i < 4; ++i) dh[i] = rs * (dh[i] - s1 - xv[i] * s2);
-    store4(dx + row * CW + lane * 4, dh);
-  }
-#pragma unroll
-  for (int i = 0; i < 4; ++i) { sg[warp][lane * 4 + i] = ag[i]; sb[warp][lane * 4 + i] = ab[i]; }
-  __syncthreads();
-  if (threadIdx.x < CW) {
-    float g = 0.f, b = 0.f;
-#pragma unroll
-    for (int w = 0; w < 8; ++w) { g += sg[w][threadIdx.x]; b += sb[w][threadIdx.x]; }
-    pg[blockIdx.x * CW + threadIdx.x] = g;
-    pb[blockIdx.x * CW + threadIdx.x] = b;
-  }
-}
-
-// ---------------------------------------------------------------------------------------------
-// LayerNorm over channels of a channel-major tensor (t -> u pixel-major), and its backward (du -> dt)
-// ---------------------------------------------------------------------------------------------
-constexpr int TP = 64;  // pixels per tile
-
 template <typename T> __device__ __forceinline__ void load8v(const T* p, float (&v)[8]) {
   if constexpr (sizeof(T) == 4) {
     const float4 a = reinterpret_cast<const float4*>(p)[0], b = reinterpret_cast<const float4*>(p)[1];
@@ -178,16 +108,136 @@ template <typename T> __device__ __forceinline__ void store8v(T* p, const float 
   }
 }
 
+// A row of 128 channels is held by 16 lanes (8 channels, one 16-byte access each), so a warp covers two rows per
+// access and keeps several row pairs in flight: with one 8-byte access per thread these kernels were bound by
+// load latency (3.0 of 6.6 TB/s).
+__device__ __forceinline__ float half_warp_sum(float v) {
+#pragma unroll
+  for (int o = 8; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+  return v;
+}
+constexpr int kLnRowPairs = 4;   // row pairs per warp and pass (8 rows)
+
+template <typename T>
+__global__ void __launch_bounds__(256) ln_rows_kernel(const T* __restrict__ x, const T* gamma, const T* beta, float eps,
+                                                       long long M, T* __restrict__ z, float* mean, float* rstd) {
+  const int lane = threadIdx.x & 31, sub = lane & 15, half = lane >> 4;
+  const long long row0 = (blockIdx.x * 8LL + (threadIdx.x >> 5)) * (2 * kLnRowPairs) + half;
+  float gm[8], bt[8];
+#pragma unroll
+  for (int i = 0; i < 8; ++i) { gm[i] = 1.f; bt[i] = 0.f; }
+  if (gamma) load8v(gamma + sub * 8, gm);
+  if (beta) load8v(beta + sub * 8, bt);
+  float v[kLnRowPairs][8];
+#pragma unroll
+  for (int p = 0; p < kLnRowPairs; ++p) {
+    const long long row = row0 + 2 * p;
+    if (row < M) load8v(x + row * CW + sub * 8, v[p]);
+    else {
+#pragma unroll
+      for (int i = 0; i < 8; ++i) v[p][i] = 0.f;
+    }
+  }
+#pragma unroll
+  for (int p = 0; p < kLnRowPairs; ++p) {
+    const long long row = row0 + 2 * p;
+    float sm = 0.f;
+#pragma unroll
+    for (int i = 0; i < 8; ++i) sm += v[p][i];
+    const float mu = half_warp_sum(sm) * (1.0f / CW);
+    float q = 0.f;
+#pragma unroll
+    for (int i = 0; i < 8; ++i) { v[p][i] -= mu; q += v[p][i] * v[p][i]; }
+    const float rs = 1.0f / sqrtf(half_warp_sum(q) * (1.0f / CW) + eps);
+#pragma unroll
+    for (int i = 0; i < 8; ++i) v[p][i] = v[p][i] * rs * gm[i] + bt[i];
+    if (row < M) {
+      store8v(z + row * CW + sub * 8, v[p]);
+      if (sub == 0) { mean[row] = mu; rstd[row] = rs; }
+    }
+  }
+}
+
+// dx = rstd * (dhat - mean(dhat) - xhat * mean(dhat*xhat)); per-block partial dgamma / dbeta
+template <typename T>
+__global__ void __launch_bounds__(256, 4) ln_rows_bwd_kernel(const T* __restrict__ dz, const T* __restrict__ x,
+                                                           const float* __restrict__ mean, const float* __restrict__ rstd,
+                                                           const T* gamma, long long M, T* __restrict__ dx, float* pg,
+                                                           float* pb) {
+  __shared__ float sg[16][CW], sb[16][CW];
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, sub = lane & 15, half = lane >> 4;
+  constexpr int RP = 1;   // row pairs per warp and pass (more would cost the registers of a fourth resident block)
+  float gm[8];
+#pragma unroll
+  for (int i = 0; i < 8; ++i) gm[i] = 1.f;
+  if (gamma) load8v(gamma + sub * 8, gm);
+  float ag[8] = {}, ab[8] = {};
+  for (long long base = (blockIdx.x * 8LL + warp) * (2 * RP); base < M; base += gridDim.x * 8LL * (2 * RP)) {
+    float xv[RP][8], dv[RP][8], mu[RP], rs[RP];
+#pragma unroll
+    for (int p = 0; p < RP; ++p) {
+      const long long row = base + 2 * p + half;
+      if (row < M) {
+        load8v(x + row * CW + sub * 8, xv[p]);
+        load8v(dz + row * CW + sub * 8, dv[p]);
+        mu[p] = mean[row]; rs[p] = rstd[row];
+      } else {
+#pragma unroll
+        for (int i = 0; i < 8; ++i) { xv[p][i] = 0.f; dv[p][i] = 0.f; }
+        mu[p] = 0.f; rs[p] = 0.f;
+      }
+    }
+#pragma unroll
+    for (int p = 0; p < RP; ++p) {
+      const long long row = base + 2 * p + half;
+      float s1 = 0.f, s2 = 0.f, dh[8];
+#pragma unroll
+      for (int i = 0; i < 8; ++i) {
+        xv[p][i] = (xv[p][i] - mu[p]) * rs[p];
+        dh[i] = dv[p][i] * gm[i];
+        s1 += dh[i];
+        s2 += dh[i] * xv[p][i];
+        ag[i] += dv[p][i] * xv[p][i];
+        ab[i] += dv[p][i];
+      }
+      s1 = half_warp_sum(s1) * (1.0f / CW);
+      s2 = half_warp_sum(s2) * (1.0f / CW);
+#pragma unroll
+      for (int i = 0; i < 8; ++i) dh[i] = rs[p] * (dh[i] - s1 - xv[p][i] * s2);
+      if (row < M) store8v(dx + row * CW + sub * 8, dh);
+    }
+  }
+#pragma unroll
+  for (int i = 0; i < 8; ++i) { sg[warp * 2 + half][sub * 8 + i] = ag[i]; sb[warp * 2 + half][sub * 8 + i] = ab[i]; }
+  __syncthreads();
+  if (threadIdx.x < CW) {
+    float g = 0.f, b = 0.f;
+#pragma unroll
+    for (int w = 0; w < 16; ++w) { g += sg[w][threadIdx.x]; b += sb[w][threadIdx.x]; }
+    pg[blockIdx.x * CW + threadIdx.x] = g;
+    pb[blockIdx.x * CW + threadIdx.x] = b;
+  }
+}
+
+// ---------------------------------------------------------------------------------------------
+// LayerNorm over channels of a channel-major tensor (t -> u pixel-major), and its backward (du -> dt)
+// ---------------------------------------------------------------------------------------------
+constexpr int TP = 64;  // pixels per tile
+
+
 // 64 pixels x 128 channels of a channel-major tensor -> smem tile[c][pixel] (fp32), 8 pixels per access.
 // The plane size is a multiple of 8 pixels, so a group of 8 never straddles two batch entries.
 template <typename T>
 __device__ __forceinline__ void load_cm_tile(float (*tile)[TP + 1], const T* src, long long m0, long long M,
                                              long long NN) {
+  const long long b0 = m0 / NN, p0 = m0 - b0 * NN;   // one division per tile, not one per access
   for (int item = threadIdx.x; item < CW * (TP / 8); item += 256) {
     const int c = item >> 3, pg = item & 7;
     const long long m = m0 + pg * 8;
+    long long bb = b0, pix = p0 + pg * 8;
+    while (pix >= NN) { pix -= NN; ++bb; }
     float v[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
-    if (m < M) load8v<T>(src + ((m / NN) * CW + c) * NN + (m % NN), v);
+    if (m < M) load8v<T>(src + (bb * CW + c) * NN + pix, v);
 #pragma unroll
     for (int e = 0; e < 8; ++e) tile[c][pg * 8 + e] = v[e];
   }
@@ -195,14 +245,17 @@ __device__ __forceinline__ void load_cm_tile(float (*tile)[TP + 1], const T* src
 template <typename T>
 __device__ __forceinline__ void store_cm_tile(const float (*tile)[TP + 1], T* dst, long long m0, long long M,
                                               long long NN) {
+  const long long b0 = m0 / NN, p0 = m0 - b0 * NN;
   for (int item = threadIdx.x; item < CW * (TP / 8); item += 256) {
     const int c = item >> 3, pg = item & 7;
     const long long m = m0 + pg * 8;
     if (m >= M) continue;
+    long long bb = b0, pix = p0 + pg * 8;
+    while (pix >= NN) { pix -= NN; ++bb; }
     float v[8];
 #pragma unroll
     for (int e = 0; e < 8; ++e) v[e] = tile[c][pg * 8 + e];
-    store8v<T>(dst + ((m / NN) * CW + c) * NN + (m % NN), v);
+    store8v<T>(dst + (bb * CW + c) * NN + pix, v);
   }
 }
 
@@ -435,7 +488,7 @@ int phase_project(cudaStream_t st, const Geom& gm, const void* x, const void* ma
   const long long M = gm.M;
   {
     KernelTimer kt("tc_ln_rows", st, 0.0, 2.0 * gm.unit());
-    ln_rows_kernel<T><<<cdiv(M, 8), 256, 0, st>>>((const T*)x, (const T*)w->norm_in_w, (const T*)w->norm_in_b, gm.eps,
+    ln_rows_kernel<T><<<cdiv(M, 8 * 2 * kLnRowPairs), 256, 0, st>>>((const T*)x, (const T*)w->norm_in_w, (const T*)w->norm_in_b, gm.eps,
                                                   M, (T*)z, mean_in, rstd_in);
     TRI_LAUNCH_OK();
   }
