@@ -399,6 +399,14 @@ def main():
         roofline = {"kernel": name, "bound": "tensor" if tensor_bound else "hbm", "achieved": ach, "peak": peak,
                     "unit": unit, "frac": ach / peak, "traffic": traffic, "peak_source": f"of {pk_kind}",
                     "launches": cnt, "avg_launch_ms": tot_ms / cnt, "share_of_step": tot_ms / prof_steps / ms}
+        if name.startswith("tc_attn_") and name != "tc_attn_delta":
+            # The attention passes are bound by neither HBM nor the tensor core but by the exponential (MUFU) pipe:
+            # one ex2 per (row, head, query, key) per pass, 16 per clock per SM.
+            sm_mhz = clocks.summary().get("sm_mhz") or 1965
+            exps = float(n) ** 3 * HEADS / world
+            peak_exp = 16.0 * 148 * sm_mhz * 1e6
+            roofline["exp_pipe"] = {"exponentials_per_launch": exps, "achieved_per_s": exps / (sec / cnt),
+                                    "peak_per_s": peak_exp, "frac": exps / (sec / cnt) / peak_exp}
     kernels = {k_: {"launches": v_[0], "ms_per_step": v_[1] / prof_steps} for k_, v_ in
                sorted(prof.items(), key=lambda kv: -kv[1][1])}
     cpu, _ = cpu_reference(1, 1) if world == 1 and not args.quick else (None, None)
