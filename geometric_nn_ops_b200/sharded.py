@@ -70,70 +70,36 @@ def shard_rows(n, rank, world):
 # ---------------------------------------------------------------------------------------------------
 # exchanges (plain torch + one collective each; differentiable where a caller needs it)
 # ---------------------------------------------------------------------------------------------------
-def _peer(group, w):
-    return w if group is None else dist.get_global_rank(group, w)
-
-
-def _exchange(ops):
-    for work in dist.batch_isend_irecv(ops):
-        work.wait()
-
-
 def rows_to_channels(t, group=None):
-    """``[L, Ch, R, N]`` (all channels, this rank's R rows) -> ``[L, Ch/P, P*R, N]`` (this rank's channels, all rows).
-
-    One message per (tensor, peer, channel), received straight into its rows of the result, so neither side
-    repacks anything: the per-peer slabs are contiguous on the sending side and each channel's ``R x N``
-    block is contiguous on the receiving side.  The messages of one call travel as one NCCL group.
-    """
-    world, me = _world(group)
+    """``[L, Ch, R, N]`` (all channels, this rank's R rows) -> ``[L, Ch/P, P*R, N]`` (this rank's channels, all rows)."""
+    world, _ = _world(group)
     L, Ch, R, N = t.shape
     if Ch % world != 0:
         raise ValueError(f"{Ch} channels are not divisible by {world} ranks")
     cs = Ch // world
-    t = t.contiguous()
-    out = torch.empty(L, cs, world * R, N, dtype=t.dtype, device=t.device)
-    with _timed("rows_to_channels.local"):
-        out[:, :, me * R:(me + 1) * R].copy_(t[:, me * cs:(me + 1) * cs])
-    ops = []
-    for w in range(world):
-        if w == me:
-            continue
-        peer = _peer(group, w)
-        for l in range(L):
-            for c in range(cs):
-                ops.append(dist.P2POp(dist.isend, t[l, w * cs + c], peer, group))
-                ops.append(dist.P2POp(dist.irecv, out[l, c, w * R:(w + 1) * R], peer, group))
-    with _timed("rows_to_channels.exchange"):
-        if ops:
-            _exchange(ops)
-    return out
+    with _timed("rows_to_channels.pack"):
+        send = t.reshape(L, world, cs, R * N).permute(1, 0, 2, 3).contiguous()
+        recv = torch.empty_like(send)
+    with _timed("rows_to_channels.all_to_all"):
+        dist.all_to_all_single(recv, send, group=group)
+    with _timed("rows_to_channels.unpack"):
+        return recv.reshape(world, L, cs, R, N).permute(1, 2, 0, 3, 4).reshape(L, cs, world * R, N)
 
 
 def channels_to_rows(t, group=None):
-    """Inverse of :func:`rows_to_channels`: ``[L, Ch/P, N_rows, N]`` -> ``[L, Ch, N_rows/P, N]`` (same message scheme)."""
-    world, me = _world(group)
+    """Inverse of :func:`rows_to_channels`: ``[L, Ch/P, N_rows, N]`` -> ``[L, Ch, N_rows/P, N]``."""
+    world, _ = _world(group)
     L, cs, rows, N = t.shape
     if rows % world != 0:
         raise ValueError(f"{rows} rows are not divisible by {world} ranks")
     R = rows // world
-    t = t.contiguous()
-    out = torch.empty(L, world * cs, R, N, dtype=t.dtype, device=t.device)
-    with _timed("channels_to_rows.local"):
-        out[:, me * cs:(me + 1) * cs].copy_(t[:, :, me * R:(me + 1) * R])
-    ops = []
-    for w in range(world):
-        if w == me:
-            continue
-        peer = _peer(group, w)
-        for l in range(L):
-            for c in range(cs):
-                ops.append(dist.P2POp(dist.isend, t[l, c, w * R:(w + 1) * R], peer, group))
-                ops.append(dist.P2POp(dist.irecv, out[l, w * cs + c], peer, group))
-    with _timed("channels_to_rows.exchange"):
-        if ops:
-            _exchange(ops)
-    return out
+    with _timed("channels_to_rows.pack"):
+        send = t.reshape(L, cs, world, R * N).permute(2, 0, 1, 3).contiguous()
+        recv = torch.empty_like(send)
+    with _timed("channels_to_rows.all_to_all"):
+        dist.all_to_all_single(recv, send, group=group)
+    with _timed("channels_to_rows.unpack"):
+        return recv.permute(1, 0, 2, 3).reshape(L, world * cs, R, N)
 
 
 class _Transpose(torch.autograd.Function):
