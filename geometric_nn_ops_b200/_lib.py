@@ -97,6 +97,8 @@ EXPORTS = {
     "tri_mul_shard_phase": (c_int, [POINTER(TriMulShardDesc), c_int, POINTER(TriMulShardBufs), c_void_p, c_size_t,
                                     c_void_p]),
     "tri_bgemm": (c_int, [POINTER(TriGemmDesc), c_void_p, c_void_p, c_void_p, c_void_p, c_size_t, c_void_p]),
+    "tri_permute_runs": (c_int, [c_void_p, c_void_p, POINTER(ctypes.c_int64 * 3), POINTER(ctypes.c_int32 * 3),
+                                 ctypes.c_int64, c_void_p]),
     "tri_ws_status": (c_int, [c_void_p, c_void_p]),
 }
 

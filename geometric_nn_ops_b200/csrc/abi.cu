@@ -235,6 +235,49 @@ int tri_mul_shard_phase(const TriMulShardDesc* d, int phase, const TriMulShardBu
   return tc::mul_shard_phase(d, phase, bufs, ws, ws_bytes, (cudaStream_t)stream);
 }
 
+// one block row per (outer index, slice of the run): 16-byte copies, source and destination both contiguous per run
+static __global__ void permute_runs_kernel(const uint4* __restrict__ src, uint4* __restrict__ dst, long long d0, long long d1,
+                                    long long d2, int p0, int p1, int p2, long long run_v) {
+  const long long outer = blockIdx.y;   // destination outer index, dimensions (d[p0], d[p1], d[p2])
+  const long long dd[3] = {d0, d1, d2};
+  const long long e2 = dd[p2], e1 = dd[p1];
+  long long idx[3];
+  idx[p2] = outer % e2;
+  idx[p1] = (outer / e2) % e1;
+  idx[p0] = outer / (e2 * e1);
+  const uint4* s = src + ((idx[0] * d1 + idx[1]) * d2 + idx[2]) * run_v;
+  uint4* d = dst + outer * run_v;
+  const long long stride = (long long)gridDim.x * blockDim.x;
+  long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x;
+  for (; i + 3 * stride < run_v; i += 4 * stride) {   // four loads in flight per thread
+    const uint4 a = __ldg(s + i), b = __ldg(s + i + stride), c = __ldg(s + i + 2 * stride), e = __ldg(s + i + 3 * stride);
+    d[i] = a; d[i + stride] = b; d[i + 2 * stride] = c; d[i + 3 * stride] = e;
+  }
+  for (; i < run_v; i += stride) d[i] = __ldg(s + i);
+}
+
+int tri_permute_runs(const void* src, void* dst, const int64_t dims[3], const int32_t perm[3], int64_t run_bytes,
+                     tri_stream_t stream) {
+  if (src == nullptr || dst == nullptr) return fail(TRI_ERR_ARG, "tri_permute_runs: null pointer");
+  if (run_bytes <= 0 || run_bytes % 16 != 0 || ((uintptr_t)src & 15) || ((uintptr_t)dst & 15))
+    return fail(TRI_ERR_ARG, "tri_permute_runs: runs must be 16-byte aligned multiples of 16 bytes");
+  int seen = 0;
+  for (int i = 0; i < 3; ++i) {
+    if (perm[i] < 0 || perm[i] > 2 || dims[i] <= 0) return fail(TRI_ERR_ARG, "tri_permute_runs: bad permutation or extent");
+    seen |= 1 << perm[i];
+  }
+  if (seen != 7) return fail(TRI_ERR_ARG, "tri_permute_runs: perm is not a permutation");
+  const long long outer = dims[0] * dims[1] * dims[2];
+  if (outer > 65535) return fail(TRI_ERR_ARG, "tri_permute_runs: more than 65535 runs");
+  const long long run_v = run_bytes / 16;
+  const int bx = (int)std::max<long long>(1, std::min<long long>(32, (run_v + 2047) / 2048));
+  KernelTimer kt("tri_permute_runs", (cudaStream_t)stream, 0.0, 2.0 * outer * run_bytes);
+  permute_runs_kernel<<<dim3(bx, (unsigned)outer), 256, 0, (cudaStream_t)stream>>>(
+      static_cast<const uint4*>(src), static_cast<uint4*>(dst), dims[0], dims[1], dims[2], perm[0], perm[1], perm[2], run_v);
+  TRI_LAUNCH_OK();
+  return 0;
+}
+
 int tri_ws_status(const void* ws, tri_stream_t stream) {
   if (ws == nullptr) return fail(TRI_ERR_ARG, "ws is null");
   int code = 0;

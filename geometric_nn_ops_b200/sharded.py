@@ -70,6 +70,26 @@ def shard_rows(n, rank, world):
 # ---------------------------------------------------------------------------------------------------
 # exchanges (plain torch + one collective each; differentiable where a caller needs it)
 # ---------------------------------------------------------------------------------------------------
+def _permute_runs(t, dims, perm, run):
+    """``t`` viewed as ``[*dims, run]`` -> a new contiguous tensor ``[dims[perm[0]], dims[perm[1]], dims[perm[2]], run]``.
+
+    On CUDA this is one launch of the library's run-copy kernel (HBM-bound); torch's ``permute().contiguous()``
+    reached a quarter of that on these shapes.  CPU tensors (the gloo tests) take the torch route.
+    """
+    out_dims = [dims[p] for p in perm]
+    if not t.is_cuda:
+        return t.reshape(*dims, run).permute(*perm, 3).contiguous()
+    t = t.contiguous()
+    out = torch.empty(*out_dims, run, dtype=t.dtype, device=t.device)
+    lib = _lib.load()
+    d = (ctypes.c_int64 * 3)(*dims)
+    pm = (ctypes.c_int32 * 3)(*perm)
+    stream = ctypes.c_void_p(torch.cuda.current_stream(t.device).cuda_stream)
+    _lib.check(lib.tri_permute_runs(ctypes.c_void_p(t.data_ptr()), ctypes.c_void_p(out.data_ptr()), ctypes.byref(d),
+                                    ctypes.byref(pm), run * t.element_size(), stream), "tri_permute_runs")
+    return out
+
+
 def rows_to_channels(t, group=None):
     """``[L, Ch, R, N]`` (all channels, this rank's R rows) -> ``[L, Ch/P, P*R, N]`` (this rank's channels, all rows)."""
     world, _ = _world(group)
@@ -78,12 +98,12 @@ def rows_to_channels(t, group=None):
         raise ValueError(f"{Ch} channels are not divisible by {world} ranks")
     cs = Ch // world
     with _timed("rows_to_channels.pack"):
-        send = t.reshape(L, world, cs, R * N).permute(1, 0, 2, 3).contiguous()
+        send = _permute_runs(t, (L, world, 1), (1, 0, 2), cs * R * N)       # [world, L, cs*R*N]
         recv = torch.empty_like(send)
     with _timed("rows_to_channels.all_to_all"):
         dist.all_to_all_single(recv, send, group=group)
     with _timed("rows_to_channels.unpack"):
-        return recv.reshape(world, L, cs, R, N).permute(1, 2, 0, 3, 4).reshape(L, cs, world * R, N)
+        return _permute_runs(recv, (world, L, cs), (1, 2, 0), R * N).reshape(L, cs, world * R, N)
 
 
 def channels_to_rows(t, group=None):
@@ -94,12 +114,12 @@ def channels_to_rows(t, group=None):
         raise ValueError(f"{rows} rows are not divisible by {world} ranks")
     R = rows // world
     with _timed("channels_to_rows.pack"):
-        send = t.reshape(L, cs, world, R * N).permute(2, 0, 1, 3).contiguous()
+        send = _permute_runs(t, (L, cs, world), (2, 0, 1), R * N)           # [world, L, cs, R*N]
         recv = torch.empty_like(send)
     with _timed("channels_to_rows.all_to_all"):
         dist.all_to_all_single(recv, send, group=group)
     with _timed("channels_to_rows.unpack"):
-        return recv.permute(1, 0, 2, 3).reshape(L, world * cs, R, N)
+        return _permute_runs(recv, (world, L, 1), (1, 0, 2), cs * R * N).reshape(L, world * cs, R, N)
 
 
 class _Transpose(torch.autograd.Function):

@@ -226,6 +226,15 @@ typedef struct TriGemmDesc {
 int tri_bgemm(const TriGemmDesc* d, const void* a, const void* b, void* c, void* ws, size_t ws_bytes,
               tri_stream_t stream);
 
+/* Layout change around the row <-> channel exchanges of the sharded multiplicative update (tri_mul_shard_phase):
+ * dst[i_p0][i_p1][i_p2][run] = src[i0][i1][i2][run], where (p0, p1, p2) = perm is a permutation of the three
+ * outer dimensions (dst dimension k is src dimension perm[k]) and `run_bytes` contiguous bytes move together
+ * (a multiple of 16; both pointers 16-byte aligned).  It replaces torch's permute().contiguous() on the packing
+ * and unpacking sides of the all-to-all, which ran at a quarter of HBM bandwidth.  No counterpart in the
+ * reference (single device). */
+int tri_permute_runs(const void* src, void* dst, const int64_t dims[3], const int32_t perm[3], int64_t run_bytes,
+                     tri_stream_t stream);
+
 /* The tensor-core kernels bound every wait; if one runs out, the kernel records a code in the first
  * word of the workspace it was given and drains instead of hanging.  This call copies that word back
  * (it synchronises the stream) and returns it: 0 = no failure. */
