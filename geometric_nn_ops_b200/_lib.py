@@ -74,6 +74,11 @@ class TriMulShardBufs(Structure):
 
 PHASE_PROJECT, PHASE_OUTPUT, PHASE_OUTPUT_BWD, PHASE_PROJECT_BWD = 0, 1, 2, 3
 
+class TriScatterDesc(ctypes.Structure):
+    _fields_ = [("dims", ctypes.c_int64 * 3), ("dst_stride", ctypes.c_int64 * 3), ("dst_base_run", ctypes.c_int64),
+                ("run_bytes", ctypes.c_int64), ("peer_dim", ctypes.c_int32), ("n_peers", ctypes.c_int32)]
+
+
 EXPORTS = {
     "tri_abi_version": (c_int, []),
     "tri_last_error": (c_char_p, []),
@@ -99,6 +104,7 @@ EXPORTS = {
     "tri_bgemm": (c_int, [POINTER(TriGemmDesc), c_void_p, c_void_p, c_void_p, c_void_p, c_size_t, c_void_p]),
     "tri_permute_runs": (c_int, [c_void_p, c_void_p, POINTER(ctypes.c_int64 * 3), POINTER(ctypes.c_int32 * 3),
                                  ctypes.c_int64, c_void_p]),
+    "tri_scatter_runs": (c_int, [POINTER(TriScatterDesc), c_void_p, POINTER(c_void_p), c_void_p]),
     "tri_ws_status": (c_int, [c_void_p, c_void_p]),
 }
 

@@ -278,6 +278,48 @@ int tri_permute_runs(const void* src, void* dst, const int64_t dims[3], const in
   return 0;
 }
 
+struct ScatterPtrs { uint4* p[16]; };
+
+static __global__ void scatter_runs_kernel(const uint4* __restrict__ src, ScatterPtrs dst, long long d1, long long d2,
+                                           long long s0, long long s1, long long s2, long long base, int peer_dim,
+                                           long long run_v) {
+  const long long outer = blockIdx.y;   // source run index (i0, i1, i2)
+  const long long i2 = outer % d2, i1 = (outer / d2) % d1, i0 = outer / (d2 * d1);
+  const long long peer = peer_dim == 0 ? i0 : (peer_dim == 1 ? i1 : i2);
+  const uint4* s = src + outer * run_v;
+  uint4* d = dst.p[peer] + (base + i0 * s0 + i1 * s1 + i2 * s2) * run_v;
+  const long long stride = (long long)gridDim.x * blockDim.x;
+  long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x;
+  for (; i + 3 * stride < run_v; i += 4 * stride) {
+    const uint4 a = __ldg(s + i), b = __ldg(s + i + stride), c = __ldg(s + i + 2 * stride), e = __ldg(s + i + 3 * stride);
+    d[i] = a; d[i + stride] = b; d[i + 2 * stride] = c; d[i + 3 * stride] = e;
+  }
+  for (; i < run_v; i += stride) d[i] = __ldg(s + i);
+}
+
+int tri_scatter_runs(const TriScatterDesc* d, const void* src, void* const* dst_ptrs, tri_stream_t stream) {
+  if (d == nullptr || src == nullptr || dst_ptrs == nullptr) return fail(TRI_ERR_ARG, "tri_scatter_runs: null pointer");
+  if (d->run_bytes <= 0 || d->run_bytes % 16 != 0 || ((uintptr_t)src & 15))
+    return fail(TRI_ERR_ARG, "tri_scatter_runs: runs must be 16-byte aligned multiples of 16 bytes");
+  if (d->peer_dim < 0 || d->peer_dim > 2 || d->n_peers < 1 || d->n_peers > 16 || d->dims[d->peer_dim] != d->n_peers)
+    return fail(TRI_ERR_ARG, "tri_scatter_runs: bad peer dimension");
+  ScatterPtrs ptrs = {};
+  for (int i = 0; i < d->n_peers; ++i) {
+    if (dst_ptrs[i] == nullptr || ((uintptr_t)dst_ptrs[i] & 15)) return fail(TRI_ERR_ARG, "tri_scatter_runs: bad destination pointer");
+    ptrs.p[i] = static_cast<uint4*>(dst_ptrs[i]);
+  }
+  const long long outer = d->dims[0] * d->dims[1] * d->dims[2];
+  if (outer <= 0 || outer > 65535) return fail(TRI_ERR_ARG, "tri_scatter_runs: between 1 and 65535 runs");
+  const long long run_v = d->run_bytes / 16;
+  const int bx = (int)std::max<long long>(1, std::min<long long>(32, (run_v + 2047) / 2048));
+  KernelTimer kt("tri_scatter_runs", (cudaStream_t)stream, 0.0, 2.0 * outer * d->run_bytes);
+  scatter_runs_kernel<<<dim3(bx, (unsigned)outer), 256, 0, (cudaStream_t)stream>>>(
+      static_cast<const uint4*>(src), ptrs, d->dims[1], d->dims[2], d->dst_stride[0], d->dst_stride[1], d->dst_stride[2],
+      d->dst_base_run, d->peer_dim, run_v);
+  TRI_LAUNCH_OK();
+  return 0;
+}
+
 int tri_ws_status(const void* ws, tri_stream_t stream) {
   if (ws == nullptr) return fail(TRI_ERR_ARG, "ws is null");
   int code = 0;

@@ -90,13 +90,77 @@ def _permute_runs(t, dims, perm, run):
     return out
 
 
-def rows_to_channels(t, group=None):
-    """``[L, Ch, R, N]`` (all channels, this rank's R rows) -> ``[L, Ch/P, P*R, N]`` (this rank's channels, all rows)."""
+# Peer-store exchange: with symmetric memory (every rank's receive buffer mapped into every other rank's address
+# space) the all-to-all and both layout changes become ONE copy kernel per rank that stores each run straight into
+# its place in the destination GPU's buffer over NVLink.  A one-element all-reduce on the same stream then orders
+# "every rank has written" before "any rank reads".  Each call site of a step has its own buffer (`tag`), so a fast
+# rank can never overwrite data a slow rank still reads: between two uses of one buffer lie all the step's
+# other exchanges, each of which synchronises the ranks.
+_PEER = {}            # (tag, bytes, device, group) -> (buffer, peer pointer array)
+_PEER_STATE = {"enabled": None}
+
+
+def peer_exchange_enabled(device):
+    """True when the exchanges can use peer stores: CUDA, NCCL, symmetric memory; TRI_B200_EXCHANGE=nccl turns it off."""
+    import os
+    if _PEER_STATE["enabled"] is None:
+        ok = os.environ.get("TRI_B200_EXCHANGE", "peer") == "peer" and device.type == "cuda" and dist.get_backend() == "nccl"
+        if ok:
+            try:
+                import torch.distributed._symmetric_memory  # noqa: F401
+            except Exception:
+                ok = False
+        _PEER_STATE["enabled"] = ok
+    return _PEER_STATE["enabled"]
+
+
+def _peer_buffer(tag, nbytes, device, group):
+    import torch.distributed._symmetric_memory as symm_mem
+    key = (tag, nbytes, device.index, id(group))
+    if key not in _PEER:
+        pg = group if group is not None else dist.group.WORLD
+        buf = symm_mem.empty(nbytes, dtype=torch.uint8, device=device)
+        hdl = symm_mem.rendezvous(buf, pg.group_name)
+        ptrs = (ctypes.c_void_p * hdl.world_size)(*[int(p) for p in hdl.buffer_ptrs])
+        _PEER[key] = (buf, ptrs, torch.zeros(1, dtype=torch.float32, device=device))
+    return _PEER[key]
+
+
+def _peer_scatter(t, dims, dst_stride, base_run, peer_dim, run, out_shape, tag, group, persist):
     world, _ = _world(group)
+    t = t.contiguous()
+    nbytes = t.numel() * t.element_size()
+    buf, ptrs, flag = _peer_buffer(tag, nbytes, t.device, group)
+    d = _lib.TriScatterDesc()
+    d.dims[:] = dims
+    d.dst_stride[:] = dst_stride
+    d.dst_base_run = base_run
+    d.run_bytes = run * t.element_size()
+    d.peer_dim = peer_dim
+    d.n_peers = world
+    stream = ctypes.c_void_p(torch.cuda.current_stream(t.device).cuda_stream)
+    with _timed(tag + ".peer_store"):
+        _lib.check(_lib.load().tri_scatter_runs(ctypes.byref(d), ctypes.c_void_p(t.data_ptr()), ptrs, stream),
+                   "tri_scatter_runs")
+    with _timed(tag + ".barrier"):
+        dist.all_reduce(flag, group=group)      # every rank's stores are complete before anyone goes on
+    # The buffer is rewritten by the next exchange with the same tag.  Results the caller keeps (tensors saved for
+    # the backward) get a private copy; temporaries are consumed before this rank reaches its next exchange, and a
+    # peer cannot write here again before this rank has joined that one.
+    out = buf.view(t.dtype)[: t.numel()].view(out_shape)
+    return out.clone() if persist else out
+
+
+def rows_to_channels(t, group=None, tag="rows_to_channels", persist=True):
+    """``[L, Ch, R, N]`` (all channels, this rank's R rows) -> ``[L, Ch/P, P*R, N]`` (this rank's channels, all rows)."""
+    world, me = _world(group)
     L, Ch, R, N = t.shape
     if Ch % world != 0:
         raise ValueError(f"{Ch} channels are not divisible by {world} ranks")
     cs = Ch // world
+    if world > 1 and peer_exchange_enabled(t.device):
+        # run (l, w, c) of the source -> GPU w, run ((l*cs + c)*world + me) of its [L, cs, world, R*N] buffer
+        return _peer_scatter(t, (L, world, cs), (cs * world, 0, world), me, 1, R * N, (L, cs, world * R, N), tag, group, persist)
     with _timed("rows_to_channels.pack"):
         send = _permute_runs(t, (L, world, 1), (1, 0, 2), cs * R * N)       # [world, L, cs*R*N]
         recv = torch.empty_like(send)
@@ -106,13 +170,16 @@ def rows_to_channels(t, group=None):
         return _permute_runs(recv, (world, L, cs), (1, 2, 0), R * N).reshape(L, cs, world * R, N)
 
 
-def channels_to_rows(t, group=None):
+def channels_to_rows(t, group=None, tag="channels_to_rows", persist=True):
     """Inverse of :func:`rows_to_channels`: ``[L, Ch/P, N_rows, N]`` -> ``[L, Ch, N_rows/P, N]``."""
-    world, _ = _world(group)
+    world, me = _world(group)
     L, cs, rows, N = t.shape
     if rows % world != 0:
         raise ValueError(f"{rows} rows are not divisible by {world} ranks")
     R = rows // world
+    if world > 1 and peer_exchange_enabled(t.device):
+        # run (l, c, w) of the source -> GPU w, run ((l*world + me)*cs + c) of its [L, world, cs, R*N] buffer
+        return _peer_scatter(t, (L, cs, world), (world * cs, 1, 0), me * cs, 2, R * N, (L, world * cs, R, N), tag, group, persist)
     with _timed("channels_to_rows.pack"):
         send = _permute_runs(t, (L, cs, world), (2, 0, 1), R * N)           # [world, L, cs, R*N]
         recv = torch.empty_like(send)
@@ -225,13 +292,13 @@ class _ShardedTriMul(torch.autograd.Function):
         bufs.x, bufs.mask, bufs.w, bufs.saved = xc.data_ptr(), None if mc is None else mc.data_ptr(), ctypes.pointer(w), saved.data_ptr()
         bufs.a_cm, bufs.b_cm = ab[0].data_ptr(), ab[1].data_ptr()
         _phase(lib, d, _lib.PHASE_PROJECT, bufs, x.device)
-        ab_ch = rows_to_channels(ab.reshape(2 * B, Ch, R, N), group)          # [2B, Cs, N, N]
+        ab_ch = rows_to_channels(ab.reshape(2 * B, Ch, R, N), group, tag="fwd.ab")          # [2B, Cs, N, N]
         cs = ab_ch.shape[1]
         a_ch = ab_ch[:B].reshape(B * cs, N, N)
         b_ch = ab_ch[B:].reshape(B * cs, N, N)
         inc = not outgoing
         t_ch = bgemm(a_ch, b_ch, a_mn_major=inc, b_mn_major=inc)              # [B*Cs, N, N]
-        t_loc = channels_to_rows(t_ch.reshape(B, cs, N, N), group)            # [B, Ch, R, N]
+        t_loc = channels_to_rows(t_ch.reshape(B, cs, N, N), group, tag="fwd.t")            # [B, Ch, R, N]
         out = torch.empty_like(xc)
         bufs.t_cm, bufs.out = t_loc.data_ptr(), out.data_ptr()
         _phase(lib, d, _lib.PHASE_OUTPUT, bufs, x.device)
@@ -271,7 +338,7 @@ class _ShardedTriMul(torch.autograd.Function):
         bufs.g = ctypes.pointer(g)
         bufs.d_out, bufs.t_cm, bufs.dt_cm = dc.data_ptr(), t_loc.data_ptr(), dt_loc.data_ptr()
         _phase(lib, d, _lib.PHASE_OUTPUT_BWD, bufs, dev)
-        dt_ch = rows_to_channels(dt_loc, group)
+        dt_ch = rows_to_channels(dt_loc, group, tag="bwd.dt", persist=False)
         cs = dt_ch.shape[1]
         dt_ch = dt_ch.reshape(B * cs, N, N)
         if ctx.outgoing:   # da[i,k] = sum_j dt[i,j] b[j,k];  db[j,k] = sum_i dt[i,j] a[i,k]
@@ -281,7 +348,7 @@ class _ShardedTriMul(torch.autograd.Function):
             da = bgemm(b_ch, dt_ch, a_mn_major=False, b_mn_major=False)
             db = bgemm(a_ch, dt_ch, a_mn_major=False, b_mn_major=True)
         dab = channels_to_rows(torch.stack([da.reshape(B, cs, N, N), db.reshape(B, cs, N, N)]).reshape(2 * B, cs, N, N),
-                               group).reshape(2, B, Ch, R, N)
+                               group, tag="bwd.dab", persist=False).reshape(2, B, Ch, R, N)
         dx = torch.empty_like(xc)
         bufs.a_cm, bufs.b_cm, bufs.dx = dab[0].data_ptr(), dab[1].data_ptr(), dx.data_ptr()
         _phase(lib, d, _lib.PHASE_PROJECT_BWD, bufs, dev)

@@ -235,6 +235,25 @@ int tri_bgemm(const TriGemmDesc* d, const void* a, const void* b, void* c, void*
 int tri_permute_runs(const void* src, void* dst, const int64_t dims[3], const int32_t perm[3], int64_t run_bytes,
                      tri_stream_t stream);
 
+/* The same run copy with the destination on other GPUs: an all-to-all with the layout change folded in, done by
+ * plain stores into peer-mapped memory over NVLink (one pass over the data, against pack + NCCL all-to-all +
+ * unpack).  Run (i0, i1, i2) of src goes to GPU i_{peer_dim}, at run index
+ *   dst_base_run + i0*dst_stride[0] + i1*dst_stride[1] + i2*dst_stride[2]
+ * of that GPU's buffer dst_ptrs[i_{peer_dim}] (device pointers valid on this GPU, e.g. from symmetric memory; the
+ * entry of this rank is its own buffer).  The caller orders the exchange: every rank's copy must have finished
+ * before any rank reads its buffer (a barrier or a tiny all-reduce on the same stream does), and a buffer must
+ * not be rewritten while a peer still reads it.  The kernel only stores to peers; it never loads from them. */
+typedef struct TriScatterDesc {
+  int64_t dims[3];
+  int64_t dst_stride[3];   /* in runs */
+  int64_t dst_base_run;
+  int64_t run_bytes;       /* multiple of 16 */
+  int32_t peer_dim;        /* which of the three indices selects the destination GPU */
+  int32_t n_peers;         /* = dims[peer_dim], at most 16 */
+} TriScatterDesc;
+
+int tri_scatter_runs(const TriScatterDesc* d, const void* src, void* const* dst_ptrs, tri_stream_t stream);
+
 /* The tensor-core kernels bound every wait; if one runs out, the kernel records a code in the first
  * word of the workspace it was given and drains instead of hanging.  This call copies that word back
  * (it synchronises the stream) and returns it: 0 = no failure. */
