@@ -1,4 +1,4 @@
-"""Row-sharded (multi-GPU) forms of the two triangle ops: one process per GPU, NCCL for the exchanges.
+"""Row-sharded (multi-GPU) forms of the two triangle ops: one process per GPU over NVLink.
 
 The pair representation ``[B, N, N, C]`` is sharded over its first pair axis: rank ``r`` of ``P`` holds rows
 ``[r*N/P, (r+1)*N/P)``.  The reference is single-device; these wrappers are new.
@@ -14,7 +14,11 @@ The pair representation ``[B, N, N, C]`` is sharded over its first pair axis: ra
   rank that moves ``3/P`` of a pair-sized tensor per forward, against ``(P-1)/P`` for all-gathering ``b``.
   Weight gradients are partial sums per rank and are all-reduced.
 
-Every tensor handed to a collective lives in this GPU's memory; the kernels never read a peer's memory.
+The row <-> channel exchange is not an NCCL all-to-all: each rank runs one copy kernel (``tri_scatter_runs``) that
+stores every run straight into its final place in the destination GPU's buffer (symmetric memory, plain stores
+over NVLink), followed by a one-element all-reduce as the barrier.  That is one pass over the data instead of
+pack + all-to-all + unpack.  ``TRI_B200_EXCHANGE=nccl`` (or a CPU / gloo group) selects the all-to-all route.
+The kernels only ever *store* to a peer; every load, and every tensor handed to NCCL, is in this GPU's memory.
 """
 
 import ctypes
