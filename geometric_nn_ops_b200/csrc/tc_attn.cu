@@ -310,23 +310,23 @@ attn_fwd_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
         float mx4[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};   // independent chains
         const float4* sMb4 = reinterpret_cast<const float4*>(sMb + stg * 128 + hh * 64);
 #pragma unroll
-        for (int cc = 0; cc < 4; ++cc) {   // 16 columns per load: with 32 the logits and the load's registers do not fit
-          uint32_t rr[16];
-          tmem_ld_32x16(t_row + hh * 64 + cc * 16, rr);
+        for (int cc = 0; cc < 2; ++cc) {
+          uint32_t rr[32];
+          tmem_ld_32x32(t_row + hh * 64 + cc * 32, rr);
           tmem_ld_wait();
 #pragma unroll
-          for (int u = 0; u < 2; ++u) {
+          for (int u = 0; u < 4; ++u) {
             uint4 raw = make_uint4(0, 0, 0, 0);
-            if constexpr (HB) raw = *reinterpret_cast<const uint4*>(sPj + sw128_chunk(r, hh * 8 + cc * 2 + u));
+            if constexpr (HB) raw = *reinterpret_cast<const uint4*>(sPj + sw128_chunk(r, hh * 8 + cc * 4 + u));
             const uint32_t bw[4] = {raw.x, raw.y, raw.z, raw.w};
-            const float4 mA = sMb4[cc * 4 + u * 2], mB = sMb4[cc * 4 + u * 2 + 1];
+            const float4 mA = sMb4[cc * 8 + u * 2], mB = sMb4[cc * 8 + u * 2 + 1];
             const float2 mk[4] = {make_float2(mA.x, mA.y), make_float2(mA.z, mA.w), make_float2(mB.x, mB.y),
                                   make_float2(mB.z, mB.w)};
 #pragma unroll
             for (int i = 0; i < 4; ++i) {
               float2 v = __ffma2_rn(pair(rr[u * 8 + 2 * i], rr[u * 8 + 2 * i + 1]), sc2, mk[i]);
               if constexpr (HB) v = __fadd2_rn(v, unpack2<T>(bw[i]));
-              x2[cc * 8 + u * 4 + i] = v;
+              x2[cc * 16 + u * 4 + i] = v;
               mx4[i] = fmax3(mx4[i], v.x, v.y);
             }
           }
@@ -359,40 +359,34 @@ attn_fwd_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
         // ---- P = 2^((x - m) log2e), its row sum; P rounded to the input dtype -----------------------------
         const float2 nm2 = splat(m_new == -INFINITY ? 0.f : -m_new);   // a half with no key in range yet: P = 2^-inf = 0
         float2 ps2[2] = {make_float2(0.f, 0.f), make_float2(0.f, 0.f)};
+        uint32_t pw[32];
+#pragma unroll
+        for (int g = 0; g < 8; ++g) {
+#pragma unroll
+          for (int i = 0; i < 4; ++i) {
+            const float2 e = __fmul2_rn(__fadd2_rn(x2[g * 4 + i], nm2), l2e2);
+            const float2 pp = make_float2(ex2_approx(e.x), ex2_approx(e.y));
+            ps2[i & 1] = __fadd2_rn(ps2[i & 1], pp);
+            pw[g * 4 + i] = pack2<T>(pp.x, pp.y);
+          }
+          if constexpr (!TMEM_P)
+            *reinterpret_cast<uint4*>(sPj + sw128_chunk(r, hh * 8 + g)) = make_uint4(pw[g * 4], pw[g * 4 + 1], pw[g * 4 + 2], pw[g * 4 + 3]);
+        }
+        l_run += (ps2[0].x + ps2[0].y) + (ps2[1].x + ps2[1].y);
         if constexpr (TMEM_P) {
-          // P goes to TMEM 16 packed columns at a time (fewer live registers than packing all 32 first); the
-          // previous tile's P V must have read the old P by now
-          if (c > 0) ok = mbar_wait(&bar_pv[(c - 1) & 1], ((c - 1) >> 1) & 1, a.err, 15) && ok;
+          if (c > 0) ok = mbar_wait(&bar_pv[(c - 1) & 1], ((c - 1) >> 1) & 1, a.err, 15) && ok;   // the previous P has been read
           tc_fence_after_sync();
 #pragma unroll
-          for (int cc = 0; cc < 2; ++cc) {
+          for (int cc = 0; cc < 2; ++cc) {   // this thread's query row, its 64 keys as 32 packed columns
             uint32_t w[16];
 #pragma unroll
-            for (int i = 0; i < 16; ++i) {
-              const float2 e = __fmul2_rn(__fadd2_rn(x2[cc * 16 + i], nm2), l2e2);
-              const float2 pp = make_float2(ex2_approx(e.x), ex2_approx(e.y));
-              ps2[i & 1] = __fadd2_rn(ps2[i & 1], pp);
-              w[i] = pack2<T>(pp.x, pp.y);
-            }
-            tmem_st_32x16(t_row + COL_P + hh * 32 + cc * 16, w);   // this thread's query row: 32 of its 64 keys
+            for (int i = 0; i < 16; ++i) w[i] = pw[cc * 16 + i];
+            tmem_st_32x16(t_row + COL_P + hh * 32 + cc * 16, w);
           }
           tmem_st_wait();
         } else {
-#pragma unroll
-          for (int g = 0; g < 8; ++g) {
-            uint32_t pw[4];
-#pragma unroll
-            for (int i = 0; i < 4; ++i) {
-              const float2 e = __fmul2_rn(__fadd2_rn(x2[g * 4 + i], nm2), l2e2);
-              const float2 pp = make_float2(ex2_approx(e.x), ex2_approx(e.y));
-              ps2[i & 1] = __fadd2_rn(ps2[i & 1], pp);
-              pw[i] = pack2<T>(pp.x, pp.y);
-            }
-            *reinterpret_cast<uint4*>(sPj + sw128_chunk(r, hh * 8 + g)) = make_uint4(pw[0], pw[1], pw[2], pw[3]);
-          }
           fence_proxy_async_smem();
         }
-        l_run += (ps2[0].x + ps2[0].y) + (ps2[1].x + ps2[1].y);
         tc_fence_before_sync();
         __syncwarp();
         if (lane == 0) mbar_arrive(bar_p);
