@@ -69,6 +69,7 @@ class TriMulShardBufs(Structure):
         ("x", c_void_p), ("mask", c_void_p), ("w", POINTER(TriMulWeights)), ("saved", c_void_p),
         ("a_cm", c_void_p), ("b_cm", c_void_p), ("t_cm", c_void_p), ("out", c_void_p),
         ("d_out", c_void_p), ("dt_cm", c_void_p), ("dx", c_void_p), ("g", POINTER(TriMulWeightGrads)),
+        ("peer_ab", POINTER(c_void_p)), ("peer_world", ctypes.c_int32), ("peer_rank", ctypes.c_int32),
     ]
 
 

@@ -166,6 +166,17 @@ int launch_gemm(cudaStream_t st, int dtype, int epi, int bn, bool out_f32, const
   }
   g.out0 = p.out0; g.out1 = p.out1; g.ld_out = p.ld_out; g.batch_out = p.batch_out;
   g.bias0 = p.bias0; g.aux = p.aux; g.aux2 = p.aux2; g.aux3 = p.aux3; g.plane = p.plane; g.err = err;
+  g.peer_world = 0; g.peer_rank = 0; g.peer_cs = 128; g.peer_batches = 0;
+  for (int i = 0; i < 16; ++i) g.peer_out[i] = nullptr;
+  if (p.peer_out != nullptr && p.peer_world > 1) {
+    if (epi != EPI_GATE_IN || p.peer_world > 16 || 128 % p.peer_world != 0)
+      return fail(TRI_ERR_ARG, "peer outputs need the gate-in epilogue and a rank count that divides 128 (at most 16)");
+    g.peer_world = p.peer_world; g.peer_rank = p.peer_rank; g.peer_cs = 128 / p.peer_world; g.peer_batches = p.peer_batches;
+    for (int i = 0; i < p.peer_world; ++i) {
+      if (p.peer_out[i] == nullptr) return fail(TRI_ERR_ARG, "null peer output buffer");
+      g.peer_out[i] = p.peer_out[i];
+    }
+  }
 
   CUtensorMap maps[4];
   TRI_TRY(operand_map(&maps[0], p.a[0], dtype, kBM));

@@ -63,6 +63,10 @@ struct GemmArgs {
   const void* aux2;              // GATE_IN_BWD: channel-major gradient of the a half
   const void* aux3;              //              ... of the b half
   long long plane;               // GATE_IN(_BWD): pixels per batch entry; channel-major plane stride
+  // GATE_IN with peer_world > 0: channel c of half tm goes to GPU c / peer_cs, into its buffer
+  // [2 * peer_batches][peer_cs][peer_world][plane] at (tm * peer_batches + batch, c % peer_cs, peer_rank)
+  void* peer_out[16];
+  int peer_world, peer_rank, peer_cs, peer_batches;
   int* err;
 };
 
@@ -182,6 +186,18 @@ __device__ __forceinline__ void ld32_f(uint32_t taddr, float (&v)[32]) {
   tmem_ld_wait();
 #pragma unroll
   for (int i = 0; i < 32; ++i) v[i] = __uint_as_float(r[i]);
+}
+
+// where the gate-in epilogue writes channel `row` of half `tm`, batch entry `bb`, pixel `pix`: this GPU's
+// channel-major output, or (row-sharded runs) the exchange buffer of the GPU that owns the channel
+template <typename TOUT>
+__device__ __forceinline__ TOUT* gate_in_dst(const GemmArgs& g, int tm, long long bb, int row, long long pix) {
+  if (g.peer_world > 0) {
+    const int w = row / g.peer_cs, cl = row - w * g.peer_cs;
+    return reinterpret_cast<TOUT*>(g.peer_out[w]) +
+           ((((long long)tm * g.peer_batches + bb) * g.peer_cs + cl) * g.peer_world + g.peer_rank) * g.plane + pix;
+  }
+  return reinterpret_cast<TOUT*>(tm == 0 ? g.out0 : g.out1) + (bb * 128 + row) * g.plane + pix;
 }
 
 template <typename TIN, typename TOUT, int BN, int EPI, int STAGES>
@@ -413,10 +429,7 @@ tc_gemm_kernel(const __grid_constant__ CUtensorMap tmA0, const __grid_constant__
                   o0[uu * 8 + i] = (p[uu * 8 + i] + bp) * fast_sigmoid(gt[uu * 8 + i] + bg);
                   if (mask != nullptr) o0[uu * 8 + i] *= mk[i];
                 }
-                if (!wide16) {
-                  TOUT* plane = reinterpret_cast<TOUT*>(tm == 0 ? g.out0 : g.out1);
-                  store8<TOUT>(plane + (bb * 128 + row) * g.plane + pix, &o0[uu * 8]);
-                }
+                if (!wide16) store8<TOUT>(gate_in_dst<TOUT>(g, tm, bb, row, pix), &o0[uu * 8]);
               } else {
                 float d[8];
                 cvtraw8<TIN>(dpre[jj][u], d);
@@ -438,8 +451,7 @@ tc_gemm_kernel(const __grid_constant__ CUtensorMap tmA0, const __grid_constant__
               const long long m16 = n0 + j * 32 + hf * 16;
               if (wide16 && m16 < g.N) {   // one 32-byte store per output row
                 if constexpr (EPI == EPI_GATE_IN) {
-                  TOUT* plane = reinterpret_cast<TOUT*>(tm == 0 ? g.out0 : g.out1);
-                  store16<TOUT>(plane + (bb16 * 128 + row) * g.plane + pix16, o0);
+                  store16<TOUT>(gate_in_dst<TOUT>(g, tm, bb16, row, pix16), o0);
                 } else {
                   TOUT* o = reinterpret_cast<TOUT*>(g.out0);
                   store16<TOUT>(o + (long long)(tm * 256 + row) * g.ld_out + m16, o0);
@@ -541,6 +553,8 @@ struct GemmPlan {
   const void* aux2 = nullptr;
   const void* aux3 = nullptr;
   long long plane = 0;
+  void* const* peer_out = nullptr;   // GATE_IN: per-rank exchange buffers (see GemmArgs)
+  int peer_world = 0, peer_rank = 0, peer_batches = 0;
   const char* name = "tc_gemm";
   double flops = 0, bytes = 0;
 };

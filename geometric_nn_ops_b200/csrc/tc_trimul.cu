@@ -484,7 +484,8 @@ void gate_in_operands(GemmPlan* p, const Geom& gm, const Prep& pr, const void* z
 // ---- phase 1: x -> z (LayerNorm), a / b (gated, masked projections, channel-major) ---------------------
 template <typename T>
 int phase_project(cudaStream_t st, const Geom& gm, const void* x, const void* mask, const TriMulWeights* w,
-                  const Prep& pr, void* z, float* mean_in, float* rstd_in, void* a_cm, void* b_cm) {
+                  const Prep& pr, void* z, float* mean_in, float* rstd_in, void* a_cm, void* b_cm,
+                  void* const* peer_ab = nullptr, int peer_world = 0, int peer_rank = 0) {
   const long long M = gm.M;
   {
     KernelTimer kt("tc_ln_rows", st, 0.0, 2.0 * gm.unit());
@@ -496,6 +497,7 @@ int phase_project(cudaStream_t st, const Geom& gm, const void* x, const void* ma
   gate_in_operands(&p, gm, pr, z);
   p.out0 = a_cm; p.out1 = b_cm; p.bias0 = (w->p_in_b || w->g_in_b) ? pr.bias_cat : nullptr; p.aux = mask;
   p.plane = gm.plane;
+  p.peer_out = peer_ab; p.peer_world = peer_world; p.peer_rank = peer_rank; p.peer_batches = (int)(M / gm.plane);
   p.name = "tc_gemm_gate_in"; p.flops = 2.0 * M * CW * 4 * CW; p.bytes = 3.0 * gm.unit();
   return launch_gemm(st, gm.dtype, EPI_GATE_IN, 256, false, p, pr.err);
 }
@@ -788,8 +790,10 @@ int shard_phase_t(const TriMulShardDesc* d, int phase, const TriMulShardBufs* bf
   TRI_TRY(run_prep<T>(st, bf->w, pr));
   switch (phase) {
     case TRI_PHASE_PROJECT:
-      if (!bf->x || !bf->a_cm || !bf->b_cm) return fail(TRI_ERR_ARG, "project phase needs x, a_cm, b_cm");
-      return phase_project<T>(st, gm, bf->x, bf->mask, bf->w, pr, s.z, s.mean_in, s.rstd_in, bf->a_cm, bf->b_cm);
+      if (!bf->x || ((!bf->a_cm || !bf->b_cm) && !(bf->peer_ab != nullptr && bf->peer_world > 1)))
+        return fail(TRI_ERR_ARG, "project phase needs x and either a_cm, b_cm or the peer buffers");
+      return phase_project<T>(st, gm, bf->x, bf->mask, bf->w, pr, s.z, s.mean_in, s.rstd_in, bf->a_cm, bf->b_cm,
+                              bf->peer_ab, bf->peer_world, bf->peer_rank);
     case TRI_PHASE_OUTPUT:
       if (!bf->t_cm || !bf->out) return fail(TRI_ERR_ARG, "output phase needs t_cm, out");
       return phase_output<T>(st, gm, bf->t_cm, s.z, bf->w, pr, s.u, s.mean_out, s.rstd_out, bf->out);

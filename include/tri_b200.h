@@ -197,6 +197,13 @@ typedef struct TriMulShardBufs {
   void* dt_cm;              /* OUTPUT_BWD: out */
   void* dx;                 /* PROJECT_BWD: out */
   const TriMulWeightGrads* g;
+  /* PROJECT with peer_world > 1: the gate-in GEMM's epilogue stores a and b straight into every rank's exchange
+   * buffer instead of a_cm / b_cm (compute and the row -> channel exchange in one kernel).  peer_ab[w] is rank w's
+   * buffer, laid out [2*B, C_hidden/peer_world, peer_world*rows, N] (a for the first B entries, then b), as a
+   * pointer valid on this GPU; channel c goes to rank c / (C_hidden/peer_world).  The caller provides the barrier
+   * afterwards, as for tri_scatter_runs.  NULL / 0 keeps the plain outputs. */
+  void* const* peer_ab;
+  int32_t peer_world, peer_rank;
 } TriMulShardBufs;
 
 enum { TRI_PHASE_PROJECT = 0, TRI_PHASE_OUTPUT = 1, TRI_PHASE_OUTPUT_BWD = 2, TRI_PHASE_PROJECT_BWD = 3 };
