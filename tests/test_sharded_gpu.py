@@ -23,8 +23,8 @@ def _rel(a, b):
     return ((a.double() - b.double()).norm() / b.double().norm().clamp_min(1e-30)).item()
 
 
-def _worker(rank, world, port, ret):
-    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), TRI_B200_CHECK="1")
+def _worker(rank, world, port, ret, exchange):
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), TRI_B200_CHECK="1", TRI_B200_EXCHANGE=exchange)
     torch.cuda.set_device(rank)
     dist.init_process_group("nccl", rank=rank, world_size=world, device_id=torch.device("cuda", rank))
     try:
@@ -69,13 +69,16 @@ def _check(rank, world):
     assert torch.equal(sharded.all_to_all_transpose(pair[:, i0:i1].contiguous()), pair.transpose(1, 2)[:, i0:i1])
 
 
+# the three exchange routes: peer stores from a copy kernel (default), NCCL all-to-all, and the gate-in GEMM's
+# epilogue storing into the peers' buffers
 @pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs at least two GPUs")
-def test_sharded_matches_single_gpu():
+@pytest.mark.parametrize("exchange", ["peer", "nccl", "fused"])
+def test_sharded_matches_single_gpu(exchange):
     world = 2
     ctx = mp.get_context("spawn")
     ret = ctx.Manager().dict()
     port = _free_port()
-    procs = [ctx.Process(target=_worker, args=(r, world, port, ret)) for r in range(world)]
+    procs = [ctx.Process(target=_worker, args=(r, world, port, ret, exchange)) for r in range(world)]
     for p in procs:
         p.start()
     for p in procs:
