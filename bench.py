@@ -206,7 +206,8 @@ def main():
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
     ap.add_argument("--n-res", type=int, default=N_RES, help="pair side (default: the headline 768)")
-    ap.add_argument("--graph", action="store_true", help="replay the step from a CUDA graph on one GPU too")
+    ap.add_argument("--graph", action="store_true", help="(default) replay the step from a CUDA graph")
+    ap.add_argument("--eager", action="store_true", help="launch the timed steps eagerly instead of replaying a CUDA graph")
     ap.add_argument("--quick", action="store_true",
                     help="timed region only: no end-to-end leg and no CPU baseline (for profiler captures)")
     args = ap.parse_args()
@@ -268,11 +269,12 @@ def main():
     barrier()
 
     # ---- timed region: device-resident inputs -------------------------------------------------
-    # On several GPUs each rank's shard is small enough for host launch latency to show, so the whole step
-    # (kernels and NCCL exchanges) is captured once in a CUDA graph and replayed; the per-kernel event
-    # brackets cannot live inside a graph, so there the kernel table comes from one extra eager step.
+    # A step is ~190 launches; on several GPUs each rank's shard is small enough for host launch latency to show,
+    # and on one GPU the library's per-kernel event brackets would otherwise sit inside the timed region.  So
+    # the whole step (kernels and exchanges) is captured once in a CUDA graph and replayed, and the kernel
+    # table comes from one extra eager step outside the timed region (--eager times eager launches instead).
     graph = None
-    if world > 1 or args.graph:
+    if not args.eager:
         try:
             side = torch.cuda.Stream()
             side.wait_stream(torch.cuda.current_stream())
