@@ -39,7 +39,6 @@ struct AttnArgs {
   float* stats;          // [2][B][S][H][N]: row max, log row sum
   const float* mask_terms;   // [B][S][npad] additive key-mask terms (0, -1e9, or -inf beyond N)
   int npad;                  // N rounded up to 128
-  int has_bias;
   int bias_b_mul;        // 0 when the bias is broadcast over the batch
   uint32_t idesc_s, idesc_pv;
   int* err;
@@ -470,7 +469,7 @@ struct AttnBwdArgs {
   const float* mask_terms;   // [B][S][npad] additive key-mask terms (0, -1e9, or -inf beyond N)
   const uint8_t* mask;
   int64_t mask_st[2];
-  int has_bias, bias_b_mul;
+  int bias_b_mul;        // 0 when the bias is broadcast over the batch
   void* out0;            // dq (MODE_DQ), dk (dK/dV kernel), dbias fp32 (MODE_DBIAS)
   void* out1;            // dv
   int64_t out0_st[4], out1_st[4];
@@ -1304,7 +1303,7 @@ int bwd_launch(const TriAttnDesc* d, const void* q, const void* k, const void* v
   AttnBwdArgs a;
   a.B = d->B; a.S = d->n_seq; a.N = d->n_res; a.H = d->H; a.scale = d->scale;
   a.stats = stats; a.delta = delta; a.prep = prep; a.prep_plane = prep_plane; a.npad = npad; a.mask_terms = mask_terms; a.mask = mask; a.mask_st[0] = d->mask_st[0]; a.mask_st[1] = d->mask_st[1];
-  a.has_bias = bias != nullptr; a.bias_b_mul = d->bias_st[0] != 0 ? 1 : 0; a.err = err;
+  a.bias_b_mul = d->bias_st[0] != 0 ? 1 : 0; a.err = err;
   a.row_chunks = 1;
   const int qblocks = (d->n_res + 127) / 128;
   CUtensorMap tq, tdo, tk, tv, tb;
@@ -1409,7 +1408,7 @@ int fwd_launch(const TriAttnDesc* d, const void* q, const void* k, const void* v
   a.B = d->B; a.S = d->n_seq; a.N = d->n_res; a.H = d->H; a.scale = d->scale;
   a.o = o; for (int i = 0; i < 4; ++i) a.o_st[i] = d->o_st[i];
   a.stats = stats; a.mask_terms = mask_terms; a.npad = (d->n_res + 127) / 128 * 128;
-  a.has_bias = bias != nullptr; a.bias_b_mul = d->bias_st[0] != 0 ? 1 : 0;
+  a.bias_b_mul = d->bias_st[0] != 0 ? 1 : 0;
   {
     const long long n = (long long)d->B * d->n_seq * a.npad;
     mask_terms_kernel<<<cdiv(n, 256), 256, 0, st>>>(mask, d->mask_st[0], d->mask_st[1], d->B, d->n_seq, d->n_res, a.npad, mask_terms);
