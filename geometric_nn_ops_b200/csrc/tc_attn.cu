@@ -1229,7 +1229,7 @@ int sm_count() {
   return n;
 }
 
-constexpr int kDbiasRowChunks = 4;
+constexpr int kDbiasRowChunks = 8;   // at most this many row chunks (the workspace holds one partial sum per chunk)
 
 // rank-5 map with a caller-chosen number of residues per box
 int qkv_map_rows(CUtensorMap* out, const void* p, const TriAttnDesc* d, const int64_t* st, int rows) {
@@ -1358,7 +1358,12 @@ int bwd_launch(const TriAttnDesc* d, const void* q, const void* k, const void* v
   }
   // ---- dbias ---------------------------------------------------------------------------------
   if (dbias != nullptr) {
-    const int chunks = d->n_seq >= 2 * kDbiasRowChunks ? kDbiasRowChunks : 1;
+    // Row chunks only as far as they are needed to fill the GPU (two CTAs per SM): with enough (batch, head, query
+    // block, key block) combinations one CTA sums all rows and no partial sums are written or added.
+    const long long combos = (long long)qblocks * ((d->n_res + 63) / 64) * d->B * d->H, slots = 2LL * sm_count();
+    int chunks = 1;
+    if (combos * 10 < slots * 9) chunks = (int)std::min<long long>(kDbiasRowChunks, (slots + combos - 1) / combos);
+    chunks = std::max(1, std::min(chunks, d->n_seq / 2));
     const long long nb = (long long)d->B * d->H * d->n_res * d->n_res;
     const int kblocks = (d->n_res + 63) / 64;
     a.row_chunks = chunks;
