@@ -79,6 +79,14 @@ __device__ __forceinline__ float fast_sigmoid(float x) {
   return __fdividef(1.0f, 1.0f + ex2_approx(-1.4426950408889634f * x));
 }
 
+// sigmoid of two values with packed fp32x2 arithmetic around the two MUFU pairs (the gate epilogues are bound by
+// instruction issue, and a packed instruction does the work of two)
+__device__ __forceinline__ float2 sigmoid2(float2 x) {
+  const float2 t = __fmul2_rn(x, make_float2(-1.4426950408889634f, -1.4426950408889634f));
+  const float2 den = __fadd2_rn(make_float2(ex2_approx(t.x), ex2_approx(t.y)), make_float2(1.0f, 1.0f));
+  return make_float2(__fdividef(1.0f, den.x), __fdividef(1.0f, den.y));
+}
+
 // 8 consecutive elements <-> registers, with 16-byte (16-bit types) or 2 x 16-byte (fp32) accesses
 template <typename T> __device__ __forceinline__ void load8(const T* p, float (&v)[8]) {
   if constexpr (sizeof(T) == 4) {
@@ -423,22 +431,32 @@ tc_gemm_kernel(const __grid_constant__ CUtensorMap tmA0, const __grid_constant__
               if (uu == 0) { bb16 = bb; pix16 = pix; }
               float mk[8];
               if (mask != nullptr) load8<TIN>(mask + m8, mk);
+              const float2 bp2 = make_float2(bp, bp), bg2 = make_float2(bg, bg);
               if constexpr (EPI == EPI_GATE_IN) {
 #pragma unroll
-                for (int i = 0; i < 8; ++i) {
-                  o0[uu * 8 + i] = (p[uu * 8 + i] + bp) * fast_sigmoid(gt[uu * 8 + i] + bg);
-                  if (mask != nullptr) o0[uu * 8 + i] *= mk[i];
+                for (int i = 0; i < 8; i += 2) {
+                  const float2 pv = __fadd2_rn(make_float2(p[uu * 8 + i], p[uu * 8 + i + 1]), bp2);
+                  const float2 sg = sigmoid2(__fadd2_rn(make_float2(gt[uu * 8 + i], gt[uu * 8 + i + 1]), bg2));
+                  float2 r = __fmul2_rn(pv, sg);
+                  if (mask != nullptr) r = __fmul2_rn(r, make_float2(mk[i], mk[i + 1]));
+                  o0[uu * 8 + i] = r.x;
+                  o0[uu * 8 + i + 1] = r.y;
                 }
                 if (!wide16) store8<TOUT>(gate_in_dst<TOUT>(g, tm, bb, row, pix), &o0[uu * 8]);
               } else {
                 float d[8];
                 cvtraw8<TIN>(dpre[jj][u], d);
 #pragma unroll
-                for (int i = 0; i < 8; ++i) {
-                  const float dd = mask != nullptr ? d[i] * mk[i] : d[i];
-                  const float sg = fast_sigmoid(gt[uu * 8 + i] + bg);
-                  o0[uu * 8 + i] = dd * sg;
-                  o1[uu * 8 + i] = dd * (p[uu * 8 + i] + bp) * sg * (1.0f - sg);
+                for (int i = 0; i < 8; i += 2) {
+                  float2 dd = make_float2(d[i], d[i + 1]);
+                  if (mask != nullptr) dd = __fmul2_rn(dd, make_float2(mk[i], mk[i + 1]));
+                  const float2 sg = sigmoid2(__fadd2_rn(make_float2(gt[uu * 8 + i], gt[uu * 8 + i + 1]), bg2));
+                  const float2 pv = __fadd2_rn(make_float2(p[uu * 8 + i], p[uu * 8 + i + 1]), bp2);
+                  const float2 dp = __fmul2_rn(dd, sg);                                           // d * sig
+                  const float2 oms = __ffma2_rn(sg, make_float2(-1.0f, -1.0f), make_float2(1.0f, 1.0f));
+                  const float2 dg = __fmul2_rn(__fmul2_rn(dp, pv), oms);                          // d * P * sig * (1 - sig)
+                  o0[uu * 8 + i] = dp.x; o0[uu * 8 + i + 1] = dp.y;
+                  o1[uu * 8 + i] = dg.x; o1[uu * 8 + i + 1] = dg.y;
                 }
                 if (!wide16) {
                   TOUT* o = reinterpret_cast<TOUT*>(g.out0);
