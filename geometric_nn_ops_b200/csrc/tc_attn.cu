@@ -916,37 +916,46 @@ attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
       const int stg = j & 1, kstg = j % G::NS;
       ok = mbar_wait(bar_s, j & 1, a.err, 24) && ok;
       tc_fence_after_sync();
-      uint32_t rs[32], rp[32];
-      tmem_ld_32x32(t_row + hh * 32, rs);
-      tmem_ld_32x32(t_row + COL_DP + hh * 32, rp);
+      ok = mbar_wait(&bar_in[kstg], (j / G::NS) & 1, a.err, 23) && ok;   // the tile's mask terms
+      if (HB) ok = mbar_wait(&bar_bias[stg], (j >> 1) & 1, a.err, 25) && ok;
+      const float4* sMb4 = reinterpret_cast<const float4*>(sMb + kstg * 64 + hh * 32);
+      const uint8_t* bias_t = sBias + stg * 16384;
+      uint32_t dw[16];
+      // 16 of this thread's 32 columns: dS = P (dP - delta), packed
+      auto half = [&](const uint32_t (&rs)[16], const uint32_t (&rp)[16], int h2) {
+#pragma unroll
+        for (int uu = 0; uu < 2; ++uu) {
+          const int u = h2 * 2 + uu;
+          uint4 raw = make_uint4(0, 0, 0, 0);
+          if constexpr (HB) raw = *reinterpret_cast<const uint4*>(bias_t + sw128_chunk1(r, hh * 4 + u));
+          const uint32_t bw[4] = {raw.x, raw.y, raw.z, raw.w};
+          const float4 mA = sMb4[u * 2], mB = sMb4[u * 2 + 1];
+          const float2 mk[4] = {make_float2(mA.x, mA.y), make_float2(mA.z, mA.w), make_float2(mB.x, mB.y),
+                                make_float2(mB.z, mB.w)};
+#pragma unroll
+          for (int i = 0; i < 4; ++i) {
+            float2 x = __ffma2_rn(pair(rs[uu * 8 + 2 * i], rs[uu * 8 + 2 * i + 1]), sc2, mk[i]);
+            if constexpr (HB) x = __fadd2_rn(x, unpack2<T>(bw[i]));
+            const float2 e = __ffma2_rn(__fadd2_rn(x, nm2), l2e2, nl2);
+            const float2 p = make_float2(ex2_approx(e.x), ex2_approx(e.y));
+            const float2 ds = __fmul2_rn(p, __fadd2_rn(pair(rp[uu * 8 + 2 * i], rp[uu * 8 + 2 * i + 1]), nd2));
+            dw[u * 4 + i] = pack2<T>(ds.x, ds.y);
+          }
+        }
+      };
+      // the second half's TMEM loads are in flight while the first half is computed
+      uint32_t rsA[16], rpA[16], rsB[16], rpB[16];
+      tmem_ld_32x16(t_row + hh * 32, rsA);
+      tmem_ld_32x16(t_row + COL_DP + hh * 32, rpA);
+      tmem_ld_wait();
+      tmem_ld_32x16(t_row + hh * 32 + 16, rsB);
+      tmem_ld_32x16(t_row + COL_DP + hh * 32 + 16, rpB);
+      half(rsA, rpA, 0);
       tmem_ld_wait();
       tc_fence_before_sync();
       __syncwarp();
       if (lane == 0) mbar_arrive(bar_free);   // this warp holds its logits: the accumulators can take the next tile
-      ok = mbar_wait(&bar_in[kstg], (j / G::NS) & 1, a.err, 23) && ok;   // the tile's mask terms
-      if (HB) ok = mbar_wait(&bar_bias[stg], (j >> 1) & 1, a.err, 25) && ok;
-
-      const float4* sMb4 = reinterpret_cast<const float4*>(sMb + kstg * 64 + hh * 32);
-      const uint8_t* bias_t = sBias + stg * 16384;
-      uint32_t dw[16];
-#pragma unroll
-      for (int u = 0; u < 4; ++u) {
-        uint4 raw = make_uint4(0, 0, 0, 0);
-        if constexpr (HB) raw = *reinterpret_cast<const uint4*>(bias_t + sw128_chunk1(r, hh * 4 + u));
-        const uint32_t bw[4] = {raw.x, raw.y, raw.z, raw.w};
-        const float4 mA = sMb4[u * 2], mB = sMb4[u * 2 + 1];
-        const float2 mk[4] = {make_float2(mA.x, mA.y), make_float2(mA.z, mA.w), make_float2(mB.x, mB.y),
-                              make_float2(mB.z, mB.w)};
-#pragma unroll
-        for (int i = 0; i < 4; ++i) {
-          float2 x = __ffma2_rn(pair(rs[u * 8 + 2 * i], rs[u * 8 + 2 * i + 1]), sc2, mk[i]);
-          if constexpr (HB) x = __fadd2_rn(x, unpack2<T>(bw[i]));
-          const float2 e = __ffma2_rn(__fadd2_rn(x, nm2), l2e2, nl2);
-          const float2 p = make_float2(ex2_approx(e.x), ex2_approx(e.y));
-          const float2 ds = __fmul2_rn(p, __fadd2_rn(pair(rp[u * 8 + 2 * i], rp[u * 8 + 2 * i + 1]), nd2));
-          dw[u * 4 + i] = pack2<T>(ds.x, ds.y);
-        }
-      }
+      half(rsB, rpB, 1);
       if (j > 0) ok = mbar_wait(&bar_dq[(j - 1) & 3], ((j - 1) >> 2) & 1, a.err, 26) && ok;   // the previous dS has been read
       tc_fence_after_sync();
       tmem_st_32x16(t_row + COL_DS + hh * 16, dw);   // this thread's query row, its 32 keys as 16 packed columns
