@@ -663,13 +663,6 @@ attn_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_const
       const int stg = j & 1, qstg = j % G::NQ;
       ok = mbar_wait(bar_s, j & 1, a.err, 33) && ok;
       tc_fence_after_sync();
-      uint32_t rs[32], rp[32];
-      tmem_ld_32x32(t_row + hh * 32, rs);
-      tmem_ld_32x32(t_row + COL_DP + hh * 32, rp);
-      tmem_ld_wait();
-      tc_fence_before_sync();
-      __syncwarp();
-      if (lane == 0) mbar_arrive(bar_free);   // this warp holds its logits: the accumulators can take the next tile
       ok = mbar_wait(&bar_in[qstg], (j / G::NQ) & 1, a.err, 32) && ok;   // the tile's row statistics
       if (HB) ok = mbar_wait(&bar_bias[stg], (j >> 1) & 1, a.err, 34) && ok;
 
@@ -681,32 +674,49 @@ attn_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_const
       const float4* sD4 = sM4 + 32;
       const int c = hh;
       uint32_t pw[16], dw[16];
+      // 16 of this thread's 32 queries
+      auto half = [&](const uint32_t (&rs)[16], const uint32_t (&rp)[16], int h2) {
 #pragma unroll
-      for (int u = 0; u < 4; ++u) {
-        uint4 raw = make_uint4(0, 0, 0, 0);
-        if constexpr (HB) raw = *reinterpret_cast<const uint4*>(sPTj + sw128_chunk1(r, c * 4 + u));
-        const uint32_t bw[4] = {raw.x, raw.y, raw.z, raw.w};
-        const float4 m0 = sM4[c * 8 + u * 2], m1 = sM4[c * 8 + u * 2 + 1];
-        const float4 l0 = sL4[c * 8 + u * 2], l1 = sL4[c * 8 + u * 2 + 1];
-        const float4 d0 = sD4[c * 8 + u * 2], d1 = sD4[c * 8 + u * 2 + 1];
-        const float2 nm[4] = {make_float2(m0.x, m0.y), make_float2(m0.z, m0.w), make_float2(m1.x, m1.y), make_float2(m1.z, m1.w)};
-        const float2 nl[4] = {make_float2(l0.x, l0.y), make_float2(l0.z, l0.w), make_float2(l1.x, l1.y), make_float2(l1.z, l1.w)};
-        const float2 nd[4] = {make_float2(d0.x, d0.y), make_float2(d0.z, d0.w), make_float2(d1.x, d1.y), make_float2(d1.z, d1.w)};
+        for (int uu = 0; uu < 2; ++uu) {
+          const int u = h2 * 2 + uu;
+          uint4 raw = make_uint4(0, 0, 0, 0);
+          if constexpr (HB) raw = *reinterpret_cast<const uint4*>(sPTj + sw128_chunk1(r, c * 4 + u));
+          const uint32_t bw[4] = {raw.x, raw.y, raw.z, raw.w};
+          const float4 m0 = sM4[c * 8 + u * 2], m1 = sM4[c * 8 + u * 2 + 1];
+          const float4 l0 = sL4[c * 8 + u * 2], l1 = sL4[c * 8 + u * 2 + 1];
+          const float4 d0 = sD4[c * 8 + u * 2], d1 = sD4[c * 8 + u * 2 + 1];
+          const float2 nm[4] = {make_float2(m0.x, m0.y), make_float2(m0.z, m0.w), make_float2(m1.x, m1.y), make_float2(m1.z, m1.w)};
+          const float2 nl[4] = {make_float2(l0.x, l0.y), make_float2(l0.z, l0.w), make_float2(l1.x, l1.y), make_float2(l1.z, l1.w)};
+          const float2 nd[4] = {make_float2(d0.x, d0.y), make_float2(d0.z, d0.w), make_float2(d1.x, d1.y), make_float2(d1.z, d1.w)};
 #pragma unroll
-        for (int i = 0; i < 4; ++i) {
-          float2 x = __ffma2_rn(pair(rs[u * 8 + 2 * i], rs[u * 8 + 2 * i + 1]), sc2, mk2);
-          if constexpr (HB) x = __fadd2_rn(x, unpack2<T>(bw[i]));
-          const float2 e = __ffma2_rn(__fadd2_rn(x, nm[i]), l2e2, nl[i]);
-          const float2 pp = make_float2(ex2_approx(e.x), ex2_approx(e.y));
-          const float2 ds = __fmul2_rn(pp, __fadd2_rn(pair(rp[u * 8 + 2 * i], rp[u * 8 + 2 * i + 1]), nd[i]));
-          pw[u * 4 + i] = pack2<T>(pp.x, pp.y);
-          dw[u * 4 + i] = pack2<T>(ds.x, ds.y);
+          for (int i = 0; i < 4; ++i) {
+            float2 x = __ffma2_rn(pair(rs[uu * 8 + 2 * i], rs[uu * 8 + 2 * i + 1]), sc2, mk2);
+            if constexpr (HB) x = __fadd2_rn(x, unpack2<T>(bw[i]));
+            const float2 e = __ffma2_rn(__fadd2_rn(x, nm[i]), l2e2, nl[i]);
+            const float2 pp = make_float2(ex2_approx(e.x), ex2_approx(e.y));
+            const float2 ds = __fmul2_rn(pp, __fadd2_rn(pair(rp[uu * 8 + 2 * i], rp[uu * 8 + 2 * i + 1]), nd[i]));
+            pw[u * 4 + i] = pack2<T>(pp.x, pp.y);
+            dw[u * 4 + i] = pack2<T>(ds.x, ds.y);
+          }
+          if constexpr (!TMEM_A) {
+            *reinterpret_cast<uint4*>(sPTj + sw128_chunk1(r, c * 4 + u)) = make_uint4(pw[u * 4], pw[u * 4 + 1], pw[u * 4 + 2], pw[u * 4 + 3]);
+            *reinterpret_cast<uint4*>(sDSTj + sw128_chunk1(r, c * 4 + u)) = make_uint4(dw[u * 4], dw[u * 4 + 1], dw[u * 4 + 2], dw[u * 4 + 3]);
+          }
         }
-        if constexpr (!TMEM_A) {
-          *reinterpret_cast<uint4*>(sPTj + sw128_chunk1(r, c * 4 + u)) = make_uint4(pw[u * 4], pw[u * 4 + 1], pw[u * 4 + 2], pw[u * 4 + 3]);
-          *reinterpret_cast<uint4*>(sDSTj + sw128_chunk1(r, c * 4 + u)) = make_uint4(dw[u * 4], dw[u * 4 + 1], dw[u * 4 + 2], dw[u * 4 + 3]);
-        }
-      }
+      };
+      // the second half's TMEM loads are in flight while the first half is computed
+      uint32_t rsA[16], rpA[16], rsB[16], rpB[16];
+      tmem_ld_32x16(t_row + hh * 32, rsA);
+      tmem_ld_32x16(t_row + COL_DP + hh * 32, rpA);
+      tmem_ld_wait();
+      tmem_ld_32x16(t_row + hh * 32 + 16, rsB);
+      tmem_ld_32x16(t_row + COL_DP + hh * 32 + 16, rpB);
+      half(rsA, rpA, 0);
+      tmem_ld_wait();
+      tc_fence_before_sync();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(bar_free);   // this warp holds its logits: the accumulators can take the next tile
+      half(rsB, rpB, 1);
       if constexpr (TMEM_A) {
         if (j > 0) ok = mbar_wait(&bar_acc[(j - 1) & 3], ((j - 1) >> 2) & 1, a.err, 35) && ok;   // the previous tile's products have read theirs
         tc_fence_after_sync();
