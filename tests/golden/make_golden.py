@@ -84,8 +84,9 @@ def trimul_case(name, lead, N, C, Ch, direction, *, biases=False, with_mask=True
 
 
 def main():
-    root = sys.argv[1] if len(sys.argv) > 1 else "/root/reference"
-    sys.path.insert(0, root)
+    if len(sys.argv) != 2:
+        sys.exit("usage: python make_golden.py <checkout of the reference project>")
+    sys.path.insert(0, sys.argv[1])
     from geometric_nn_ops_torch.triangle._reference.triangle_attention import (
         triangle_attention_torch,
     )
