@@ -38,9 +38,10 @@ enum Epilogue {
 
 constexpr int kBM = 128;
 constexpr int kStageA = kBM * 128;  // bytes
-// warp 0 producer, warp 1 MMA, then the epilogue warps: 8 for the plain store, 16 for the gate epilogues, whose
-// per-element arithmetic (sigmoid, products) is latency-bound with fewer warps per scheduler
-constexpr int gemm_epi_warps(int epi) { return epi == 0 ? 8 : 16; }
+// warp 0 producer, warp 1 MMA, then the epilogue warps: 16 for the gate-in, gate-out and gate-out backward
+// epilogues, whose per-element arithmetic (sigmoid, products) is latency-bound with fewer warps per scheduler; 8 for
+// the plain store and for gate-in backward (which spends its registers on a tile-ahead prefetch instead)
+constexpr int gemm_epi_warps(int epi) { return (epi == 0 || epi == 4) ? 8 : 16; }
 constexpr int gemm_threads(int epi) { return 64 + 32 * gemm_epi_warps(epi); }
 
 struct GemmArgs {
@@ -341,11 +342,13 @@ tc_gemm_kernel(const __grid_constant__ CUtensorMap tmA0, const __grid_constant__
     const int row = quarter * 32 + lane;
     int acc = 0;
     uint32_t acc_phase = 0;
-    for (int tile = blockIdx.x; tile < total; tile += gridDim.x) {
+    // The backward gate epilogues read a gradient tile from global memory.  Gate-in backward fetches it a whole tile
+    // ahead (the loads of tile t+1 are issued before tile t's arithmetic): its warps are too few to hide a load
+    // issued just before its use.
+    constexpr bool kGradTile = EPI == EPI_GATE_IN_BWD || EPI == EPI_GATE_OUT_BWD;
+    auto fetch_grad = [&](int t, Raw8<TIN> (&dst)[CPG][4]) {
       int tm, tn, bz;
-      decode(tile, tm, tn, bz);
-      // the backward gate epilogues read a gradient tile from global memory: fetch it before waiting for the product
-      Raw8<TIN> dpre[CPG][4];
+      decode(t, tm, tn, bz);
       if constexpr (EPI == EPI_GATE_IN_BWD) {
         const TIN* dplane = reinterpret_cast<const TIN*>(tm == 0 ? g.aux2 : g.aux3);
         const long long t0 = (long long)tn * 128, tb0 = t0 / g.plane, tp0 = t0 - tb0 * g.plane;   // one division per tile
@@ -360,10 +363,10 @@ tc_gemm_kernel(const __grid_constant__ CUtensorMap tmA0, const __grid_constant__
               while (pix >= g.plane) { pix -= g.plane; ++bb; }
               const TIN* src = dplane + (bb * 128 + row) * g.plane + pix;
               if constexpr (sizeof(TIN) == 2) {
-                if (wide) { if ((u & 1) == 0) ldraw16<TIN>(src, dpre[jj][u], dpre[jj][u + 1]); }
-                else dpre[jj][u] = ldraw8<TIN>(src);
+                if (wide) { if ((u & 1) == 0) ldraw16<TIN>(src, dst[jj][u], dst[jj][u + 1]); }
+                else dst[jj][u] = ldraw8<TIN>(src);
               } else {
-                dpre[jj][u] = ldraw8<TIN>(src);
+                dst[jj][u] = ldraw8<TIN>(src);
               }
             }
           }
@@ -376,13 +379,34 @@ tc_gemm_kernel(const __grid_constant__ CUtensorMap tmA0, const __grid_constant__
 #pragma unroll
             for (int u = 0; u < 4; u += 2) {
               if constexpr (sizeof(TIN) == 2) {   // rows of 256 bytes: 32-byte loads are aligned
-                ldraw16<TIN>(dout + (grp * CPG + jj) * 32 + u * 8, dpre[jj][u], dpre[jj][u + 1]);
+                ldraw16<TIN>(dout + (grp * CPG + jj) * 32 + u * 8, dst[jj][u], dst[jj][u + 1]);
               } else {
-                dpre[jj][u] = ldraw8<TIN>(dout + (grp * CPG + jj) * 32 + u * 8);
-                dpre[jj][u + 1] = ldraw8<TIN>(dout + (grp * CPG + jj) * 32 + u * 8 + 8);
+                dst[jj][u] = ldraw8<TIN>(dout + (grp * CPG + jj) * 32 + u * 8);
+                dst[jj][u + 1] = ldraw8<TIN>(dout + (grp * CPG + jj) * 32 + u * 8 + 8);
               }
             }
         }
+      }
+    };
+    // (gate-in backward: 8 epilogue warps with registers to spare; gate-out backward, on 16 warps and already at 70 %
+    // of HBM bandwidth, fetches its tile just before waiting for the product)
+    constexpr bool kAhead = EPI == EPI_GATE_IN_BWD && sizeof(TIN) == 2;   // (fp32 tiles would not fit the registers twice)
+    Raw8<TIN> dnext[kAhead ? CPG : 1][4];
+    if constexpr (kAhead) {
+      if ((int)blockIdx.x < total) fetch_grad(blockIdx.x, dnext);
+    }
+    for (int tile = blockIdx.x; tile < total; tile += gridDim.x) {
+      int tm, tn, bz;
+      decode(tile, tm, tn, bz);
+      Raw8<TIN> dpre[CPG][4];
+      if constexpr (kAhead) {
+#pragma unroll
+        for (int jj = 0; jj < CPG; ++jj)
+#pragma unroll
+          for (int u = 0; u < 4; ++u) dpre[jj][u] = dnext[jj][u];
+        if (tile + (int)gridDim.x < total) fetch_grad(tile + gridDim.x, dnext);
+      } else if constexpr (kGradTile) {
+        fetch_grad(tile, dpre);
       }
       if (!mbar_wait(&tfull[acc], acc_phase, g.err, 4)) break;
       tc_fence_after_sync();
