@@ -106,15 +106,24 @@ _PEER = {}            # (tag, bytes, device, group) -> (buffer, peer pointer arr
 _PEER_STATE = {"enabled": None}
 
 
-def peer_exchange_enabled(device):
-    """True when the exchanges can use peer stores: CUDA, NCCL, symmetric memory; TRI_B200_EXCHANGE=nccl turns it off."""
+def peer_exchange_enabled(device, group=None):
+    """True when the exchanges can use peer stores: CUDA, NCCL, symmetric memory; TRI_B200_EXCHANGE=nccl turns it off.
+
+    The first call tries a small symmetric allocation and lets the ranks agree on the outcome (a MIN all-reduce), so
+    that either every rank takes the peer-store route or every rank takes the all-to-all.
+    """
     if _PEER_STATE["enabled"] is None:
         ok = os.environ.get("TRI_B200_EXCHANGE", "peer") in ("peer", "fused") and device.type == "cuda" and dist.get_backend() == "nccl"
         if ok:
             try:
-                import torch.distributed._symmetric_memory  # noqa: F401
-            except Exception:
-                ok = False
+                _peer_buffer("probe", 4096, device, group)
+                good = 1.0
+            except Exception as exc:   # no symmetric memory on this system: use the collective route
+                print(f"[sharded] peer-store exchange unavailable ({exc!r}); using all-to-all", flush=True)
+                good = 0.0
+            flag = torch.tensor([good], device=device)
+            dist.all_reduce(flag, op=dist.ReduceOp.MIN, group=group)
+            ok = bool(flag.item() > 0.5)
         _PEER_STATE["enabled"] = ok
     return _PEER_STATE["enabled"]
 
@@ -163,7 +172,7 @@ def rows_to_channels(t, group=None, tag="rows_to_channels", persist=True):
     if Ch % world != 0:
         raise ValueError(f"{Ch} channels are not divisible by {world} ranks")
     cs = Ch // world
-    if world > 1 and peer_exchange_enabled(t.device):
+    if world > 1 and peer_exchange_enabled(t.device, group):
         # run (l, w, c) of the source -> GPU w, run ((l*cs + c)*world + me) of its [L, cs, world, R*N] buffer
         return _peer_scatter(t, (L, world, cs), (cs * world, 0, world), me, 1, R * N, (L, cs, world * R, N), tag, group, persist)
     with _timed("rows_to_channels.pack"):
@@ -182,7 +191,7 @@ def channels_to_rows(t, group=None, tag="channels_to_rows", persist=True):
     if rows % world != 0:
         raise ValueError(f"{rows} rows are not divisible by {world} ranks")
     R = rows // world
-    if world > 1 and peer_exchange_enabled(t.device):
+    if world > 1 and peer_exchange_enabled(t.device, group):
         # run (l, c, w) of the source -> GPU w, run ((l*world + me)*cs + c) of its [L, world, cs, R*N] buffer
         return _peer_scatter(t, (L, cs, world), (world * cs, 1, 0), me * cs, 2, R * N, (L, world * cs, R, N), tag, group, persist)
     with _timed("channels_to_rows.pack"):
@@ -296,7 +305,7 @@ class _ShardedTriMul(torch.autograd.Function):
         bufs = _lib.TriMulShardBufs()
         bufs.x, bufs.mask, bufs.w, bufs.saved = xc.data_ptr(), None if mc is None else mc.data_ptr(), ctypes.pointer(w), saved.data_ptr()
         world, me = _world(group)
-        if world > 1 and peer_exchange_enabled(x.device) and os.environ.get("TRI_B200_EXCHANGE") == "fused":
+        if world > 1 and peer_exchange_enabled(x.device, group) and os.environ.get("TRI_B200_EXCHANGE") == "fused":
             # compute and exchange in one kernel: the gate-in epilogue stores a and b straight into the channel
             # owners' buffers; the one-element all-reduce orders "all ranks have stored" before "anyone reads".
             # Opt-in: at 2 GPUs it measured 6.1 ms per step against 5.95 ms for GEMM + copy kernel (32-byte
