@@ -3,6 +3,7 @@
 #include <algorithm>
 #include <atomic>
 #include <cstring>
+#include <initializer_list>
 #include <mutex>
 #include <map>
 #include <string>
@@ -43,6 +44,21 @@ KernelTimer::~KernelTimer() {
   if (g_prof != nullptr && slot < (int)g_prof->size()) cudaEventRecord((*g_prof)[slot].end, st);
 }
 
+int sm_count() {
+  constexpr int kMaxDevices = 64;
+  static std::atomic<int> cache[kMaxDevices];   // zero-initialised; 0 = not queried yet
+  int dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess) return 148;
+  if (dev >= 0 && dev < kMaxDevices) {
+    const int n = cache[dev].load(std::memory_order_relaxed);
+    if (n > 0) return n;
+  }
+  int n = 0;
+  if (cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || n <= 0) n = 148;
+  if (dev >= 0 && dev < kMaxDevices) cache[dev].store(n, std::memory_order_relaxed);
+  return n;
+}
+
 char* last_error_buf() { return g_err; }
 void set_path(const char* name) { g_path.store(name); }
 void count_launch(int n) { g_launches += n; }
@@ -73,6 +89,20 @@ static int check_mul(const TriMulDesc* d) {
   if ((long long)d->B * d->N * d->N * 2 * std::max(d->C, d->Ch) > 2147483647LL * 8)
     return fail(TRI_ERR_UNSUPPORTED, "pair tensor too large");
   return 0;
+}
+
+// What the tensor-core attention kernels need beyond the descriptor: every tensor they reach through a tensor map
+// starts on a 16-byte boundary, and a bias that is present is not a broadcast view over heads or queries (its batch
+// stride may be zero).  Anything else runs on the CUDA-core kernels, which take any pointer and stride.
+static bool attn_operands_fit_tma(const TriAttnDesc* d, const void* bias, std::initializer_list<const void*> ptrs) {
+  for (const void* p : ptrs)
+    if ((reinterpret_cast<uintptr_t>(p) & 15) != 0) return false;
+  if (bias != nullptr) {
+    if ((reinterpret_cast<uintptr_t>(bias) & 15) != 0) return false;
+    if (d->bias_st[1] == 0 && d->H > 1) return false;
+    if (d->bias_st[2] == 0 && d->n_res > 1) return false;
+  }
+  return true;
 }
 
 }  // namespace tri
@@ -132,7 +162,7 @@ int tri_attn_fwd(const TriAttnDesc* d, const void* q, const void* k, const void*
                  const uint8_t* mask, void* o, float* lse, void* ws, size_t ws_bytes, tri_stream_t stream) {
   TRI_TRY(check_attn(d));
   if (!q || !k || !v || !o || !lse) return fail(TRI_ERR_ARG, "q, k, v, o and lse must not be null");
-  if (tc::attn_fwd_supported(d)) {
+  if (tc::attn_fwd_supported(d) && attn_operands_fit_tma(d, bias, {q, k, v})) {
     set_path("tcgen05");
     return tc::attn_forward(d, q, k, v, bias, mask, o, lse, ws, ws_bytes, (cudaStream_t)stream);
   }
@@ -146,7 +176,7 @@ int tri_attn_bwd(const TriAttnDesc* d, const void* q, const void* k, const void*
   TRI_TRY(check_attn(d));
   if (!q || !k || !v || !o || !lse || !d_o || !dq || !dk || !dv || !ws)
     return fail(TRI_ERR_ARG, "q, k, v, o, lse, d_o, dq, dk, dv and ws must not be null");
-  if (tc::attn_bwd_supported(d)) {
+  if (tc::attn_bwd_supported(d) && attn_operands_fit_tma(d, bias, {q, k, v, d_o})) {
     set_path("tcgen05");
     return tc::attn_backward(d, q, k, v, bias, mask, o, lse, d_o, dq, dk, dv, dbias, ws, ws_bytes,
                              (cudaStream_t)stream);

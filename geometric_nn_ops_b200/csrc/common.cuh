@@ -79,6 +79,10 @@ __device__ __forceinline__ float round_tf32(float v) {
 
 __device__ __forceinline__ float sigmoidf_acc(float v) { return 1.0f / (1.0f + expf(-v)); }
 
+// Multiprocessors of the CURRENT device.  Cached per device: one process may drive several GPUs (one thread each,
+// or autograd's backward thread), so neither this nor any launch attribute may be remembered process-wide.
+int sm_count();
+
 inline size_t dtype_size(int dtype) { return dtype == TRI_F32 ? 4 : 2; }
 inline size_t align_up(size_t v, size_t a = 256) { return (v + a - 1) / a * a; }
 inline int cdiv(long long a, long long b) { return (int)((a + b - 1) / b); }

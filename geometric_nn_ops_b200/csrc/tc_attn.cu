@@ -1237,17 +1237,6 @@ __global__ void sum_partials_kernel(const float* partial, int nparts, long long 
   out[i] = s;
 }
 
-// multiprocessors of the current device (persistent kernels launch two CTAs per SM)
-int sm_count() {
-  static int n = 0;
-  if (n == 0) {
-    int dev = 0;
-    cudaGetDevice(&dev);
-    cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev);
-  }
-  return n;
-}
-
 constexpr int kDbiasRowChunks = 8;   // at most this many row chunks (the workspace holds one partial sum per chunk)
 
 // rank-5 map with a caller-chosen number of residues per box
@@ -1351,8 +1340,7 @@ int bwd_launch(const TriAttnDesc* d, const void* q, const void* k, const void* v
   a.idesc_b = make_idesc(kind, 128, HD, false, true);
   {
     auto kern = bias ? attn_bwd_dkdv_kernel<T, HD, true> : attn_bwd_dkdv_kernel<T, HD, false>;
-    static bool configured[2] = {false, false};
-    if (!configured[bias != nullptr]) { TRI_TRY(set_dyn_smem(kern, GeoC<HD>::SMEM)); configured[bias != nullptr] = true; }
+    TRI_TRY(set_dyn_smem(kern, GeoC<HD>::SMEM));   // per-device attribute: set on every launch
     KernelTimer kt("tc_attn_bwd_dkdv", st, 8.0 * pairs * d->D, 6.0 * tensor_bytes);
     kern<<<(unsigned)((long long)qblocks * d->B * d->n_seq * d->H), 320, GeoC<HD>::SMEM, st>>>(tq, tdo, tk, tv, tb, a);
     TRI_LAUNCH_OK();
@@ -1369,8 +1357,7 @@ int bwd_launch(const TriAttnDesc* d, const void* q, const void* k, const void* v
   a.idesc_b = make_idesc(kind, 128, HD, false, true);
   {
     auto kern = bias ? attn_bwd_dq_kernel<T, HD, true> : attn_bwd_dq_kernel<T, HD, false>;
-    static bool configured[2] = {false, false};
-    if (!configured[bias != nullptr]) { TRI_TRY(set_dyn_smem(kern, GeoQ<HD>::SMEM)); configured[bias != nullptr] = true; }
+    TRI_TRY(set_dyn_smem(kern, GeoQ<HD>::SMEM));
     KernelTimer kt("tc_attn_bwd_dq", st, 2.0 * pairs * d->D, 5.0 * tensor_bytes);
     kern<<<(unsigned)((long long)qblocks * d->B * d->n_seq * d->H), 320, GeoQ<HD>::SMEM, st>>>(tq, tdo, tk, tv, tb, a);
     TRI_LAUNCH_OK();
@@ -1389,8 +1376,7 @@ int bwd_launch(const TriAttnDesc* d, const void* q, const void* k, const void* v
     a.out0 = chunks > 1 ? dbias_partial : dbias;
     a.idesc_a = make_idesc(kind, 128, 64, false, false);
     auto kern = attn_bwd_dbias_kernel<T, HD>;   // (K / V maps with 64-key boxes and the bias map are those of the dQ pass)
-    static bool configured = false;
-    if (!configured) { TRI_TRY(set_dyn_smem(kern, GeoB<HD>::SMEM)); configured = true; }
+    TRI_TRY(set_dyn_smem(kern, GeoB<HD>::SMEM));
     KernelTimer kt("tc_attn_bwd_dbias", st, 0.0, 4.0 * tensor_bytes);
     kern<<<(unsigned)((long long)qblocks * kblocks * d->B * d->H * chunks), 320, GeoB<HD>::SMEM, st>>>(tq, tdo, tk, tv, tb, a);
     TRI_LAUNCH_OK();
@@ -1407,9 +1393,14 @@ bool forced_simt() {
   return e != nullptr && e[0] == '1';
 }
 
-bool strides_ok(const int64_t* st) {
-  for (int i = 0; i < 4; ++i)
+// A tensor map needs strides that are non-zero multiples of 16 bytes on every axis with more than one entry; a
+// broadcast (zero-stride) view therefore goes to the CUDA-core kernels, which take any stride.
+bool strides_ok(const TriAttnDesc* d, const int64_t* st) {
+  const int extent[4] = {d->B, d->n_seq, d->n_res, d->H};
+  for (int i = 0; i < 4; ++i) {
     if (st[i] % 8 != 0) return false;
+    if (st[i] == 0 && extent[i] > 1) return false;
+  }
   return true;
 }
 
@@ -1455,11 +1446,7 @@ int fwd_launch(const TriAttnDesc* d, const void* q, const void* k, const void* v
   const double pairs = (double)d->B * d->n_seq * d->H * d->n_res * (double)d->n_res;
   KernelTimer kt("tc_attn_fwd", st, 4.0 * pairs * d->D, 2.0 * 4.0 * d->B * d->n_seq * (double)d->n_res * d->H * d->D);
   auto kern = bias != nullptr ? attn_fwd_tc_kernel<T, HD, true> : attn_fwd_tc_kernel<T, HD, false>;
-  static bool configured[2] = {false, false};
-  if (!configured[bias != nullptr]) {
-    TRI_CUDA_OK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, Geo<HD>::SMEM));
-    configured[bias != nullptr] = true;
-  }
+  TRI_CUDA_OK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, Geo<HD>::SMEM));
   kern<<<(unsigned)std::min<long long>(blocks, 2LL * sm_count()), 320, Geo<HD>::SMEM, st>>>(tq, tk, tv, tb, a);
   TRI_LAUNCH_OK();
   return 0;
@@ -1472,15 +1459,15 @@ bool attn_fwd_supported(const TriAttnDesc* d) {
   if (d->dtype != TRI_BF16 && d->dtype != TRI_F16) return false;
   if (d->D != 32 && d->D != 64) return false;
   if (d->n_res % 8 != 0 || d->n_res > 16384) return false;
-  if (!strides_ok(d->q_st) || !strides_ok(d->k_st) || !strides_ok(d->v_st) || !strides_ok(d->o_st)) return false;
+  if (!strides_ok(d, d->q_st) || !strides_ok(d, d->k_st) || !strides_ok(d, d->v_st) || !strides_ok(d, d->o_st)) return false;
   if (d->bias_st[1] % 8 != 0 || d->bias_st[2] % 8 != 0 || d->bias_st[0] % 8 != 0) return false;
   if ((long long)((d->n_res + 127) / 128) * d->B * d->n_seq * d->H > 2147483647LL) return false;
   return true;
 }
 
 bool attn_bwd_supported(const TriAttnDesc* d) {
-  return attn_fwd_supported(d) && strides_ok(d->do_st) && strides_ok(d->dq_st) && strides_ok(d->dk_st) &&
-         strides_ok(d->dv_st) && d->n_seq <= 65535;
+  return attn_fwd_supported(d) && strides_ok(d, d->do_st) && strides_ok(d, d->dq_st) && strides_ok(d, d->dk_st) &&
+         strides_ok(d, d->dv_st) && d->n_seq <= 65535;
 }
 
 static size_t attn_npad(const TriAttnDesc* d) { return ((size_t)d->n_res + 127) / 128 * 128; }

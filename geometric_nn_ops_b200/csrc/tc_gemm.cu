@@ -24,17 +24,6 @@ EncodeFn encode_fn() {
   return fn;
 }
 
-int sm_count() {
-  static int n = 0;
-  if (n == 0) {
-    int dev = 0;
-    cudaGetDevice(&dev);
-    cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev);
-    if (n <= 0) n = 148;
-  }
-  return n;
-}
-
 }  // namespace
 
 int make_tmap_3d(CUtensorMap* out, const void* base, int elem_bytes, bool is_f16, const uint64_t dims[3],
@@ -107,11 +96,9 @@ static int launch_t(cudaStream_t st, const CUtensorMap* maps, const GemmArgs& g,
   constexpr int STAGES = BN == 256 ? 4 : 6;
   constexpr size_t smem = 1024 + (size_t)STAGES * (kStageA + BN * 128) + (2 * STAGES + 4) * 8 + 16;
   auto kern = tc_gemm_kernel<TIN, TOUT, BN, EPI, STAGES>;
-  static bool configured = false;
-  if (!configured) {
-    TRI_CUDA_OK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
-    configured = true;
-  }
+  // The opt-in to more than 48 KB of dynamic shared memory is a per-device attribute: set it on every launch
+  // (a host-side call of about a microsecond) instead of remembering it process-wide.
+  TRI_CUDA_OK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
   const int total = g.batches * g.tiles_m * g.tiles_n;
   const int grid = std::min(total, sm_count());
   KernelTimer kt(p.name, st, p.flops, p.bytes);

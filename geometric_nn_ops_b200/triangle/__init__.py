@@ -1,9 +1,11 @@
 """Triangle (protein-folding) ops, B200 implementation."""
 
+from ._attention_pair_bias import attention_pair_bias
 from ._triattn import triangle_attention, triangle_attention_b200
 from ._trimul import triangle_multiplicative_update, trimul_b200
 
 __all__ = [
+    "attention_pair_bias",
     "triangle_attention",
     "triangle_attention_b200",
     "triangle_multiplicative_update",

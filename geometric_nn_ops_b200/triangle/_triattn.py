@@ -96,10 +96,11 @@ class _TriangleAttention(torch.autograd.Function):
             _lib.check_device_status(ws, stream)
         ctx.save_for_backward(q, k, v, bias, mask_u8, o, lse)
         ctx.scale, ctx.precision = scale, precision
-        return o
+        ctx.mark_non_differentiable(lse)
+        return o, lse
 
     @staticmethod
-    def backward(ctx, d_o):
+    def backward(ctx, d_o, _d_stats=None):
         lib = _lib.load()
         q, k, v, bias, mask_u8, o, lse = ctx.saved_tensors
         B, S, N, H, D = q.shape
@@ -123,21 +124,40 @@ class _TriangleAttention(torch.autograd.Function):
         return dq, dk, dv, grad_bias, None, None
 
 
-def triangle_attention_b200(q, k, v, bias=None, mask=None, scale=None, dynamic=False, use_exp2=False):
+def _aux(stats):
+    """Softmax statistics ``[2, B, N_seq, H, N_res]`` (row maximum, log row sum) -> ``(lse, max)``, each
+    ``[B, N_seq, H, N_res, 1]`` fp32, the cuequivariance ``(B, N, H, Q, 1)`` layout.
+
+    ``lse`` is exact.  ``max`` is the reference point the kernel used for the exponentials: the exact row maximum on
+    the CUDA-core path; on the tensor-core path, which rescales its accumulator only when the maximum grows by more
+    than ``8 ln 2``, a value between ``max - 8 ln 2`` and ``max``."""
+    m, log_l = stats[0], stats[1]
+    return (m + log_l).unsqueeze(-1), m.unsqueeze(-1)
+
+
+def triangle_attention_b200(q, k, v, bias=None, mask=None, scale=None, dynamic=False, use_exp2=False,
+                            return_aux=False):
     """Kernel-level entry on canonical 5-D shapes.
 
     ``q, k, v``: ``[B, N_seq, N_res, H, D]``; ``bias``: ``[B, 1, H, N_res, N_res]`` (batch may be
     a broadcast view); ``mask``: bool ``[B, N_seq, 1, 1, N_res]``, ``True`` keeps.
     ``dynamic`` and ``use_exp2`` are accepted for signature compatibility; the CUDA kernels
     take shapes at run time, so both settings give the same result.
+    ``return_aux=True`` returns ``(out, lse, max)``: the log-sum-exp and the maximum of each query's
+    logits, fp32 ``[B, N_seq, H, N_res, 1]``, not differentiable.  (The reference's kernels do not expose
+    them and its cuequivariance shim raises for ``return_aux``,
+    ``cuequivariance_ops_torch/triangle_attention.py:34-38``; these kernels write them anyway.)
     """
     del dynamic, use_exp2
     if scale is None:
         scale = q.shape[-1] ** -0.5
-    return _TriangleAttention.apply(q, k, v, bias, mask, float(scale))
+    o, stats = _TriangleAttention.apply(q, k, v, bias, mask, float(scale))
+    if return_aux:
+        return (o, *_aux(stats))
+    return o
 
 
-def triangle_attention(q, k, v, bias=None, mask=None, scale=None, dynamic=False, use_exp2=False):
+def triangle_attention(q, k, v, bias=None, mask=None, scale=None, dynamic=False, use_exp2=False, return_aux=False):
     """Triangle attention with the reference's (cuequivariance-compatible) signature.
 
     Args:
@@ -146,7 +166,8 @@ def triangle_attention(q, k, v, bias=None, mask=None, scale=None, dynamic=False,
         mask: bool, ``True`` keeps; broadcastable to ``[B, N_seq, 1, 1, N_res]``, or ``None``.
         scale: softmax scale, default ``D ** -0.5``.
 
-    Returns a tensor of q's shape and dtype.  fp32 matmuls follow
+    Returns a tensor of q's shape and dtype; with ``return_aux=True`` also the log-sum-exp and the
+    maximum of every query's logits (fp32, ``[B, N_seq, H, N_res, 1]``).  fp32 matmuls follow
     ``torch.backends.cuda.matmul.fp32_precision``.
     """
     if mask is not None and mask.dtype != torch.bool:
@@ -172,8 +193,11 @@ def triangle_attention(q, k, v, bias=None, mask=None, scale=None, dynamic=False,
         mask = mask.broadcast_to(B, S, 1, 1, N)
 
     compute = orig_dtype if orig_dtype in _DTYPES else torch.float32
-    o = triangle_attention_b200(
+    res = triangle_attention_b200(
         q.to(compute), k.to(compute), v.to(compute),
-        None if bias is None else bias.to(compute), mask, scale, dynamic, use_exp2,
+        None if bias is None else bias.to(compute), mask, scale, dynamic, use_exp2, return_aux,
     )
-    return o.to(orig_dtype).reshape(orig_shape)
+    if return_aux:
+        o, lse, amax = res
+        return o.to(orig_dtype).reshape(orig_shape), lse, amax
+    return res.to(orig_dtype).reshape(orig_shape)

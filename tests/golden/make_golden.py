@@ -83,6 +83,36 @@ def trimul_case(name, lead, N, C, Ch, direction, *, biases=False, with_mask=True
     print("wrote", name, {k_: v_.shape for k_, v_ in rec.items()})
 
 
+def pair_bias_case(name, B, M, H, U, V, DH, Zc, *, mask_batch="B", biases=False, inf=None, seed=0, ref=None):
+    """attention_pair_bias on pre-projected q, k, v (reference: _reference/attention_pair_bias.py:26-89)."""
+    g = torch.Generator().manual_seed(seed)
+    rn = lambda *s, sc=1.0: torch.randn(*s, generator=g, dtype=torch.float32) * sc  # noqa: E731
+    D = H * DH
+    t = dict(s=rn(B * M, U, D), q=rn(B * M, H, U, DH), k=rn(B * M, H, V, DH), v=rn(B * M, H, V, DH), z=rn(B, U, V, Zc),
+             proj_g_weight=rn(D, D, sc=D ** -0.5), proj_o_weight=rn(D, D, sc=D ** -0.5),
+             proj_z_weight=rn(H, Zc, sc=Zc ** -0.5), ln_z_weight=1 + rn(Zc, sc=0.05))
+    if biases:
+        t |= dict(proj_g_bias=rn(D, sc=0.05), proj_o_bias=rn(D, sc=0.05))
+    mask = None
+    if mask_batch is not None:
+        mask = (torch.rand(B if mask_batch == "B" else B * M, V, generator=g) < 0.8).float()
+        mask[:, 0] = 1.0
+    d_out = rn(B * M, U, D)
+    leaves = {n: x.double().requires_grad_() for n, x in t.items()}
+    pos = [leaves[n] for n in ("s", "q", "k", "v", "z")]
+    kw = {n: x for n, x in leaves.items() if n not in ("s", "q", "k", "v", "z")}
+    out, pz = ref(*pos, mask=None if mask is None else mask.double(), inf=inf, return_z_proj=True, **kw)
+    grads = torch.autograd.grad(out, list(leaves.values()), grad_outputs=d_out.double())
+    rec = {"in_" + n: _np(x) for n, x in t.items()}
+    rec |= dict(d_out=_np(d_out), out=_np(out), proj_z=_np(pz), M=np.array(M), inf=np.array(-1.0 if inf is None else inf))
+    if mask is not None:
+        rec["mask"] = _np(mask)
+    for n, gr in zip(leaves, grads):
+        rec["grad_" + n] = _np(gr)
+    np.savez_compressed(os.path.join(HERE, name + ".npz"), **rec)
+    print("wrote", name, {k_: v_.shape for k_, v_ in rec.items()})
+
+
 def main():
     if len(sys.argv) != 2:
         sys.exit("usage: python make_golden.py <checkout of the reference project>")
@@ -92,7 +122,16 @@ def main():
     )
     from geometric_nn_ops_torch.triangle._reference.trimul import trimul_torch
 
+    from geometric_nn_ops_torch.triangle._reference.attention_pair_bias import (
+        attention_pair_bias_torch,
+    )
+
     a, t = triangle_attention_torch, trimul_torch
+    pair_bias_case("apb_self", 2, 3, 2, 16, 16, 8, 12, ref=attention_pair_bias_torch)
+    pair_bias_case("apb_self_bias_maskbm", 1, 2, 4, 24, 24, 16, 8, mask_batch="BM", biases=True, seed=1,
+                   ref=attention_pair_bias_torch)
+    pair_bias_case("apb_cross_inf", 2, 1, 2, 6, 10, 8, 8, inf=1e6, seed=2, ref=attention_pair_bias_torch)
+    pair_bias_case("apb_nomask", 1, 2, 2, 8, 8, 32, 16, mask_batch=None, seed=3, ref=attention_pair_bias_torch)
     attention_case("attn_small", 2, 5, 12, 2, 8, ref=a)
     attention_case("attn_bias_bcast", 2, 3, 9, 3, 16, bias_batch=1, scale=0.3, seed=1, ref=a)
     attention_case("attn_nobias_nomask", 1, 4, 17, 2, 32, with_bias=False, with_mask=False, seed=2, ref=a)

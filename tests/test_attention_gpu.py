@@ -199,3 +199,91 @@ def test_rows_are_independent_at_full_size(ta):
     vmax = t["v"].float().amax(dim=2, keepdim=True)
     vmin = t["v"].float().amin(dim=2, keepdim=True)
     assert (full.float() <= vmax + 1e-2).all() and (full.float() >= vmin - 1e-2).all()
+
+
+# ---- the sizes BASELINE.json times, against the oracle -------------------------------------------------------
+# Rows are independent in triangle attention (a row only shares the pair bias with the others), so a slice of rows at
+# the full N_res = N_seq size runs exactly the tile loops, masks and key counts of the full problem while the fp64
+# oracle stays cheap; the bias gradient is the sum over the rows of the slice.
+@pytest.mark.parametrize("n,rows", [(512, 16), (768, 16), (768, 64)], ids=lambda v: str(v))
+def test_baseline_sizes_row_slice_fwd_bwd(ta, n, rows):
+    """BASELINE config 2 (N=512) and the headline size (N=768): bf16, H=4, D=32, keep 0.95, first key kept."""
+    from geometric_nn_ops_b200 import _lib
+    t, mask, d_out = util.attn_inputs(1, rows, n, 4, 32, torch.bfloat16, seed=n + rows, keep=0.95)
+    out, grads = util.attn_fwd_bwd(ta, t, mask, 32 ** -0.5, d_out)
+    torch.cuda.synchronize()
+    assert _lib.last_path() == "tcgen05"
+    cos_min, fro, mar = _tol(torch.bfloat16, "ieee")
+    o_ref = np.empty(out.shape)
+    g_ref = {k: np.empty(v.shape) for k, v in grads.items()}
+    g_ref["bias"][:] = 0.0
+    for r0 in range(0, rows, 8):      # oracle in row chunks: the fp64 logits of 8 rows are 150 MB at N=768
+        sl = slice(r0, r0 + 8)
+        tt = {k: (v[:, sl] if k != "bias" else v) for k, v in t.items()}
+        o_c, g_c = util.attn_oracle(tt, mask[:, sl], 32 ** -0.5, d_out[:, sl])
+        o_ref[:, sl] = o_c
+        for k in ("q", "k", "v"):
+            g_ref[k][:, sl] = g_c[k]
+        g_ref["bias"] += g_c["bias"]
+    util.check_close("out", out, o_ref, cos_min, fro, mar)
+    for name, val in grads.items():
+        util.check_close("grad_" + name, val, g_ref[name], cos_min, fro, mar)
+
+
+def test_headline_full_size_against_oracle_rows_and_row_additivity(ta):
+    """The full N_seq = N_res = 768 problem bench.py times: a slice of rows of out / dq / dk / dv against the fp64
+    oracle, and the full bias gradient against the sum of the bias gradients of row blocks run on their own."""
+    from geometric_nn_ops_b200 import _lib
+    n = 768
+    t, mask, d_out = util.attn_inputs(1, n, n, 4, 32, torch.bfloat16, seed=11, keep=0.95)
+    out, grads = util.attn_fwd_bwd(ta, t, mask, None, d_out)
+    torch.cuda.synchronize()
+    assert _lib.last_path() == "tcgen05"
+    cos_min, fro, mar = _tol(torch.bfloat16, "ieee")
+    for r0 in (0, 377, 760):
+        sl = slice(r0, r0 + 8)
+        tt = {k: (v[:, sl] if k != "bias" else v) for k, v in t.items()}
+        o_ref, g_ref = util.attn_oracle(tt, mask[:, sl], None, d_out[:, sl])
+        util.check_close("out", out[:, sl], o_ref, cos_min, fro, mar)
+        for name in ("q", "k", "v"):
+            util.check_close("grad_" + name, grads[name][:, sl], g_ref[name], cos_min, fro, mar)
+    acc = torch.zeros_like(grads["bias"], dtype=torch.float32)
+    for r0 in range(0, n, 192):
+        sl = slice(r0, r0 + 192)
+        tt = {k: (v[:, sl].contiguous() if k != "bias" else v) for k, v in t.items()}
+        _, g = util.attn_fwd_bwd(ta, tt, mask[:, sl].contiguous(), None, d_out[:, sl].contiguous())
+        acc += g["bias"].float()
+    # each block's gradient is rounded to bf16 before it is summed here: four roundings against one
+    util.check_close("grad_bias", grads["bias"], util.f64(acc), 1 - 1e-5, 6e-3)
+
+
+@pytest.mark.parametrize("broadcast", ["heads", "queries", "heads+queries"])
+def test_broadcast_bias_views_bf16(ta, broadcast):
+    """A bias handed in as a broadcast view over heads or queries (zero strides) has no tensor map: the call must run
+    (on the CUDA-core kernels) and agree with the oracle, forward and backward, not fail."""
+    B, S, N, H, D = 1, 4, 64, 4, 32
+    t, mask, d_out = util.attn_inputs(B, S, N, H, D, torch.bfloat16, seed=12)
+    shape = {"heads": (B, 1, 1, N, N), "queries": (B, 1, H, 1, N), "heads+queries": (B, 1, 1, 1, N)}[broadcast]
+    small = torch.randn(shape, generator=torch.Generator().manual_seed(1)).to(torch.bfloat16).cuda().requires_grad_()
+    q, k, v = (t[n].clone().requires_grad_() for n in ("q", "k", "v"))
+    out = ta(q, k, v, small, mask)
+    gq, gk, gv, gb = torch.autograd.grad(out, [q, k, v, small], grad_outputs=d_out)
+    tt = dict(t, bias=small.detach().expand(B, 1, H, N, N).contiguous())
+    o_ref, g_ref = util.attn_oracle(tt, mask, None, d_out)
+    cos_min, fro, mar = _tol(torch.bfloat16, "ieee")
+    util.check_close("out", out, o_ref, cos_min, fro, mar)
+    for name, val in (("q", gq), ("k", gk), ("v", gv)):
+        util.check_close("grad_" + name, val, g_ref[name], cos_min, fro, mar)
+    dims = tuple(i for i, (a, b) in enumerate(zip(shape, (B, 1, H, N, N))) if a != b)
+    util.check_close("grad_bias", gb, g_ref["bias"].sum(axis=dims, keepdims=True), cos_min, fro, mar)
+
+
+def test_pairformer_point_h16_d48(ta):
+    """The pairformer-style point of the reference's grid (tests/test_triangle_attention.py:591-608): H=16, D=48."""
+    t, mask, d_out = util.attn_inputs(1, 4, 384, 16, 48, torch.bfloat16, seed=13, keep=0.9)
+    out, grads = util.attn_fwd_bwd(ta, t, mask, None, d_out)
+    o_ref, g_ref = util.attn_oracle(t, mask, None, d_out)
+    cos_min, fro, mar = _tol(torch.bfloat16, "ieee")
+    util.check_close("out", out, o_ref, cos_min, fro, mar)
+    for name, val in grads.items():
+        util.check_close("grad_" + name, val, g_ref[name], cos_min, fro, mar)

@@ -61,3 +61,37 @@ def test_mask_bias_sign_and_value():
 def test_bad_direction():
     with pytest.raises(ValueError, match="direction must be one of"):
         orc.trimul_fwd(np.zeros((2, 2, 4)), "sideways", None, p_in_weight=np.zeros((4, 4)))
+
+
+# ---- the torch restatement that bench.py times on the host cores, against the same fixtures ---------------------
+def _t64(a):
+    import torch
+    return None if a is None else torch.from_numpy(np.asarray(a)).double() if np.asarray(a).dtype != bool else torch.from_numpy(a)
+
+
+@pytest.mark.parametrize("path", ATTN, ids=[os.path.basename(p) for p in ATTN])
+def test_torch_restatement_attention_matches_reference(path):
+    from oracle import torch_reference as tr
+    g = dict(np.load(path))
+    scale = None if g["scale"] < 0 else float(g["scale"])
+    q, k, v, d_out = (_t64(g[n]) for n in ("q", "k", "v", "d_out"))
+    bias, mask = _t64(g.get("bias")), _t64(g.get("mask"))
+    for chunk in (None, 2):     # whole problem, and row blocks with the bias gradient summed over blocks
+        out, dq, dk, dv, db = tr.attention_fwd_bwd(q, k, v, bias, mask, scale, d_out, row_chunk=chunk)
+        _close(out.numpy(), g["out"])
+        _close(dq.numpy(), g["grad_q"])
+        _close(dk.numpy(), g["grad_k"])
+        _close(dv.numpy(), g["grad_v"])
+        if bias is not None:
+            _close(db.numpy(), g["grad_bias"])
+
+
+@pytest.mark.parametrize("path", TRIMUL, ids=[os.path.basename(p) for p in TRIMUL])
+def test_torch_restatement_trimul_matches_reference(path):
+    from oracle import torch_reference as tr
+    g = dict(np.load(path))
+    w = {k[2:]: _t64(v) for k, v in g.items() if k.startswith("w_")}
+    out, grads = tr.trimul_fwd_bwd(_t64(g["x"]), str(g["direction"]), _t64(g.get("mask")), w, _t64(g["d_out"]))
+    _close(out.numpy(), g["out"])
+    for name, val in grads.items():
+        _close(val.numpy(), g["grad_" + name], tol=1e-10)

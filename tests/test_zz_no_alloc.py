@@ -3,7 +3,7 @@
 Collected last on purpose (file name), so a run that stops at the first failure has already seen every
 other test.  The entry point keeps its scratch in an array built into the library, so the test calls it
 straight through the C ABI with nothing but inputs and outputs, twice in a row, and compares each result
-with what the regular workspace-taking entry point returns for the same inputs.
+with what the regular workspace-taking entry point returns for the same inputs and with the fp64 oracle.
 """
 
 import ctypes
@@ -52,6 +52,11 @@ def _run(dtype, shape, seed):
     cos_min, fro = util.ATTN_TOL[dtype, "ieee"]
     for name, a, b in zip(("dq", "dk", "dv", "dbias"), got, want):
         util.check_close(name, a, util.f64(b), cos_min, util.IEEE_REL_FRO if dtype == torch.float32 else fro)
+    # and on its own feet: against the oracle (the softmax statistics it consumed came from the forward above)
+    _, g_ref = util.attn_oracle(t, mask, None, d_o)
+    for name, a, key in zip(("dq", "dk", "dv", "dbias"), got, ("q", "k", "v", "bias")):
+        util.check_close(name + " vs oracle", a, g_ref[key].reshape(a.shape), cos_min,
+                         util.IEEE_REL_FRO if dtype == torch.float32 else fro)
 
 
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16], ids=str)
