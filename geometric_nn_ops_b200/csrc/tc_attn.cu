@@ -474,6 +474,9 @@ struct AttnBwdArgs {
   void* out1;            // dv
   int64_t out0_st[4], out1_st[4];
   uint32_t idesc_a, idesc_b;   // the two MMA shapes of the kernel
+  uint32_t idesc_c;            // merged dK/dV + dQ pass: the dQ product (both operands MN-major)
+  void* dq_part;               // merged pass: per key block, dS K of that block: [key blocks][B][S][N][H][D] in the input dtype
+  long long dq_part_plane;     // elements per key block
   int row_chunks;              // MODE_DBIAS: the row loop is split into this many CTAs, each writing its own partial
   int* err;
 };
@@ -510,7 +513,15 @@ template <int HD> struct GeoC {
 //   bar_acc  MMA -> TMA, threads those products are done: the tile's stage and its P^T / dS^T buffers are free
 // P^T and dS^T are double buffered (P^T over the bias tile it was computed from), so the threads do not wait for
 // the dV / dK products of one tile before the arithmetic of the next.
-template <typename T, int HD, bool HB>
+//
+// MERGE (head dim 32): the same pass also produces this key block's share of dQ, so that S, the exponentials and dP
+// are computed once for dK, dV and dQ instead of once per gradient.  dS^T then goes to shared memory ([128 keys x 64
+// queries], the two buffers of a pair of query tiles 16 KB apart) instead of TMEM: dK reads it K-major as before, and
+// after every second tile one product dQ_pair[128 queries x D] = dS_pair K reads the pair MN-major (M = queries) with
+// K as the MN-major B operand, into the TMEM columns dS^T no longer needs.  The arithmetic warps fetch that
+// accumulator one step later and store it, unscaled, as this key block's partial; attn_dq_sum_kernel adds the key
+// blocks' partials in fixed order.  A last tile without a partner is paired with a buffer of zeros.
+template <typename T, int HD, bool HB, bool MERGE>
 __global__ void __launch_bounds__(320, 2)
 attn_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmDO,
                      const __grid_constant__ CUtensorMap tmK, const __grid_constant__ CUtensorMap tmV,
@@ -566,6 +577,8 @@ attn_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_const
   // They are single buffered, so a tile's values are stored once the previous tile's products are done.
   constexpr bool TMEM_A = HD == 32;
   constexpr uint32_t COL_PT = 192, COL_DST = 224;
+  constexpr uint32_t COL_DQ = COL_DST;   // MERGE: dS^T lives in shared memory and its columns hold the dQ accumulator
+  static_assert(!MERGE || TMEM_A, "the merged pass is built for head dim 32");
   bool ok = true;
 
   if (warp == 9) {
@@ -611,6 +624,8 @@ attn_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_const
       const uint32_t q_lo = desc_lo(smem_u32(sQ), 16), do_lo = desc_lo(smem_u32(sDO), 16);
       const uint32_t qmn_lo = desc_lo(smem_u32(sQ), 64 * G::RB), domn_lo = desc_lo(smem_u32(sDO), 64 * G::RB);   // MN-major view
       const uint32_t pt_lo = desc_lo(smem_u32(sPT), 16), dst_lo = desc_lo(smem_u32(sDST), 16);
+      const uint32_t dsmn_lo = desc_lo(smem_u32(sDST), 16384);      // dS of a tile pair as [m = query, k = key]: MN-major A
+      const uint32_t kmn_lo = desc_lo(smem_u32(sK), 128 * G::RB);   // K as [n = d, k = key]: MN-major B
       // S^T = K Q^T and dP^T = V dO^T of one 64-query tile
       auto issue_scores = [&](int step) {
         const int stg = step % G::NQ;
@@ -645,8 +660,16 @@ attn_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_const
         for (int kk = 0; kk < 4; ++kk) {   // dK += dS^T Q
           const uint64_t bd = desc_join(qmn_lo + so + kk * G::RB, HI_KMAJ);
           const uint32_t accf = (j > 0 || kk > 0) ? 1u : 0u;
-          if constexpr (TMEM_A) umma_ts_f16(tmem_base + COL_DK, tmem_base + COL_DST + kk * 8, bd, a.idesc_b, accf);
+          if constexpr (TMEM_A && !MERGE) umma_ts_f16(tmem_base + COL_DK, tmem_base + COL_DST + kk * 8, bd, a.idesc_b, accf);
           else umma<KIND_F16>(tmem_base + COL_DK, desc_join(dst_lo + bo + kk * 2, HI_PT), bd, a.idesc_b, accf);
+        }
+        if constexpr (MERGE) {
+          if ((j & 1) || j == nsteps - 1) {   // a pair of query tiles is complete: dQ_pair = dS_pair K (16 keys per product)
+#pragma unroll
+            for (int ks = 0; ks < 8; ++ks)
+              umma<KIND_F16>(tmem_base + COL_DQ, desc_join(dsmn_lo + ks * 128, HI_PT), desc_join(kmn_lo + ks * G::RB, HI_KMAJ),
+                             a.idesc_c, ks > 0);
+          }
         }
         umma_commit(&bar_acc[j & 3]);
       }
@@ -658,6 +681,27 @@ attn_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_const
     if (kj >= a.N) mb = -INFINITY;
     else if (a.mask != nullptr) mb = kMaskSentinel * ((a.mask[b * a.mask_st[0] + s * a.mask_st[1] + kj] ? 1.0f : 0.0f) - 1.0f);
     const float2 sc2 = splat(a.scale), mk2 = splat(mb), l2e2 = splat(kLog2e);
+    // MERGE: fetch the dQ accumulator of query-tile pair `pair` (row r = query 128 pair + r, this thread's half of the
+    // head dim) and store it, unscaled, as this key block's partial.  tcgen05.ld is warp-wide: every thread loads.
+    auto store_dq_pair = [&](int pair) {
+      uint32_t v[16];
+      tmem_ld_32x16(t_row + COL_DQ + hh * 16, v);
+      tmem_ld_wait();
+      const int qi = pair * 128 + r;
+      if (qi < a.N && ok) {
+        T* dst = reinterpret_cast<T*>(a.dq_part) + kvb * a.dq_part_plane +
+                 ((((long long)b * a.S + s) * a.N + qi) * a.H + h) * HD + hh * 16;
+#pragma unroll
+        for (int g = 0; g < 2; ++g) {
+          uint4 pk;
+          pk.x = pack2<T>(__uint_as_float(v[g * 8 + 0]), __uint_as_float(v[g * 8 + 1]));
+          pk.y = pack2<T>(__uint_as_float(v[g * 8 + 2]), __uint_as_float(v[g * 8 + 3]));
+          pk.z = pack2<T>(__uint_as_float(v[g * 8 + 4]), __uint_as_float(v[g * 8 + 5]));
+          pk.w = pack2<T>(__uint_as_float(v[g * 8 + 6]), __uint_as_float(v[g * 8 + 7]));
+          reinterpret_cast<uint4*>(dst)[g] = pk;
+        }
+      }
+    };
 
     for (int j = 0; j < nsteps; ++j) {
       const int stg = j & 1, qstg = j % G::NQ;
@@ -720,8 +764,23 @@ attn_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_const
       if constexpr (TMEM_A) {
         if (j > 0) ok = mbar_wait(&bar_acc[(j - 1) & 3], ((j - 1) >> 2) & 1, a.err, 35) && ok;   // the previous tile's products have read theirs
         tc_fence_after_sync();
+        if constexpr (MERGE) {
+          if (j >= 2 && (j & 1) == 0) store_dq_pair(j / 2 - 1);   // the pair before this tile: its dQ product is done too
+        }
         tmem_st_32x16(t_row + COL_PT + hh * 16, pw);    // this thread's key row, its 32 queries as 16 packed columns
-        tmem_st_32x16(t_row + COL_DST + hh * 16, dw);
+        if constexpr (MERGE) {
+#pragma unroll
+          for (int u = 0; u < 4; ++u)
+            *reinterpret_cast<uint4*>(sDSTj + sw128_chunk1(r, c * 4 + u)) = make_uint4(dw[u * 4], dw[u * 4 + 1], dw[u * 4 + 2], dw[u * 4 + 3]);
+          if (j == nsteps - 1 && (j & 1) == 0) {   // no partner tile: the pair's second buffer reads as zeros
+#pragma unroll
+            for (int u = 0; u < 4; ++u)
+              *reinterpret_cast<uint4*>(sDST + 16384 + sw128_chunk1(r, c * 4 + u)) = make_uint4(0, 0, 0, 0);
+          }
+          fence_proxy_async_smem();
+        } else {
+          tmem_st_32x16(t_row + COL_DST + hh * 16, dw);
+        }
         tmem_st_wait();
       } else {
         fence_proxy_async_smem();
@@ -733,6 +792,7 @@ attn_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_const
     }
     ok = mbar_wait(&bar_acc[(nsteps - 1) & 3], ((nsteps - 1) >> 2) & 1, a.err, 36) && ok;
     tc_fence_after_sync();
+    if constexpr (MERGE) store_dq_pair((nsteps - 1) / 2);   // the last pair
     {
       const bool st_ok = kj < a.N && ok && hh == 0;
       T* krow = reinterpret_cast<T*>(a.out0) + b * a.out0_st[0] + s * a.out0_st[1] + kj * a.out0_st[2] + h * a.out0_st[3];
@@ -1229,6 +1289,32 @@ __global__ void attn_delta_tc_kernel(TriAttnDesc d, const T* o, const T* d_o, co
   prep[2 * plane + pi] = -acc;
 }
 
+// dq = scale * sum over key blocks of the merged pass's partials ([nparts][B][S][N][H][D] contiguous), added in key
+// block order in fp32; 8 elements per thread.
+template <typename T>
+__global__ void attn_dq_sum_kernel(const T* __restrict__ part, int nparts, long long plane, TriAttnDesc d, T* __restrict__ dq) {
+  const long long c = blockIdx.x * (long long)blockDim.x + threadIdx.x;
+  if (c >= plane / 8) return;
+  const int dc = d.D / 8;
+  long long z = c;
+  const int d8 = z % dc; z /= dc;
+  const int h = z % d.H; z /= d.H;
+  const int q = z % d.n_res; z /= d.n_res;
+  const int s = z % d.n_seq; const int b = z / d.n_seq;
+  float acc[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+  for (int p = 0; p < nparts; ++p) {
+    float v[8];
+    unpack8<T>(*reinterpret_cast<const uint4*>(part + p * plane + c * 8), v);
+#pragma unroll
+    for (int e = 0; e < 8; ++e) acc[e] += v[e];
+  }
+  uint4 pk;
+  pk.x = pack2<T>(acc[0] * d.scale, acc[1] * d.scale); pk.y = pack2<T>(acc[2] * d.scale, acc[3] * d.scale);
+  pk.z = pack2<T>(acc[4] * d.scale, acc[5] * d.scale); pk.w = pack2<T>(acc[6] * d.scale, acc[7] * d.scale);
+  T* row = dq + b * d.dq_st[0] + s * d.dq_st[1] + q * d.dq_st[2] + h * d.dq_st[3];
+  reinterpret_cast<uint4*>(row)[d8] = pk;
+}
+
 __global__ void sum_partials_kernel(const float* partial, int nparts, long long n, float* out) {
   const long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x;
   if (i >= n) return;
@@ -1290,7 +1376,7 @@ template <typename T, int HD>
 int bwd_launch(const TriAttnDesc* d, const void* q, const void* k, const void* v, const void* bias,
                const uint8_t* mask, const void* o, const float* stats, const void* d_o, void* dq, void* dk, void* dv,
                float* dbias, int* err, float* delta, float* dbias_partial, void* bias_t, float* prep, float* mask_terms,
-               cudaStream_t st) {
+               void* dq_part, cudaStream_t st) {
   const long long rows = (long long)d->B * d->n_seq * d->H * d->n_res;
   const double pairs = (double)rows * d->n_res;
   const double tensor_bytes = 2.0 * d->B * d->n_seq * (double)d->n_res * d->H * d->D;
@@ -1338,11 +1424,24 @@ int bwd_launch(const TriAttnDesc* d, const void* q, const void* k, const void* v
   for (int i = 0; i < 4; ++i) { a.out0_st[i] = d->dk_st[i]; a.out1_st[i] = d->dv_st[i]; }
   a.idesc_a = make_idesc(kind, 128, 64, false, false);
   a.idesc_b = make_idesc(kind, 128, HD, false, true);
+  a.idesc_c = make_idesc(kind, 128, HD, true, true);
+  // Head dim 32: dK, dV and dQ come from one pass (dQ as per-key-block partials, summed below); head dim 64 has no
+  // TMEM columns to spare for the dQ accumulator and keeps the separate dQ pass.
+  constexpr bool kMerge = HD == 32;
+  const long long dq_plane = (long long)d->B * d->n_seq * d->n_res * d->H * d->D;
+  a.dq_part = dq_part; a.dq_part_plane = dq_plane;
   {
-    auto kern = bias ? attn_bwd_dkdv_kernel<T, HD, true> : attn_bwd_dkdv_kernel<T, HD, false>;
+    auto kern = bias ? attn_bwd_dkdv_kernel<T, HD, true, kMerge> : attn_bwd_dkdv_kernel<T, HD, false, kMerge>;
     TRI_TRY(set_dyn_smem(kern, GeoC<HD>::SMEM));   // per-device attribute: set on every launch
-    KernelTimer kt("tc_attn_bwd_dkdv", st, 8.0 * pairs * d->D, 6.0 * tensor_bytes);
+    KernelTimer kt(kMerge ? "tc_attn_bwd_dkdvdq" : "tc_attn_bwd_dkdv", st, (kMerge ? 10.0 : 8.0) * pairs * d->D,
+                   (kMerge ? 7.0 : 6.0) * tensor_bytes);
     kern<<<(unsigned)((long long)qblocks * d->B * d->n_seq * d->H), 320, GeoC<HD>::SMEM, st>>>(tq, tdo, tk, tv, tb, a);
+    TRI_LAUNCH_OK();
+  }
+  if (kMerge) {
+    KernelTimer kt("tc_attn_dq_sum", st, 0.0, (qblocks + 1.0) * tensor_bytes);
+    attn_dq_sum_kernel<T><<<cdiv(dq_plane / 8, 256), 256, 0, st>>>(static_cast<const T*>(dq_part), qblocks, dq_plane, *d,
+                                                               static_cast<T*>(dq));
     TRI_LAUNCH_OK();
   }
   // ---- dQ ------------------------------------------------------------------------------------
@@ -1355,7 +1454,7 @@ int bwd_launch(const TriAttnDesc* d, const void* q, const void* k, const void* v
   for (int i = 0; i < 4; ++i) a.out0_st[i] = d->dq_st[i];
   a.idesc_a = make_idesc(kind, 128, 64, false, false);
   a.idesc_b = make_idesc(kind, 128, HD, false, true);
-  {
+  if (!kMerge) {
     auto kern = bias ? attn_bwd_dq_kernel<T, HD, true> : attn_bwd_dq_kernel<T, HD, false>;
     TRI_TRY(set_dyn_smem(kern, GeoQ<HD>::SMEM));
     KernelTimer kt("tc_attn_bwd_dq", st, 2.0 * pairs * d->D, 5.0 * tensor_bytes);
@@ -1471,6 +1570,11 @@ bool attn_bwd_supported(const TriAttnDesc* d) {
 }
 
 static size_t attn_npad(const TriAttnDesc* d) { return ((size_t)d->n_res + 127) / 128 * 128; }
+// partial dQ of the merged dK/dV + dQ pass (head dim 32 only): one 16-bit tensor of q's size per 128-key block
+static size_t attn_dq_part_bytes(const TriAttnDesc* d) {
+  if (d->D != 32) return 0;
+  return align_up(attn_npad(d) / 128 * (size_t)d->B * d->n_seq * d->n_res * d->H * d->D * 2);
+}
 
 size_t attn_ws_bytes(const TriAttnDesc* d, int is_bwd) {
   if (!is_bwd) return 512 + align_up((size_t)d->B * d->n_seq * attn_npad(d) * sizeof(float));   // additive key-mask terms
@@ -1478,7 +1582,8 @@ size_t attn_ws_bytes(const TriAttnDesc* d, int is_bwd) {
          align_up((size_t)kDbiasRowChunks * d->B * d->H * d->n_res * d->n_res * sizeof(float)) +
          align_up((size_t)d->B * d->H * d->n_res * d->n_res * 2) +   // transposed 16-bit copy of the bias
          align_up(3 * (size_t)d->B * d->n_seq * d->H * attn_npad(d) * sizeof(float)) +   // padded per-row constants
-         align_up((size_t)d->B * d->n_seq * attn_npad(d) * sizeof(float));               // additive key-mask terms
+         align_up((size_t)d->B * d->n_seq * attn_npad(d) * sizeof(float)) +              // additive key-mask terms
+         attn_dq_part_bytes(d);                                                          // merged pass: dQ per key block
 }
 
 int attn_forward(const TriAttnDesc* d, const void* q, const void* k, const void* v, const void* bias,
@@ -1507,12 +1612,13 @@ int attn_backward(const TriAttnDesc* d, const void* q, const void* k, const void
   void* bias_t = reinterpret_cast<char*>(part) + align_up((size_t)kDbiasRowChunks * d->B * d->H * d->n_res * d->n_res * sizeof(float));
   float* prep = reinterpret_cast<float*>(static_cast<char*>(bias_t) + align_up((size_t)d->B * d->H * d->n_res * d->n_res * 2));
   float* mterms = reinterpret_cast<float*>(reinterpret_cast<char*>(prep) + align_up(3 * (size_t)d->B * d->n_seq * d->H * attn_npad(d) * sizeof(float)));
+  void* dq_part = reinterpret_cast<char*>(mterms) + align_up((size_t)d->B * d->n_seq * attn_npad(d) * sizeof(float));
   if (d->dtype == TRI_BF16) {
-    if (d->D == 32) return bwd_launch<__nv_bfloat16, 32>(d, q, k, v, bias, mask, o, lse, d_o, dq, dk, dv, dbias, err, delta, part, bias_t, prep, mterms, st);
-    return bwd_launch<__nv_bfloat16, 64>(d, q, k, v, bias, mask, o, lse, d_o, dq, dk, dv, dbias, err, delta, part, bias_t, prep, mterms, st);
+    if (d->D == 32) return bwd_launch<__nv_bfloat16, 32>(d, q, k, v, bias, mask, o, lse, d_o, dq, dk, dv, dbias, err, delta, part, bias_t, prep, mterms, dq_part, st);
+    return bwd_launch<__nv_bfloat16, 64>(d, q, k, v, bias, mask, o, lse, d_o, dq, dk, dv, dbias, err, delta, part, bias_t, prep, mterms, dq_part, st);
   }
-  if (d->D == 32) return bwd_launch<__half, 32>(d, q, k, v, bias, mask, o, lse, d_o, dq, dk, dv, dbias, err, delta, part, bias_t, prep, mterms, st);
-  return bwd_launch<__half, 64>(d, q, k, v, bias, mask, o, lse, d_o, dq, dk, dv, dbias, err, delta, part, bias_t, prep, mterms, st);
+  if (d->D == 32) return bwd_launch<__half, 32>(d, q, k, v, bias, mask, o, lse, d_o, dq, dk, dv, dbias, err, delta, part, bias_t, prep, mterms, dq_part, st);
+  return bwd_launch<__half, 64>(d, q, k, v, bias, mask, o, lse, d_o, dq, dk, dv, dbias, err, delta, part, bias_t, prep, mterms, dq_part, st);
 }
 
 }  // namespace tc
