@@ -282,6 +282,7 @@ def parity_sharded(res, dev_t, dev_w, rank, world, torch, triangle_attention, tr
         whole = name == "attn.dbias" or (".d_" in name)
         if not whole:
             b = b[:, i0:i1]
+        a, b = a.detach(), b.detach()
         errs.append(float((a.double() - b.double()).norm() / b.double().norm().clamp_min(1e-30)))
     e = torch.tensor(errs, device="cuda", dtype=torch.float64)
     dist.all_reduce(e, op=dist.ReduceOp.MAX)
@@ -294,7 +295,7 @@ def parity_sharded(res, dev_t, dev_w, rank, world, torch, triangle_attention, tr
         ok = ok and err <= lim
     return {"against": "single-GPU ops on the same rank, whole problem", "metric": "rel-Frobenius, max over ranks",
             "max_rel_fro": dict(zip(RESULT_NAMES, errs)), "ok": ok,
-            "exchange": "peer stores" if sharded._PEER_STATE.get("enabled") else "nccl all_to_all"}
+            "exchange": sharded.exchange_route(torch.device("cuda", torch.cuda.current_device()))}
 
 
 def _finish(dist):

@@ -80,6 +80,10 @@ class TriScatterDesc(ctypes.Structure):
                 ("run_bytes", ctypes.c_int64), ("peer_dim", ctypes.c_int32), ("n_peers", ctypes.c_int32)]
 
 
+class TriPeerSignal(ctypes.Structure):
+    _fields_ = [("flag_ptrs", POINTER(c_void_p)), ("state", c_void_p), ("rank", ctypes.c_int32), ("n_peers", ctypes.c_int32)]
+
+
 EXPORTS = {
     "tri_abi_version": (c_int, []),
     "tri_last_error": (c_char_p, []),
@@ -106,6 +110,8 @@ EXPORTS = {
     "tri_permute_runs": (c_int, [c_void_p, c_void_p, POINTER(ctypes.c_int64 * 3), POINTER(ctypes.c_int32 * 3),
                                  ctypes.c_int64, c_void_p]),
     "tri_scatter_runs": (c_int, [POINTER(TriScatterDesc), c_void_p, POINTER(c_void_p), c_void_p]),
+    "tri_scatter_runs_signal": (c_int, [POINTER(TriScatterDesc), c_void_p, POINTER(c_void_p), POINTER(TriPeerSignal), c_void_p]),
+    "tri_peer_wait": (c_int, [POINTER(TriPeerSignal), c_int64, c_void_p]),
     "tri_ws_status": (c_int, [c_void_p, c_void_p]),
 }
 

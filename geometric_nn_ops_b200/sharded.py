@@ -98,22 +98,57 @@ def _permute_runs(t, dims, perm, run):
 
 # Peer-store exchange: with symmetric memory (every rank's receive buffer mapped into every other rank's address
 # space) the all-to-all and both layout changes become ONE copy kernel per rank that stores each run straight into
-# its place in the destination GPU's buffer over NVLink.  A one-element all-reduce on the same stream then orders
-# "every rank has written" before "any rank reads".  Each call site of a step has its own buffer (`tag`), so a fast
-# rank can never overwrite data a slow rank still reads: between two uses of one buffer lie all the step's
-# other exchanges, each of which synchronises the ranks.
-_PEER = {}            # (tag, bytes, device, group) -> (buffer, peer pointer array)
-_PEER_STATE = {"enabled": None}
+# its place in the destination GPU's buffer over NVLink.  "Every rank has written" is ordered before "any rank reads"
+# by arrival flags, not by a collective: the copy kernel's last block stores this rank's exchange number into a flag
+# slot on every peer, and a one-block kernel queued behind it waits (bounded, about a second) until all peers' slots
+# have reached the same number.  No host round trip, nothing for NCCL to launch, and a captured graph replays as is.
+# TRI_B200_EXCHANGE=peer_allreduce keeps the former barrier, a one-element all-reduce.
+#
+# Buffer reuse: a peer may overwrite a buffer only after this rank has finished reading it.  Each (call site, size)
+# owns TWO buffers used alternately.  A peer's copy kernel of exchange k+2 (the next one into the same buffer) is
+# queued behind its wait of exchange k+1, which completes only when this rank's copy kernel of k+1 has run, and that
+# one is queued on this rank's stream behind whatever read exchange k.  So two calls in a row with the same tag
+# are safe as long as the readers run on the stream the exchange was issued on.
+_PEER = {}            # (tag, bytes, device, group, parity) -> _PeerBuffer
+_PEER_TURN = {}       # (tag, bytes, device, group) -> which of the two buffers the next exchange uses
+_PEER_STATE = {}      # (group, device) -> bool: every rank can take the peer-store route
+_FLAG_BYTES = 256
+
+
+class _PeerBuffer:
+    """One symmetric allocation: the receive buffer followed by this rank's 16 arrival flags, plus the peers' views."""
+
+    def __init__(self, nbytes, device, group):
+        import torch.distributed._symmetric_memory as symm_mem
+        pg = group if group is not None else dist.group.WORLD
+        data = (nbytes + 255) // 256 * 256
+        self.buf = symm_mem.empty(data + _FLAG_BYTES, dtype=torch.uint8, device=device)
+        self.buf[data:].zero_()
+        hdl = symm_mem.rendezvous(self.buf, pg.group_name)
+        world = hdl.world_size
+        self.ptrs = (ctypes.c_void_p * world)(*[int(p) for p in hdl.buffer_ptrs])
+        self.flag_ptrs = (ctypes.c_void_p * world)(*[int(p) + data for p in hdl.buffer_ptrs])
+        self.state = torch.zeros(4, dtype=torch.int32, device=device)
+        self.sig = _lib.TriPeerSignal()
+        self.sig.flag_ptrs = ctypes.cast(self.flag_ptrs, ctypes.POINTER(ctypes.c_void_p))
+        self.sig.state = self.state.data_ptr()
+        self.sig.rank, self.sig.n_peers = dist.get_rank(group), world
+        self.token = torch.zeros(1, dtype=torch.float32, device=device)    # for the all-reduce form of the barrier
+        # nobody may raise a flag here before it has been zeroed
+        torch.cuda.synchronize(device)
+        dist.barrier(group=group)
 
 
 def peer_exchange_enabled(device, group=None):
     """True when the exchanges can use peer stores: CUDA, NCCL, symmetric memory; TRI_B200_EXCHANGE=nccl turns it off.
 
-    The first call tries a small symmetric allocation and lets the ranks agree on the outcome (a MIN all-reduce), so
-    that either every rank takes the peer-store route or every rank takes the all-to-all.
+    The first call for a (group, device) tries a small symmetric allocation and lets the ranks agree on the outcome
+    (a MIN all-reduce), so that either every rank takes the peer-store route or every rank takes the all-to-all.
     """
-    if _PEER_STATE["enabled"] is None:
-        ok = os.environ.get("TRI_B200_EXCHANGE", "peer") in ("peer", "fused") and device.type == "cuda" and dist.get_backend() == "nccl"
+    key = (id(group), device.index)
+    if key not in _PEER_STATE:
+        ok = (os.environ.get("TRI_B200_EXCHANGE", "peer") in ("peer", "peer_allreduce", "fused") and device.type == "cuda"
+              and dist.get_backend(group) == "nccl")
         if ok:
             try:
                 _peer_buffer("probe", 4096, device, group)
@@ -124,27 +159,47 @@ def peer_exchange_enabled(device, group=None):
             flag = torch.tensor([good], device=device)
             dist.all_reduce(flag, op=dist.ReduceOp.MIN, group=group)
             ok = bool(flag.item() > 0.5)
-        _PEER_STATE["enabled"] = ok
-    return _PEER_STATE["enabled"]
+        _PEER_STATE[key] = ok
+    return _PEER_STATE[key]
+
+
+def exchange_route(device, group=None):
+    """Name of the route the row <-> channel exchanges take for this (group, device): for logs and benchmarks."""
+    if not peer_exchange_enabled(device, group):
+        return "nccl all_to_all"
+    mode = os.environ.get("TRI_B200_EXCHANGE", "peer")
+    return {"peer": "peer stores + arrival flags", "peer_allreduce": "peer stores + all-reduce barrier",
+            "fused": "gate-in epilogue peer stores + all-reduce barrier"}[mode]
 
 
 def _peer_buffer(tag, nbytes, device, group):
-    import torch.distributed._symmetric_memory as symm_mem
-    key = (tag, nbytes, device.index, id(group))
+    base = (tag, nbytes, device.index, id(group))
+    turn = _PEER_TURN.get(base, 0)
+    _PEER_TURN[base] = turn ^ 1
+    key = base + (turn,)
     if key not in _PEER:
-        pg = group if group is not None else dist.group.WORLD
-        buf = symm_mem.empty(nbytes, dtype=torch.uint8, device=device)
-        hdl = symm_mem.rendezvous(buf, pg.group_name)
-        ptrs = (ctypes.c_void_p * hdl.world_size)(*[int(p) for p in hdl.buffer_ptrs])
-        _PEER[key] = (buf, ptrs, torch.zeros(1, dtype=torch.float32, device=device))
+        _PEER[key] = _PeerBuffer(nbytes, device, group)
     return _PEER[key]
+
+
+def _peer_barrier(pb, tag, group, stream):
+    """Order "every rank's stores have landed" before this rank's readers (queued next on ``stream``)."""
+    with _timed(tag + ".barrier"):
+        if os.environ.get("TRI_B200_EXCHANGE", "peer") == "peer":
+            _lib.check(_lib.load().tri_peer_wait(ctypes.byref(pb.sig), 0, stream), "tri_peer_wait")
+            if os.environ.get("TRI_B200_CHECK") == "1" and not torch.cuda.is_current_stream_capturing():
+                status = int(pb.state[3].item())
+                if status != 0:
+                    raise RuntimeError(f"peer exchange {tag!r}: rank {status - 100} did not arrive within the wait limit")
+        else:
+            dist.all_reduce(pb.token, group=group)
 
 
 def _peer_scatter(t, dims, dst_stride, base_run, peer_dim, run, out_shape, tag, group, persist):
     world, _ = _world(group)
     t = t.contiguous()
     nbytes = t.numel() * t.element_size()
-    buf, ptrs, flag = _peer_buffer(tag, nbytes, t.device, group)
+    pb = _peer_buffer(tag, nbytes, t.device, group)
     d = _lib.TriScatterDesc()
     d.dims[:] = dims
     d.dst_stride[:] = dst_stride
@@ -153,15 +208,17 @@ def _peer_scatter(t, dims, dst_stride, base_run, peer_dim, run, out_shape, tag, 
     d.peer_dim = peer_dim
     d.n_peers = world
     stream = ctypes.c_void_p(torch.cuda.current_stream(t.device).cuda_stream)
+    lib = _lib.load()
     with _timed(tag + ".peer_store"):
-        _lib.check(_lib.load().tri_scatter_runs(ctypes.byref(d), ctypes.c_void_p(t.data_ptr()), ptrs, stream),
-                   "tri_scatter_runs")
-    with _timed(tag + ".barrier"):
-        dist.all_reduce(flag, group=group)      # every rank's stores are complete before anyone goes on
-    # The buffer is rewritten by the next exchange with the same tag.  Results the caller keeps (tensors saved for
-    # the backward) get a private copy; temporaries are consumed before this rank reaches its next exchange, and a
-    # peer cannot write here again before this rank has joined that one.
-    out = buf.view(t.dtype)[: t.numel()].view(out_shape)
+        if os.environ.get("TRI_B200_EXCHANGE", "peer") == "peer":
+            _lib.check(lib.tri_scatter_runs_signal(ctypes.byref(d), ctypes.c_void_p(t.data_ptr()), pb.ptrs, ctypes.byref(pb.sig),
+                                                   stream), "tri_scatter_runs_signal")
+        else:
+            _lib.check(lib.tri_scatter_runs(ctypes.byref(d), ctypes.c_void_p(t.data_ptr()), pb.ptrs, stream), "tri_scatter_runs")
+    _peer_barrier(pb, tag, group, stream)
+    # The buffer is rewritten two exchanges with this tag from now.  Results the caller keeps beyond that (tensors
+    # saved for the backward) get a private copy.
+    out = pb.buf.view(t.dtype)[: t.numel()].view(out_shape)
     return out.clone() if persist else out
 
 
@@ -234,6 +291,59 @@ def all_to_all_transpose(x, group=None):
     return _Transpose.apply(x, group)
 
 
+# Gradients that are sums over ranks (the pair bias, every weight) each cost one small all-reduce; a training step that
+# runs several sharded ops pays that latency several times.  Inside `deferred_grad_sync()` the ops hand back their
+# rank-local sums and register the tensors; leaving the context (or `flush()`) adds them over ranks IN PLACE with one
+# all-reduce per dtype.  Until then the registered gradients hold this rank's partial sums only.
+_DEFERRED = []
+
+
+class deferred_grad_sync:
+    def __init__(self, group=None):
+        self.group, self.items = group, []
+
+    def __enter__(self):
+        _DEFERRED.append(self)
+        return self
+
+    def __exit__(self, exc_type, exc, tb):
+        _DEFERRED.remove(self)
+        if exc_type is None:
+            self.flush()
+        return False
+
+    def add(self, t):
+        self.items.append(t)
+
+    def flush(self):
+        by_dtype = {}
+        for t in self.items:
+            by_dtype.setdefault(t.dtype, []).append(t)
+        self.items = []
+        for tensors in by_dtype.values():
+            with _timed("grads.all_reduce"):
+                if len(tensors) == 1 and tensors[0].is_contiguous():
+                    dist.all_reduce(tensors[0], op=dist.ReduceOp.SUM, group=self.group)
+                    continue
+                flat = torch.cat([t.reshape(-1) for t in tensors])
+                dist.all_reduce(flat, op=dist.ReduceOp.SUM, group=self.group)
+                off = 0
+                for t in tensors:
+                    t.copy_(flat[off:off + t.numel()].view(t.shape))
+                    off += t.numel()
+
+
+def _sum_over_ranks(tensors, group, name):
+    """All-reduce ``tensors`` now, or register them with the enclosing `deferred_grad_sync`."""
+    if _DEFERRED:
+        for t in tensors:
+            _DEFERRED[-1].add(t)
+        return
+    with _timed(name):
+        for t in tensors:
+            dist.all_reduce(t, op=dist.ReduceOp.SUM, group=group)
+
+
 class _SumGradOverRanks(torch.autograd.Function):
     """Identity whose gradient is all-reduced: for tensors replicated on every rank (the pair bias)."""
 
@@ -245,8 +355,7 @@ class _SumGradOverRanks(torch.autograd.Function):
     @staticmethod
     def backward(ctx, g):
         g = g.contiguous()
-        with _timed("bias_grad.all_reduce"):
-            dist.all_reduce(g, op=dist.ReduceOp.SUM, group=ctx.group)
+        _sum_over_ranks([g], ctx.group, "bias_grad.all_reduce")
         return g, None
 
 
@@ -310,15 +419,15 @@ class _ShardedTriMul(torch.autograd.Function):
             # owners' buffers; the one-element all-reduce orders "all ranks have stored" before "anyone reads".
             # Opt-in: at 2 GPUs it measured 6.1 ms per step against 5.95 ms for GEMM + copy kernel (32-byte
             # remote stores from the epilogue use NVLink less well than the copy kernel's long runs).
-            buf, ptrs, flag = _peer_buffer("fwd.ab", 2 * B * Ch * R * N * xc.element_size(), x.device, group)
-            bufs.peer_ab = ctypes.cast(ptrs, ctypes.POINTER(ctypes.c_void_p))
+            pb = _peer_buffer("fwd.ab", 2 * B * Ch * R * N * xc.element_size(), x.device, group)
+            bufs.peer_ab = ctypes.cast(pb.ptrs, ctypes.POINTER(ctypes.c_void_p))
             bufs.peer_world, bufs.peer_rank = world, me
             with _timed("fwd.ab.gemm_with_peer_store"):
                 _phase(lib, d, _lib.PHASE_PROJECT, bufs, x.device)
             with _timed("fwd.ab.barrier"):
-                dist.all_reduce(flag, group=group)
+                dist.all_reduce(pb.token, group=group)
             bufs.peer_ab, bufs.peer_world = None, 0
-            ab_ch = buf.view(xc.dtype)[: 2 * B * Ch * R * N].view(2 * B, Ch // world, N, N).clone()   # saved for the backward
+            ab_ch = pb.buf.view(xc.dtype)[: 2 * B * Ch * R * N].view(2 * B, Ch // world, N, N).clone()   # saved for the backward
         else:
             bufs.a_cm, bufs.b_cm = ab[0].data_ptr(), ab[1].data_ptr()
             _phase(lib, d, _lib.PHASE_PROJECT, bufs, x.device)
@@ -382,9 +491,27 @@ class _ShardedTriMul(torch.autograd.Function):
         dx = torch.empty_like(xc)
         bufs.a_cm, bufs.b_cm, bufs.dx = dab[0].data_ptr(), dab[1].data_ptr(), dx.data_ptr()
         _phase(lib, d, _lib.PHASE_PROJECT_BWD, bufs, dev)
+        out = [dx if ctx.needs_input_grad[0] else None, None, None, None, None]
+        if _DEFERRED:
+            # the caller sums over ranks later, in one call for the whole step: hand back this rank's partial sums in
+            # the weights' dtype (one cast of the flat buffer) and register them
+            lows = {}
+            for dt in {d_ for d_ in ctx.weight_dtypes if d_ is not None}:
+                lows[dt] = flat.to(dt)
+                _DEFERRED[-1].add(lows[dt])
+            off = 0
+            views = {}
+            for n, sz in zip(names, sizes):
+                views[n] = off
+                off += sz
+            for i, (n, dt) in enumerate(zip(_lib.WEIGHT_NAMES, ctx.weight_dtypes)):
+                if n in grads and ctx.needs_input_grad[5 + i]:
+                    out.append(lows[dt][views[n]:views[n] + wc[n].numel()].view(wc[n].shape))
+                else:
+                    out.append(None)
+            return tuple(out)
         with _timed("weight_grads.all_reduce"):
             dist.all_reduce(flat, op=dist.ReduceOp.SUM, group=group)
-        out = [dx if ctx.needs_input_grad[0] else None, None, None, None, None]
         for i, (n, dt) in enumerate(zip(_lib.WEIGHT_NAMES, ctx.weight_dtypes)):
             out.append(grads[n].to(dt) if n in grads and ctx.needs_input_grad[5 + i] else None)
         return tuple(out)
@@ -410,22 +537,40 @@ def sharded_triangle_multiplicative_update(x, direction="outgoing", mask=None, *
 # ---------------------------------------------------------------------------------------------------
 # benchmark step (used by bench.py --gpus N)
 # ---------------------------------------------------------------------------------------------------
+_SIDE_STREAM = {}
+
+
 def make_bench_step(n, rank, world, host_inputs):
-    """One forward+backward of the three ops on this rank's row shard of the N-sized problem."""
+    """One forward+backward of the three ops on this rank's row shard of the N-sized problem.
+
+    The three ops are independent, so the attention (which needs no exchange) runs on a second stream beside the two
+    multiplicative updates: its kernels fill the gaps the updates' exchanges leave.  Every gradient that is a sum over
+    ranks (pair bias, weights) is added in ONE all-reduce at the end of the step.
+    """
     i0, i1 = shard_rows(n, rank, world)
     t, w = host_inputs(n, 0, torch)                  # same seed everywhere: weights and bias are replicated
     for name in ("q", "k", "v", "d_o", "key_mask", "x", "d_out", "pair_mask"):
         t[name] = t[name][:, i0:i1].contiguous()
+    overlap = os.environ.get("TRI_B200_OVERLAP", "1") == "1"
 
     def step(td, wd):
-        q, k, v, bias = (td[m].detach().requires_grad_() for m in ("q", "k", "v", "bias"))
-        o = sharded_triangle_attention(q, k, v, bias, td["key_mask"], q.shape[-1] ** -0.5)
-        res = [o, *torch.autograd.grad(o, [q, k, v, bias], grad_outputs=td["d_o"])]
-        for direction in ("outgoing", "incoming"):
-            x = td["x"].detach().requires_grad_()
-            wl = {m: p.detach().requires_grad_() for m, p in wd.items()}
-            out = sharded_triangle_multiplicative_update(x, direction, td["pair_mask"], **wl)
-            res += [out, *torch.autograd.grad(out, [x, *wl.values()], grad_outputs=td["d_out"])]
+        main = torch.cuda.current_stream()
+        dev = main.device.index
+        side = _SIDE_STREAM.setdefault(dev, torch.cuda.Stream()) if overlap else main
+        with deferred_grad_sync() as sync:
+            side.wait_stream(main)
+            with torch.cuda.stream(side):
+                q, k, v, bias = (td[m].detach().requires_grad_() for m in ("q", "k", "v", "bias"))
+                o = sharded_triangle_attention(q, k, v, bias, td["key_mask"], q.shape[-1] ** -0.5)
+                res = [o, *torch.autograd.grad(o, [q, k, v, bias], grad_outputs=td["d_o"])]
+            for direction in ("outgoing", "incoming"):
+                x = td["x"].detach().requires_grad_()
+                wl = {m: p.detach().requires_grad_() for m, p in wd.items()}
+                out = sharded_triangle_multiplicative_update(x, direction, td["pair_mask"], **wl)
+                res += [out, *torch.autograd.grad(out, [x, *wl.values()], grad_outputs=td["d_out"])]
+            main.wait_stream(side)
+            for r_ in res[:5]:
+                r_.record_stream(main)
         return res
 
     return step, t, w

@@ -80,7 +80,28 @@ def check_replicated_grad(rank, world):
     assert torch.equal(bias.grad, torch.full((4,), float(sum(range(1, world + 1)))))
 
 
-@pytest.mark.parametrize("fn", ["check_channel_exchange", "check_transpose", "check_replicated_grad"])
+def check_deferred_grad_sync(rank, world):
+    """Inside the context the gradients are this rank's partial sums; leaving it adds them over ranks in place, one
+    all-reduce per dtype, through the tensors autograd handed back."""
+    from geometric_nn_ops_b200 import sharded
+    a = torch.ones(4, requires_grad=True)
+    b = torch.ones(2, 3, requires_grad=True)
+    c = torch.ones(5, dtype=torch.float64, requires_grad=True)
+    with sharded.deferred_grad_sync() as sync:
+        outs = [sharded._SumGradOverRanks.apply(t, None) * float(rank + 1) for t in (a, b, c)]
+        ga, gb, gc = torch.autograd.grad([o.sum() for o in outs], [a, b, c])
+        assert torch.equal(ga, torch.full((4,), float(rank + 1)))          # not summed yet
+        assert len(sync.items) == 3
+    total = float(sum(range(1, world + 1)))
+    assert torch.equal(ga, torch.full((4,), total)) and torch.equal(gb, torch.full((2, 3), total))
+    assert torch.equal(gc, torch.full((5,), total, dtype=torch.float64))
+    # outside a context the sum happens at once
+    (g2,) = torch.autograd.grad((sharded._SumGradOverRanks.apply(a, None) * float(rank + 1)).sum(), [a])
+    assert torch.equal(g2, torch.full((4,), total))
+
+
+@pytest.mark.parametrize("fn", ["check_channel_exchange", "check_transpose", "check_replicated_grad",
+                                "check_deferred_grad_sync"])
 def test_two_ranks(fn):
     _run(fn)
 
