@@ -110,8 +110,7 @@ EXPORTS = {
     "tri_permute_runs": (c_int, [c_void_p, c_void_p, POINTER(ctypes.c_int64 * 3), POINTER(ctypes.c_int32 * 3),
                                  ctypes.c_int64, c_void_p]),
     "tri_scatter_runs": (c_int, [POINTER(TriScatterDesc), c_void_p, POINTER(c_void_p), c_void_p]),
-    "tri_scatter_runs_signal": (c_int, [POINTER(TriScatterDesc), c_void_p, POINTER(c_void_p), POINTER(TriPeerSignal), c_void_p]),
-    "tri_peer_wait": (c_int, [POINTER(TriPeerSignal), c_int64, c_void_p]),
+    "tri_peer_barrier": (c_int, [POINTER(TriPeerSignal), c_int64, c_void_p]),
     "tri_ws_status": (c_int, [c_void_p, c_void_p]),
 }
 

@@ -351,9 +351,8 @@ int tri_scatter_runs(const TriScatterDesc* d, const void* src, void* const* dst_
 }
 
 // ---- arrival flags for the peer-store exchange -------------------------------------------------------------------
-// state[0] = exchanges sent, state[1] = exchanges awaited, state[2] = blocks of the running copy kernel that are done,
-// state[3] = status of the last wait (0 = ok).  All four live in this GPU's memory and are advanced by the kernels
-// themselves, so a captured graph can be replayed without changing an argument.
+// state[0] = number of barriers this rank has entered, state[3] = status of the last wait (0 = ok).  Both live in this
+// GPU's memory and are advanced by the kernel itself, so a captured graph can be replayed without changing an argument.
 struct SignalPtrs { uint32_t* flags[16]; };
 
 __device__ __forceinline__ void store_release_sys(uint32_t* p, uint32_t v) {
@@ -365,94 +364,41 @@ __device__ __forceinline__ uint32_t load_acquire_sys(const uint32_t* p) {
   return v;
 }
 
-// The run copy of scatter_runs_kernel; the block that finishes last then tells every peer "exchange number e of this
-// rank has landed" by storing e into slot `rank` of the peer's flag array (release at system scope, after every
-// block's data stores have been fenced at system scope).
-static __global__ void scatter_runs_signal_kernel(const uint4* __restrict__ src, ScatterPtrs dst, long long d1, long long d2,
-                                                  long long s0, long long s1, long long s2, long long base, int peer_dim,
-                                                  long long run_v, SignalPtrs sig, int rank, int n_peers, uint32_t* state) {
-  const long long outer = blockIdx.y;
-  const long long i2 = outer % d2, i1 = (outer / d2) % d1, i0 = outer / (d2 * d1);
-  const long long peer = peer_dim == 0 ? i0 : (peer_dim == 1 ? i1 : i2);
-  const uint4* s = src + outer * run_v;
-  uint4* d = dst.p[peer] + (base + i0 * s0 + i1 * s1 + i2 * s2) * run_v;
-  const long long stride = (long long)gridDim.x * blockDim.x;
-  long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x;
-  for (; i + 3 * stride < run_v; i += 4 * stride) {
-    const uint4 a = __ldg(s + i), b = __ldg(s + i + stride), c = __ldg(s + i + 2 * stride), e = __ldg(s + i + 3 * stride);
-    d[i] = a; d[i + stride] = b; d[i + 2 * stride] = c; d[i + 3 * stride] = e;
-  }
-  for (; i < run_v; i += stride) d[i] = __ldg(s + i);
-  __threadfence_system();
-  __syncthreads();
-  if (threadIdx.x == 0) {
-    const unsigned total = gridDim.x * gridDim.y;
-    if (atomicAdd(&state[2], 1u) == total - 1) {   // every other block has fenced its stores and counted itself
-      __threadfence_system();
-      state[2] = 0;
-      const uint32_t epoch = state[0] + 1;
-      state[0] = epoch;
-      for (int w = 0; w < n_peers; ++w) store_release_sys(sig.flags[w] + rank, epoch);
-    }
-  }
-}
-
-// One thread per peer waits until that peer's arrival flag has reached this rank's next exchange number.  The wait is
-// bounded (about a second of SM clocks): on timeout state[3] records which peer was missing and the kernel returns,
-// so a rank that never arrives shows up as an error status instead of a hung GPU.
-static __global__ void peer_wait_kernel(const uint32_t* flags, int n_peers, uint32_t* state, long long limit_cycles) {
+// One block, one thread per peer.  Thread w tells peer w "everything this rank queued before barrier number e has
+// been stored" (slot `rank` of that peer's flag array := e, release at system scope; the copy kernel ahead of this
+// one on the stream has completed, so its stores are performed), then waits until peer w has said the same here.
+// The wait is bounded: when the limit runs out state[3] records which peer was missing and the kernel returns, so
+// a rank that never arrives shows up as an error status instead of a hung GPU.
+static __global__ void peer_barrier_kernel(SignalPtrs sig, int rank, int n_peers, uint32_t* state, long long limit_cycles) {
   __shared__ uint32_t epoch;
-  if (threadIdx.x == 0) { epoch = state[1] + 1; state[1] = epoch; }
+  if (threadIdx.x == 0) { epoch = state[0] + 1; state[0] = epoch; }
   __syncthreads();
-  if ((int)threadIdx.x < n_peers) {
+  const int w = threadIdx.x;
+  if (w < n_peers) {
+    store_release_sys(sig.flags[w] + rank, epoch);
+    const uint32_t* mine = sig.flags[rank] + w;
     const long long t0 = clock64();
     bool ok = false;
     for (;;) {
-      if ((int32_t)(load_acquire_sys(flags + threadIdx.x) - epoch) >= 0) { ok = true; break; }
+      if ((int32_t)(load_acquire_sys(mine) - epoch) >= 0) { ok = true; break; }
       if (clock64() - t0 > limit_cycles) break;
-      __nanosleep(200);
     }
-    if (!ok) atomicCAS(&state[3], 0u, 100u + threadIdx.x);
+    if (!ok) atomicCAS(&state[3], 0u, 100u + w);
   }
 }
 
-int tri_scatter_runs_signal(const TriScatterDesc* d, const void* src, void* const* dst_ptrs, const TriPeerSignal* sig,
-                            tri_stream_t stream) {
-  if (d == nullptr || src == nullptr || dst_ptrs == nullptr || sig == nullptr || sig->flag_ptrs == nullptr || sig->state == nullptr)
-    return fail(TRI_ERR_ARG, "tri_scatter_runs_signal: null pointer");
-  if (d->run_bytes <= 0 || d->run_bytes % 16 != 0 || ((uintptr_t)src & 15))
-    return fail(TRI_ERR_ARG, "tri_scatter_runs_signal: runs must be 16-byte aligned multiples of 16 bytes");
-  if (d->peer_dim < 0 || d->peer_dim > 2 || d->n_peers < 1 || d->n_peers > 16 || d->dims[d->peer_dim] != d->n_peers ||
-      sig->n_peers != d->n_peers || sig->rank < 0 || sig->rank >= d->n_peers)
-    return fail(TRI_ERR_ARG, "tri_scatter_runs_signal: bad peer dimension or rank");
-  ScatterPtrs ptrs = {};
+int tri_peer_barrier(const TriPeerSignal* sig, int64_t limit_cycles, tri_stream_t stream) {
+  if (sig == nullptr || sig->flag_ptrs == nullptr || sig->state == nullptr || sig->n_peers < 1 || sig->n_peers > 16 ||
+      sig->rank < 0 || sig->rank >= sig->n_peers)
+    return fail(TRI_ERR_ARG, "tri_peer_barrier: bad signal descriptor");
   SignalPtrs sp = {};
-  for (int i = 0; i < d->n_peers; ++i) {
-    if (dst_ptrs[i] == nullptr || ((uintptr_t)dst_ptrs[i] & 15) || sig->flag_ptrs[i] == nullptr)
-      return fail(TRI_ERR_ARG, "tri_scatter_runs_signal: bad destination or flag pointer");
-    ptrs.p[i] = static_cast<uint4*>(dst_ptrs[i]);
+  for (int i = 0; i < sig->n_peers; ++i) {
+    if (sig->flag_ptrs[i] == nullptr) return fail(TRI_ERR_ARG, "tri_peer_barrier: null flag pointer");
     sp.flags[i] = static_cast<uint32_t*>(sig->flag_ptrs[i]);
   }
-  const long long outer = d->dims[0] * d->dims[1] * d->dims[2];
-  if (outer <= 0 || outer > 65535) return fail(TRI_ERR_ARG, "tri_scatter_runs_signal: between 1 and 65535 runs");
-  const long long run_v = d->run_bytes / 16;
-  const int bx = (int)std::max<long long>(1, std::min<long long>(32, (run_v + 2047) / 2048));
-  KernelTimer kt("tri_scatter_runs", (cudaStream_t)stream, 0.0, 2.0 * outer * d->run_bytes);
-  scatter_runs_signal_kernel<<<dim3(bx, (unsigned)outer), 256, 0, (cudaStream_t)stream>>>(
-      static_cast<const uint4*>(src), ptrs, d->dims[1], d->dims[2], d->dst_stride[0], d->dst_stride[1], d->dst_stride[2],
-      d->dst_base_run, d->peer_dim, run_v, sp, sig->rank, d->n_peers, sig->state);
-  TRI_LAUNCH_OK();
-  return 0;
-}
-
-int tri_peer_wait(const TriPeerSignal* sig, int64_t limit_cycles, tri_stream_t stream) {
-  if (sig == nullptr || sig->flag_ptrs == nullptr || sig->state == nullptr || sig->n_peers < 1 || sig->n_peers > 16 ||
-      sig->rank < 0 || sig->rank >= sig->n_peers || sig->flag_ptrs[sig->rank] == nullptr)
-    return fail(TRI_ERR_ARG, "tri_peer_wait: bad signal descriptor");
   if (limit_cycles <= 0) limit_cycles = 2000000000LL;   // about a second of SM clocks
-  KernelTimer kt("tri_peer_wait", (cudaStream_t)stream, 0.0, 0.0);
-  peer_wait_kernel<<<1, 32, 0, (cudaStream_t)stream>>>(static_cast<const uint32_t*>(sig->flag_ptrs[sig->rank]), sig->n_peers,
-                                                       sig->state, limit_cycles);
+  KernelTimer kt("tri_peer_barrier", (cudaStream_t)stream, 0.0, 0.0);
+  peer_barrier_kernel<<<1, 32, 0, (cudaStream_t)stream>>>(sp, sig->rank, sig->n_peers, sig->state, limit_cycles);
   TRI_LAUNCH_OK();
   return 0;
 }

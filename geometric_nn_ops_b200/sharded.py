@@ -99,9 +99,9 @@ def _permute_runs(t, dims, perm, run):
 # Peer-store exchange: with symmetric memory (every rank's receive buffer mapped into every other rank's address
 # space) the all-to-all and both layout changes become ONE copy kernel per rank that stores each run straight into
 # its place in the destination GPU's buffer over NVLink.  "Every rank has written" is ordered before "any rank reads"
-# by arrival flags, not by a collective: the copy kernel's last block stores this rank's exchange number into a flag
-# slot on every peer, and a one-block kernel queued behind it waits (bounded, about a second) until all peers' slots
-# have reached the same number.  No host round trip, nothing for NCCL to launch, and a captured graph replays as is.
+# by arrival flags, not by a collective: a one-block kernel queued behind the copy kernel stores this rank's barrier
+# number into a flag slot on every peer and then waits (bounded, about a second) until all peers' slots here have
+# reached the same number.  No host round trip, nothing for NCCL to launch, and a captured graph replays as is.
 # TRI_B200_EXCHANGE=peer_allreduce keeps the former barrier, a one-element all-reduce.
 #
 # Buffer reuse: a peer may overwrite a buffer only after this rank has finished reading it.  Each (call site, size)
@@ -186,7 +186,7 @@ def _peer_barrier(pb, tag, group, stream):
     """Order "every rank's stores have landed" before this rank's readers (queued next on ``stream``)."""
     with _timed(tag + ".barrier"):
         if os.environ.get("TRI_B200_EXCHANGE", "peer") == "peer":
-            _lib.check(_lib.load().tri_peer_wait(ctypes.byref(pb.sig), 0, stream), "tri_peer_wait")
+            _lib.check(_lib.load().tri_peer_barrier(ctypes.byref(pb.sig), 0, stream), "tri_peer_barrier")
             if os.environ.get("TRI_B200_CHECK") == "1" and not torch.cuda.is_current_stream_capturing():
                 status = int(pb.state[3].item())
                 if status != 0:
@@ -210,11 +210,7 @@ def _peer_scatter(t, dims, dst_stride, base_run, peer_dim, run, out_shape, tag, 
     stream = ctypes.c_void_p(torch.cuda.current_stream(t.device).cuda_stream)
     lib = _lib.load()
     with _timed(tag + ".peer_store"):
-        if os.environ.get("TRI_B200_EXCHANGE", "peer") == "peer":
-            _lib.check(lib.tri_scatter_runs_signal(ctypes.byref(d), ctypes.c_void_p(t.data_ptr()), pb.ptrs, ctypes.byref(pb.sig),
-                                                   stream), "tri_scatter_runs_signal")
-        else:
-            _lib.check(lib.tri_scatter_runs(ctypes.byref(d), ctypes.c_void_p(t.data_ptr()), pb.ptrs, stream), "tri_scatter_runs")
+        _lib.check(lib.tri_scatter_runs(ctypes.byref(d), ctypes.c_void_p(t.data_ptr()), pb.ptrs, stream), "tri_scatter_runs")
     _peer_barrier(pb, tag, group, stream)
     # The buffer is rewritten two exchanges with this tag from now.  Results the caller keeps beyond that (tensors
     # saved for the backward) get a private copy.
@@ -414,30 +410,32 @@ class _ShardedTriMul(torch.autograd.Function):
         bufs = _lib.TriMulShardBufs()
         bufs.x, bufs.mask, bufs.w, bufs.saved = xc.data_ptr(), None if mc is None else mc.data_ptr(), ctypes.pointer(w), saved.data_ptr()
         world, me = _world(group)
+        # one set of exchange buffers per direction: an outgoing and an incoming update may run side by side on two streams
+        tag = "out." if outgoing else "in."
         if world > 1 and peer_exchange_enabled(x.device, group) and os.environ.get("TRI_B200_EXCHANGE") == "fused":
             # compute and exchange in one kernel: the gate-in epilogue stores a and b straight into the channel
             # owners' buffers; the one-element all-reduce orders "all ranks have stored" before "anyone reads".
             # Opt-in: at 2 GPUs it measured 6.1 ms per step against 5.95 ms for GEMM + copy kernel (32-byte
             # remote stores from the epilogue use NVLink less well than the copy kernel's long runs).
-            pb = _peer_buffer("fwd.ab", 2 * B * Ch * R * N * xc.element_size(), x.device, group)
+            pb = _peer_buffer(tag + "fwd.ab", 2 * B * Ch * R * N * xc.element_size(), x.device, group)
             bufs.peer_ab = ctypes.cast(pb.ptrs, ctypes.POINTER(ctypes.c_void_p))
             bufs.peer_world, bufs.peer_rank = world, me
-            with _timed("fwd.ab.gemm_with_peer_store"):
+            with _timed(tag + "fwd.ab.gemm_with_peer_store"):
                 _phase(lib, d, _lib.PHASE_PROJECT, bufs, x.device)
-            with _timed("fwd.ab.barrier"):
+            with _timed(tag + "fwd.ab.barrier"):
                 dist.all_reduce(pb.token, group=group)
             bufs.peer_ab, bufs.peer_world = None, 0
             ab_ch = pb.buf.view(xc.dtype)[: 2 * B * Ch * R * N].view(2 * B, Ch // world, N, N).clone()   # saved for the backward
         else:
             bufs.a_cm, bufs.b_cm = ab[0].data_ptr(), ab[1].data_ptr()
             _phase(lib, d, _lib.PHASE_PROJECT, bufs, x.device)
-            ab_ch = rows_to_channels(ab.reshape(2 * B, Ch, R, N), group, tag="fwd.ab")      # [2B, Cs, N, N]
+            ab_ch = rows_to_channels(ab.reshape(2 * B, Ch, R, N), group, tag=tag + "fwd.ab")      # [2B, Cs, N, N]
         cs = ab_ch.shape[1]
         a_ch = ab_ch[:B].reshape(B * cs, N, N)
         b_ch = ab_ch[B:].reshape(B * cs, N, N)
         inc = not outgoing
         t_ch = bgemm(a_ch, b_ch, a_mn_major=inc, b_mn_major=inc)              # [B*Cs, N, N]
-        t_loc = channels_to_rows(t_ch.reshape(B, cs, N, N), group, tag="fwd.t")            # [B, Ch, R, N]
+        t_loc = channels_to_rows(t_ch.reshape(B, cs, N, N), group, tag=tag + "fwd.t")            # [B, Ch, R, N]
         out = torch.empty_like(xc)
         bufs.t_cm, bufs.out = t_loc.data_ptr(), out.data_ptr()
         _phase(lib, d, _lib.PHASE_OUTPUT, bufs, x.device)
@@ -477,7 +475,8 @@ class _ShardedTriMul(torch.autograd.Function):
         bufs.g = ctypes.pointer(g)
         bufs.d_out, bufs.t_cm, bufs.dt_cm = dc.data_ptr(), t_loc.data_ptr(), dt_loc.data_ptr()
         _phase(lib, d, _lib.PHASE_OUTPUT_BWD, bufs, dev)
-        dt_ch = rows_to_channels(dt_loc, group, tag="bwd.dt", persist=False)
+        tag = "out." if ctx.outgoing else "in."
+        dt_ch = rows_to_channels(dt_loc, group, tag=tag + "bwd.dt", persist=False)
         cs = dt_ch.shape[1]
         dt_ch = dt_ch.reshape(B * cs, N, N)
         if ctx.outgoing:   # da[i,k] = sum_j dt[i,j] b[j,k];  db[j,k] = sum_i dt[i,j] a[i,k]
@@ -487,7 +486,7 @@ class _ShardedTriMul(torch.autograd.Function):
             da = bgemm(b_ch, dt_ch, a_mn_major=False, b_mn_major=False)
             db = bgemm(a_ch, dt_ch, a_mn_major=False, b_mn_major=True)
         dab = channels_to_rows(torch.stack([da.reshape(B, cs, N, N), db.reshape(B, cs, N, N)]).reshape(2 * B, cs, N, N),
-                               group, tag="bwd.dab", persist=False).reshape(2, B, Ch, R, N)
+                               group, tag=tag + "bwd.dab", persist=False).reshape(2, B, Ch, R, N)
         dx = torch.empty_like(xc)
         bufs.a_cm, bufs.b_cm, bufs.dx = dab[0].data_ptr(), dab[1].data_ptr(), dx.data_ptr()
         _phase(lib, d, _lib.PHASE_PROJECT_BWD, bufs, dev)
@@ -537,15 +536,16 @@ def sharded_triangle_multiplicative_update(x, direction="outgoing", mask=None, *
 # ---------------------------------------------------------------------------------------------------
 # benchmark step (used by bench.py --gpus N)
 # ---------------------------------------------------------------------------------------------------
-_SIDE_STREAM = {}
+_SIDE_STREAMS = {}
 
 
 def make_bench_step(n, rank, world, host_inputs):
     """One forward+backward of the three ops on this rank's row shard of the N-sized problem.
 
-    The three ops are independent, so the attention (which needs no exchange) runs on a second stream beside the two
-    multiplicative updates: its kernels fill the gaps the updates' exchanges leave.  Every gradient that is a sum over
-    ranks (pair bias, weights) is added in ONE all-reduce at the end of the step.
+    The three ops of the step are independent of one another, so each runs on its own stream: the attention needs no
+    exchange and its kernels fill the gaps the two multiplicative updates' exchanges leave, and one update's copy
+    kernels run beside the other's GEMMs (TRI_B200_OVERLAP=0 puts everything back on one stream).  Every gradient
+    that is a sum over ranks (pair bias, weights) is added in ONE all-reduce at the end of the step.
     """
     i0, i1 = shard_rows(n, rank, world)
     t, w = host_inputs(n, 0, torch)                  # same seed everywhere: weights and bias are replicated
@@ -555,22 +555,34 @@ def make_bench_step(n, rank, world, host_inputs):
 
     def step(td, wd):
         main = torch.cuda.current_stream()
-        dev = main.device.index
-        side = _SIDE_STREAM.setdefault(dev, torch.cuda.Stream()) if overlap else main
-        with deferred_grad_sync() as sync:
-            side.wait_stream(main)
-            with torch.cuda.stream(side):
-                q, k, v, bias = (td[m].detach().requires_grad_() for m in ("q", "k", "v", "bias"))
-                o = sharded_triangle_attention(q, k, v, bias, td["key_mask"], q.shape[-1] ** -0.5)
-                res = [o, *torch.autograd.grad(o, [q, k, v, bias], grad_outputs=td["d_o"])]
-            for direction in ("outgoing", "incoming"):
-                x = td["x"].detach().requires_grad_()
-                wl = {m: p.detach().requires_grad_() for m, p in wd.items()}
-                out = sharded_triangle_multiplicative_update(x, direction, td["pair_mask"], **wl)
-                res += [out, *torch.autograd.grad(out, [x, *wl.values()], grad_outputs=td["d_out"])]
-            main.wait_stream(side)
-            for r_ in res[:5]:
-                r_.record_stream(main)
-        return res
+        if overlap:
+            streams = _SIDE_STREAMS.setdefault(main.device.index, [torch.cuda.Stream() for _ in range(3)])
+        else:
+            streams = [main, main, main]
+        res = [None, None, None]
+
+        def attention():
+            q, k, v, bias = (td[m].detach().requires_grad_() for m in ("q", "k", "v", "bias"))
+            o = sharded_triangle_attention(q, k, v, bias, td["key_mask"], q.shape[-1] ** -0.5)
+            return [o, *torch.autograd.grad(o, [q, k, v, bias], grad_outputs=td["d_o"])]
+
+        def update(direction):
+            x = td["x"].detach().requires_grad_()
+            wl = {m: p.detach().requires_grad_() for m, p in wd.items()}
+            out = sharded_triangle_multiplicative_update(x, direction, td["pair_mask"], **wl)
+            return [out, *torch.autograd.grad(out, [x, *wl.values()], grad_outputs=td["d_out"])]
+
+        with deferred_grad_sync():
+            for i, (st, fn) in enumerate(zip(streams, (attention, lambda: update("outgoing"), lambda: update("incoming")))):
+                st.wait_stream(main)
+                with torch.cuda.stream(st):
+                    res[i] = fn()
+            for st in streams:
+                main.wait_stream(st)
+            out = res[0] + res[1] + res[2]
+            if overlap:
+                for r_ in out:
+                    r_.record_stream(main)      # allocated on a side stream, used (summed, copied out) on this one
+        return out
 
     return step, t, w

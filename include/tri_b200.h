@@ -263,29 +263,26 @@ int tri_scatter_runs(const TriScatterDesc* d, const void* src, void* const* dst_
 
 /* Arrival flags for the peer-store exchange, in place of a collective as the barrier after tri_scatter_runs.
  * No counterpart in the reference (single device).  Every rank owns an array of 16 uint32 arrival flags in memory
- * that all peers can store to (symmetric memory); flag_ptrs[w] is rank w's array as mapped on this GPU.  `state` is
- * 4 uint32 in this GPU's own memory, zero-initialised once: exchanges sent, exchanges awaited, a block counter, and
- * the status of the last wait.
- *   tri_scatter_runs_signal  the run copy of tri_scatter_runs; when all of it has been stored, slot `rank` of every
- *                            peer's flag array is set to this rank's exchange number (release at system scope).
- *   tri_peer_wait            a one-block kernel that waits until all n_peers slots of this rank's own array have
- *                            reached its next exchange number; kernels queued behind it on the stream then read
- *                            the exchanged data.  The wait is BOUNDED: after limit_cycles SM clocks (<= 0: about a
- *                            second) it gives up, stores 100 + the missing peer in state[3] and returns, so a
- *                            missing rank becomes an error the host can read, never a hung GPU.
- * Both advance their exchange numbers on the device, so a captured CUDA graph replays without changed arguments.
- * Every rank must call the pair once per exchange, in the same order.  A buffer may be rewritten by a later
- * exchange once this rank has passed a wait on a LATER exchange that involves the same peers: their copy kernel
- * for that one is ordered, on their stream, behind whatever read the earlier data. */
+ * that all peers can store to (symmetric memory), zeroed before first use; flag_ptrs[w] is rank w's array as mapped
+ * on this GPU.  `state` is 4 uint32 in this GPU's own memory, zero-initialised once: state[0] counts the barriers this
+ * rank has entered, state[3] is the status of the last wait.
+ * tri_peer_barrier queues a one-block kernel that (1) stores this rank's barrier number into slot `rank` of every
+ * peer's flag array (release at system scope: whatever this rank queued on the stream before it, e.g. the copy kernel
+ * of tri_scatter_runs, has completed and is visible), then (2) waits until all n_peers slots of this rank's own array
+ * have reached that number; kernels queued behind it then read the exchanged data.  The wait is BOUNDED: after
+ * limit_cycles SM clocks (<= 0: about a second) it gives up, stores 100 + the missing peer in state[3] and returns,
+ * so a missing rank becomes an error the host can read, never a hung GPU.  The barrier number advances on the
+ * device, so a captured CUDA graph replays without changed arguments.  Every rank must enter the same barriers in
+ * the same order.  A receive buffer may be rewritten by a later exchange once this rank has passed a barrier of a
+ * LATER exchange with the same peers: their copy kernel for that one is ordered, on their stream, behind whatever
+ * read the earlier data. */
 typedef struct TriPeerSignal {
   void* const* flag_ptrs;  /* [n_peers] */
   uint32_t* state;         /* 4 words, this GPU */
   int32_t rank, n_peers;
 } TriPeerSignal;
 
-int tri_scatter_runs_signal(const TriScatterDesc* d, const void* src, void* const* dst_ptrs, const TriPeerSignal* sig,
-                            tri_stream_t stream);
-int tri_peer_wait(const TriPeerSignal* sig, int64_t limit_cycles, tri_stream_t stream);
+int tri_peer_barrier(const TriPeerSignal* sig, int64_t limit_cycles, tri_stream_t stream);
 
 /* The tensor-core kernels bound every wait; if one runs out, the kernel records a code in the first
  * word of the workspace it was given and drains instead of hanging.  This call copies that word back

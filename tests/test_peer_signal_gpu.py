@@ -1,6 +1,6 @@
-"""Arrival flags of the peer-store exchange on one GPU: the copy kernel raises its flag, the wait kernel sees it, and a
-wait for a flag that nobody raises runs out after its limit and reports which peer was missing (the GPU stays usable:
-the wait is bounded by design, nothing here hangs or faults)."""
+"""Arrival flags of the peer-store exchange on one GPU: a barrier among "peers" that all map to this GPU passes and
+advances its number, and a wait for a flag that nobody raises runs out after its limit and reports which peer was
+missing (the GPU stays usable: the wait is bounded by design, nothing here hangs or faults)."""
 
 import ctypes
 
@@ -10,50 +10,41 @@ import torch
 pytestmark = pytest.mark.gpu
 
 
-def _signal(flags, state, rank, n_peers):
+def _signal(flag_arrays, state, rank):
     from geometric_nn_ops_b200 import _lib
-    ptrs = (ctypes.c_void_p * n_peers)(*[flags.data_ptr()] * n_peers)
+    n = len(flag_arrays)
+    ptrs = (ctypes.c_void_p * n)(*[f.data_ptr() for f in flag_arrays])
     sig = _lib.TriPeerSignal()
     sig.flag_ptrs = ctypes.cast(ptrs, ctypes.POINTER(ctypes.c_void_p))
-    sig.state, sig.rank, sig.n_peers = state.data_ptr(), rank, n_peers
+    sig.state, sig.rank, sig.n_peers = state.data_ptr(), rank, n
     return sig, ptrs   # keep the pointer array alive
 
 
-def test_copy_raises_the_flag_and_the_wait_passes():
+def test_a_barrier_with_itself_passes_and_counts():
     from geometric_nn_ops_b200 import _lib
     lib = _lib.load()
     flags = torch.zeros(16, dtype=torch.int32, device="cuda")
     state = torch.zeros(4, dtype=torch.int32, device="cuda")
-    sig, keep = _signal(flags, state, 0, 1)
-    src = torch.arange(3 * 4 * 64, dtype=torch.float32, device="cuda").reshape(3, 1, 4, 64)
-    dst = torch.zeros(4, 3, 64, dtype=torch.float32, device="cuda")          # dst[i2][i0] = src[i0][0][i2]
-    d = _lib.TriScatterDesc()
-    d.dims[:] = (3, 1, 4)
-    d.dst_stride[:] = (1, 0, 3)
-    d.dst_base_run, d.run_bytes, d.peer_dim, d.n_peers = 0, 64 * 4, 1, 1
-    dptr = (ctypes.c_void_p * 1)(dst.data_ptr())
+    sig, keep = _signal([flags], state, 0)       # a world of one: this rank raises its own slot and waits for it
     stream = ctypes.c_void_p(torch.cuda.current_stream().cuda_stream)
     for epoch in (1, 2, 3):
-        dst.zero_()
-        _lib.check(lib.tri_scatter_runs_signal(ctypes.byref(d), ctypes.c_void_p(src.data_ptr()), dptr, ctypes.byref(sig),
-                                               stream), "tri_scatter_runs_signal")
-        _lib.check(lib.tri_peer_wait(ctypes.byref(sig), 0, stream), "tri_peer_wait")
+        _lib.check(lib.tri_peer_barrier(ctypes.byref(sig), 0, stream), "tri_peer_barrier")
         torch.cuda.synchronize()
-        assert torch.equal(dst, src[:, 0].transpose(0, 1))
-        assert flags[0].item() == epoch and state.tolist() == [epoch, epoch, 0, 0]
+        assert flags[0].item() == epoch and state.tolist() == [epoch, 0, 0, 0]
 
 
 def test_a_wait_nobody_answers_runs_out_and_reports_the_peer():
     from geometric_nn_ops_b200 import _lib
     lib = _lib.load()
-    flags = torch.zeros(16, dtype=torch.int32, device="cuda")
-    flags[0] = 1                                   # peer 0 has arrived, peer 1 never does
+    mine = torch.zeros(16, dtype=torch.int32, device="cuda")      # this rank's flags: slot 1 is never raised
+    theirs = torch.zeros(16, dtype=torch.int32, device="cuda")    # stands for the silent peer's array
     state = torch.zeros(4, dtype=torch.int32, device="cuda")
-    sig, keep = _signal(flags, state, 0, 2)
+    sig, keep = _signal([mine, theirs], state, 0)
     stream = ctypes.c_void_p(torch.cuda.current_stream().cuda_stream)
-    _lib.check(lib.tri_peer_wait(ctypes.byref(sig), 4_000_000, stream), "tri_peer_wait")   # ~2 ms of SM clocks
+    _lib.check(lib.tri_peer_barrier(ctypes.byref(sig), 4_000_000, stream), "tri_peer_barrier")   # ~2 ms of SM clocks
     torch.cuda.synchronize()
-    assert state.tolist() == [0, 1, 0, 101]
+    assert state.tolist() == [1, 0, 0, 101]                       # peer 1 was missing
+    assert mine[0].item() == 1 and theirs[0].item() == 1          # this rank did raise its flag on both
     # the context is intact: the next kernel runs normally
     assert (torch.ones(8, device="cuda") * 2).sum().item() == 16.0
 
@@ -62,5 +53,4 @@ def test_bad_descriptors_are_refused():
     from geometric_nn_ops_b200 import _lib
     lib = _lib.load()
     sig = _lib.TriPeerSignal()
-    assert lib.tri_peer_wait(ctypes.byref(sig), 0, None) == -1
-    assert lib.tri_scatter_runs_signal(None, None, None, None, None) == -1
+    assert lib.tri_peer_barrier(ctypes.byref(sig), 0, None) == -1
