@@ -329,8 +329,8 @@ def main():
                     help="--impl reference: stop after this many seconds of timed CPU steps")
     args = ap.parse_args()
     if args.workload == "stack":
-        from geometric_nn_ops_b200 import pairstack_bench
-        return pairstack_bench.main(args)
+        import bench_stack
+        return bench_stack.main(args)
     rank = int(os.environ.get("RANK", "0"))
     world = int(os.environ.get("WORLD_SIZE", "1"))
     n, only = args.n_res, args.only

@@ -13,7 +13,7 @@ import sys
 
 import torch
 
-from . import _lib, pairstack, sharded
+from geometric_nn_ops_b200 import _lib, pairstack, sharded
 
 N_STACK, N_BLOCKS, N_CHECK = 1024, 4, 128
 

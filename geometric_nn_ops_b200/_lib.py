@@ -33,6 +33,11 @@ class TriMulDesc(Structure):
     ]
 
 
+class TriAttnProjDesc(Structure):
+    _fields_ = [("M", c_int64), ("C", c_int32), ("H", c_int32), ("D", c_int32), ("dtype", c_int32), ("precision", c_int32),
+                ("eps", c_float)]
+
+
 class TriGemmDesc(Structure):
     _fields_ = [
         ("M", c_int32), ("N", c_int32), ("K", c_int32), ("batch", c_int32), ("dtype", c_int32),
@@ -96,6 +101,8 @@ EXPORTS = {
     "tri_attn_fwd": (c_int, [POINTER(TriAttnDesc)] + [c_void_p] * 8 + [c_size_t, c_void_p]),
     "tri_attn_bwd": (c_int, [POINTER(TriAttnDesc)] + [c_void_p] * 13 + [c_size_t, c_void_p]),
     "tri_attn_bwd_noalloc": (c_int, [POINTER(TriAttnDesc)] + [c_void_p] * 12 + [c_void_p]),
+    "tri_attn_project_ws_bytes": (c_size_t, [POINTER(TriAttnProjDesc)]),
+    "tri_attn_project": (c_int, [POINTER(TriAttnProjDesc)] + [c_void_p] * 8 + [c_size_t, c_void_p]),
     "tri_mul_saved_bytes": (c_size_t, [POINTER(TriMulDesc)]),
     "tri_mul_ws_bytes": (c_size_t, [POINTER(TriMulDesc), c_int]),
     "tri_mul_fwd": (c_int, [POINTER(TriMulDesc), c_void_p, c_void_p, POINTER(TriMulWeights), c_void_p, c_void_p,

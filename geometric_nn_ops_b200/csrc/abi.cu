@@ -195,6 +195,26 @@ int tri_attn_bwd_noalloc(const TriAttnDesc* d, const void* q, const void* k, con
   return simt::attn_backward_static(d, q, k, v, bias, mask, o, lse, d_o, dq, dk, dv, dbias, (cudaStream_t)stream);
 }
 
+static int check_project(const TriAttnProjDesc* d) {
+  if (d == nullptr) return fail(TRI_ERR_ARG, "descriptor is null");
+  if (d->dtype < TRI_F32 || d->dtype > TRI_F16) return fail(TRI_ERR_ARG, "bad dtype %d", d->dtype);
+  if (!tc::attn_project_supported(d))
+    return fail(TRI_ERR_UNSUPPORTED, "the fused projection needs C = 128, 1 <= H <= 8, H*D a multiple of 8, and bf16 / fp16 or fp32-tf32");
+  return 0;
+}
+
+size_t tri_attn_project_ws_bytes(const TriAttnProjDesc* d) {
+  return check_project(d) != 0 ? 0 : tc::attn_project_ws_bytes(d);
+}
+
+int tri_attn_project(const TriAttnProjDesc* d, const void* z, const void* ln_w, const void* ln_b, const void* w_qkv,
+                     const void* w_bias, void* qkv, void* bias, void* ws, size_t ws_bytes, tri_stream_t stream) {
+  TRI_TRY(check_project(d));
+  if (!z || !w_qkv || !w_bias || !qkv || !bias || !ws) return fail(TRI_ERR_ARG, "z, w_qkv, w_bias, qkv, bias and ws must not be null");
+  set_path("tcgen05");
+  return tc::attn_project(d, z, ln_w, ln_b, w_qkv, w_bias, qkv, bias, ws, ws_bytes, (cudaStream_t)stream);
+}
+
 size_t tri_mul_saved_bytes(const TriMulDesc* d) {
   if (check_mul(d) != 0) return 0;
   return tc::mul_supported(d) ? tc::mul_saved_bytes(d) : simt::saved_bytes(d);

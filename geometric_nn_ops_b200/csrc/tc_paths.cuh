@@ -27,5 +27,10 @@ size_t mul_shard_saved_bytes(const TriMulShardDesc* d);
 size_t mul_shard_ws_bytes(const TriMulShardDesc* d, int phase);
 int mul_shard_phase(const TriMulShardDesc* d, int phase, const TriMulShardBufs* bufs, void* ws, size_t ws_size,
                     cudaStream_t st);
+// Fused LayerNorm + q / k / v / pair-bias projection feeding triangle attention (see tri_attn_project in the C header).
+bool attn_project_supported(const TriAttnProjDesc* d);
+size_t attn_project_ws_bytes(const TriAttnProjDesc* d);
+int attn_project(const TriAttnProjDesc* d, const void* z, const void* ln_w, const void* ln_b, const void* w_qkv,
+                 const void* w_bias, void* qkv, void* bias, void* ws, size_t ws_size, cudaStream_t st);
 }  // namespace tc
 }  // namespace tri

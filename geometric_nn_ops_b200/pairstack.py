@@ -25,7 +25,7 @@ import torch
 import torch.nn.functional as F
 
 from . import sharded
-from .triangle import triangle_attention, triangle_multiplicative_update
+from .triangle import attention_input_projection, triangle_attention, triangle_multiplicative_update
 
 HEADS, HEAD_DIM = 4, 32
 TRIMUL_NAMES = ("norm_in_weight", "norm_in_bias", "p_in_weight", "g_in_weight", "norm_out_weight", "norm_out_bias",
@@ -40,7 +40,7 @@ class BlockWeights:
     attn_end: dict
 
     def to(self, device=None, dtype=None):
-        mv = lambda d: {k: v.to(device=device, dtype=dtype) for k, v in d.items()}  # noqa: E731
+        mv = lambda d: {k: v.to(device=device, dtype=dtype) for k, v in d.items() if not k.startswith("_")}  # noqa: E731
         return BlockWeights(mv(self.trimul_out), mv(self.trimul_in), mv(self.attn_start), mv(self.attn_end))
 
 
@@ -74,8 +74,23 @@ def make_inputs(n, c=128, masked_tail=64, dtype=torch.bfloat16, seed=100):
     return z, (res[:, None] * res[None, :]).reshape(1, n, n).to(dtype)
 
 
+def _fused_weights(w):
+    """The projection weights in the layout the fused kernel takes, built once per block and kept with it."""
+    if "_w_qkv" not in w:
+        w["_w_qkv"] = torch.cat([w["wq"].t(), w["wk"].t(), w["wv"].t()]).contiguous()    # [3*H*D, C]
+        w["_w_bias"] = w["wb"].t().contiguous()                                            # [H, C]
+    return w["_w_qkv"], w["_w_bias"]
+
+
 def project_attention_inputs(z, w):
-    """``z`` ``[B, R, N, C]`` (R rows) -> q, k, v ``[B, R, N, H, D]`` and this rows' bias ``[B, H, R, N]``."""
+    """``z`` ``[B, R, N, C]`` (R rows) -> q, k, v ``[B, R, N, H, D]`` and this rows' bias ``[B, H, R, N]``.
+
+    On the GPU with C = 128 this is the library's fused projection (one LayerNorm + bias kernel, one GEMM); the
+    torch composition below it defines what that computes and serves every other case."""
+    if z.is_cuda and z.shape[-1] == 128 and z.dtype in (torch.bfloat16, torch.float16) and not torch.is_grad_enabled():
+        w_qkv, w_bias = _fused_weights(w)
+        q, k, v, bias = attention_input_projection(z, w_qkv, w_bias, HEADS)
+        return q, k, v, bias.contiguous()
     zn = F.layer_norm(z, z.shape[-1:])
     B, R, N, _ = z.shape
     q, k, v = ((zn @ w[m]).view(B, R, N, HEADS, HEAD_DIM) for m in ("wq", "wk", "wv"))

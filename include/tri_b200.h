@@ -118,6 +118,26 @@ int tri_attn_bwd_noalloc(const TriAttnDesc* d, const void* q, const void* k, con
                          const void* d_o, void* dq, void* dk, void* dv, float* dbias /*nullable*/,
                          tri_stream_t stream);
 
+/* Fused input projection of triangle attention inside a pair stack: zn = LayerNorm(z) over the 128 channels, then
+ *   qkv[m][0 : 3*H*D] = zn[m] Wqkv^T   (one [M, 3*H*D] buffer: columns [0, H*D) are q, then k, then v, each read by
+ *                                       tri_attn_fwd as [.., H, D] with a residue stride of 3*H*D elements)
+ *   bias[h][m]        = zn[m] . Wb[h]  (head-major: with M = B*N*N pixels this is the [B, H, N, N] pair bias for B = 1)
+ * No counterpart in the reference, whose attention takes pre-projected tensors
+ * (geometric_nn_ops_torch/triangle/_triattn.py:36-44); callers there run a LayerNorm, four linears and a permute.
+ * z: [M, C] contiguous, C = 128; ln_w / ln_b: [C] or NULL; w_qkv: [3*H*D, C]; w_bias: [H, C], H <= 8; everything in
+ * `dtype` (fp32 needs precision tf32: tensor-core path only).  Forward only. */
+typedef struct TriAttnProjDesc {
+  int64_t M;
+  int32_t C, H, D;
+  int32_t dtype, precision;
+  float eps;
+} TriAttnProjDesc;
+
+size_t tri_attn_project_ws_bytes(const TriAttnProjDesc* d);
+int tri_attn_project(const TriAttnProjDesc* d, const void* z, const void* ln_w /*nullable*/, const void* ln_b /*nullable*/,
+                     const void* w_qkv, const void* w_bias, void* qkv, void* bias, void* ws, size_t ws_bytes,
+                     tri_stream_t stream);
+
 /* ------------------------------------------------------------------------ */
 /* Triangle multiplicative update                                           */
 /* ------------------------------------------------------------------------ */

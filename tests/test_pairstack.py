@@ -33,3 +33,32 @@ def test_flop_count_matches_the_stated_figures():
     from geometric_nn_ops_b200 import pairstack
     per_block = pairstack.stack_flops(1024, 1)
     assert abs(per_block - (2 * 481.0e9 + 2 * 549.8e9 + 208e9)) / per_block < 0.01
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16], ids=str)
+@pytest.mark.parametrize("shape", [(1, 24, 40, 4), (2, 16, 16, 8), (1, 128, 128, 4)], ids=str)
+def test_fused_projection_against_torch_fp32(shape, dtype):
+    """LayerNorm + q/k/v/bias projection kernel against the same composition in fp32 torch on the rounded inputs."""
+    from geometric_nn_ops_b200.triangle import attention_input_projection
+    B, R, N, H = shape
+    D = 128 // H
+    g = torch.Generator().manual_seed(R + N)
+    z = (torch.randn(B, R, N, 128, generator=g) * 2 + 0.5).to(dtype).cuda()
+    w_qkv = (torch.randn(3 * H * D, 128, generator=g) * 128 ** -0.5).to(dtype).cuda()
+    w_bias = (torch.randn(H, 128, generator=g) * 128 ** -0.5).to(dtype).cuda()
+    ln_w = (1 + 0.1 * torch.randn(128, generator=g)).to(dtype).cuda()
+    ln_b = (0.1 * torch.randn(128, generator=g)).to(dtype).cuda()
+    for lw, lb in ((None, None), (ln_w, ln_b)):
+        with torch.no_grad():
+            q, k, v, bias = attention_input_projection(z, w_qkv, w_bias, H, lw, lb)
+        assert q.shape == (B, R, N, H, D) and bias.shape == (B, H, R, N)
+        zn = torch.nn.functional.layer_norm(z.float(), (128,), None if lw is None else lw.float(), None if lb is None else lb.float())
+        zn = zn.to(dtype).float()                      # the kernel stores zn in the input dtype before the GEMM
+        ref = (zn @ w_qkv.float().t()).view(B, R, N, 3, H, D)
+        for got, want in ((q, ref[:, :, :, 0]), (k, ref[:, :, :, 1]), (v, ref[:, :, :, 2]),
+                          (bias, (zn @ w_bias.float().t()).permute(0, 3, 1, 2))):
+            rel = (got.float() - want).norm() / want.norm()
+            assert rel < (6e-3 if dtype == torch.bfloat16 else 1e-3), rel
+    with pytest.raises(RuntimeError, match="forward only"):
+        attention_input_projection(z.requires_grad_(), w_qkv, w_bias, H)
