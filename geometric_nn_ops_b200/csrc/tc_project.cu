@@ -52,14 +52,23 @@ __device__ __forceinline__ float half_warp_sum(float v) {
 }
 
 // A row of 128 channels is held by 16 lanes (8 channels each), two rows per warp access, kRowPairs pairs in flight.
-template <typename T>
+// H4 = true is the common four-head case: the lane's 32 bias weights live in registers and the four dot products are
+// reduced over the 16 lanes with a halving butterfly (each step keeps half of the values and adds the partner's),
+// 5 shuffles per row instead of 16.
+template <typename T, bool H4>
 __global__ void __launch_bounds__(256) ln_bias_kernel(const T* __restrict__ z, const T* gamma, const T* beta, float eps,
                                                        long long M, const T* __restrict__ wb, int H, T* __restrict__ zn,
                                                        T* __restrict__ bias) {
-  __shared__ float sWb[kMaxHeads][CW];
-  for (int i = threadIdx.x; i < H * CW; i += 256) sWb[i / CW][i % CW] = to_f32(wb[i]);
-  __syncthreads();
+  __shared__ float sWb[H4 ? 1 : kMaxHeads][CW];
   const int lane = threadIdx.x & 31, sub = lane & 15, half = lane >> 4;
+  float wr[4][8];
+  if constexpr (H4) {
+#pragma unroll
+    for (int h = 0; h < 4; ++h) ld8(wb + h * CW + sub * 8, wr[h]);
+  } else {
+    for (int i = threadIdx.x; i < H * CW; i += 256) sWb[i / CW][i % CW] = to_f32(wb[i]);
+    __syncthreads();
+  }
   const long long row0 = (blockIdx.x * 8LL + (threadIdx.x >> 5)) * (2 * kRowPairs) + half;
   float gm[8], bt[8];
 #pragma unroll
@@ -93,12 +102,29 @@ __global__ void __launch_bounds__(256) ln_bias_kernel(const T* __restrict__ z, c
     // the bias is projected from the values the GEMM will see: zn rounded to the storage dtype
 #pragma unroll
     for (int i = 0; i < 8; ++i) v[p][i] = to_f32(from_f32<T>(v[p][i]));
-    for (int h = 0; h < H; ++h) {
-      float d = 0.f;
+    if constexpr (H4) {
+      float d[4] = {0.f, 0.f, 0.f, 0.f};
 #pragma unroll
-      for (int i = 0; i < 8; ++i) d += v[p][i] * sWb[h][sub * 8 + i];
-      d = half_warp_sum(d);
-      if (sub == 0 && row < M) bias[(long long)h * M + row] = from_f32<T>(d);
+      for (int h = 0; h < 4; ++h)
+#pragma unroll
+        for (int i = 0; i < 8; ++i) d[h] += v[p][i] * wr[h][i];
+      // lanes with bit 3 clear keep heads 0, 1 and those with it set heads 2, 3; then bit 2 picks one of the two
+      const bool hi8 = (sub & 8) != 0, hi4 = (sub & 4) != 0;
+      const float a = (hi8 ? d[2] : d[0]) + __shfl_xor_sync(0xffffffffu, hi8 ? d[0] : d[2], 8);
+      const float b = (hi8 ? d[3] : d[1]) + __shfl_xor_sync(0xffffffffu, hi8 ? d[1] : d[3], 8);
+      float c = (hi4 ? b : a) + __shfl_xor_sync(0xffffffffu, hi4 ? a : b, 4);
+      c += __shfl_xor_sync(0xffffffffu, c, 2);
+      c += __shfl_xor_sync(0xffffffffu, c, 1);
+      const int h = (hi8 ? 2 : 0) + (hi4 ? 1 : 0);
+      if ((sub & 3) == 0 && row < M) bias[(long long)h * M + row] = from_f32<T>(c);
+    } else {
+      for (int h = 0; h < H; ++h) {
+        float d = 0.f;
+#pragma unroll
+        for (int i = 0; i < 8; ++i) d += v[p][i] * sWb[h][sub * 8 + i];
+        d = half_warp_sum(d);
+        if (sub == 0 && row < M) bias[(long long)h * M + row] = from_f32<T>(d);
+      }
     }
   }
 }
@@ -113,8 +139,9 @@ int project_t(const TriAttnProjDesc* d, const void* z, const void* ln_w, const v
   const double unit = (double)M * CW * sizeof(T);
   {
     KernelTimer kt("tc_ln_bias", st, 2.0 * M * CW * d->H, 2.0 * unit);
-    ln_bias_kernel<T><<<cdiv(M, 8 * 2 * kRowPairs), 256, 0, st>>>((const T*)z, (const T*)ln_w, (const T*)ln_b, d->eps, M,
-                                                               (const T*)w_bias, d->H, (T*)zn, (T*)bias);
+    auto kern = d->H == 4 ? ln_bias_kernel<T, true> : ln_bias_kernel<T, false>;
+    kern<<<cdiv(M, 8 * 2 * kRowPairs), 256, 0, st>>>((const T*)z, (const T*)ln_w, (const T*)ln_b, d->eps, M, (const T*)w_bias,
+                                                      d->H, (T*)zn, (T*)bias);
     TRI_LAUNCH_OK();
   }
   const int n_out = 3 * d->H * d->D;
