@@ -19,6 +19,7 @@
 // Math follows trimul_torch (geometric_nn_ops_torch/triangle/_reference/trimul.py:57-97).
 #include <algorithm>
 #include <cstdlib>
+#include <initializer_list>
 
 #include "tc_gemm.cuh"
 #include "tc_paths.cuh"
@@ -376,6 +377,27 @@ __global__ void __launch_bounds__(256) reduce_kernel(const float* partial, int n
   if (lane4 == 0 && j < n) out[j] = (sub[0][o] + sub[1][o]) + (sub[2][o] + sub[3][o]);
 }
 
+// Up to four such reductions in one launch (blockIdx.y selects the job): the backward has pairs of small reductions
+// (two weight gradients, LayerNorm weight and bias) whose launches cost more than their work.
+struct ReduceJobs {
+  const float* partial[4];
+  float* out[4];
+  int nparts[4], n[4];
+};
+__global__ void __launch_bounds__(256) reduce_multi_kernel(const ReduceJobs jobs) {
+  __shared__ float sub[4][64];
+  const int job = blockIdx.y, n = jobs.n[job], nparts = jobs.nparts[job];
+  const float* partial = jobs.partial[job];
+  const int o = threadIdx.x & 63, lane4 = threadIdx.x >> 6;
+  const int j = blockIdx.x * 64 + o;
+  float s = 0.f;
+  if (j < n)
+    for (int p = lane4; p < nparts; p += 4) s += partial[(long long)p * n + j];
+  sub[lane4][o] = s;
+  __syncthreads();
+  if (lane4 == 0 && j < n) jobs.out[job][j] = (sub[0][o] + sub[1][o]) + (sub[2][o] + sub[3][o]);
+}
+
 // Row sums of the channel-major dPG [512, M] scattered to the p_in / g_in bias gradients (one block per row,
 // fixed summation order).
 template <typename T>
@@ -549,6 +571,26 @@ int split_k_grad(cudaStream_t st, const Geom& gm, const void* lhs, int lhs_w, co
   return launch_gemm(st, gm.dtype, EPI_STORE, 128, true, p, err);
 }
 
+// reduce_to for several (partial, nparts, n, out) jobs at once; jobs whose `out` is null are dropped
+struct ReduceJob { const float* partial; int nparts, n; float* out; };
+int reduce_many(cudaStream_t st, std::initializer_list<ReduceJob> list) {
+  ReduceJobs jobs = {};
+  int count = 0, nmax = 0;
+  double bytes = 0.0;
+  for (const ReduceJob& j : list) {
+    if (j.out == nullptr) continue;
+    jobs.partial[count] = j.partial; jobs.out[count] = j.out; jobs.nparts[count] = j.nparts; jobs.n[count] = j.n;
+    nmax = std::max(nmax, j.n);
+    bytes += 4.0 * (j.nparts + 1) * j.n;
+    ++count;
+  }
+  if (count == 0) return 0;
+  KernelTimer kt("tc_reduce", st, 0.0, bytes);
+  reduce_multi_kernel<<<dim3(cdiv(nmax, 64), count), 256, 0, st>>>(jobs);
+  TRI_LAUNCH_OK();
+  return 0;
+}
+
 int reduce_to(cudaStream_t st, const float* partial, int nparts, int n, float* out) {
   KernelTimer kt("tc_reduce", st, 0.0, 4.0 * (nparts + 1) * n);
   reduce_kernel<<<cdiv(n, 64), 256, 0, st>>>(partial, nparts, n, out);
@@ -585,13 +627,12 @@ int phase_output_bwd(cudaStream_t st, const Geom& gm, const void* d_out, const v
     p.name = "tc_gemm_gate_out_bwd"; p.flops = 0.0; p.bytes = 5.0 * gm.unit();  // recompute: no algorithmic flops
     TRI_TRY(launch_gemm(st, gm.dtype, EPI_GATE_OUT_BWD, 256, false, p, pr.err));
   }
-  if (g->p_out_w) {
-    TRI_TRY(split_k_grad(st, gm, dy, CW, u, partial, pr.err, "tc_gemm_wgrad", &nparts));
-    TRI_TRY(reduce_to(st, partial, nparts, CW * CW, g->p_out_w));
-  }
-  if (g->g_out_w) {
-    TRI_TRY(split_k_grad(st, gm, dgo, CW, z, partial, pr.err, "tc_gemm_wgrad", &nparts));
-    TRI_TRY(reduce_to(st, partial, nparts, CW * CW, g->g_out_w));
+  {   // the two output weight gradients: split-K partials side by side, one reduction launch for both
+    float* part2 = partial + (size_t)kSplitK * CW * CW;
+    int n1 = 0, n2 = 0;
+    if (g->p_out_w) TRI_TRY(split_k_grad(st, gm, dy, CW, u, partial, pr.err, "tc_gemm_wgrad", &n1));
+    if (g->g_out_w) TRI_TRY(split_k_grad(st, gm, dgo, CW, z, part2, pr.err, "tc_gemm_wgrad", &n2));
+    TRI_TRY(reduce_many(st, {{partial, n1, CW * CW, g->p_out_w}, {part2, n2, CW * CW, g->g_out_w}}));
   }
   if (g->p_out_b) {
     TRI_TRY(colsum_to<T>(st, dy, M, CW, partial, &nparts));
@@ -617,9 +658,7 @@ int phase_output_bwd(cudaStream_t st, const Geom& gm, const void* d_out, const v
                                                   (const T*)w->norm_out_w, M, gm.plane, (T*)dt_cm, pg, pb);
     TRI_LAUNCH_OK();
   }
-  if (g->norm_out_w) TRI_TRY(reduce_to(st, pg, kLnCmBwdBlocks, CW, g->norm_out_w));
-  if (g->norm_out_b) TRI_TRY(reduce_to(st, pb, kLnCmBwdBlocks, CW, g->norm_out_b));
-  return 0;
+  return reduce_many(st, {{pg, kLnCmBwdBlocks, CW, g->norm_out_w}, {pb, kLnCmBwdBlocks, CW, g->norm_out_b}});
 }
 
 // ---- backward of phase 1: da, db (channel-major), dgo -> gradients of the input weights, dx ---------------
@@ -670,9 +709,7 @@ int phase_project_bwd(cudaStream_t st, const Geom& gm, const void* x, const void
                                                   M, (T*)dx, pg, pb);
     TRI_LAUNCH_OK();
   }
-  if (g->norm_in_w) TRI_TRY(reduce_to(st, pg, blocks, CW, g->norm_in_w));
-  if (g->norm_in_b) TRI_TRY(reduce_to(st, pb, blocks, CW, g->norm_in_b));
-  return 0;
+  return reduce_many(st, {{pg, blocks, CW, g->norm_in_w}, {pb, blocks, CW, g->norm_in_b}});
 }
 
 // ---------------------------------------------------------------------------------------------
