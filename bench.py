@@ -401,6 +401,7 @@ def main():
         res = step_fn(dev_t, dev_w)
         torch.cuda.synchronize()
         if world > 1:
+            sharded.check_exchange_status()      # no barrier wait may have run out
             parity = parity_sharded(res, dev_t, dev_w, rank, world, torch, triangle_attention, trimul_b200, dist, n)
         else:
             parity = parity_single_gpu(res, host_t, host_w, torch, only)
@@ -459,6 +460,8 @@ def main():
         end.record()
         barrier()
     ms = beg.elapsed_time(end) / args.steps
+    if world > 1:
+        sharded.check_exchange_status()
     launches = _lib.launch_count()
     prof_steps = args.steps
     exchanges = None

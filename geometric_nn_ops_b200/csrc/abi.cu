@@ -416,7 +416,8 @@ int tri_peer_barrier(const TriPeerSignal* sig, int64_t limit_cycles, tri_stream_
     if (sig->flag_ptrs[i] == nullptr) return fail(TRI_ERR_ARG, "tri_peer_barrier: null flag pointer");
     sp.flags[i] = static_cast<uint32_t*>(sig->flag_ptrs[i]);
   }
-  if (limit_cycles <= 0) limit_cycles = 2000000000LL;   // about a second of SM clocks
+  if (limit_cycles <= 0) limit_cycles = 10000000000LL;   // about five seconds of SM clocks: ranks may be skewed by a
+                                                          // first-call set-up (module load, buffer rendezvous)
   KernelTimer kt("tri_peer_barrier", (cudaStream_t)stream, 0.0, 0.0);
   peer_barrier_kernel<<<1, 32, 0, (cudaStream_t)stream>>>(sp, sig->rank, sig->n_peers, sig->state, limit_cycles);
   TRI_LAUNCH_OK();

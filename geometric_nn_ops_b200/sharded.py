@@ -172,6 +172,16 @@ def exchange_route(device, group=None):
             "fused": "gate-in epilogue peer stores + all-reduce barrier"}[mode]
 
 
+def check_exchange_status():
+    """Read the status word of every exchange buffer (synchronises) and raise if a barrier wait ever ran out: a peer
+    that did not arrive within the limit means the data read after that barrier cannot be trusted."""
+    torch.cuda.synchronize()
+    for key, pb in _PEER.items():
+        status = int(pb.state[3].item())
+        if status != 0:
+            raise RuntimeError(f"peer exchange {key[0]!r}: rank {status - 100} did not arrive within the wait limit")
+
+
 def _peer_buffer(tag, nbytes, device, group):
     base = (tag, nbytes, device.index, id(group))
     turn = _PEER_TURN.get(base, 0)

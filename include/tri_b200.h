@@ -290,7 +290,7 @@ int tri_scatter_runs(const TriScatterDesc* d, const void* src, void* const* dst_
  * peer's flag array (release at system scope: whatever this rank queued on the stream before it, e.g. the copy kernel
  * of tri_scatter_runs, has completed and is visible), then (2) waits until all n_peers slots of this rank's own array
  * have reached that number; kernels queued behind it then read the exchanged data.  The wait is BOUNDED: after
- * limit_cycles SM clocks (<= 0: about a second) it gives up, stores 100 + the missing peer in state[3] and returns,
+ * limit_cycles SM clocks (<= 0: about five seconds) it gives up, stores 100 + the missing peer in state[3] and returns,
  * so a missing rank becomes an error the host can read, never a hung GPU.  The barrier number advances on the
  * device, so a captured CUDA graph replays without changed arguments.  Every rank must enter the same barriers in
  * the same order.  A receive buffer may be rewritten by a later exchange once this rank has passed a barrier of a
