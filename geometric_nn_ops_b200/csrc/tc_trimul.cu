@@ -226,14 +226,26 @@ __global__ void __launch_bounds__(256, 4) ln_rows_bwd_kernel(const T* __restrict
 // ---------------------------------------------------------------------------------------------
 // LayerNorm over channels of a channel-major tensor (t -> u pixel-major), and its backward (du -> dt)
 // ---------------------------------------------------------------------------------------------
-constexpr int TP = 64;  // pixels per tile
+constexpr int TP = 64;        // pixels per tile
+constexpr int TROW = CW + 5;  // floats per tile row: 128 channels, one pad word after every 32, one more for the row
 
+// The transposing tile lives in shared memory pixel-major, tile[pixel][channel], with two twists that make both
+// sides free of bank conflicts (row stride 133 words = 5 mod 32):
+//  * a pad word after every 32 channels: on the pixel-major side a warp reads one pixel, lane l channels 4l..4l+3,
+//    one word per instruction; lanes l, l+8, l+16, l+24 would share a bank (4l mod 32), the pads shift them apart;
+//  * the channel index of pixels 32..63 XOR-ed with 4: on the channel-major side a lane holds 8 consecutive pixels of
+//    one channel and the 32 lanes of an access are 4 channels x 8 pixel groups; groups pg and pg + 4 would collide
+//    (40 pg = 8 pg mod 32), the XOR moves the upper four onto the neighbouring channels' banks.
+// The first version kept tile[channel][pixel + 1]: 2-way conflicts on one side and 4-way on the other held the LSU
+// pipe at 85 % and these kernels at 2.5 TB/s.
+__device__ __forceinline__ int tile_at(int pixel, int channel) {
+  return pixel * TROW + (channel ^ ((pixel >> 5) << 2)) + (channel >> 5);
+}
 
-// 64 pixels x 128 channels of a channel-major tensor -> smem tile[c][pixel] (fp32), 8 pixels per access.
+// 64 pixels x 128 channels of a channel-major tensor -> smem tile (fp32), 8 pixels per access.
 // The plane size is a multiple of 8 pixels, so a group of 8 never straddles two batch entries.
 template <typename T>
-__device__ __forceinline__ void load_cm_tile(float (*tile)[TP + 1], const T* src, long long m0, long long M,
-                                             long long NN) {
+__device__ __forceinline__ void load_cm_tile(float* tile, const T* src, long long m0, long long M, long long NN) {
   const long long b0 = m0 / NN, p0 = m0 - b0 * NN;   // one division per tile, not one per access
   for (int item = threadIdx.x; item < CW * (TP / 8); item += 256) {
     const int c = item / (TP / 8), pg = item % (TP / 8);
@@ -243,12 +255,11 @@ __device__ __forceinline__ void load_cm_tile(float (*tile)[TP + 1], const T* src
     float v[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
     if (m < M) load8v<T>(src + (bb * CW + c) * NN + pix, v);
 #pragma unroll
-    for (int e = 0; e < 8; ++e) tile[c][pg * 8 + e] = v[e];
+    for (int e = 0; e < 8; ++e) tile[tile_at(pg * 8 + e, c)] = v[e];
   }
 }
 template <typename T>
-__device__ __forceinline__ void store_cm_tile(const float (*tile)[TP + 1], T* dst, long long m0, long long M,
-                                              long long NN) {
+__device__ __forceinline__ void store_cm_tile(const float* tile, T* dst, long long m0, long long M, long long NN) {
   const long long b0 = m0 / NN, p0 = m0 - b0 * NN;
   for (int item = threadIdx.x; item < CW * (TP / 8); item += 256) {
     const int c = item / (TP / 8), pg = item % (TP / 8);
@@ -258,7 +269,7 @@ __device__ __forceinline__ void store_cm_tile(const float (*tile)[TP + 1], T* ds
     while (pix >= NN) { pix -= NN; ++bb; }
     float v[8];
 #pragma unroll
-    for (int e = 0; e < 8; ++e) v[e] = tile[c][pg * 8 + e];
+    for (int e = 0; e < 8; ++e) v[e] = tile[tile_at(pg * 8 + e, c)];
     store8v<T>(dst + (bb * CW + c) * NN + pix, v);
   }
 }
@@ -268,7 +279,7 @@ __device__ __forceinline__ void store_cm_tile(const float (*tile)[TP + 1], T* ds
 template <typename T>
 __global__ void __launch_bounds__(256) ln_cm_kernel(const T* t_cm, const T* gamma, const T* beta, float eps,
                                                      long long M, long long NN, T* u, float* mean, float* rstd) {
-  __shared__ float tile[CW][TP + 1];
+  __shared__ float tile[TP * TROW];
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
   float gm[4] = {1.f, 1.f, 1.f, 1.f}, bt[4] = {0.f, 0.f, 0.f, 0.f};
   if (gamma) load4(gamma + lane * 4, gm);
@@ -284,7 +295,7 @@ __global__ void __launch_bounds__(256) ln_cm_kernel(const T* t_cm, const T* gamm
       if (m >= M) break;
       float v[4];
 #pragma unroll
-      for (int k = 0; k < 4; ++k) v[k] = tile[lane * 4 + k][pl];
+      for (int k = 0; k < 4; ++k) v[k] = tile[tile_at(pl, lane * 4 + k)];
       const float mu = warp_sum(v[0] + v[1] + v[2] + v[3]) * (1.0f / CW);
       float q = 0.f;
 #pragma unroll
@@ -302,7 +313,7 @@ template <typename T>
 __global__ void __launch_bounds__(256) ln_cm_bwd_kernel(const T* du, const T* t_cm, const float* mean,
                                                          const float* rstd, const T* gamma, long long M,
                                                          long long NN, T* dt_cm, float* pg, float* pb) {
-  __shared__ float tile[CW][TP + 1];
+  __shared__ float tile[TP * TROW];
   __shared__ float sg[8][CW], sb[8][CW];
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
   float gm[4] = {1.f, 1.f, 1.f, 1.f}, ag[4] = {}, ab[4] = {};
@@ -321,7 +332,7 @@ __global__ void __launch_bounds__(256) ln_cm_bwd_kernel(const T* du, const T* t_
       load4(du + m * CW + lane * 4, d);
 #pragma unroll
       for (int k = 0; k < 4; ++k) {
-        th[k] = (tile[lane * 4 + k][pl] - mu) * rs;
+        th[k] = (tile[tile_at(pl, lane * 4 + k)] - mu) * rs;
         dh[k] = d[k] * gm[k];
         s1 += dh[k];
         s2 += dh[k] * th[k];
@@ -331,7 +342,7 @@ __global__ void __launch_bounds__(256) ln_cm_bwd_kernel(const T* du, const T* t_
       s1 = warp_sum(s1) * (1.0f / CW);
       s2 = warp_sum(s2) * (1.0f / CW);
 #pragma unroll
-      for (int k = 0; k < 4; ++k) tile[lane * 4 + k][pl] = rs * (dh[k] - s1 - th[k] * s2);
+      for (int k = 0; k < 4; ++k) tile[tile_at(pl, lane * 4 + k)] = rs * (dh[k] - s1 - th[k] * s2);
     }
     __syncthreads();
     store_cm_tile(tile, dt_cm, m0, M, NN);
