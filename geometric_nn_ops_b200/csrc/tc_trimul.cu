@@ -277,7 +277,7 @@ __device__ __forceinline__ void store_cm_tile(const float* tile, T* dst, long lo
 // One warp per pixel; lane l owns channels 4l..4l+3, so the pixel-major side is read / written 8 or 16
 // bytes per lane (256 or 512 contiguous bytes per warp).
 template <typename T>
-__global__ void __launch_bounds__(256) ln_cm_kernel(const T* t_cm, const T* gamma, const T* beta, float eps,
+__global__ void __launch_bounds__(256, 6) ln_cm_kernel(const T* t_cm, const T* gamma, const T* beta, float eps,
                                                      long long M, long long NN, T* u, float* mean, float* rstd) {
   __shared__ float tile[TP * TROW];
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
@@ -310,7 +310,7 @@ __global__ void __launch_bounds__(256) ln_cm_kernel(const T* t_cm, const T* gamm
 }
 
 template <typename T>
-__global__ void __launch_bounds__(256) ln_cm_bwd_kernel(const T* du, const T* t_cm, const float* mean,
+__global__ void __launch_bounds__(256, 5) ln_cm_bwd_kernel(const T* du, const T* t_cm, const float* mean,
                                                          const float* rstd, const T* gamma, long long M,
                                                          long long NN, T* dt_cm, float* pg, float* pb) {
   __shared__ float tile[TP * TROW];
