@@ -75,6 +75,7 @@ class TriMulShardBufs(Structure):
         ("a_cm", c_void_p), ("b_cm", c_void_p), ("t_cm", c_void_p), ("out", c_void_p),
         ("d_out", c_void_p), ("dt_cm", c_void_p), ("dx", c_void_p), ("g", POINTER(TriMulWeightGrads)),
         ("peer_ab", POINTER(c_void_p)), ("peer_world", ctypes.c_int32), ("peer_rank", ctypes.c_int32),
+        ("prep", c_void_p), ("prep_ready", ctypes.c_int32),
     ]
 
 
@@ -111,6 +112,7 @@ EXPORTS = {
                             c_void_p, POINTER(TriMulWeightGrads), c_void_p, c_size_t, c_void_p]),
     "tri_mul_shard_saved_bytes": (c_size_t, [POINTER(TriMulShardDesc)]),
     "tri_mul_shard_ws_bytes": (c_size_t, [POINTER(TriMulShardDesc), c_int]),
+    "tri_mul_shard_prep_bytes": (c_size_t, [POINTER(TriMulShardDesc)]),
     "tri_mul_shard_phase": (c_int, [POINTER(TriMulShardDesc), c_int, POINTER(TriMulShardBufs), c_void_p, c_size_t,
                                     c_void_p]),
     "tri_bgemm": (c_int, [POINTER(TriGemmDesc), c_void_p, c_void_p, c_void_p, c_void_p, c_size_t, c_void_p]),

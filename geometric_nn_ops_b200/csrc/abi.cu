@@ -276,6 +276,10 @@ size_t tri_mul_shard_ws_bytes(const TriMulShardDesc* d, int phase) {
   return check_shard(d) != 0 ? 0 : tc::mul_shard_ws_bytes(d, phase);
 }
 
+size_t tri_mul_shard_prep_bytes(const TriMulShardDesc* d) {
+  return check_shard(d) != 0 ? 0 : tc::mul_shard_prep_bytes(d);
+}
+
 int tri_mul_shard_phase(const TriMulShardDesc* d, int phase, const TriMulShardBufs* bufs, void* ws, size_t ws_bytes,
                         tri_stream_t stream) {
   TRI_TRY(check_shard(d));

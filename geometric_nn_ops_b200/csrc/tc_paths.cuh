@@ -25,6 +25,7 @@ int mul_backward(const TriMulDesc* d, const void* x, const void* mask, const Tri
 bool mul_shard_supported(const TriMulShardDesc* d);
 size_t mul_shard_saved_bytes(const TriMulShardDesc* d);
 size_t mul_shard_ws_bytes(const TriMulShardDesc* d, int phase);
+size_t mul_shard_prep_bytes(const TriMulShardDesc* d);
 int mul_shard_phase(const TriMulShardDesc* d, int phase, const TriMulShardBufs* bufs, void* ws, size_t ws_size,
                     cudaStream_t st);
 // Fused LayerNorm + q / k / v / pair-bias projection feeding triangle attention (see tri_attn_project in the C header).

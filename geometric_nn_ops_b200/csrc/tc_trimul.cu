@@ -395,18 +395,29 @@ struct ReduceJobs {
   float* out[4];
   int nparts[4], n[4];
 };
+// 32 outputs per block (one warp reads 128 contiguous bytes of a partial), 8 warps each summing every eighth
+// partial with eight independent accumulators so that loads overlap (the first version walked 37 partials with one
+// dependent load each: 16 us per launch of pure latency); the warps' sums are added in a fixed order, so the
+// result does not depend on scheduling.
 __global__ void __launch_bounds__(256) reduce_multi_kernel(const ReduceJobs jobs) {
-  __shared__ float sub[4][64];
+  __shared__ float sub[8][32];
   const int job = blockIdx.y, n = jobs.n[job], nparts = jobs.nparts[job];
   const float* partial = jobs.partial[job];
-  const int o = threadIdx.x & 63, lane4 = threadIdx.x >> 6;
-  const int j = blockIdx.x * 64 + o;
-  float s = 0.f;
-  if (j < n)
-    for (int p = lane4; p < nparts; p += 4) s += partial[(long long)p * n + j];
-  sub[lane4][o] = s;
+  const int o = threadIdx.x & 31, w = threadIdx.x >> 5;
+  const int j = blockIdx.x * 32 + o;
+  float a[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+  if (j < n) {
+    int p = w;
+    for (; p + 56 < nparts; p += 64) {   // eight independent loads in flight
+#pragma unroll
+      for (int u = 0; u < 8; ++u) a[u] += partial[(long long)(p + 8 * u) * n + j];
+    }
+    for (; p < nparts; p += 8) a[0] += partial[(long long)p * n + j];
+  }
+  sub[w][o] = ((a[0] + a[1]) + (a[2] + a[3])) + ((a[4] + a[5]) + (a[6] + a[7]));
   __syncthreads();
-  if (lane4 == 0 && j < n) jobs.out[job][j] = (sub[0][o] + sub[1][o]) + (sub[2][o] + sub[3][o]);
+  if (w == 0 && j < n)
+    jobs.out[job][j] = ((sub[0][o] + sub[1][o]) + (sub[2][o] + sub[3][o])) + ((sub[4][o] + sub[5][o]) + (sub[6][o] + sub[7][o]));
 }
 
 // Row sums of the channel-major dPG [512, M] scattered to the p_in / g_in bias gradients (one block per row,
@@ -428,16 +439,28 @@ __global__ void __launch_bounds__(256) rowsum_wcat_kernel(const T* dpg, long lon
 }
 
 // Sum partials of a [512, rowlen] tensor in Wcat row order and scatter the rows to the p_in / g_in gradients.
-__global__ void reduce_wcat_kernel(const float* partial, int nparts, int rowlen, float* d_p, float* d_g) {
-  const int j = blockIdx.x * blockDim.x + threadIdx.x;
+__global__ void __launch_bounds__(256) reduce_wcat_kernel(const float* partial, int nparts, int rowlen, float* d_p, float* d_g) {
+  __shared__ float sub[8][32];
+  const int o = threadIdx.x & 31, w = threadIdx.x >> 5;
+  const int j = blockIdx.x * 32 + o;
   const int n = 4 * CW * rowlen;
-  if (j >= n) return;
+  float a[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+  if (j < n) {
+    int p = w;
+    for (; p + 56 < nparts; p += 64) {   // eight independent loads in flight
+#pragma unroll
+      for (int u = 0; u < 8; ++u) a[u] += partial[(long long)(p + 8 * u) * n + j];
+    }
+    for (; p < nparts; p += 8) a[0] += partial[(long long)p * n + j];
+  }
+  sub[w][o] = ((a[0] + a[1]) + (a[2] + a[3])) + ((a[4] + a[5]) + (a[6] + a[7]));
+  __syncthreads();
+  if (w != 0 || j >= n) return;
   const int r = j / rowlen, k = j % rowlen, blk = r / CW, c = r % CW;
   float* dst = (blk & 1) ? d_g : d_p;
   if (dst == nullptr) return;
-  float s = 0.f;
-  for (int p = 0; p < nparts; ++p) s += partial[(long long)p * n + j];
-  dst[((blk >> 1) * CW + c) * rowlen + k] = s;
+  dst[((blk >> 1) * CW + c) * rowlen + k] =
+      ((sub[0][o] + sub[1][o]) + (sub[2][o] + sub[3][o])) + ((sub[4][o] + sub[5][o]) + (sub[6][o] + sub[7][o]));
 }
 
 // ---------------------------------------------------------------------------------------------
@@ -456,11 +479,14 @@ struct Geom {
 
 struct Prep { int* err; void* wcat; float* bias_cat; float* bias_out; };
 
-void carve_prep(Arena& a, size_t es, Prep* p) {
-  p->err = a.take<int>(64);
+void carve_prep_weights(Arena& a, size_t es, Prep* p) {
   p->wcat = a.take<char>(4 * CW * CW * es);
   p->bias_cat = a.take<float>(4 * CW);
   p->bias_out = a.take<float>(2 * CW);
+}
+void carve_prep(Arena& a, size_t es, Prep* p) {
+  p->err = a.take<int>(64);
+  carve_prep_weights(a, es, p);
 }
 
 constexpr int kSplitK = 148;
@@ -494,8 +520,9 @@ int contraction(cudaStream_t st, int dtype, int planes, int n, const void* a, bo
 }
 
 template <typename T>
-int run_prep(cudaStream_t st, const TriMulWeights* w, const Prep& pr) {
+int run_prep(cudaStream_t st, const TriMulWeights* w, const Prep& pr, bool weights_ready = false) {
   TRI_CUDA_OK(cudaMemsetAsync(pr.err, 0, 256, st));
+  if (weights_ready) return 0;   // the caller kept the prepared weights of an earlier phase of the same call
   KernelTimer kt("tc_prep_weights", st, 0.0, 0.0);
   prep_weights_kernel<T><<<cdiv(4 * CW * CW, 256), 256, 0, st>>>(
       (const T*)w->p_in_w, (const T*)w->g_in_w, (const T*)w->p_in_b, (const T*)w->g_in_b, (const T*)w->p_out_b,
@@ -597,7 +624,7 @@ int reduce_many(cudaStream_t st, std::initializer_list<ReduceJob> list) {
   }
   if (count == 0) return 0;
   KernelTimer kt("tc_reduce", st, 0.0, bytes);
-  reduce_multi_kernel<<<dim3(cdiv(nmax, 64), count), 256, 0, st>>>(jobs);
+  reduce_multi_kernel<<<dim3(cdiv(nmax, 32), count), 256, 0, st>>>(jobs);
   TRI_LAUNCH_OK();
   return 0;
 }
@@ -691,7 +718,7 @@ int phase_project_bwd(cudaStream_t st, const Geom& gm, const void* x, const void
   if (g->p_in_w || g->g_in_w) {
     TRI_TRY(split_k_grad(st, gm, dpg, 4 * CW, z, partial, pr.err, "tc_gemm_wgrad", &nparts, /*lhs_channel_major=*/true));
     KernelTimer kt("tc_reduce", st, 0.0, 4.0 * (nparts + 1) * 4 * CW * CW);
-    reduce_wcat_kernel<<<cdiv(4 * CW * CW, 256), 256, 0, st>>>(partial, nparts, CW, g->p_in_w, g->g_in_w);
+    reduce_wcat_kernel<<<cdiv(4 * CW * CW, 32), 256, 0, st>>>(partial, nparts, CW, g->p_in_w, g->g_in_w);
     TRI_LAUNCH_OK();
   }
   if (g->p_in_b || g->g_in_b) {
@@ -833,12 +860,16 @@ int shard_phase_t(const TriMulShardDesc* d, int phase, const TriMulShardBufs* bf
   Arena a(ws, ws_size);
   Prep pr;
   carve_prep(a, gm.es(), &pr);
+  if (bf->prep != nullptr) {   // prepared weights kept by the caller across the phases of one forward + backward
+    Arena pa(bf->prep, mul_shard_prep_bytes(d));
+    carve_prep_weights(pa, gm.es(), &pr);
+  }
   ShardWs sw;
   carve_shard_ws(a, gm, phase, &sw);
   if (!a.ok()) return fail(TRI_ERR_WORKSPACE, "trimul shard workspace too small: need %zu, got %zu", a.off, ws_size);
   ShardSaved s;
   { Arena sa(bf->saved, mul_shard_saved_bytes(d)); carve_shard_saved(sa, gm, &s); }
-  TRI_TRY(run_prep<T>(st, bf->w, pr));
+  TRI_TRY(run_prep<T>(st, bf->w, pr, bf->prep != nullptr && bf->prep_ready != 0));
   switch (phase) {
     case TRI_PHASE_PROJECT:
       if (!bf->x || ((!bf->a_cm || !bf->b_cm) && !(bf->peer_ab != nullptr && bf->peer_world > 1)))
@@ -902,6 +933,13 @@ size_t mul_shard_saved_bytes(const TriMulShardDesc* d) {
   Arena a(nullptr, 0);
   ShardSaved s;
   carve_shard_saved(a, geom_of(d), &s);
+  return a.off;
+}
+
+size_t mul_shard_prep_bytes(const TriMulShardDesc* d) {
+  Arena a(nullptr, 0);
+  Prep p;
+  carve_prep_weights(a, geom_of(d).es(), &p);
   return a.off;
 }
 

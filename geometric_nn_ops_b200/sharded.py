@@ -419,6 +419,9 @@ class _ShardedTriMul(torch.autograd.Function):
         ab = torch.empty(2, B, Ch, R, N, dtype=x.dtype, device=x.device)
         bufs = _lib.TriMulShardBufs()
         bufs.x, bufs.mask, bufs.w, bufs.saved = xc.data_ptr(), None if mc is None else mc.data_ptr(), ctypes.pointer(w), saved.data_ptr()
+        # the prepared weights travel from phase to phase (and to the backward) instead of being rebuilt in each
+        prep = torch.empty(lib.tri_mul_shard_prep_bytes(ctypes.byref(d)), dtype=torch.uint8, device=x.device)
+        bufs.prep, bufs.prep_ready = prep.data_ptr(), 0
         world, me = _world(group)
         # one set of exchange buffers per direction: an outgoing and an incoming update may run side by side on two streams
         tag = "out." if outgoing else "in."
@@ -435,10 +438,12 @@ class _ShardedTriMul(torch.autograd.Function):
             with _timed(tag + "fwd.ab.barrier"):
                 dist.all_reduce(pb.token, group=group)
             bufs.peer_ab, bufs.peer_world = None, 0
+            bufs.prep_ready = 1
             ab_ch = pb.buf.view(xc.dtype)[: 2 * B * Ch * R * N].view(2 * B, Ch // world, N, N).clone()   # saved for the backward
         else:
             bufs.a_cm, bufs.b_cm = ab[0].data_ptr(), ab[1].data_ptr()
             _phase(lib, d, _lib.PHASE_PROJECT, bufs, x.device)
+            bufs.prep_ready = 1
             ab_ch = rows_to_channels(ab.reshape(2 * B, Ch, R, N), group, tag=tag + "fwd.ab")      # [2B, Cs, N, N]
         cs = ab_ch.shape[1]
         a_ch = ab_ch[:B].reshape(B * cs, N, N)
@@ -450,7 +455,7 @@ class _ShardedTriMul(torch.autograd.Function):
         bufs.t_cm, bufs.out = t_loc.data_ptr(), out.data_ptr()
         _phase(lib, d, _lib.PHASE_OUTPUT, bufs, x.device)
 
-        ctx.save_for_backward(xc, mc, saved, a_ch, b_ch, t_loc, *[t for t in wc.values() if t is not None])
+        ctx.save_for_backward(xc, mc, saved, a_ch, b_ch, t_loc, prep, *[t for t in wc.values() if t is not None])
         ctx.present = [t is not None for t in wc.values()]
         ctx.desc, ctx.group, ctx.outgoing = d, group, outgoing
         ctx.weight_dtypes = [None if t is None else t.dtype for t in weights]
@@ -459,7 +464,7 @@ class _ShardedTriMul(torch.autograd.Function):
     @staticmethod
     def backward(ctx, d_out):
         lib = _lib.load()
-        xc, mc, saved, a_ch, b_ch, t_loc, *present_w = ctx.saved_tensors
+        xc, mc, saved, a_ch, b_ch, t_loc, prep, *present_w = ctx.saved_tensors
         it = iter(present_w)
         wc = {n: (next(it) if has else None) for n, has in zip(_lib.WEIGHT_NAMES, ctx.present)}
         d, group = ctx.desc, ctx.group
@@ -483,6 +488,7 @@ class _ShardedTriMul(torch.autograd.Function):
         bufs = _lib.TriMulShardBufs()
         bufs.x, bufs.mask, bufs.w, bufs.saved = xc.data_ptr(), None if mc is None else mc.data_ptr(), ctypes.pointer(w), saved.data_ptr()
         bufs.g = ctypes.pointer(g)
+        bufs.prep, bufs.prep_ready = prep.data_ptr(), 1
         bufs.d_out, bufs.t_cm, bufs.dt_cm = dc.data_ptr(), t_loc.data_ptr(), dt_loc.data_ptr()
         _phase(lib, d, _lib.PHASE_OUTPUT_BWD, bufs, dev)
         tag = "out." if ctx.outgoing else "in."

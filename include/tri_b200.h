@@ -224,12 +224,19 @@ typedef struct TriMulShardBufs {
    * afterwards, as for tri_scatter_runs.  NULL / 0 keeps the plain outputs. */
   void* const* peer_ab;
   int32_t peer_world, peer_rank;
+  /* Optional: a buffer of tri_mul_shard_prep_bytes() that carries the prepared weights (the concatenated, reordered
+   * input projections and the fp32 bias vectors) from phase to phase.  Every phase needs them; with prep == NULL each
+   * phase prepares them again in its workspace.  Pass prep_ready = 0 to the first phase that sees a set of weights
+   * (it fills the buffer) and 1 to later phases of the same forward + backward. */
+  void* prep;
+  int32_t prep_ready;
 } TriMulShardBufs;
 
 enum { TRI_PHASE_PROJECT = 0, TRI_PHASE_OUTPUT = 1, TRI_PHASE_OUTPUT_BWD = 2, TRI_PHASE_PROJECT_BWD = 3 };
 
 size_t tri_mul_shard_saved_bytes(const TriMulShardDesc* d);
 size_t tri_mul_shard_ws_bytes(const TriMulShardDesc* d, int phase);
+size_t tri_mul_shard_prep_bytes(const TriMulShardDesc* d);
 int tri_mul_shard_phase(const TriMulShardDesc* d, int phase, const TriMulShardBufs* bufs, void* ws,
                         size_t ws_bytes, tri_stream_t stream);
 
