@@ -31,9 +31,8 @@ namespace {
 
 constexpr int CW = 128;        // channel width this path is built for
 constexpr int kPersist = 592;  // blocks of the persistent memory-bound kernels (4 per SM)
-constexpr int kLnCmBlocks = 888;    // ln_cm: 6 per SM (what its 33 KB tile allows), so that one block's load phase overlaps
-                                    // another's arithmetic (0.30 -> 0.24 ms per step; 32-pixel tiles with 8 per SM: 0.30)
-constexpr int kLnCmBwdBlocks = 740; // ln_cm_bwd: 5 per SM (41 KB)
+constexpr int kLnCmBlocks = 592;    // ln_cm: 4 per SM (64 registers per thread hold the next tile's loads)
+constexpr int kLnCmBwdBlocks = 444; // ln_cm_bwd: 3 per SM (80 registers: next tile, eight pixels' gradients and statistics)
 
 __device__ __forceinline__ float warp_sum(float v) {
 #pragma unroll
@@ -242,18 +241,60 @@ __device__ __forceinline__ int tile_at(int pixel, int channel) {
   return pixel * TROW + (channel ^ ((pixel >> 5) << 2)) + (channel >> 5);
 }
 
-// 64 pixels x 128 channels of a channel-major tensor -> smem tile (fp32), 8 pixels per access.
-// The plane size is a multiple of 8 pixels, so a group of 8 never straddles two batch entries.
+// 64 pixels x 128 channels of a channel-major tensor <-> smem tile (fp32), 8 pixels (16 or 32 bytes) per access, four
+// accesses per thread.  The plane size is a multiple of 8 pixels, so a group of 8 never straddles two batch entries.
+// The global loads of a tile are issued into registers (fetch_cm_tile) while the block still works on the previous
+// tile and written to shared memory afterwards (put_cm_tile): with the loads issued at the top of a tile's own
+// phase, a block had nothing in flight during its arithmetic and the kernels sat at 2.1-2.5 TB/s.
+// four consecutive elements as raw words (converted when used)
+template <typename T> struct Raw4 { uint32_t w[sizeof(T) == 4 ? 4 : 2]; };
+template <typename T> __device__ __forceinline__ Raw4<T> ldraw4(const T* p) {
+  Raw4<T> r;
+  if constexpr (sizeof(T) == 4) {
+    const uint4 t = __ldg(reinterpret_cast<const uint4*>(p));
+    r.w[0] = t.x; r.w[1] = t.y; r.w[2] = t.z; r.w[3] = t.w;
+  } else {
+    const uint2 t = __ldg(reinterpret_cast<const uint2*>(p));
+    r.w[0] = t.x; r.w[1] = t.y;
+  }
+  return r;
+}
+template <typename T> __device__ __forceinline__ void cvtraw4(const Raw4<T>& r, float (&v)[4]) {
+  if constexpr (sizeof(T) == 4) {
+#pragma unroll
+    for (int i = 0; i < 4; ++i) v[i] = __uint_as_float(r.w[i]);
+  } else {
+    union { uint2 u; T h[4]; } pk;
+    pk.u = make_uint2(r.w[0], r.w[1]);
+#pragma unroll
+    for (int i = 0; i < 4; ++i) v[i] = to_f32(pk.h[i]);
+  }
+}
+
+template <typename T> struct CmRegs { Raw8<T> v[4]; bool ok[4]; };   // raw 16-byte words: converted when written to the tile
+
 template <typename T>
-__device__ __forceinline__ void load_cm_tile(float* tile, const T* src, long long m0, long long M, long long NN) {
+__device__ __forceinline__ void fetch_cm_tile(CmRegs<T>& r, const T* src, long long m0, long long M, long long NN) {
   const long long b0 = m0 / NN, p0 = m0 - b0 * NN;   // one division per tile, not one per access
-  for (int item = threadIdx.x; item < CW * (TP / 8); item += 256) {
+#pragma unroll
+  for (int k = 0; k < 4; ++k) {
+    const int item = threadIdx.x + k * 256;
     const int c = item / (TP / 8), pg = item % (TP / 8);
     const long long m = m0 + pg * 8;
     long long bb = b0, pix = p0 + pg * 8;
     while (pix >= NN) { pix -= NN; ++bb; }
+    r.ok[k] = m < M;
+    if (r.ok[k]) r.v[k] = ldraw8<T>(src + (bb * CW + c) * NN + pix);
+  }
+}
+template <typename T>
+__device__ __forceinline__ void put_cm_tile(float* tile, const CmRegs<T>& r) {
+#pragma unroll
+  for (int k = 0; k < 4; ++k) {
+    const int item = threadIdx.x + k * 256;
+    const int c = item / (TP / 8), pg = item % (TP / 8);
     float v[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
-    if (m < M) load8v<T>(src + (bb * CW + c) * NN + pix, v);
+    if (r.ok[k]) cvtraw8<T>(r.v[k], v);
 #pragma unroll
     for (int e = 0; e < 8; ++e) tile[tile_at(pg * 8 + e, c)] = v[e];
   }
@@ -277,19 +318,22 @@ __device__ __forceinline__ void store_cm_tile(const float* tile, T* dst, long lo
 // One warp per pixel; lane l owns channels 4l..4l+3, so the pixel-major side is read / written 8 or 16
 // bytes per lane (256 or 512 contiguous bytes per warp).
 template <typename T>
-__global__ void __launch_bounds__(256, 6) ln_cm_kernel(const T* t_cm, const T* gamma, const T* beta, float eps,
-                                                     long long M, long long NN, T* u, float* mean, float* rstd) {
+__global__ void __launch_bounds__(256, 4) ln_cm_kernel(const T* t_cm, const T* gamma, const T* beta, float eps,
+                                                        long long M, long long NN, T* u, float* mean, float* rstd) {
   __shared__ float tile[TP * TROW];
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
   float gm[4] = {1.f, 1.f, 1.f, 1.f}, bt[4] = {0.f, 0.f, 0.f, 0.f};
   if (gamma) load4(gamma + lane * 4, gm);
   if (beta) load4(beta + lane * 4, bt);
   const long long tiles = (M + TP - 1) / TP;
+  CmRegs<T> next;
+  if ((long long)blockIdx.x < tiles) fetch_cm_tile(next, t_cm, (long long)blockIdx.x * TP, M, NN);
   for (long long tl = blockIdx.x; tl < tiles; tl += gridDim.x) {
     const long long m0 = tl * TP;
+    __syncthreads();                       // the previous tile has been read out of shared memory
+    put_cm_tile(tile, next);
     __syncthreads();
-    load_cm_tile(tile, t_cm, m0, M, NN);
-    __syncthreads();
+    if (tl + gridDim.x < tiles) fetch_cm_tile(next, t_cm, (tl + gridDim.x) * TP, M, NN);   // in flight during the arithmetic
     for (int pl = warp; pl < TP; pl += 8) {
       const long long m = m0 + pl;
       if (m >= M) break;
@@ -310,26 +354,40 @@ __global__ void __launch_bounds__(256, 6) ln_cm_kernel(const T* t_cm, const T* g
 }
 
 template <typename T>
-__global__ void __launch_bounds__(256, 5) ln_cm_bwd_kernel(const T* du, const T* t_cm, const float* mean,
-                                                         const float* rstd, const T* gamma, long long M,
-                                                         long long NN, T* dt_cm, float* pg, float* pb) {
+__global__ void __launch_bounds__(256, 3) ln_cm_bwd_kernel(const T* du, const T* t_cm, const float* mean,
+                                                            const float* rstd, const T* gamma, long long M,
+                                                            long long NN, T* dt_cm, float* pg, float* pb) {
   __shared__ float tile[TP * TROW];
   __shared__ float sg[8][CW], sb[8][CW];
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
   float gm[4] = {1.f, 1.f, 1.f, 1.f}, ag[4] = {}, ab[4] = {};
   if (gamma) load4(gamma + lane * 4, gm);
   const long long tiles = (M + TP - 1) / TP;
+  CmRegs<T> next;
+  if ((long long)blockIdx.x < tiles) fetch_cm_tile(next, t_cm, (long long)blockIdx.x * TP, M, NN);
   for (long long tl = blockIdx.x; tl < tiles; tl += gridDim.x) {
     const long long m0 = tl * TP;
+    __syncthreads();                       // the previous tile has been stored from shared memory
+    put_cm_tile(tile, next);
+    // this warp's eight pixels: their upstream gradients and statistics, fetched together instead of one pixel at a
+    // time in front of their use (eight exposed load latencies per tile)
+    Raw4<T> d8[TP / 8];
+    float mu8[TP / 8], rs8[TP / 8];
+#pragma unroll
+    for (int i = 0; i < TP / 8; ++i) {
+      const long long m = m0 + warp + 8 * i;
+      mu8[i] = 0.f; rs8[i] = 0.f;
+      if (m < M) { d8[i] = ldraw4<T>(du + m * CW + lane * 4); mu8[i] = mean[m]; rs8[i] = rstd[m]; }
+    }
     __syncthreads();
-    load_cm_tile(tile, t_cm, m0, M, NN);
-    __syncthreads();
-    for (int pl = warp; pl < TP; pl += 8) {
-      const long long m = m0 + pl;
-      if (m >= M) break;
-      const float mu = mean[m], rs = rstd[m];
+    if (tl + gridDim.x < tiles) fetch_cm_tile(next, t_cm, (tl + gridDim.x) * TP, M, NN);   // in flight during the arithmetic
+#pragma unroll
+    for (int i = 0; i < TP / 8; ++i) {
+      const int pl = warp + 8 * i;
+      if (m0 + pl >= M) break;
+      const float mu = mu8[i], rs = rs8[i];
       float d[4], th[4], dh[4], s1 = 0.f, s2 = 0.f;
-      load4(du + m * CW + lane * 4, d);
+      cvtraw4<T>(d8[i], d);
 #pragma unroll
       for (int k = 0; k < 4; ++k) {
         th[k] = (tile[tile_at(pl, lane * 4 + k)] - mu) * rs;
