@@ -446,12 +446,16 @@ __global__ void __launch_bounds__(256) reduce_kernel(const float* partial, int n
   if (lane4 == 0 && j < n) out[j] = (sub[0][o] + sub[1][o]) + (sub[2][o] + sub[3][o]);
 }
 
-// Up to four such reductions in one launch (blockIdx.y selects the job): the backward has pairs of small reductions
-// (two weight gradients, LayerNorm weight and bias) whose launches cost more than their work.
+// Up to six such reductions in one launch (blockIdx.y selects the job): the backward has groups of small reductions
+// (weight gradients, LayerNorm weight and bias) whose launches cost more than their work.  A job with `rowlen` set
+// sums partials of a [512, rowlen] tensor in Wcat row order and scatters its rows to the p_in (out) and g_in (out2)
+// gradients; either may be null.
+constexpr int kReduceJobs = 6;
 struct ReduceJobs {
-  const float* partial[4];
-  float* out[4];
-  int nparts[4], n[4];
+  const float* partial[kReduceJobs];
+  float* out[kReduceJobs];
+  float* out2[kReduceJobs];
+  int nparts[kReduceJobs], n[kReduceJobs], rowlen[kReduceJobs];
 };
 // 32 outputs per block (one warp reads 128 contiguous bytes of a partial), 8 warps each summing every eighth
 // partial with eight independent accumulators so that loads overlap (the first version walked 37 partials with one
@@ -460,6 +464,7 @@ struct ReduceJobs {
 __global__ void __launch_bounds__(256) reduce_multi_kernel(const ReduceJobs jobs) {
   __shared__ float sub[8][32];
   const int job = blockIdx.y, n = jobs.n[job], nparts = jobs.nparts[job];
+  if (blockIdx.x * 32 >= n) return;
   const float* partial = jobs.partial[job];
   const int o = threadIdx.x & 31, w = threadIdx.x >> 5;
   const int j = blockIdx.x * 32 + o;
@@ -474,8 +479,16 @@ __global__ void __launch_bounds__(256) reduce_multi_kernel(const ReduceJobs jobs
   }
   sub[w][o] = ((a[0] + a[1]) + (a[2] + a[3])) + ((a[4] + a[5]) + (a[6] + a[7]));
   __syncthreads();
-  if (w == 0 && j < n)
-    jobs.out[job][j] = ((sub[0][o] + sub[1][o]) + (sub[2][o] + sub[3][o])) + ((sub[4][o] + sub[5][o]) + (sub[6][o] + sub[7][o]));
+  if (w != 0 || j >= n) return;
+  const float sum = ((sub[0][o] + sub[1][o]) + (sub[2][o] + sub[3][o])) + ((sub[4][o] + sub[5][o]) + (sub[6][o] + sub[7][o]));
+  const int rowlen = jobs.rowlen[job];
+  if (rowlen == 0) {
+    jobs.out[job][j] = sum;
+  } else {
+    const int r = j / rowlen, k = j % rowlen, blk = r / CW, c = r % CW;
+    float* dst = (blk & 1) ? jobs.out2[job] : jobs.out[job];
+    if (dst != nullptr) dst[((blk >> 1) * CW + c) * rowlen + k] = sum;
+  }
 }
 
 // Row sums of the channel-major dPG [512, M] scattered to the p_in / g_in bias gradients (one block per row,
@@ -494,31 +507,6 @@ __global__ void __launch_bounds__(256) rowsum_wcat_kernel(const T* dpg, long lon
     __syncthreads();
   }
   if (threadIdx.x == 0 && dst != nullptr) dst[(blk >> 1) * CW + c] = red[0];
-}
-
-// Sum partials of a [512, rowlen] tensor in Wcat row order and scatter the rows to the p_in / g_in gradients.
-__global__ void __launch_bounds__(256) reduce_wcat_kernel(const float* partial, int nparts, int rowlen, float* d_p, float* d_g) {
-  __shared__ float sub[8][32];
-  const int o = threadIdx.x & 31, w = threadIdx.x >> 5;
-  const int j = blockIdx.x * 32 + o;
-  const int n = 4 * CW * rowlen;
-  float a[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
-  if (j < n) {
-    int p = w;
-    for (; p + 56 < nparts; p += 64) {   // eight independent loads in flight
-#pragma unroll
-      for (int u = 0; u < 8; ++u) a[u] += partial[(long long)(p + 8 * u) * n + j];
-    }
-    for (; p < nparts; p += 8) a[0] += partial[(long long)p * n + j];
-  }
-  sub[w][o] = ((a[0] + a[1]) + (a[2] + a[3])) + ((a[4] + a[5]) + (a[6] + a[7]));
-  __syncthreads();
-  if (w != 0 || j >= n) return;
-  const int r = j / rowlen, k = j % rowlen, blk = r / CW, c = r % CW;
-  float* dst = (blk & 1) ? d_g : d_p;
-  if (dst == nullptr) return;
-  dst[((blk >> 1) * CW + c) * rowlen + k] =
-      ((sub[0][o] + sub[1][o]) + (sub[2][o] + sub[3][o])) + ((sub[4][o] + sub[5][o]) + (sub[6][o] + sub[7][o]));
 }
 
 // ---------------------------------------------------------------------------------------------
@@ -548,7 +536,11 @@ void carve_prep(Arena& a, size_t es, Prep* p) {
 }
 
 constexpr int kSplitK = 148;
-size_t partial_floats() { return std::max((size_t)kSplitK * 4 * CW * CW, (size_t)2 * kLnCmBwdBlocks * 4 * CW); }
+// The partials of one backward phase live side by side until the phase's single reduction launch: the split-K
+// weight-gradient partials (dWcat, or dWo | dWgo) first, then the LayerNorm weight / bias partials.
+constexpr size_t kWgradPartialFloats = (size_t)kSplitK * 4 * CW * CW;
+constexpr size_t kLnPartialFloats = (size_t)2 * kPersist * CW;
+size_t partial_floats() { return kWgradPartialFloats + kLnPartialFloats; }
 
 Operand rows_operand(const void* p, int width, long long rows, bool as_mn) {
   // pixel-major [rows, width]: K-major with K = width, or MN-major with MN = width and K = rows
@@ -667,15 +659,16 @@ int split_k_grad(cudaStream_t st, const Geom& gm, const void* lhs, int lhs_w, co
   return launch_gemm(st, gm.dtype, EPI_STORE, 128, true, p, err);
 }
 
-// reduce_to for several (partial, nparts, n, out) jobs at once; jobs whose `out` is null are dropped
-struct ReduceJob { const float* partial; int nparts, n; float* out; };
+// reduce_to for several (partial, nparts, n, out) jobs at once; jobs with nothing to write are dropped
+struct ReduceJob { const float* partial; int nparts, n; float* out; float* out2 = nullptr; int rowlen = 0; };
 int reduce_many(cudaStream_t st, std::initializer_list<ReduceJob> list) {
   ReduceJobs jobs = {};
   int count = 0, nmax = 0;
   double bytes = 0.0;
   for (const ReduceJob& j : list) {
-    if (j.out == nullptr) continue;
-    jobs.partial[count] = j.partial; jobs.out[count] = j.out; jobs.nparts[count] = j.nparts; jobs.n[count] = j.n;
+    if ((j.out == nullptr && j.out2 == nullptr) || j.nparts == 0) continue;
+    jobs.partial[count] = j.partial; jobs.out[count] = j.out; jobs.out2[count] = j.out2;
+    jobs.nparts[count] = j.nparts; jobs.n[count] = j.n; jobs.rowlen[count] = j.rowlen;
     nmax = std::max(nmax, j.n);
     bytes += 4.0 * (j.nparts + 1) * j.n;
     ++count;
@@ -723,20 +716,20 @@ int phase_output_bwd(cudaStream_t st, const Geom& gm, const void* d_out, const v
     p.name = "tc_gemm_gate_out_bwd"; p.flops = 0.0; p.bytes = 5.0 * gm.unit();  // recompute: no algorithmic flops
     TRI_TRY(launch_gemm(st, gm.dtype, EPI_GATE_OUT_BWD, 256, false, p, pr.err));
   }
-  {   // the two output weight gradients: split-K partials side by side, one reduction launch for both
-    float* part2 = partial + (size_t)kSplitK * CW * CW;
-    int n1 = 0, n2 = 0;
-    if (g->p_out_w) TRI_TRY(split_k_grad(st, gm, dy, CW, u, partial, pr.err, "tc_gemm_wgrad", &n1));
-    if (g->g_out_w) TRI_TRY(split_k_grad(st, gm, dgo, CW, z, part2, pr.err, "tc_gemm_wgrad", &n2));
-    TRI_TRY(reduce_many(st, {{partial, n1, CW * CW, g->p_out_w}, {part2, n2, CW * CW, g->g_out_w}}));
-  }
+  // the two output weight gradients: split-K partials side by side, reduced at the end of the phase together
+  // with the LayerNorm partials
+  float* part2 = partial + (size_t)kSplitK * CW * CW;
+  float* scratch = partial + (size_t)2 * kSplitK * CW * CW;   // the rest of the weight-gradient area
+  int n1 = 0, n2 = 0;
+  if (g->p_out_w) TRI_TRY(split_k_grad(st, gm, dy, CW, u, partial, pr.err, "tc_gemm_wgrad", &n1));
+  if (g->g_out_w) TRI_TRY(split_k_grad(st, gm, dgo, CW, z, part2, pr.err, "tc_gemm_wgrad", &n2));
   if (g->p_out_b) {
-    TRI_TRY(colsum_to<T>(st, dy, M, CW, partial, &nparts));
-    TRI_TRY(reduce_to(st, partial, nparts, CW, g->p_out_b));
+    TRI_TRY(colsum_to<T>(st, dy, M, CW, scratch, &nparts));
+    TRI_TRY(reduce_to(st, scratch, nparts, CW, g->p_out_b));
   }
   if (g->g_out_b) {
-    TRI_TRY(colsum_to<T>(st, dgo, M, CW, partial, &nparts));
-    TRI_TRY(reduce_to(st, partial, nparts, CW, g->g_out_b));
+    TRI_TRY(colsum_to<T>(st, dgo, M, CW, scratch, &nparts));
+    TRI_TRY(reduce_to(st, scratch, nparts, CW, g->g_out_b));
   }
   {
     GemmPlan p;   // du = dy Wo
@@ -746,15 +739,16 @@ int phase_output_bwd(cudaStream_t st, const Geom& gm, const void* d_out, const v
     p.name = "tc_gemm_du"; p.flops = 2.0 * M * CW * CW; p.bytes = 2.0 * gm.unit();
     TRI_TRY(launch_gemm(st, gm.dtype, EPI_STORE, 128, false, p, pr.err));
   }
-  float* pg = partial;
-  float* pb = partial + (size_t)kLnCmBwdBlocks * CW;
+  float* pg = partial + kWgradPartialFloats;
+  float* pb = pg + (size_t)kLnCmBwdBlocks * CW;
   {
     KernelTimer kt("tc_ln_cm_bwd", st, 0.0, 3.0 * gm.unit());
     ln_cm_bwd_kernel<T><<<kLnCmBwdBlocks, 256, 0, st>>>((const T*)du, (const T*)t_cm, mean_out, rstd_out,
                                                   (const T*)w->norm_out_w, M, gm.plane, (T*)dt_cm, pg, pb);
     TRI_LAUNCH_OK();
   }
-  return reduce_many(st, {{pg, kLnCmBwdBlocks, CW, g->norm_out_w}, {pb, kLnCmBwdBlocks, CW, g->norm_out_b}});
+  return reduce_many(st, {{partial, n1, CW * CW, g->p_out_w}, {part2, n2, CW * CW, g->g_out_w},
+                          {pg, kLnCmBwdBlocks, CW, g->norm_out_w}, {pb, kLnCmBwdBlocks, CW, g->norm_out_b}});
 }
 
 // ---- backward of phase 1: da, db (channel-major), dgo -> gradients of the input weights, dx ---------------
@@ -773,12 +767,8 @@ int phase_project_bwd(cudaStream_t st, const Geom& gm, const void* x, const void
     p.name = "tc_gemm_gate_in_bwd"; p.flops = 0.0; p.bytes = 7.0 * gm.unit();
     TRI_TRY(launch_gemm(st, gm.dtype, EPI_GATE_IN_BWD, 256, false, p, pr.err));
   }
-  if (g->p_in_w || g->g_in_w) {
+  if (g->p_in_w || g->g_in_w)   // reduced at the end of the phase together with the LayerNorm partials
     TRI_TRY(split_k_grad(st, gm, dpg, 4 * CW, z, partial, pr.err, "tc_gemm_wgrad", &nparts, /*lhs_channel_major=*/true));
-    KernelTimer kt("tc_reduce", st, 0.0, 4.0 * (nparts + 1) * 4 * CW * CW);
-    reduce_wcat_kernel<<<cdiv(4 * CW * CW, 32), 256, 0, st>>>(partial, nparts, CW, g->p_in_w, g->g_in_w);
-    TRI_LAUNCH_OK();
-  }
   if (g->p_in_b || g->g_in_b) {
     KernelTimer kt("tc_rowsum", st, 0.0, 4.0 * gm.unit());
     rowsum_wcat_kernel<T><<<4 * CW, 256, 0, st>>>((const T*)dpg, M, g->p_in_b, g->g_in_b);
@@ -797,15 +787,16 @@ int phase_project_bwd(cudaStream_t st, const Geom& gm, const void* x, const void
     TRI_TRY(launch_gemm(st, gm.dtype, EPI_STORE, 128, false, p, pr.err));
   }
   const int blocks = (int)std::min<long long>(kPersist, (M + 7) / 8);
-  float* pg = partial;
-  float* pb = partial + (size_t)kPersist * CW;
+  float* pg = partial + kWgradPartialFloats;
+  float* pb = pg + (size_t)kPersist * CW;
   {
     KernelTimer kt("tc_ln_rows_bwd", st, 0.0, 3.0 * gm.unit());
     ln_rows_bwd_kernel<T><<<blocks, 256, 0, st>>>((const T*)dz, (const T*)x, mean_in, rstd_in, (const T*)w->norm_in_w,
                                                   M, (T*)dx, pg, pb);
     TRI_LAUNCH_OK();
   }
-  return reduce_many(st, {{pg, blocks, CW, g->norm_in_w}, {pb, blocks, CW, g->norm_in_b}});
+  return reduce_many(st, {{partial, nparts, 4 * CW * CW, g->p_in_w, g->g_in_w, CW},
+                          {pg, blocks, CW, g->norm_in_w}, {pb, blocks, CW, g->norm_in_b}});
 }
 
 // ---------------------------------------------------------------------------------------------

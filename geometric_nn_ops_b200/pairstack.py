@@ -98,6 +98,21 @@ def project_attention_inputs(z, w):
     return q, k, v, bias
 
 
+def _ending_node_update(z, pair_mask, w):
+    """Ending-node triangle attention of a whole ``z`` ``[B, N, N, C]`` on one GPU, without transposing ``z``.
+
+    The projections act on single pair positions, so q, k, v of the transposed pair representation are transposed
+    *views* of the ones projected from ``z`` as it lies; the kernels take the strides.  Only the ``[B, H, N, N]``
+    bias and the mask (both small) are copied transposed, and the result comes back through a transposed view.
+    Returns the update in ``z``'s orientation, ``[B, N, N, C]``."""
+    q, k, v, bias = project_attention_inputs(z, w)                    # [B, i, j, H, D], [B, H, i, j]
+    B, N = z.shape[0], z.shape[1]
+    keep = (pair_mask.transpose(1, 2) != 0).reshape(B, N, 1, 1, N)     # row j of the transposed problem masks keys i
+    o = triangle_attention(q.transpose(1, 2), k.transpose(1, 2), v.transpose(1, 2),
+                           bias.transpose(2, 3).contiguous().unsqueeze(1), keep)   # [B, j, i, H, D]
+    return o.transpose(1, 2).reshape(B, N, N, HEADS * HEAD_DIM)
+
+
 def _attention_update(z, pair_mask, w, group):
     """Starting-node triangle attention on the rows held here; returns ``[B, R, N, C]``."""
     q, k, v, bias = project_attention_inputs(z, w)
@@ -125,8 +140,7 @@ def pair_block(z, pair_mask, w: BlockWeights, group=None):
         mt = sharded.all_to_all_transpose(pair_mask.contiguous(), group)
         z = z + sharded.all_to_all_transpose(_attention_update(zt, mt, w.attn_end, group).contiguous(), group)
     else:
-        zt, mt = z.transpose(1, 2).contiguous(), pair_mask.transpose(1, 2).contiguous()
-        z = z + _attention_update(zt, mt, w.attn_end, None).transpose(1, 2)
+        z = z + _ending_node_update(z, pair_mask, w.attn_end)
     return z
 
 

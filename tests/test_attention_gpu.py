@@ -287,3 +287,38 @@ def test_pairformer_point_h16_d48(ta):
     util.check_close("out", out, o_ref, cos_min, fro, mar)
     for name, val in grads.items():
         util.check_close("grad_" + name, val, g_ref[name], cos_min, fro, mar)
+
+
+def test_rows_and_residues_swapped_in_memory_bit_exact(ta):
+    """q, k, v handed in as transposed views of ``[B, N_res, N_seq, H, D]`` storage (the ending-node attention of a
+    pair stack reads the projections of the untransposed pair representation this way; one of them a column
+    slice of a wider buffer, as the fused projection produces it): same kernels, same bits as the contiguous call,
+    forward and backward."""
+    from geometric_nn_ops_b200 import _lib
+
+    B, S, N, H, D = 1, 136, 136, 4, 32
+    t, mask, d_out = util.attn_inputs(B, S, N, H, D, torch.bfloat16, seed=14)
+    base = {n: t[n].clone().requires_grad_() for n in ("q", "k", "v", "bias")}
+    out = ta(base["q"], base["k"], base["v"], base["bias"], mask)
+    g0 = torch.autograd.grad(out, list(base.values()), grad_outputs=d_out)
+
+    def stored_transposed(x, wide):
+        y = x.detach().transpose(1, 2).contiguous()                    # [B, N_res, N_seq, H, D] in memory
+        if wide:                                                       # a slice of a [..., 3*H*D] buffer
+            buf = torch.zeros(B, N, S, 3 * H * D, dtype=x.dtype, device=x.device)
+            buf[..., H * D:2 * H * D] = y.reshape(B, N, S, H * D)
+            y = buf[..., H * D:2 * H * D].view(B, N, S, H, D)
+        return y.requires_grad_()
+    store = {"q": stored_transposed(t["q"], False), "k": stored_transposed(t["k"], True),
+             "v": stored_transposed(t["v"], False)}
+    bias = t["bias"].clone().requires_grad_()
+    _lib.profile_enable(True)
+    out_t = ta(store["q"].transpose(1, 2), store["k"].transpose(1, 2), store["v"].transpose(1, 2), bias, mask)
+    names = set(_lib.profile_summary())
+    _lib.profile_enable(False)
+    assert "tc_attn_fwd" in names, names                               # the tensor-core kernels took the strides
+    g1 = torch.autograd.grad(out_t, [store["q"], store["k"], store["v"], bias], grad_outputs=d_out)
+    assert torch.equal(out_t, out)
+    for a, b in zip(g1[:3], g0[:3]):
+        assert torch.equal(a.transpose(1, 2), b)
+    assert torch.equal(g1[3], g0[3])
