@@ -22,6 +22,7 @@
 #include <initializer_list>
 
 #include "tc_gemm.cuh"
+#include "tc_lngemm.cuh"
 #include "tc_paths.cuh"
 
 namespace tri {
@@ -600,6 +601,15 @@ int phase_project(cudaStream_t st, const Geom& gm, const void* x, const void* ma
                   const Prep& pr, void* z, float* mean_in, float* rstd_in, void* a_cm, void* b_cm,
                   void* const* peer_ab = nullptr, int peer_world = 0, int peer_rank = 0) {
   const long long M = gm.M;
+  if (peer_ab == nullptr && ln_gate_in_supported(gm.dtype, M, gm.plane)) {
+    // 16-bit dtypes: one kernel normalises each x tile in shared memory and feeds both halves' products from it
+    LnGateIn f;
+    f.dtype = gm.dtype; f.M = M; f.plane = gm.plane; f.eps = gm.eps;
+    f.x = x; f.gamma = w->norm_in_w; f.beta = w->norm_in_b; f.wcat = pr.wcat;
+    f.bias_cat = (w->p_in_b || w->g_in_b) ? pr.bias_cat : nullptr; f.mask = mask;
+    f.z = z; f.mean = mean_in; f.rstd = rstd_in; f.a_cm = a_cm; f.b_cm = b_cm; f.err = pr.err;
+    return ln_gate_in(st, f);
+  }
   {
     KernelTimer kt("tc_ln_rows", st, 0.0, 2.0 * gm.unit());
     ln_rows_kernel<T><<<cdiv(M, 8 * 2 * kLnRowPairs), 256, 0, st>>>((const T*)x, (const T*)w->norm_in_w, (const T*)w->norm_in_b, gm.eps,
