@@ -536,6 +536,10 @@ void carve_prep(Arena& a, size_t es, Prep* p) {
   carve_prep_weights(a, es, p);
 }
 
+// The layout of the saved u = LayerNorm(t): channel-major [128, M] where the fused output kernel runs (it never
+// transposes t), pixel-major [M, 128] otherwise.  Forward and backward decide from the same geometry.
+bool u_channel_major(const Geom& gm) { return ln_gate_out_supported(gm.dtype, gm.M, gm.plane); }
+
 constexpr int kSplitK = 148;
 // The partials of one backward phase live side by side until the phase's single reduction launch: the split-K
 // weight-gradient partials (dWcat, or dWo | dWgo) first, then the LayerNorm weight / bias partials.
@@ -628,8 +632,18 @@ int phase_project(cudaStream_t st, const Geom& gm, const void* x, const void* ma
 // ---- phase 3: t -> u (LayerNorm over channels), out = (u Wo^T + bo) * sigmoid(z Wgo^T + bgo) --------------
 template <typename T>
 int phase_output(cudaStream_t st, const Geom& gm, const void* t_cm, const void* z, const TriMulWeights* w,
-                 const Prep& pr, void* u, float* mean_out, float* rstd_out, void* out) {
+                 const Prep& pr, void* u, float* mean_out, float* rstd_out, void* out, bool keep_u = true) {
   const long long M = gm.M;
+  if (u_channel_major(gm)) {
+    // one batch entry, 16-bit dtype: t is normalised in shared memory as the MMA's MN-major operand; u (kept for
+    // the backward pass only) stays channel-major
+    LnGateOut f;
+    f.dtype = gm.dtype; f.M = M; f.eps = gm.eps; f.t_cm = t_cm; f.z = z;
+    f.gamma = w->norm_out_w; f.beta = w->norm_out_b; f.w_out = w->p_out_w; f.w_gate = w->g_out_w;
+    f.bias_out = (w->p_out_b || w->g_out_b) ? pr.bias_out : nullptr;
+    f.u_cm = keep_u ? u : nullptr; f.mean = mean_out; f.rstd = rstd_out; f.out = out; f.err = pr.err;
+    return ln_gate_out(st, f);
+  }
   {
     KernelTimer kt("tc_ln_cm", st, 0.0, 2.0 * gm.unit());
     ln_cm_kernel<T><<<kLnCmBlocks, 256, 0, st>>>((const T*)t_cm, (const T*)w->norm_out_w, (const T*)w->norm_out_b, gm.eps,
@@ -648,9 +662,10 @@ int phase_output(cudaStream_t st, const Geom& gm, const void* t_cm, const void* 
 }
 
 int split_k_grad(cudaStream_t st, const Geom& gm, const void* lhs, int lhs_w, const void* rhs, float* partial,
-                 int* err, const char* name, int* nparts, bool lhs_channel_major = false) {
+                 int* err, const char* name, int* nparts, bool lhs_channel_major = false,
+                 bool rhs_channel_major = false) {
   // partial[s][lhs_w][128] = sum over the pixels of split s of lhs[pixel][:]^T rhs[pixel][:]
-  // (lhs pixel-major [M, lhs_w], or channel-major [lhs_w, M])
+  // (lhs pixel-major [M, lhs_w], or channel-major [lhs_w, M]; rhs pixel-major [M, 128], or channel-major [128, M])
   const long long M = gm.M;
   const int bke = gm.dtype == TRI_F32 ? 32 : 64;
   int splits = (int)std::min<long long>(kSplitK, (M + bke - 1) / bke);
@@ -662,6 +677,9 @@ int split_k_grad(cudaStream_t st, const Geom& gm, const void* lhs, int lhs_w, co
     p.a[0].mn_major = false; p.a[0].inner = M; p.a[0].outer = lhs_w; p.a[0].st_outer = M;
   }
   p.b[0] = rows_operand(rhs, CW, M, true);
+  if (rhs_channel_major) {  // K (pixels) contiguous: a K-major operand with 128 rows
+    p.b[0].mn_major = false; p.b[0].inner = M; p.b[0].outer = CW; p.b[0].st_outer = M;
+  }
   p.M = lhs_w; p.N = CW; p.K0 = (int)kper; p.batches = splits; p.split_k = 1;
   p.out0 = partial; p.ld_out = CW; p.batch_out = (long long)lhs_w * CW;
   p.name = name; p.flops = 2.0 * M * lhs_w * CW; p.bytes = (double)M * (lhs_w + CW) * gm.es();
@@ -718,6 +736,9 @@ int phase_output_bwd(cudaStream_t st, const Geom& gm, const void* d_out, const v
   {
     GemmPlan p;   // dy = d_out * sig(go), dgo = d_out * y * sig * (1 - sig), with y and go recomputed
     p.a[0] = rows_operand(u, CW, M, false);
+    if (u_channel_major(gm)) {   // A(m = pixel, k = channel) with the pixels contiguous
+      p.a[0].mn_major = true; p.a[0].inner = M; p.a[0].outer = CW; p.a[0].st_outer = M;
+    }
     p.b[0] = rows_operand(w->p_out_w, CW, CW, false);
     p.a[1] = rows_operand(z, CW, M, false);
     p.b[1] = rows_operand(w->g_out_w, CW, CW, false);
@@ -731,7 +752,8 @@ int phase_output_bwd(cudaStream_t st, const Geom& gm, const void* d_out, const v
   float* part2 = partial + (size_t)kSplitK * CW * CW;
   float* scratch = partial + (size_t)2 * kSplitK * CW * CW;   // the rest of the weight-gradient area
   int n1 = 0, n2 = 0;
-  if (g->p_out_w) TRI_TRY(split_k_grad(st, gm, dy, CW, u, partial, pr.err, "tc_gemm_wgrad", &n1));
+  if (g->p_out_w)
+    TRI_TRY(split_k_grad(st, gm, dy, CW, u, partial, pr.err, "tc_gemm_wgrad", &n1, false, u_channel_major(gm)));
   if (g->g_out_w) TRI_TRY(split_k_grad(st, gm, dgo, CW, z, part2, pr.err, "tc_gemm_wgrad", &n2));
   if (g->p_out_b) {
     TRI_TRY(colsum_to<T>(st, dy, M, CW, scratch, &nparts));
@@ -853,7 +875,7 @@ int forward_t(const TriMulDesc* d, const void* x, const void* mask, const TriMul
   TRI_TRY(phase_project<T>(st, gm, x, mask, w, pr, s.z, s.mean_in, s.rstd_in, s.a, s.b));
   const bool incoming = d->direction == TRI_INCOMING;
   TRI_TRY(contraction(st, d->dtype, d->B * CW, d->N, s.a, incoming, s.b, incoming, s.t, pr.err, "tc_gemm_contract"));
-  return phase_output<T>(st, gm, s.t, s.z, w, pr, s.u, s.mean_out, s.rstd_out, out);
+  return phase_output<T>(st, gm, s.t, s.z, w, pr, s.u, s.mean_out, s.rstd_out, out, /*keep_u=*/saved != nullptr);
 }
 
 template <typename T>
