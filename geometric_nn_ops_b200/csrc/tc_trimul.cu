@@ -418,6 +418,102 @@ __global__ void __launch_bounds__(256, 3) ln_cm_bwd_kernel(const T* du, const T*
   }
 }
 
+// The same backward with every tensor channel-major ([128][M]: du from the transposed du GEMM, t, dt): nothing is
+// transposed.  A block of 256 threads takes 64 pixels; a thread holds 8 pixels (16 bytes of a channel row) of 4
+// channels in registers, raw, for both passes.  A pixel's two sums over its 128 channels are combined from the 32
+// channel parts through shared memory; the per-channel sums over pixels (gradients of the LayerNorm weight and bias)
+// stay in the thread's registers across tiles, since its 4 channels never change.
+constexpr int kLnCmCmBlocks = 296;   // 2 per SM (about 100 registers per thread)
+template <typename T>
+__global__ void __launch_bounds__(256, 2) ln_cm_bwd_cm_kernel(const T* __restrict__ du, const T* __restrict__ t,
+                                                              const float* __restrict__ mean, const float* __restrict__ rstd,
+                                                              const T* gamma, long long M, T* __restrict__ dt, float* pg,
+                                                              float* pb) {
+  static_assert(sizeof(T) == 2, "16-bit types");
+  __shared__ __align__(16) float s_p1[32][64], s_p2[32][64], s_s1[64], s_s2[64];
+  const int tid = threadIdx.x, pgp = tid & 7, kp = tid >> 3;   // 8-pixel group of the tile; 4-channel part
+  float gm[4], dg[4] = {}, db[4] = {};
+#pragma unroll
+  for (int r = 0; r < 4; ++r) gm[r] = gamma ? to_f32(gamma[kp * 4 + r]) : 1.f;
+  const long long tiles = (M + 63) / 64;
+  for (long long tile = blockIdx.x; tile < tiles; tile += gridDim.x) {
+    const long long px0 = tile * 64 + pgp * 8;   // 8 pixels: all inside the tensor or none (M is a multiple of 8)
+    const bool valid = px0 < M;
+    uint4 tw[4], dw[4];
+    float mu[8], rs[8];
+#pragma unroll
+    for (int r = 0; r < 4; ++r) {
+      tw[r] = make_uint4(0, 0, 0, 0); dw[r] = tw[r];
+      if (valid) {
+        tw[r] = __ldg(reinterpret_cast<const uint4*>(t + (long long)(kp * 4 + r) * M + px0));
+        dw[r] = __ldg(reinterpret_cast<const uint4*>(du + (long long)(kp * 4 + r) * M + px0));
+      }
+    }
+#pragma unroll
+    for (int e = 0; e < 8; ++e) { mu[e] = 0.f; rs[e] = 0.f; }
+    if (valid) {
+      const float4 a = *reinterpret_cast<const float4*>(mean + px0), b = *reinterpret_cast<const float4*>(mean + px0 + 4);
+      const float4 c = *reinterpret_cast<const float4*>(rstd + px0), d = *reinterpret_cast<const float4*>(rstd + px0 + 4);
+      mu[0] = a.x; mu[1] = a.y; mu[2] = a.z; mu[3] = a.w; mu[4] = b.x; mu[5] = b.y; mu[6] = b.z; mu[7] = b.w;
+      rs[0] = c.x; rs[1] = c.y; rs[2] = c.z; rs[3] = c.w; rs[4] = d.x; rs[5] = d.y; rs[6] = d.z; rs[7] = d.w;
+    }
+    {
+      float p1[8] = {}, p2[8] = {};
+#pragma unroll
+      for (int r = 0; r < 4; ++r) {
+        union { uint4 u; T h[8]; } xt, xd;
+        xt.u = tw[r]; xd.u = dw[r];
+#pragma unroll
+        for (int e = 0; e < 8; ++e) {
+          const float xh = (to_f32(xt.h[e]) - mu[e]) * rs[e], gd = to_f32(xd.h[e]) * gm[r];
+          p1[e] += gd;
+          p2[e] = fmaf(gd, xh, p2[e]);
+        }
+      }
+      float4* d1 = reinterpret_cast<float4*>(&s_p1[kp][pgp * 8]);
+      float4* d2 = reinterpret_cast<float4*>(&s_p2[kp][pgp * 8]);
+      d1[0] = make_float4(p1[0], p1[1], p1[2], p1[3]); d1[1] = make_float4(p1[4], p1[5], p1[6], p1[7]);
+      d2[0] = make_float4(p2[0], p2[1], p2[2], p2[3]); d2[1] = make_float4(p2[4], p2[5], p2[6], p2[7]);
+    }
+    __syncthreads();
+    if (tid < 128) {   // 64 pixels x 2 sums
+      const int px = tid & 63;
+      const float(*src)[64] = tid < 64 ? s_p1 : s_p2;
+      float a = 0.f, b = 0.f;
+#pragma unroll
+      for (int k = 0; k < 32; k += 2) { a += src[k][px]; b += src[k + 1][px]; }
+      (tid < 64 ? s_s1 : s_s2)[px] = (a + b) * (1.0f / CW);
+    }
+    __syncthreads();
+    {
+      const float4 a = *reinterpret_cast<const float4*>(&s_s1[pgp * 8]), b = *reinterpret_cast<const float4*>(&s_s1[pgp * 8 + 4]);
+      const float4 c = *reinterpret_cast<const float4*>(&s_s2[pgp * 8]), d = *reinterpret_cast<const float4*>(&s_s2[pgp * 8 + 4]);
+      const float s1[8] = {a.x, a.y, a.z, a.w, b.x, b.y, b.z, b.w}, s2[8] = {c.x, c.y, c.z, c.w, d.x, d.y, d.z, d.w};
+#pragma unroll
+      for (int r = 0; r < 4; ++r) {
+        union { uint4 u; T h[8]; } xt, xd, o;
+        xt.u = tw[r]; xd.u = dw[r];
+#pragma unroll
+        for (int e = 0; e < 8; ++e) {
+          const float dv = to_f32(xd.h[e]), xh = (to_f32(xt.h[e]) - mu[e]) * rs[e];
+          o.h[e] = from_f32<T>(rs[e] * (dv * gm[r] - s1[e] - xh * s2[e]));
+          dg[r] = fmaf(dv, xh, dg[r]);
+          db[r] += dv;
+        }
+        if (valid) *reinterpret_cast<uint4*>(dt + (long long)(kp * 4 + r) * M + px0) = o.u;
+      }
+    }
+  }
+  // the 8 threads of a channel part are a quarter of a warp
+#pragma unroll
+  for (int r = 0; r < 4; ++r) {
+    float a = dg[r], b = db[r];
+#pragma unroll
+    for (int o = 4; o > 0; o >>= 1) { a += __shfl_xor_sync(0xffffffffu, a, o); b += __shfl_xor_sync(0xffffffffu, b, o); }
+    if (pgp == 0) { pg[blockIdx.x * CW + kp * 4 + r] = a; pb[blockIdx.x * CW + kp * 4 + r] = b; }
+  }
+}
+
 // ---------------------------------------------------------------------------------------------
 // reductions
 // ---------------------------------------------------------------------------------------------
@@ -763,6 +859,28 @@ int phase_output_bwd(cudaStream_t st, const Geom& gm, const void* d_out, const v
     TRI_TRY(colsum_to<T>(st, dgo, M, CW, scratch, &nparts));
     TRI_TRY(reduce_to(st, scratch, nparts, CW, g->g_out_b));
   }
+  float* pg = partial + kWgradPartialFloats;
+  if (u_channel_major(gm)) {
+    // du^T = Wo^T dy^T: a thread of the store epilogue owns a channel and consecutive pixels, so du comes out
+    // channel-major like t and dt, and the LayerNorm backward needs no transposition
+    GemmPlan p;
+    p.a[0] = rows_operand(w->p_out_w, CW, CW, true);   // A(m = ch, k = c) = Wo[c][ch]: m contiguous
+    p.b[0] = rows_operand(dy, CW, M, false);           // B(n = pixel, k = c)
+    p.M = CW; p.N = (int)M; p.K0 = CW; p.out0 = du; p.ld_out = M;
+    p.name = "tc_gemm_du"; p.flops = 2.0 * M * CW * CW; p.bytes = 2.0 * gm.unit();
+    TRI_TRY(launch_gemm(st, gm.dtype, EPI_STORE, 256, false, p, pr.err));
+    const int blocks = (int)std::min<long long>(kLnCmCmBlocks, (M + 63) / 64);
+    float* pb = pg + (size_t)blocks * CW;
+    {
+      KernelTimer kt("tc_ln_cm_bwd", st, 0.0, 3.0 * gm.unit());
+      if constexpr (sizeof(T) == 2)
+        ln_cm_bwd_cm_kernel<T><<<blocks, 256, 0, st>>>((const T*)du, (const T*)t_cm, mean_out, rstd_out,
+                                                       (const T*)w->norm_out_w, M, (T*)dt_cm, pg, pb);
+      TRI_LAUNCH_OK();
+    }
+    return reduce_many(st, {{partial, n1, CW * CW, g->p_out_w}, {part2, n2, CW * CW, g->g_out_w},
+                            {pg, blocks, CW, g->norm_out_w}, {pb, blocks, CW, g->norm_out_b}});
+  }
   {
     GemmPlan p;   // du = dy Wo
     p.a[0] = rows_operand(dy, CW, M, false);
@@ -771,7 +889,6 @@ int phase_output_bwd(cudaStream_t st, const Geom& gm, const void* d_out, const v
     p.name = "tc_gemm_du"; p.flops = 2.0 * M * CW * CW; p.bytes = 2.0 * gm.unit();
     TRI_TRY(launch_gemm(st, gm.dtype, EPI_STORE, 128, false, p, pr.err));
   }
-  float* pg = partial + kWgradPartialFloats;
   float* pb = pg + (size_t)kLnCmBwdBlocks * CW;
   {
     KernelTimer kt("tc_ln_cm_bwd", st, 0.0, 3.0 * gm.unit());
