@@ -1,6 +1,6 @@
-// LayerNorm fused into the input projection of the triangle multiplicative update (see tc_lngemm.cuh).
+// LayerNorm fused into the two projection kernels of the triangle multiplicative update (see tc_lngemm.cuh).
 //
-// One persistent CTA per SM, 704 threads:
+// ln_gate_in.  One persistent CTA per SM, 704 threads:
 //   warp 0       TMA: the concatenated weights once (128 KB, resident), then one 128-pixel x tile per step into one of
 //                two 32 KB buffers
 //   warp 1       tcgen05.mma: per tile and half (a, b) the P and G products, M = the half's 128 channels, N = 128

@@ -51,6 +51,9 @@ def test_golden_fp32_ieee(tmu, path):
 CASES = [  # B, N, C, Ch, biases
     (1, 32, 128, 128, False), (2, 17, 64, 32, True), (1, 40, 96, 96, False), (1, 24, 256, 128, True),
     (1, 128, 128, 128, False),
+    # 128 channels with a ragged last tile (1600 = 12 * 128 + 64 pixels) and projection biases; two batch entries
+    # (the fused input kernel across a plane boundary inside a tile, the two-kernel output path)
+    (1, 40, 128, 128, True), (2, 24, 128, 128, True),
 ]
 MODES = [(torch.float32, "ieee"), (torch.float32, "tf32"), (torch.bfloat16, "ieee"), (torch.float16, "ieee")]
 
