@@ -12,6 +12,7 @@ _HERE = os.path.dirname(os.path.abspath(__file__))
 LIB_PATH = os.environ.get("TRI_B200_LIB", os.path.join(_HERE, "libtri_b200.so"))
 
 F32, BF16, F16 = 0, 1, 2
+ERR_UNSUPPORTED = -3   # TRI_ERR_UNSUPPORTED
 PREC_IEEE, PREC_TF32 = 0, 1
 OUTGOING, INCOMING = 0, 1
 
@@ -119,6 +120,7 @@ EXPORTS = {
     "tri_permute_runs": (c_int, [c_void_p, c_void_p, POINTER(ctypes.c_int64 * 3), POINTER(ctypes.c_int32 * 3),
                                  ctypes.c_int64, c_void_p]),
     "tri_scatter_runs": (c_int, [POINTER(TriScatterDesc), c_void_p, POINTER(c_void_p), c_void_p]),
+    "tri_scatter_runs_dma": (c_int, [POINTER(TriScatterDesc), c_void_p, POINTER(c_void_p), c_void_p]),
     "tri_peer_barrier": (c_int, [POINTER(TriPeerSignal), c_int64, c_void_p]),
     "tri_ws_status": (c_int, [c_void_p, c_void_p]),
 }

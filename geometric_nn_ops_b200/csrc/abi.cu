@@ -374,6 +374,35 @@ int tri_scatter_runs(const TriScatterDesc* d, const void* src, void* const* dst_
   return 0;
 }
 
+int tri_scatter_runs_dma(const TriScatterDesc* d, const void* src, void* const* dst_ptrs, tri_stream_t stream) {
+  if (d == nullptr || src == nullptr || dst_ptrs == nullptr) return fail(TRI_ERR_ARG, "tri_scatter_runs_dma: null pointer");
+  if (d->run_bytes <= 0 || d->run_bytes % 16 != 0 || ((uintptr_t)src & 15))
+    return fail(TRI_ERR_ARG, "tri_scatter_runs_dma: runs must be 16-byte aligned multiples of 16 bytes");
+  if (d->peer_dim < 0 || d->peer_dim > 2 || d->n_peers < 1 || d->n_peers > 16 || d->dims[d->peer_dim] != d->n_peers)
+    return fail(TRI_ERR_ARG, "tri_scatter_runs_dma: bad peer dimension");
+  for (int i = 0; i < d->n_peers; ++i)
+    if (dst_ptrs[i] == nullptr || ((uintptr_t)dst_ptrs[i] & 15)) return fail(TRI_ERR_ARG, "tri_scatter_runs_dma: bad destination pointer");
+  const long long outer = d->dims[0] * d->dims[1] * d->dims[2];
+  if (outer <= 0) return fail(TRI_ERR_ARG, "tri_scatter_runs_dma: empty exchange");
+  // source strides in runs (the source is contiguous); rows of a 2-D copy walk the longer of the two other dimensions
+  const long long ss[3] = {d->dims[1] * d->dims[2], d->dims[2], 1};
+  const int p = d->peer_dim, o0 = p == 0 ? 1 : 0, o1 = p == 2 ? 1 : 2;
+  const int b = d->dims[o0] >= d->dims[o1] ? o0 : o1, a = b == o0 ? o1 : o0;
+  const long long run = d->run_bytes;
+  const long long spitch = std::max<long long>(ss[b], 1) * run, dpitch = std::max<long long>(d->dst_stride[b], 1) * run;
+  if (d->dims[b] > 1 && (d->dst_stride[b] < 1 || spitch > 2147483647LL || dpitch > 2147483647LL))
+    return fail(TRI_ERR_UNSUPPORTED, "tri_scatter_runs_dma: pitch beyond a two-dimensional copy");
+  KernelTimer kt("tri_scatter_dma", (cudaStream_t)stream, 0.0, 2.0 * outer * run);
+  for (long long w = 0; w < d->n_peers; ++w)
+    for (long long ia = 0; ia < d->dims[a]; ++ia) {
+      const char* s = static_cast<const char*>(src) + (w * ss[p] + ia * ss[a]) * run;
+      char* t = static_cast<char*>(dst_ptrs[w]) + (d->dst_base_run + w * d->dst_stride[p] + ia * d->dst_stride[a]) * run;
+      TRI_CUDA_OK(cudaMemcpy2DAsync(t, (size_t)dpitch, s, (size_t)spitch, (size_t)run, (size_t)d->dims[b],
+                                    cudaMemcpyDeviceToDevice, (cudaStream_t)stream));
+    }
+  return 0;
+}
+
 // ---- arrival flags for the peer-store exchange -------------------------------------------------------------------
 // state[0] = number of barriers this rank has entered, state[3] = status of the last wait (0 = ok).  Both live in this
 // GPU's memory and are advanced by the kernel itself, so a captured graph can be replayed without changing an argument.

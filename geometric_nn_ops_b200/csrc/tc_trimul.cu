@@ -616,6 +616,7 @@ struct Geom {
   int dtype;
   float eps;
   long long M, plane;
+  bool sharded = false;      // a row shard of a multi-GPU op (other streams' kernels run beside this one's)
   size_t es() const { return dtype == TRI_F32 ? 4 : 2; }
   double unit() const { return (double)M * CW * es(); }
 };
@@ -764,7 +765,11 @@ int split_k_grad(cudaStream_t st, const Geom& gm, const void* lhs, int lhs_w, co
   // (lhs pixel-major [M, lhs_w], or channel-major [lhs_w, M]; rhs pixel-major [M, 128], or channel-major [128, M])
   const long long M = gm.M;
   const int bke = gm.dtype == TRI_F32 ? 32 : 64;
-  int splits = (int)std::min<long long>(kSplitK, (M + bke - 1) / bke);
+  // One split per SM for the single-GPU op.  A row shard gets proportionally fewer (at least 2048 pixels per split,
+  // never under 37 splits), so that the partials written here and summed by the reduction shrink with the shard
+  // instead of staying sized for 148 SMs; the SMs this leaves idle run the other streams' kernels of the sharded step.
+  int splits = gm.sharded ? (int)std::min<long long>(kSplitK, std::max<long long>(37, M / 2048)) : kSplitK;
+  splits = (int)std::min<long long>(splits, (M + bke - 1) / bke);
   long long kper = ((M + splits - 1) / splits + bke - 1) / bke * bke;
   splits = (int)((M + kper - 1) / kper);
   GemmPlan p;
@@ -1032,6 +1037,7 @@ Geom geom_of(const TriMulShardDesc* d) {
   Geom g;
   g.dtype = d->dtype; g.eps = d->eps;
   g.plane = (long long)d->rows * d->N; g.M = g.plane * d->B;
+  g.sharded = true;
   return g;
 }
 

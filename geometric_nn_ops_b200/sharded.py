@@ -14,12 +14,17 @@ The pair representation ``[B, N, N, C]`` is sharded over its first pair axis: ra
   rank that moves ``3/P`` of a pair-sized tensor per forward, against ``(P-1)/P`` for all-gathering ``b``.
   Weight gradients are partial sums per rank and are all-reduced.
 
-The row <-> channel exchange is not an NCCL all-to-all: each rank runs one copy kernel (``tri_scatter_runs``) that
-stores every run straight into its final place in the destination GPU's buffer (symmetric memory, plain stores
-over NVLink), followed by a one-element all-reduce as the barrier.  That is one pass over the data instead of
-pack + all-to-all + unpack.  ``TRI_B200_EXCHANGE=nccl`` (or a CPU / gloo group) selects the all-to-all route, ``TRI_B200_EXCHANGE=fused``
-additionally lets the gate-in GEMM's epilogue store a and b straight into the peers' buffers.
-The kernels only ever *store* to a peer; every load, and every tensor handed to NCCL, is in this GPU's memory.
+The row <-> channel exchange is not an NCCL all-to-all: each rank writes every run straight into its final place in
+the destination GPU's buffer (symmetric memory over NVLink), one pass over the data instead of pack + all-to-all +
+unpack, and a one-block kernel with arrival flags and a bounded wait orders it (``tri_peer_barrier``).  The writes
+are done by a copy kernel (``tri_scatter_runs``) or, on two GPUs, by strided two-dimensional copies on the copy
+engines (``tri_scatter_runs_dma``: no SM is used, the step's other kernels keep the GPU; with more destinations the
+copies of an exchange, which run one after the other, cost more latency than they free).
+``TRI_B200_EXCHANGE=peer_kernel`` / ``peer_dma`` force one or the other, ``peer_allreduce`` uses the copy kernel and a
+one-element all-reduce as the barrier,
+``fused`` lets the gate-in GEMM's epilogue store a and b into the peers' buffers, ``nccl`` (or a CPU / gloo group)
+selects the all-to-all route.
+Kernels and copies only ever *write* to a peer; every load, and every tensor handed to NCCL, is in this GPU's memory.
 """
 
 import ctypes
@@ -147,7 +152,7 @@ def peer_exchange_enabled(device, group=None):
     """
     key = (id(group), device.index)
     if key not in _PEER_STATE:
-        ok = (os.environ.get("TRI_B200_EXCHANGE", "peer") in ("peer", "peer_allreduce", "fused") and device.type == "cuda"
+        ok = (os.environ.get("TRI_B200_EXCHANGE", "peer") in ("peer", "peer_kernel", "peer_dma", "peer_allreduce", "fused") and device.type == "cuda"
               and dist.get_backend(group) == "nccl")
         if ok:
             try:
@@ -168,7 +173,10 @@ def exchange_route(device, group=None):
     if not peer_exchange_enabled(device, group):
         return "nccl all_to_all"
     mode = os.environ.get("TRI_B200_EXCHANGE", "peer")
-    return {"peer": "peer stores + arrival flags", "peer_allreduce": "peer stores + all-reduce barrier",
+    world = _world(group)[0]
+    moved = "copy-engine peer copies" if _use_copy_engines(world) else "peer stores"
+    return {"peer": moved + " + arrival flags", "peer_kernel": moved + " + arrival flags",
+            "peer_dma": moved + " + arrival flags", "peer_allreduce": "peer stores + all-reduce barrier",
             "fused": "gate-in epilogue peer stores + all-reduce barrier"}[mode]
 
 
@@ -195,7 +203,7 @@ def _peer_buffer(tag, nbytes, device, group):
 def _peer_barrier(pb, tag, group, stream):
     """Order "every rank's stores have landed" before this rank's readers (queued next on ``stream``)."""
     with _timed(tag + ".barrier"):
-        if os.environ.get("TRI_B200_EXCHANGE", "peer") == "peer":
+        if os.environ.get("TRI_B200_EXCHANGE", "peer") in ("peer", "peer_kernel", "peer_dma"):
             _lib.check(_lib.load().tri_peer_barrier(ctypes.byref(pb.sig), 0, stream), "tri_peer_barrier")
             if os.environ.get("TRI_B200_CHECK") == "1" and not torch.cuda.is_current_stream_capturing():
                 status = int(pb.state[3].item())
@@ -203,6 +211,15 @@ def _peer_barrier(pb, tag, group, stream):
                     raise RuntimeError(f"peer exchange {tag!r}: rank {status - 100} did not arrive within the wait limit")
         else:
             dist.all_reduce(pb.token, group=group)
+
+
+def _use_copy_engines(world):
+    """The default route's choice between the copy engines and the copy kernel.  The copies of one exchange run one
+    after the other on the stream; with one remote destination that costs nothing and frees the SMs (2 GPUs: 4.75
+    against 4.93 ms per bench step), with seven it lengthens every exchange (8 GPUs: 1.72 against 1.55 ms; spread over
+    four streams, 2.09)."""
+    mode = os.environ.get("TRI_B200_EXCHANGE", "peer")
+    return mode == "peer_dma" or (mode == "peer" and world == 2)
 
 
 def _peer_scatter(t, dims, dst_stride, base_run, peer_dim, run, out_shape, tag, group, persist):
@@ -220,7 +237,13 @@ def _peer_scatter(t, dims, dst_stride, base_run, peer_dim, run, out_shape, tag, 
     stream = ctypes.c_void_p(torch.cuda.current_stream(t.device).cuda_stream)
     lib = _lib.load()
     with _timed(tag + ".peer_store"):
-        _lib.check(lib.tri_scatter_runs(ctypes.byref(d), ctypes.c_void_p(t.data_ptr()), pb.ptrs, stream), "tri_scatter_runs")
+        rc = _lib.ERR_UNSUPPORTED
+        if _use_copy_engines(world):                                  # strided copies on the copy engines: no SM used
+            rc = lib.tri_scatter_runs_dma(ctypes.byref(d), ctypes.c_void_p(t.data_ptr()), pb.ptrs, stream)
+            if rc not in (0, _lib.ERR_UNSUPPORTED):
+                _lib.check(rc, "tri_scatter_runs_dma")
+        if rc != 0:                                                   # the copy kernel
+            _lib.check(lib.tri_scatter_runs(ctypes.byref(d), ctypes.c_void_p(t.data_ptr()), pb.ptrs, stream), "tri_scatter_runs")
     _peer_barrier(pb, tag, group, stream)
     # The buffer is rewritten two exchanges with this tag from now.  Results the caller keeps beyond that (tensors
     # saved for the backward) get a private copy.

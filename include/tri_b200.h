@@ -288,6 +288,14 @@ typedef struct TriScatterDesc {
 
 int tri_scatter_runs(const TriScatterDesc* d, const void* src, void* const* dst_ptrs, tri_stream_t stream);
 
+/* The same exchange issued to the copy engines instead of a kernel: one strided two-dimensional device-to-device
+ * copy per (destination GPU, index of the shorter of the two other dimensions), each moving dims[longer] runs.  It
+ * occupies no SM, so the step's other kernels keep the whole GPU while the slabs cross NVLink; the copies of one call
+ * run one after the other, which costs more latency than the kernel once there are many destinations (measured on
+ * B200: better than the kernel at 2 GPUs, worse at 8).  Same contract as
+ * tri_scatter_runs (ordering by the caller; capturable into a CUDA graph as copy nodes).  Returns
+ * TRI_ERR_UNSUPPORTED when a pitch exceeds what a two-dimensional copy takes (2 GiB); use the kernel then. */
+int tri_scatter_runs_dma(const TriScatterDesc* d, const void* src, void* const* dst_ptrs, tri_stream_t stream);
 /* Arrival flags for the peer-store exchange, in place of a collective as the barrier after tri_scatter_runs.
  * No counterpart in the reference (single device).  Every rank owns an array of 16 uint32 arrival flags in memory
  * that all peers can store to (symmetric memory), zeroed before first use; flag_ptrs[w] is rank w's array as mapped

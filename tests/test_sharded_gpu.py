@@ -97,10 +97,10 @@ def _compare(results):
     return problems
 
 
-# the three exchange routes: peer stores from a copy kernel (default), NCCL all-to-all, and the gate-in GEMM's
-# epilogue storing into the peers' buffers
+# the four exchange routes: strided peer copies on the copy engines (default), peer stores from a copy kernel, NCCL
+# all-to-all, and the gate-in GEMM's epilogue storing into the peers' buffers
 @pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs at least two GPUs")
-@pytest.mark.parametrize("exchange", ["peer", "nccl", "fused"])
+@pytest.mark.parametrize("exchange", ["peer", "peer_kernel", "nccl", "fused"])
 def test_sharded_matches_single_gpu(exchange):
     world = 2
     ctx = mp.get_context("spawn")
