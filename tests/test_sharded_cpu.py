@@ -111,3 +111,19 @@ def test_shard_rows_rejects_uneven_split():
     assert sharded.shard_rows(768, 3, 8) == (288, 384)
     with pytest.raises(ValueError, match="not divisible"):
         sharded.shard_rows(10, 0, 4)
+
+
+def test_default_route_uses_copy_engines_on_two_gpus_only(monkeypatch):
+    """The default peer route moves the slabs with copy-engine copies on 2 GPUs and with the copy kernel beyond (the
+    measured crossover); the two forcing values override that."""
+    from geometric_nn_ops_b200 import sharded
+
+    monkeypatch.delenv("TRI_B200_EXCHANGE", raising=False)
+    assert sharded._use_copy_engines(2)
+    assert not sharded._use_copy_engines(4) and not sharded._use_copy_engines(8)
+    monkeypatch.setenv("TRI_B200_EXCHANGE", "peer_kernel")
+    assert not sharded._use_copy_engines(2)
+    monkeypatch.setenv("TRI_B200_EXCHANGE", "peer_dma")
+    assert sharded._use_copy_engines(2) and sharded._use_copy_engines(8)
+    monkeypatch.setenv("TRI_B200_EXCHANGE", "nccl")
+    assert not sharded._use_copy_engines(2)
