@@ -62,3 +62,26 @@ def test_fused_projection_against_torch_fp32(shape, dtype):
             assert rel < (6e-3 if dtype == torch.bfloat16 else 1e-3), rel
     with pytest.raises(RuntimeError, match="forward only"):
         attention_input_projection(z.requires_grad_(), w_qkv, w_bias, H)
+
+
+def test_glue_on_cpu_with_the_ops_replaced_by_the_torch_restatement(monkeypatch):
+    """The stack's own glue -- LayerNorm, projections, residual adds, and the ending-node attention on transposed
+    *views* of the projections -- on the CPU in fp64, with the two CUDA ops swapped for the torch restatement of the
+    reference, against the numpy composition: an index or transposition error in the glue shows up here without a GPU."""
+    from geometric_nn_ops_b200 import pairstack
+    from oracle import pairstack_oracle as po
+    from oracle import torch_reference as tr
+
+    monkeypatch.setattr(pairstack, "triangle_attention",
+                        lambda q, k, v, bias, mask: tr.cpu_triangle_attention(q, k, v, bias, mask))
+    monkeypatch.setattr(pairstack, "triangle_multiplicative_update",
+                        lambda x, direction, mask, **w: tr.cpu_trimul(x, direction, mask, **w))
+    n, tail = 24, 4
+    z, mask = pairstack.make_inputs(n, masked_tail=tail, dtype=torch.float64, seed=3)
+    blocks = [pairstack.make_block_weights(s, dtype=torch.float64) for s in (0, 1)]
+    got = pairstack.pair_stack(z, mask, blocks).numpy()
+    want = po.pair_stack(z.numpy(), mask.numpy(), _oracle_weights(blocks))
+    assert np.isfinite(got).all()
+    # the last `tail` rows of the ending-node problem are fully masked: uniform averages in both
+    rel = np.linalg.norm(got - want) / np.linalg.norm(want)
+    assert rel < 1e-9, rel
