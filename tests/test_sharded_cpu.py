@@ -100,8 +100,36 @@ def check_deferred_grad_sync(rank, world):
     assert torch.equal(g2, torch.full((4,), total))
 
 
+def check_pair_block_glue(rank, world):
+    """The sharded branch of the pair stack's block (bias all-gather, the two all-to-all transposes around the
+    ending-node attention) against the single-process branch, in fp64, with the two CUDA ops replaced by the torch
+    restatement of the reference (the sharded multiplicative update by gather + whole-tensor op + slice)."""
+    from geometric_nn_ops_b200 import pairstack, sharded
+    from oracle import torch_reference as tr
+
+    n = 8 * world
+    z, mask = pairstack.make_inputs(n, masked_tail=3, dtype=torch.float64, seed=5)
+    w = pairstack.make_block_weights(7, dtype=torch.float64)
+    i0, i1 = sharded.shard_rows(n, rank, world)
+
+    def gathered_trimul(x, direction, m, group=None, **weights):
+        xs = [torch.empty_like(x) for _ in range(world)]
+        ms = [torch.empty_like(m) for _ in range(world)]
+        dist.all_gather(xs, x.contiguous(), group=group)
+        dist.all_gather(ms, m.contiguous(), group=group)
+        return tr.cpu_trimul(torch.cat(xs, 1), direction, torch.cat(ms, 1), **weights)[:, i0:i1]
+
+    pairstack.triangle_attention = lambda q, k, v, bias, m: tr.cpu_triangle_attention(q, k, v, bias, m)
+    pairstack.triangle_multiplicative_update = lambda x, direction, m, **weights: tr.cpu_trimul(x, direction, m, **weights)
+    sharded.sharded_triangle_multiplicative_update = gathered_trimul
+    whole = pairstack.pair_block(z, mask, w)
+    mine = pairstack.pair_block(z[:, i0:i1].contiguous(), mask[:, i0:i1].contiguous(), w, group=dist.group.WORLD)
+    err = float((mine - whole[:, i0:i1]).norm() / whole[:, i0:i1].norm())
+    assert err < 1e-12, err
+
+
 @pytest.mark.parametrize("fn", ["check_channel_exchange", "check_transpose", "check_replicated_grad",
-                                "check_deferred_grad_sync"])
+                                "check_deferred_grad_sync", "check_pair_block_glue"])
 def test_two_ranks(fn):
     _run(fn)
 
